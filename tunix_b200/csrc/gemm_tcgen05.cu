@@ -1,0 +1,340 @@
+// bf16 GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   C[M,N] (+)= alpha * A[M,K] * B[N,K]^T        (fp32 accumulation in TMEM)
+//
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 256 or 128).
+// Warp roles inside a CTA (192 threads):
+//   warp 0     : TMA producer - one elected lane issues cp.async.bulk.tensor loads into a
+//                ring of 128-byte-swizzled shared-memory stages.
+//   warp 1     : owns TMEM allocation; one elected lane issues tcgen05.mma (UMMA 128xBNx16)
+//                and tcgen05.commit to hand stages back / publish finished accumulators.
+//   warps 2..5 : epilogue - tcgen05.ld the accumulator (one row per thread), scale,
+//                optionally add the existing C, convert and store.
+// Two accumulators live in TMEM (2 x BN columns), so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Operand layouts. Either operand may be "K-major" (the reduction dimension is the
+// contiguous one: A given as [M,K], B as [N,K]) or "MN-major" (A given as [K,M], B as
+// [K,N]). That covers the three products of a linear layer without any transposes:
+//   forward   y  = x  W^T   : A K-major,  B K-major
+//   dgrad     dx = dy W     : A K-major,  B MN-major
+//   wgrad     dW = dy^T x   : A MN-major, B MN-major
+//
+// No cluster launch and no multicast copies are used, so the kernel is safe to run in
+// multi-GPU jobs, and its operands may live in peer memory.
+#include "tx_host.h"
+#include "tx_ptx.cuh"
+
+namespace {
+
+using namespace tx;
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;      // tile-order swizzle: 8 row-blocks share their B tiles in L2
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct GemmParams {
+  void* C;
+  long long ldc;
+  int M, N, K;
+  int c_fp32;      // 1: C is fp32, 0: C is bf16
+  int accumulate;  // 1: C += result, 0: C = result
+  float alpha;
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int mb, int nb, int& pm, int& pn) {
+  const int per_group = GROUP_M * nb;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(mb - first_m, GROUP_M);
+  const int r = t - g * per_group;
+  pm = first_m + (r % gsize);
+  pn = r / gsize;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle needs every stage 1024-byte aligned.
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
+  // barrier layout: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * C::kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int mb = (p.M + BM - 1) / BM;
+  const int nb = (p.N + BN - 1) / BN;
+  const int num_tiles = mb * nb;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 128);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int pm, pn;
+        tile_coords(t, mb, nb, pm, pn);
+        const int m0 = pm * BM, n0 = pn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
+            atomicOr(p.status, kStatusWaitTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t sa = smem_base + stage * C::kStageBytes;
+          const uint32_t sb = sa + C::kABytes;
+          mbar_expect_tx(full, C::kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), &map_a, m0 + i * 64, kb * BK, full);
+          } else {
+            tma_load_2d(sa, &map_a, kb * BK, m0, full);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &map_b, n0 + i * 64, kb * BK, full);
+          } else {
+            tma_load_2d(sb, &map_b, kb * BK, n0, full);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
+          atomicOr(p.status, kStatusWaitTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            atomicOr(p.status, kStatusWaitTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * C::kStageBytes;
+          const uint32_t sb = sa + C::kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_bf16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int pm, pn;
+      tile_coords(t, mb, nb, pm, pn);
+      const int row = pm * BM + quarter * 32 + lane;
+      const int n0 = pn * BN;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+        atomicOr(p.status, kStatusWaitTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col = n0 + c;
+        if (row < p.M && col < p.N) {
+          if (p.c_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (col + j < p.N) {
+                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
+                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
+                float4* d4 = reinterpret_cast<float4*>(dst + j);
+                if (p.accumulate) {
+                  const float4 o = *d4;
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                *d4 = v;
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col + j < p.N) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
+                uint4* d4 = reinterpret_cast<uint4*>(dst + j);
+                if (p.accumulate) {
+                  const uint4 o = *d4;
+                  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&o);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 of = __bfloat1622float2(o2[e]);
+                    f[2 * e] += of.x;
+                    f[2 * e + 1] += of.y;
+                  }
+                }
+                uint4 v;
+                __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                *d4 = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // Teardown. On an aborted run give outstanding bulk copies a moment to land before the
+  // shared memory is released.
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+int launch(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
+           cudaStream_t stream, int max_ctas) {
+  using C = Cfg<BN>;
+  CUtensorMap ma, mbm;
+  int rc;
+  if (A_MN) rc = txh::make_map_2d_bf16(&ma, A, p.K, p.M, lda, BK, 64);
+  else      rc = txh::make_map_2d_bf16(&ma, A, p.M, p.K, lda, BM, BK);
+  if (rc) return 100 + rc;
+  if (B_MN) rc = txh::make_map_2d_bf16(&mbm, B, p.K, p.N, ldb, BK, 64);
+  else      rc = txh::make_map_2d_bf16(&mbm, B, p.N, p.K, ldb, BN, BK);
+  if (rc) return 200 + rc;
+  static bool attr_set = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)
+      return 300;
+    attr_set = true;
+  }
+  const int mb = (p.M + BM - 1) / BM, nb = (p.N + BN - 1) / BN;
+  int grid = mb * nb;
+  int sms = txh::sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  if (grid > sms) grid = sms;
+  kern<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mbm, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+}  // namespace
+
+// C ABI. a_mn / b_mn select the operand layout described at the top of this file:
+//   a_mn == 0: A points at [M,K] (row stride lda);  a_mn == 1: A points at [K,M].
+//   b_mn == 0: B points at [N,K] (row stride ldb);  b_mn == 1: B points at [K,N].
+// Requirements: bf16 operands, 16-byte aligned bases, lda/ldb multiples of 8, N and ldc
+// multiples of 8 (4 for fp32 C). `status` is a device int32 that receives error bits.
+// `max_ctas` > 0 caps the grid (leaves SMs free for a concurrent copy/collective).
+extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                            long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, int accumulate,
+                            float alpha, int* status, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+  if ((lda & 7) || (ldb & 7) || (N & 7) || (ldc & 3)) return 2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15))
+    return 3;
+  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status};
+  // Wide tiles unless that would leave most SMs idle.
+  const long long tiles256 = static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256);
+  const bool bn256 = tiles256 >= txh::sm_count() || (N % 256 == 0 && tiles256 * 2 > 3 * txh::sm_count());
+  const int sel = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (bn256 || tiles256 >= 96) {
+    switch (sel) {
+      case 0: return launch<256, false, false>(A, B, p, lda, ldb, stream, max_ctas);
+      case 1: return launch<256, false, true>(A, B, p, lda, ldb, stream, max_ctas);
+      case 2: return launch<256, true, false>(A, B, p, lda, ldb, stream, max_ctas);
+      default: return launch<256, true, true>(A, B, p, lda, ldb, stream, max_ctas);
+    }
+  }
+  switch (sel) {
+    case 0: return launch<128, false, false>(A, B, p, lda, ldb, stream, max_ctas);
+    case 1: return launch<128, false, true>(A, B, p, lda, ldb, stream, max_ctas);
+    case 2: return launch<128, true, false>(A, B, p, lda, ldb, stream, max_ctas);
+    default: return launch<128, true, true>(A, B, p, lda, ldb, stream, max_ctas);
+  }
+}

@@ -1,0 +1,129 @@
+"""ctypes loader for the in-tree sm_100a kernel library.
+
+The library is plain C ABI (no torch headers); tensors cross as raw device pointers plus
+the current CUDA stream. On a machine with a GPU a missing library is an error, never a
+silent fallback: `require()` raises with the build command.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LOCK = threading.Lock()
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libtunix_b200.so"
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_ll = ctypes.c_longlong
+c_float = ctypes.c_float
+
+
+def lib_path() -> Path:
+  return _LIB_PATH
+
+
+def available() -> bool:
+  """True when the compiled library exists and a CUDA device is usable."""
+  return _LIB_PATH.exists() and torch.cuda.is_available()
+
+
+def _declare(lib):
+  P, I, L, F = c_void_p, c_int, c_ll, c_float
+  sigs = {
+      "tx_gemm_bf16": [P, P, P, I, I, I, L, L, L, I, I, I, I, F, P, I, P],
+      "tx_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, F, P],
+      "tx_rmsnorm_bwd_partials": [I],
+      "tx_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, F, F, P],
+      "tx_qknorm_rope_fwd": [P, P, P, P, P, P, P, L, I, I, I, I, L, L, F, F, I, P],
+      "tx_qknorm_rope_bwd": [P, P, P, P, P, P, P, P, P, L, I, I, I, I, L, L, L, F, F, P],
+      "tx_glu_fwd": [P, P, L, I, I, P],
+      "tx_glu_bwd": [P, P, P, L, I, I, P],
+      "tx_embedding_fwd": [P, P, P, L, I, I, F, P],
+      "tx_embedding_bwd": [P, P, P, L, I, I, F, P],
+      "tx_adamw": [P, P, P, P, P, L, F, F, F, F, F, F, F, P, I, P],
+      "tx_sumsq_partials": [],
+      "tx_sumsq": [P, L, P, P, I, P],
+      "tx_clip_scale": [P, P, F, P, P, P],
+      "tx_cast_f32_bf16": [P, P, L, P],
+      "tx_accum_bf16_f32": [P, P, L, F, P],
+      "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
+      "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],
+  }
+  for name, argtypes in sigs.items():
+    fn = getattr(lib, name, None)
+    if fn is None:
+      continue
+    fn.argtypes = argtypes
+    fn.restype = c_int
+  return lib
+
+
+def declare(name: str, argtypes, restype=c_int):
+  """Registers the signature of an additional exported symbol (used by optional modules)."""
+  lib = require()
+  fn = getattr(lib, name)
+  fn.argtypes = argtypes
+  fn.restype = restype
+  return fn
+
+
+def load():
+  """Returns the ctypes library or None when it has not been built."""
+  global _LIB
+  if _LIB is not None:
+    return _LIB
+  with _LOCK:
+    if _LIB is None and _LIB_PATH.exists():
+      _LIB = _declare(ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL))
+  return _LIB
+
+
+def require():
+  lib = load()
+  if lib is None:
+    raise RuntimeError(
+        f"{_LIB_PATH} is missing. Build it with `python -m tunix_b200.build_kernels` "
+        "(needs nvcc); CUDA tensors cannot be processed without the sm_100a kernels.")
+  return lib
+
+
+def stream_ptr() -> int:
+  return torch.cuda.current_stream().cuda_stream
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+  """Per-device int32 word that kernels OR error bits into (bounded waits that gave up...)."""
+  key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+  t = _status.get(key)
+  if t is None:
+    t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{key}")
+    _status[key] = t
+  return t
+
+
+def check_status(device=None) -> None:
+  """Synchronising check of the kernel status word; raises if any kernel reported an error."""
+  if not torch.cuda.is_available():
+    return
+  dev = torch.cuda.current_device() if device is None else torch.device(device).index
+  t = _status.get(dev)
+  if t is None:
+    return
+  v = int(t.item())
+  if v != 0:
+    t.zero_()
+    raise RuntimeError(f"tunix_b200 kernel reported error status 0x{v:x} "
+                       "(1/2/4: producer/MMA/epilogue wait timed out, 8: bad argument, 16: peer wait timed out)")
+
+
+def check_rc(rc: int, what: str) -> None:
+  if rc != 0:
+    raise RuntimeError(f"{what} failed with code {rc}")

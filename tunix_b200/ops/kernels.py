@@ -1,0 +1,231 @@
+"""Raw (non-autograd) Python entry points of the sm_100a kernels.
+
+Each function validates shapes/dtypes, allocates outputs with torch and launches the kernel
+on the current stream. Autograd glue and the CPU oracle live in `functional.py`.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+bf16 = torch.bfloat16
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+  return None if t is None else t.data_ptr()
+
+
+def gemm_supported(M: int, N: int, K: int, *tensors: torch.Tensor) -> bool:
+  """Shapes the tcgen05 GEMM accepts: bf16, 16-byte aligned rows (multiples of 8)."""
+  if M <= 0 or N <= 0 or K <= 0 or N % 8 or K % 8 or M % 8:
+    return False
+  return all(t.dtype == bf16 and t.is_cuda and t.data_ptr() % 16 == 0 for t in tensors)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         out: Optional[torch.Tensor] = None, out_dtype: torch.dtype = bf16, accumulate: bool = False,
+         alpha: float = 1.0, max_ctas: int = 0) -> torch.Tensor:
+  """C[M,N] (+)= alpha * op(a) @ op(b)^T on the tcgen05 tensor cores.
+
+  a: [M,K] (a_mn=False) or [K,M] (a_mn=True); b: [N,K] (b_mn=False) or [K,N] (b_mn=True).
+  Both are 2-D bf16 with unit inner stride. `out` may be bf16 or fp32 and, with
+  `accumulate`, is added to in the epilogue (fp32 gradient accumulation, residual adds).
+  """
+  assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+  if a_mn:
+    K, M = a.shape
+  else:
+    M, K = a.shape
+  if b_mn:
+    Kb, N = b.shape
+  else:
+    N, Kb = b.shape
+  assert K == Kb, f"inner dims differ: {K} vs {Kb}"
+  if out is None:
+    assert not accumulate
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+  assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (bf16, torch.float32)
+  lib = _lib.require()
+  rc = lib.tx_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                        out.stride(0), int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate),
+                        float(alpha), _lib.status_word(a.device).data_ptr(), int(max_ctas), _lib.stream_ptr())
+  _lib.check_rc(rc, f"tx_gemm_bf16(M={M},N={N},K={K},a_mn={a_mn},b_mn={b_mn})")
+  return out
+
+
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, w_offset: float = 0.0,
+                residual: Optional[torch.Tensor] = None, want_rstd: bool = True):
+  """Returns (y, summed_residual_or_None, rstd). x, residual: [T, D] bf16 contiguous."""
+  T, D = x.shape
+  y = torch.empty_like(x)
+  s = torch.empty_like(x) if residual is not None else None
+  rstd = torch.empty(T, dtype=torch.float32, device=x.device) if want_rstd else None
+  rc = _lib.require().tx_rmsnorm_fwd(x.data_ptr(), _p(residual), w.data_ptr(), y.data_ptr(), _p(s), _p(rstd), T, D,
+                                     float(eps), float(w_offset), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_rmsnorm_fwd")
+  return y, s, rstd
+
+
+def rmsnorm_bwd(x, w, dy, rstd, eps, w_offset=0.0, dres=None, dw_out: Optional[torch.Tensor] = None,
+                dw_accumulate: bool = False):
+  """Returns (dx, dw fp32). `dres` is added into dx (gradient of the residual stream)."""
+  T, D = x.shape
+  lib = _lib.require()
+  P = lib.tx_rmsnorm_bwd_partials(T)
+  partial = torch.empty((P, D), dtype=torch.float32, device=x.device)
+  dx = torch.empty_like(x)
+  if dw_out is None:
+    dw_out = torch.empty(D, dtype=torch.float32, device=x.device)
+    dw_accumulate = False
+  rc = lib.tx_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), dy.data_ptr(), _p(rstd), _p(dres), dx.data_ptr(),
+                          partial.data_ptr(), dw_out.data_ptr(), int(dw_accumulate), T, D, float(eps),
+                          float(w_offset), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_rmsnorm_bwd")
+  return dx, dw_out
+
+
+def qknorm_rope_fwd(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, n_q: int, n_k: int,
+                    head_dim: int, wq: Optional[torch.Tensor] = None, wk: Optional[torch.Tensor] = None,
+                    eps: float = 1e-6, w_offset: float = 0.0, inverse: bool = False) -> torch.Tensor:
+  """x: [T, n_total*H] bf16 (q heads, then k heads, then anything else, e.g. v). The first
+  n_q + n_k heads get (optional per-head RMSNorm and) rotary embedding; the rest is copied."""
+  T, W = x.shape
+  n_total = W // head_dim
+  out = torch.empty_like(x)
+  rc = _lib.require().tx_qknorm_rope_fwd(x.data_ptr(), out.data_ptr(), positions.data_ptr(), cos_sin.data_ptr(),
+                                         _p(wq), _p(wk), None, T, n_total, n_q, n_q + n_k, head_dim, x.stride(0),
+                                         out.stride(0), float(eps), float(w_offset), int(inverse),
+                                         _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_qknorm_rope_fwd")
+  return out
+
+
+def qknorm_rope_bwd(x, dy, positions, cos_sin, n_q, n_k, head_dim, wq=None, wk=None, eps=1e-6, w_offset=0.0):
+  """Returns (dx, dwq fp32 or None, dwk fp32 or None)."""
+  T, W = x.shape
+  n_total = W // head_dim
+  dx = torch.empty_like(x)
+  dwq = dwk = None
+  if wq is not None:
+    dwq = torch.zeros(head_dim, dtype=torch.float32, device=x.device)
+    dwk = torch.zeros(head_dim, dtype=torch.float32, device=x.device)
+  rc = _lib.require().tx_qknorm_rope_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), positions.data_ptr(),
+                                         cos_sin.data_ptr(), _p(wq), _p(wk), _p(dwq), _p(dwk), T, n_total, n_q,
+                                         n_q + n_k, head_dim, x.stride(0), dy.stride(0), dx.stride(0), float(eps),
+                                         float(w_offset), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_qknorm_rope_bwd")
+  return dx, dwq, dwk
+
+
+def glu_fwd(gu: torch.Tensor, gelu: bool) -> torch.Tensor:
+  T, F2 = gu.shape
+  out = torch.empty((T, F2 // 2), dtype=gu.dtype, device=gu.device)
+  _lib.check_rc(_lib.require().tx_glu_fwd(gu.data_ptr(), out.data_ptr(), T, F2 // 2, int(gelu), _lib.stream_ptr()),
+                "tx_glu_fwd")
+  return out
+
+
+def glu_bwd(gu: torch.Tensor, dout: torch.Tensor, gelu: bool) -> torch.Tensor:
+  T, F2 = gu.shape
+  dgu = torch.empty_like(gu)
+  _lib.check_rc(_lib.require().tx_glu_bwd(gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), T, F2 // 2, int(gelu),
+                                          _lib.stream_ptr()), "tx_glu_bwd")
+  return dgu
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+  ids32 = ids.reshape(-1).to(torch.int32)
+  V, D = table.shape
+  out = torch.empty((ids32.numel(), D), dtype=table.dtype, device=table.device)
+  _lib.check_rc(_lib.require().tx_embedding_fwd(ids32.data_ptr(), table.data_ptr(), out.data_ptr(), ids32.numel(),
+                                                D, V, float(scale), _lib.stream_ptr()), "tx_embedding_fwd")
+  return out
+
+
+def embedding_bwd(ids: torch.Tensor, dout: torch.Tensor, grad_table: torch.Tensor, scale: float = 1.0) -> None:
+  """grad_table (fp32 [V, D]) += scatter of dout rows."""
+  ids32 = ids.reshape(-1).to(torch.int32)
+  V, D = grad_table.shape
+  _lib.check_rc(_lib.require().tx_embedding_bwd(ids32.data_ptr(), dout.data_ptr(), grad_table.data_ptr(),
+                                                ids32.numel(), D, V, float(scale), _lib.stream_ptr()),
+                "tx_embedding_bwd")
+
+
+def adamw_step(master, m, v, grad, param_bf16, *, lr, beta1, beta2, eps, weight_decay, step: int,
+               grad_scale: Optional[torch.Tensor] = None, zero_grad: bool = True) -> None:
+  """Flat fused AdamW on fp32 master weights; refreshes the bf16 compute copy."""
+  n = master.numel()
+  bc1 = 1.0 - beta1 ** step
+  bc2 = 1.0 - beta2 ** step
+  _lib.check_rc(_lib.require().tx_adamw(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(),
+                                        _p(param_bf16), n, float(lr), float(beta1), float(beta2), float(eps),
+                                        float(weight_decay), float(bc1), float(bc2), _p(grad_scale),
+                                        int(zero_grad), _lib.stream_ptr()), "tx_adamw")
+
+
+_scratch = {}
+
+
+def _partials(device) -> torch.Tensor:
+  key = torch.device(device).index
+  t = _scratch.get(key)
+  if t is None:
+    t = torch.empty(_lib.require().tx_sumsq_partials(), dtype=torch.float32, device=device)
+    _scratch[key] = t
+  return t
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+  """out[0] (+)= sum(x**2) for a flat fp32 tensor, deterministic reduction order."""
+  assert x.dtype == torch.float32 and x.is_contiguous()
+  _lib.check_rc(_lib.require().tx_sumsq(x.data_ptr(), x.numel(), _partials(x.device).data_ptr(), out.data_ptr(),
+                                        int(accumulate), _lib.stream_ptr()), "tx_sumsq")
+
+
+def clip_scale(sumsq_t, inv_denom_t, max_norm: float, norm_out, scale_out) -> None:
+  _lib.check_rc(_lib.require().tx_clip_scale(sumsq_t.data_ptr(), _p(inv_denom_t), float(max_norm or 0.0),
+                                             norm_out.data_ptr(), scale_out.data_ptr(), _lib.stream_ptr()),
+                "tx_clip_scale")
+
+
+def logprob_fwd(logits: torch.Tensor, targets: torch.Tensor, inv_temp: float = 1.0, softcap: float = 0.0,
+                want_entropy: bool = False, n_valid: Optional[int] = None):
+  """logits [T, >=V] fp32/bf16 -> (logp[T], lse[T], entropy[T] or None), all fp32."""
+  T = logits.shape[0]
+  V = n_valid if n_valid is not None else logits.shape[1]
+  dev = logits.device
+  logp = torch.empty(T, dtype=torch.float32, device=dev)
+  lse = torch.empty(T, dtype=torch.float32, device=dev)
+  ent = torch.empty(T, dtype=torch.float32, device=dev) if want_entropy else None
+  tg = targets.to(torch.int32)
+  _lib.check_rc(_lib.require().tx_logprob_fwd(logits.data_ptr(), int(logits.dtype == torch.float32), logits.stride(0),
+                                              tg.data_ptr(), logp.data_ptr(), lse.data_ptr(), _p(ent), T, V,
+                                              float(inv_temp), float(softcap), _lib.stream_ptr()), "tx_logprob_fwd")
+  return logp, lse, ent
+
+
+def logprob_bwd(logits, targets, lse, entropy, g_logp, g_ent, inv_temp=1.0, softcap=0.0, n_valid=None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+  """Returns bf16 dlogits [T, V_pad] where V_pad = logits.shape[1]."""
+  T, V_pad = logits.shape
+  V = n_valid if n_valid is not None else V_pad
+  if out is None:
+    out = torch.empty((T, V_pad), dtype=bf16, device=logits.device)
+  tg = targets.to(torch.int32)
+  _lib.check_rc(_lib.require().tx_logprob_bwd(logits.data_ptr(), int(logits.dtype == torch.float32), logits.stride(0),
+                                              tg.data_ptr(), lse.data_ptr(), _p(entropy), _p(g_logp), _p(g_ent),
+                                              out.data_ptr(), out.stride(0), T, V, V_pad, float(inv_temp),
+                                              float(softcap), _lib.stream_ptr()), "tx_logprob_bwd")
+  return out
+
+
+def rope_table(max_pos: int, head_dim: int, theta: float, device, scale: float = 1.0) -> torch.Tensor:
+  """[max_pos, head_dim] fp32 = [cos(H/2) | sin(H/2)], timescale theta^(2i/H)."""
+  half = head_dim // 2
+  inv = 1.0 / (theta ** (torch.arange(half, dtype=torch.float64) * 2.0 / head_dim))
+  ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / scale * inv[None, :]
+  return torch.cat([ang.cos(), ang.sin()], dim=-1).to(torch.float32).to(device)
