@@ -1,0 +1,228 @@
+"""Trainer semantics on CPU: accumulation equivalence, weighted denominators, hooks, metrics,
+checkpoint save / resume, LoRA-only training."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tunix_b200 import optim
+from tunix_b200.common.configs import TrainingConfig
+from tunix_b200.models.transformer import ModelConfig, Transformer
+from tunix_b200.sft import hooks as hooks_lib
+from tunix_b200.sft import utils
+from tunix_b200.sft.peft_trainer import PeftTrainer, TrainingInput
+
+
+def tiny(seed=0, **kw):
+  cfg = ModelConfig(num_layers=2, vocab_size=128, embed_dim=32, hidden_dim=64, num_heads=4, head_dim=8, num_kv_heads=2,
+                    **kw)
+  return Transformer(cfg).init_weights(seed=seed)
+
+
+def batches(n, B=4, L=16, seed=0, ragged=False):
+  g = torch.Generator().manual_seed(seed)
+  out = []
+  for i in range(n):
+    tok = torch.randint(0, 128, (B, L), generator=g)
+    mask = torch.ones(B, L)
+    if ragged:
+      for b in range(B):
+        mask[b, int(torch.randint(4, L, (1,), generator=g)):] = 0
+    out.append(TrainingInput(tok, mask))
+  return out
+
+
+def cfg(**kw):
+  kw.setdefault("eval_every_n_steps", 100)
+  kw.setdefault("pbar_description", None)
+  return TrainingConfig(**kw)
+
+
+def test_positions_and_masks():
+  m = torch.tensor([[0, 0, 1, 1, 1], [1, 1, 1, 0, 0]])
+  assert utils.build_positions_from_mask(m).tolist() == [[0, 0, 0, 1, 2], [0, 1, 2, 2, 2]]
+  am = utils.make_causal_attn_mask(m)
+  assert am.shape == (2, 5, 5)
+  assert am[0, 4].tolist() == [False, False, True, True, True]
+  assert am[1, 1].tolist() == [True, True, False, False, False]
+  with pytest.raises(ValueError):
+    utils.make_causal_attn_mask(torch.ones(3))
+
+
+def test_weighted_metric_zero_safe():
+  w = utils.WeightedMetric(torch.tensor(6.0), torch.tensor(3.0))
+  assert w.compute().item() == 2.0
+  z = utils.WeightedMetric(torch.tensor(6.0), torch.tensor(0.0))
+  assert z.compute().item() == 0.0
+  e = utils.WeightedMetric(torch.tensor(6.0), torch.tensor(0.0), eps=1e-8, min_denom=1.0)
+  assert e.compute().item() == 6.0
+
+
+def test_loss_decreases_and_metrics_logged():
+  model = tiny()
+  tr = PeftTrainer(model, optim.inject_hyperparams(optim.adamw)(learning_rate=1e-2), cfg(max_steps=8))
+  data = batches(1) * 8
+  tr.train(data)
+  losses = tr.metrics_logger.get_metric_history("", "loss", "train")
+  assert len(losses) == 8
+  assert losses[-1] < losses[0] - 0.1
+  ppl = tr.metrics_logger.get_metric_history("", "perplexity", "train")
+  np.testing.assert_allclose(ppl, np.exp(losses), rtol=1e-5)
+  assert tr.metrics_logger.metric_exists("", "learning_rate", "train")
+  assert tr.metrics_logger.metric_exists("", "grad_norm", "train")
+  assert tr.train_steps == 8 and tr.iter_steps == 8
+
+
+def test_grad_accumulation_equals_full_batch_with_ragged_masks():
+  """K micro-batches with different token counts == one concatenated batch (global weighted
+  mean, not mean of means)."""
+  data = batches(2, B=2, ragged=True, seed=3)
+  big = TrainingInput(torch.cat([d.input_tokens for d in data]), torch.cat([d.input_mask for d in data]))
+  m1, m2 = tiny(seed=1), tiny(seed=1)
+  t1 = PeftTrainer(m1, optim.sgd(0.5), cfg(gradient_accumulation_steps=2))
+  t1.train(data)
+  t2 = PeftTrainer(m2, optim.sgd(0.5), cfg())
+  t2.train([big])
+  for (n, p), (_, q) in zip(m1.named_parameters(), m2.named_parameters()):
+    torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-6, msg=n)
+  assert t1.train_steps == 1 and t1.iter_steps == 2
+  l1 = t1.metrics_logger.get_metric_history("", "loss", "train")
+  l2 = t2.metrics_logger.get_metric_history("", "loss", "train")
+  np.testing.assert_allclose(l1, l2, rtol=1e-5)
+  gn = t1.metrics_logger.get_metric_history("", "grad_norm", "train")
+  assert gn.shape == (1,)
+
+
+def test_grad_clipping_through_chain():
+  m1, m2 = tiny(seed=2), tiny(seed=2)
+  data = batches(1, seed=5)
+  t1 = PeftTrainer(m1, optim.chain(optim.clip_by_global_norm(1e-3), optim.sgd(1.0)), cfg())
+  t1.train(data)
+  before = {n: p.clone() for n, p in tiny(seed=2).named_parameters()}
+  delta = math.sqrt(sum((p - before[n]).pow(2).sum().item() for n, p in m1.named_parameters()))
+  assert abs(delta - 1e-3) < 1e-4      # the whole update has exactly the clipped norm
+
+
+def test_hooks_are_called():
+  calls = []
+
+  class H(hooks_lib.TrainingHooks):
+    def on_train_start(self, ctx): calls.append("start")
+    def on_train_end(self, ctx): calls.append("end")
+    def on_train_step_start(self, ctx): calls.append("s")
+    def on_train_step_end(self, ctx, step, loss): calls.append(("e", step))
+    def on_eval_step_start(self, ctx): calls.append("es")
+    def on_eval_step_end(self, ctx, loss): calls.append("ee")
+
+  tr = PeftTrainer(tiny(), optim.sgd(0.1), cfg(max_steps=3, eval_every_n_steps=2))
+  tr.with_training_hooks(H())
+  tr.train(batches(3), eval_ds=batches(2, seed=9))
+  assert calls[0] == "es" and "ee" in calls            # initial eval
+  assert calls.count("s") == 3
+  assert [c for c in calls if isinstance(c, tuple)] == [("e", 1), ("e", 2), ("e", 3)]
+  assert "end" in calls and calls[0 if False else calls.index("end") - 1] in (("e", 2), "ee", "s")
+  assert tr.metrics_logger.metric_exists("", "loss", "eval")
+
+
+def test_data_hooks_supply_batches():
+  class D(hooks_lib.DataHooks):
+    def __init__(self): self.it = iter(batches(2))
+    def load_next_train_batch(self, ctx): return next(self.it, None)
+    def load_next_eval_batch(self, ctx): return None
+  tr = PeftTrainer(tiny(), optim.sgd(0.1), cfg())
+  tr.with_data_hooks(D())
+  tr.train([])
+  assert tr.train_steps == 2
+
+
+def test_custom_loss_with_aux_and_plain_scalar():
+  def loss_fn(model, input_tokens, input_mask):
+    logits, _ = model(input_tokens)
+    return logits.float().pow(2).mean(), {"foo": 1}
+  seen = []
+
+  class T(PeftTrainer):
+    def _post_process_train_step(self, aux): seen.append(aux)
+  tr = T(tiny(), optim.sgd(0.01), cfg())
+  tr.with_loss_fn(loss_fn, has_aux=True)
+  tr.train(batches(2))
+  assert seen == [{"foo": 1}, {"foo": 1}]
+
+
+def test_checkpoint_save_and_resume(tmp_path):
+  d = str(tmp_path / "ckpt")
+  data = batches(6)
+  m = tiny(seed=4)
+  tr = PeftTrainer(m, optim.adamw(1e-2), cfg(max_steps=3, checkpoint_root_directory=d))
+  tr.train(data)
+  assert tr.checkpoint_manager.latest_step() == 3
+  assert os.path.exists(os.path.join(d, "3", "model_params", "_METADATA"))
+  assert os.path.exists(os.path.join(d, "3", "optimizer_state", "_METADATA"))
+  # resume: parameters, optimizer count and step counters come back; iterator is fast-forwarded
+  m2 = tiny(seed=99)
+  tr2 = PeftTrainer(m2, optim.adamw(1e-2), cfg(max_steps=6, checkpoint_root_directory=d))
+  assert tr2.train_steps == 3 and tr2.iter_steps == 3
+  for (n, p), (_, q) in zip(m.named_parameters(), m2.named_parameters()):
+    torch.testing.assert_close(p, q, msg=n)
+  assert int(tr2.optimizer.opt_state["count"]) == 3
+  tr2.train(data)
+  assert tr2.train_steps == 6
+  # uninterrupted run reaches the same weights
+  m3 = tiny(seed=4)
+  tr3 = PeftTrainer(m3, optim.adamw(1e-2), cfg(max_steps=6))
+  tr3.train(data)
+  for (n, p), (_, q) in zip(m2.named_parameters(), m3.named_parameters()):
+    torch.testing.assert_close(p, q, rtol=1e-4, atol=1e-6, msg=n)
+
+
+def test_lora_training_touches_only_lora_params(tmp_path):
+  from tunix_b200.models import lora
+  m = tiny(seed=6)
+  lora.apply_lora_to_model(m, rank=4, alpha=8.0, module_path=".*(q_proj|k_proj|v_proj|o_proj)")
+  before = {n: p.clone() for n, p in m.named_parameters()}
+  d = str(tmp_path / "c")
+  tr = PeftTrainer(m, optim.adamw(1e-2), cfg(max_steps=3, checkpoint_root_directory=d))
+  tr.train(batches(3))
+  changed = {n for n, p in m.named_parameters() if not torch.equal(p, before[n])}
+  assert changed and all("lora" in n for n in changed)
+  lora_b_changed = [n for n in changed if "lora_b" in n]
+  assert lora_b_changed
+  # the checkpoint holds only the adapters
+  from tunix_b200.ckpt import orbax_layout
+  keys = orbax_layout.read_tree_metadata(os.path.join(d, "3", "model_params")).keys()
+  assert keys and all(any("lora" in str(k) for k in key) for key in keys)
+  m2 = tiny(seed=6)
+  lora.apply_lora_to_model(m2, rank=4, alpha=8.0, module_path=".*(q_proj|k_proj|v_proj|o_proj)")
+  tr2 = PeftTrainer(m2, optim.adamw(1e-2), cfg(checkpoint_root_directory=d))
+  assert tr2.train_steps == 3
+  for (n, p), (_, q) in zip(m.named_parameters(), m2.named_parameters()):
+    if "lora" in n:
+      torch.testing.assert_close(p, q, msg=n)
+
+
+def test_schedules_and_optimizer_factories():
+  s = optim.warmup_cosine_decay_schedule(0.0, 1.0, 10, 110, end_value=0.1)
+  assert s(0) == 0.0 and abs(s(10) - 1.0) < 1e-9 and abs(s(110) - 0.1) < 1e-9 and abs(s(5) - 0.5) < 1e-9
+  assert optim.get_optimizer_factory("adamw") is optim.adamw
+  with pytest.raises(ValueError):
+    optim.get_optimizer_factory("nope")
+  kw = optim.filter_kwargs(optim.adamw, {"learning_rate": 1.0, "b1": 0.5, "bogus": 3, "eps": None})
+  assert kw == {"learning_rate": 1.0, "b1": 0.5}
+
+
+def test_adamw_matches_torch():
+  torch.manual_seed(0)
+  p = torch.nn.Parameter(torch.randn(7, 5))
+  q = torch.nn.Parameter(p.detach().clone())
+  ref = torch.optim.AdamW([q], lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.05)
+  tx = optim.adamw(1e-2, b1=0.9, b2=0.99, eps=1e-8, weight_decay=0.05)
+  st = tx.init({"p": p})
+  for i in range(5):
+    g = torch.randn(7, 5)
+    q.grad = g.clone()
+    ref.step()
+    tx.apply({"p": p}, {"p": g}, st)
+  torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+  assert int(st["count"]) == 5

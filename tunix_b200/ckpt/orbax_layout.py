@@ -1,0 +1,276 @@
+"""Reading and writing parameter trees in the Orbax on-disk layout.
+
+A checkpointable directory (`<root>/<step>/model_params`, `.../optimizer_state`) holds
+`_METADATA` (tree structure keyed by stringified key tuples), `_sharding`,
+`array_metadatas/process_<r>` and the arrays. Arrays are written as plain zarr-v2 directories
+(`<a.b.c>/.zarray` + chunk files) - the variant Orbax itself produces when OCDBT is disabled
+(tunix/sft/checkpoint_manager.py:156-159) and reads back transparently. Reading also accepts
+the OCDBT key-value-store variant (`manifest.ocdbt` + `d/*`), see `ocdbt.py`.
+
+Trees are flat dicts `{("layers", 0, "attn", "q_proj", "w", "value"): ndarray}`: string keys are
+dict keys (key_type 2), ints are sequence indices (key_type 1).
+"""
+from __future__ import annotations
+
+import base64
+import ctypes
+import ctypes.util
+import json
+import os
+import time
+from typing import Any, Dict, Iterable, List, Mapping, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+Key = Tuple[Union[str, int], ...]
+
+_ZARR_DTYPES = {
+    "float32": "<f4", "float64": "<f8", "float16": "<f2", "bfloat16": "bfloat16", "int32": "<i4", "int64": "<i8",
+    "int16": "<i2", "int8": "|i1", "uint8": "|u1", "bool": "|b1", "uint32": "<u4", "uint16": "<u2",
+}
+_NP_FROM_ZARR = {v: k for k, v in _ZARR_DTYPES.items()}
+
+
+def key_to_str(key: Key) -> str:
+  return "(" + ", ".join(repr(k) for k in key) + ("," if len(key) == 1 else "") + ")"
+
+
+def param_name(key: Key) -> str:
+  return ".".join(str(k) for k in key)
+
+
+def _tensor_to_bytes(t: torch.Tensor) -> Tuple[bytes, str, List[int]]:
+  t = t.detach()
+  if t.is_cuda:
+    t = t.cpu()
+  t = t.contiguous()
+  shape = list(t.shape)
+  if t.dtype == torch.bfloat16:
+    return t.view(torch.int16).numpy().tobytes(), "bfloat16", shape
+  a = t.numpy()
+  return a.tobytes(), _ZARR_DTYPES[str(a.dtype)], shape
+
+
+def _bytes_to_tensor(buf: bytes, zdtype: str, shape: Sequence[int]) -> torch.Tensor:
+  if zdtype == "bfloat16":
+    a = np.frombuffer(buf, dtype=np.int16).reshape(shape).copy()
+    return torch.from_numpy(a).view(torch.bfloat16)
+  name = _NP_FROM_ZARR.get(zdtype)
+  if name is None:
+    a = np.frombuffer(buf, dtype=np.dtype(zdtype)).reshape(shape).copy()
+  else:
+    a = np.frombuffer(buf, dtype=np.dtype(name)).reshape(shape).copy()
+  return torch.from_numpy(a)
+
+
+# ---------------------------------------------------------------------------- zstd (optional)
+_zstd = None
+
+
+def _load_zstd():
+  global _zstd
+  if _zstd is None:
+    for cand in ("libzstd.so.1", ctypes.util.find_library("zstd")):
+      if not cand:
+        continue
+      try:
+        lib = ctypes.CDLL(cand)
+        lib.ZSTD_getFrameContentSize.restype = ctypes.c_ulonglong
+        lib.ZSTD_getFrameContentSize.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+        lib.ZSTD_decompress.restype = ctypes.c_size_t
+        lib.ZSTD_decompress.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t]
+        lib.ZSTD_isError.restype = ctypes.c_uint
+        lib.ZSTD_isError.argtypes = [ctypes.c_size_t]
+        _zstd = lib
+        break
+      except OSError:
+        continue
+    if _zstd is None:
+      _zstd = False
+  return _zstd
+
+
+def zstd_decompress(data: bytes, max_out: Optional[int] = None) -> bytes:
+  lib = _load_zstd()
+  if not lib:
+    raise RuntimeError("libzstd is not available; cannot read a zstd-compressed checkpoint")
+  n = lib.ZSTD_getFrameContentSize(data, len(data))
+  if n in (2**64 - 1, 2**64 - 2):   # unknown / error
+    n = max_out or (len(data) * 64)
+  out = ctypes.create_string_buffer(int(n))
+  got = lib.ZSTD_decompress(out, int(n), data, len(data))
+  if lib.ZSTD_isError(got):
+    raise RuntimeError("zstd decompression failed")
+  return out.raw[:got]
+
+
+# ---------------------------------------------------------------------------- write
+def _write_file(path: str, data: bytes) -> None:
+  tmp = path + ".tmp"
+  with open(tmp, "wb") as f:
+    f.write(data)
+  os.replace(tmp, path)
+
+
+def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: int = 0,
+               sharding_desc: Optional[Mapping[Key, Mapping[str, Any]]] = None) -> None:
+  """Writes `{key tuple: tensor}` under `directory` in the Orbax plain-zarr layout."""
+  os.makedirs(directory, exist_ok=True)
+  tree_md: Dict[str, Any] = {}
+  arr_md: List[Dict[str, Any]] = []
+  shard_md: Dict[str, str] = {}
+  for key, t in tree.items():
+    if not isinstance(t, torch.Tensor):
+      t = torch.as_tensor(t)
+    data, zdtype, shape = _tensor_to_bytes(t)
+    name = param_name(key)
+    pdir = os.path.join(directory, name)
+    os.makedirs(pdir, exist_ok=True)
+    zarray = {
+        "chunks": shape if shape else [], "compressor": None, "dimension_separator": ".", "dtype": zdtype,
+        "fill_value": None, "filters": None, "order": "C", "shape": shape, "zarr_format": 2,
+    }
+    _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
+    chunk_name = ".".join("0" for _ in shape) if shape else "0"
+    _write_file(os.path.join(pdir, chunk_name), data)
+    tree_md[key_to_str(key)] = {
+        "key_metadata": [{"key": str(k), "key_type": 1 if isinstance(k, int) else 2} for k in key],
+        "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, "write_shape": shape},
+    }
+    arr_md.append({"array_metadata": {"param_name": name, "write_shape": shape, "chunk_shape": shape,
+                                      "ext_metadata": None}})
+    desc = (sharding_desc or {}).get(key) or {"sharding_type": "SingleDeviceSharding", "device_str": "cuda:0"}
+    shard_md[base64.b64encode(name.encode()).decode()] = json.dumps(desc)
+  if process_index == 0:
+    _write_file(os.path.join(directory, "_METADATA"), json.dumps({
+        "tree_metadata": tree_md, "use_zarr3": False, "store_array_data_equal_to_fill_value": True,
+        "custom_metadata": None}).encode())
+    _write_file(os.path.join(directory, "_sharding"), json.dumps(shard_md).encode())
+  os.makedirs(os.path.join(directory, "array_metadatas"), exist_ok=True)
+  _write_file(os.path.join(directory, "array_metadatas", f"process_{process_index}"),
+              json.dumps({"array_metadatas": arr_md}).encode())
+
+
+# ---------------------------------------------------------------------------- read
+def _parse_key_str(s: str, md: Mapping[str, Any]) -> Key:
+  out: List[Union[str, int]] = []
+  for k in md["key_metadata"]:
+    out.append(int(k["key"]) if k.get("key_type") == 1 else k["key"])
+  return tuple(out)
+
+
+def read_tree_metadata(directory: str) -> Dict[Key, Dict[str, Any]]:
+  with open(os.path.join(directory, "_METADATA")) as f:
+    md = json.load(f)
+  return {_parse_key_str(s, v): v for s, v in md["tree_metadata"].items()}
+
+
+def _decode_chunk(raw: bytes, zarray: Mapping[str, Any], nbytes: int) -> bytes:
+  comp = zarray.get("compressor")
+  if comp is None:
+    return raw
+  cid = comp.get("id")
+  if cid == "zstd":
+    return zstd_decompress(raw, nbytes)
+  if cid in ("zlib", "gzip"):
+    import zlib
+    return zlib.decompress(raw, 15 + (16 if cid == "gzip" else 0))
+  raise RuntimeError(f"unsupported zarr compressor {cid!r}")
+
+
+class _DirKV:
+  """Key-value view of a plain directory (keys are relative paths)."""
+
+  def __init__(self, root: str):
+    self.root = root
+
+  def get(self, key: str) -> Optional[bytes]:
+    p = os.path.join(self.root, key)
+    if not os.path.isfile(p):
+      return None
+    with open(p, "rb") as f:
+      return f.read()
+
+
+def open_kv(directory: str):
+  """Directory-backed store, or the OCDBT store when `manifest.ocdbt` is present."""
+  if os.path.exists(os.path.join(directory, "manifest.ocdbt")):
+    from . import ocdbt
+    return ocdbt.OcdbtStore(directory)
+  return _DirKV(directory)
+
+
+def read_array(kv, name: str) -> torch.Tensor:
+  zraw = kv.get(f"{name}/.zarray")
+  if zraw is None:
+    raise KeyError(name)
+  zarray = json.loads(zraw)
+  shape = list(zarray["shape"])
+  chunks = list(zarray["chunks"]) or []
+  zdtype = zarray["dtype"]
+  sep = zarray.get("dimension_separator", ".")
+  itemsize = 2 if zdtype == "bfloat16" else np.dtype(_NP_FROM_ZARR.get(zdtype, zdtype)).itemsize
+  if not shape:
+    raw = kv.get(f"{name}/0")
+    if raw is None:
+      return _bytes_to_tensor(b"\0" * itemsize, zdtype, [])
+    return _bytes_to_tensor(_decode_chunk(raw, zarray, itemsize), zdtype, [])
+  npd = np.int16 if zdtype == "bfloat16" else np.dtype(_NP_FROM_ZARR.get(zdtype, zdtype))
+  out = np.zeros(shape, dtype=npd)
+  grid = [max(1, -(-s // c)) for s, c in zip(shape, chunks)]
+  for idx in np.ndindex(*grid):
+    raw = kv.get(f"{name}/" + sep.join(str(i) for i in idx))
+    if raw is None:
+      continue   # chunk equal to the fill value
+    nbytes = int(np.prod(chunks)) * itemsize
+    buf = _decode_chunk(raw, zarray, nbytes)
+    block = np.frombuffer(buf, dtype=npd).reshape(chunks)
+    sl = tuple(slice(i * c, min((i + 1) * c, s)) for i, c, s in zip(idx, chunks, shape))
+    out[sl] = block[tuple(slice(0, s.stop - s.start) for s in sl)]
+  t = torch.from_numpy(out)
+  return t.view(torch.bfloat16) if zdtype == "bfloat16" else t
+
+
+def read_tree(directory: str, keys: Optional[Iterable[Key]] = None, partial: bool = False) -> Dict[Key, torch.Tensor]:
+  """Reads arrays (all, or the requested keys). Missing keys raise KeyError unless `partial`."""
+  md = read_tree_metadata(directory)
+  kv = open_kv(directory)
+  want = list(keys) if keys is not None else list(md.keys())
+  out: Dict[Key, torch.Tensor] = {}
+  for key in want:
+    if key not in md:
+      if partial:
+        continue
+      raise KeyError(f"{key} not found in checkpoint {directory}")
+    out[key] = read_array(kv, param_name(key))
+  return out
+
+
+# ---------------------------------------------------------------------------- step directories
+def write_checkpoint_metadata(step_dir: str, item_names: Sequence[str], custom_metadata: Optional[Mapping[str, Any]],
+                              init_ns: int) -> None:
+  handler = "orbax.checkpoint._src.handlers.standard_checkpoint_handler.StandardCheckpointHandler"
+  md = {"item_handlers": {n: handler for n in item_names}, "metrics": {}, "performance_metrics": {},
+        "init_timestamp_nsecs": init_ns, "commit_timestamp_nsecs": time.time_ns(),
+        "custom_metadata": dict(custom_metadata or {})}
+  _write_file(os.path.join(step_dir, "_CHECKPOINT_METADATA"), json.dumps(md).encode())
+
+
+def read_checkpoint_metadata(step_dir: str) -> Dict[str, Any]:
+  p = os.path.join(step_dir, "_CHECKPOINT_METADATA")
+  if not os.path.exists(p):
+    return {}
+  with open(p) as f:
+    return json.load(f)
+
+
+def list_steps(root: str) -> List[int]:
+  """Committed step directories (those with `_CHECKPOINT_METADATA`)."""
+  if not root or not os.path.isdir(root):
+    return []
+  steps = []
+  for n in os.listdir(root):
+    if n.isdigit() and os.path.exists(os.path.join(root, n, "_CHECKPOINT_METADATA")):
+      steps.append(int(n))
+  return sorted(steps)

@@ -124,6 +124,11 @@ def check_status(device=None) -> None:
                        "(1/2/4: producer/MMA/epilogue wait timed out, 8: bad argument, 16: peer wait timed out)")
 
 
+launch_calls = 0   # number of library launches issued by this process (each is >= 1 kernel)
+
+
 def check_rc(rc: int, what: str) -> None:
+  global launch_calls
+  launch_calls += 1
   if rc != 0:
     raise RuntimeError(f"{what} failed with code {rc}")
