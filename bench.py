@@ -153,12 +153,10 @@ def main():
   tx = optim.adamw(learning_rate=1e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.1)
   tcfg = TrainingConfig(eval_every_n_steps=10**9, gradient_accumulation_steps=ga, max_grad_norm=1.0,
                         pbar_description=None, max_inflight_computations=2 * ga)
-  if mesh is not None:
-    from tunix_b200.dist import fsdp
-    model = fsdp.shard_model(model, mesh)
+  from tunix_b200.dist import fsdp
+  model = fsdp.shard_model(model, mesh)     # flat bf16 params + fp32 grads, sharded optimizer state
   trainer = PeftTrainer(model, tx, tcfg)
-  if mesh is not None:
-    trainer.with_grad_sync(fsdp.GradSync(model, mesh))
+  trainer.with_grad_sync(fsdp.GradSync(model, mesh))
   trainer.is_managed_externally = True
 
   # Synthetic data: uniform token ids from a seed, loss on all tokens. This rank's share only.

@@ -124,17 +124,23 @@ class GradientAccumulator:
 
 class ModelOptimizer:
   """Binds a `GradientTransformation` to the trainable parameters of a model (the role
-  `nnx.Optimizer(model, tx, wrt=...)` plays in the reference)."""
+  `nnx.Optimizer(model, tx, wrt=...)` plays in the reference). When the model carries a
+  `flat_store` (`tunix_b200.dist.fsdp.shard_model`) the optimizer state is flat and sharded
+  and the update is the store's fused step."""
 
   def __init__(self, model: torch.nn.Module, tx: optim_lib.GradientTransformation, lora_only: bool):
     self.tx = tx
-    self.named_params = {n: p for n, p in model.named_parameters()
-                         if p.requires_grad and (getattr(p, "is_lora", False) or not lora_only)}
     if lora_only:
       for n, p in model.named_parameters():
         if not getattr(p, "is_lora", False):
           p.requires_grad_(False)
-    self.opt_state = tx.init(self.named_params)
+    self.named_params = {n: p for n, p in model.named_parameters()
+                         if p.requires_grad and (getattr(p, "is_lora", False) or not lora_only)}
+    self.flat = getattr(model, "flat_store", None)
+    inner = getattr(tx, "inner", tx)
+    if self.flat is not None and not (hasattr(inner, "fused_flat_step") and inner.fusable):
+      raise ValueError("a flat parameter store needs an Adam-family optimizer without mask/eps_root")
+    self.opt_state = self.flat.init_state(tx) if self.flat is not None else tx.init(self.named_params)
 
   def update(self, grads: Mapping[str, torch.Tensor], grad_scale: Any = None) -> None:
     self.tx.apply(self.named_params, grads, self.opt_state, grad_scale)
@@ -148,6 +154,31 @@ class ModelOptimizer:
     if hp is not None and "learning_rate" in hp:
       return _to_float(hp["learning_rate"])
     return None
+
+  # checkpoint hooks used by CheckpointManager
+  def gather_for_checkpoint(self):
+    from ..ckpt import layout
+    st = self.flat.opt_state_tree(self.opt_state) if self.flat is not None else self.opt_state
+    return layout.opt_state_to_tree(st)
+
+  def scatter_from_checkpoint(self, tree) -> None:
+    from ..ckpt import layout
+    if self.flat is None:
+      layout.tree_to_opt_state(self.opt_state, tree)
+      return
+    shadow = {k: ({n: torch.zeros(self.flat.shapes[n], dtype=torch.float32) for n in self.flat.names}
+                  if k in ("mu", "nu", "master") else v) for k, v in self.opt_state.items()}
+    layout.tree_to_opt_state(shadow, tree)
+    self.flat.load_opt_state_tree(self.opt_state, shadow)
+    if "hyperparams" in shadow and "hyperparams" in self.opt_state:
+      self.opt_state["hyperparams"] = shadow["hyperparams"]
+    self._master_restored = True
+
+  def sync_master_if_needed(self) -> None:
+    """After a restore that did not carry optimizer state the fp32 master shard is re-derived
+    from the restored bf16 parameters."""
+    if self.flat is not None and not getattr(self, "_master_restored", False):
+      self.flat.refresh_master_from_params(self.opt_state)
 
 
 class _NoopSpan:
@@ -212,6 +243,8 @@ class PeftTrainer:
 
     self._train_steps, self._restored_custom_metadata = self.checkpoint_manager.maybe_restore(
         self.model, self.optimizer, restore_only_lora_params=self._lora_enabled)
+    if self._train_steps > 0:
+      self.optimizer.sync_master_if_needed()
     ga = self.config.get_with_default("gradient_accumulation_steps", 1)
     self._iter_steps = self._train_steps * ga
     max_step = self.config.max_steps * ga if self.config.max_steps is not None else None
@@ -293,9 +326,10 @@ class PeftTrainer:
     """Scales accumulated grads by 1/sum(denom), computes the fp32 global norm, clips, steps."""
     acc = self.grad_accumulator
     scale = acc.get_scale()
-    flat = getattr(self._grad_sync, "flat", None) if self._grad_sync is not None else None
-    if flat is not None:
-      return flat.fused_update(self.optimizer, scale, self._max_grad_norm, acc)
+    if self.optimizer.flat is not None:
+      norm = self.optimizer.flat.step(self.optimizer.tx, self.optimizer.opt_state, acc.denom, self._max_grad_norm)
+      acc.reset(zero_grads=False)
+      return norm
     grads = acc.acc
     if all(g.is_cuda and g.is_contiguous() for g in grads.values()):
       from ..ops import kernels
