@@ -140,11 +140,11 @@ def main():
     cfg = cfg.replace(num_layers=args.layers)
   S, GB = args.seq_len, args.global_batch
   per_gpu = GB // world
-  micro = args.micro_batch or min(per_gpu, 4 if world == 1 else 2)
-  ga = per_gpu // micro
   remat = args.remat
   if remat == "auto":
-    remat = "block"
+    remat = "none"      # the fused decoder-layer node stores only what is expensive to rebuild
+  micro = args.micro_batch or min(per_gpu, (1 if remat == "none" else 4) if world == 1 else 2)
+  ga = per_gpu // micro
   cfg = cfg.replace(dtype=torch.bfloat16, max_position=S,
                     remat_config=RematConfig.BLOCK if remat == "block" else RematConfig.NONE)
 
@@ -152,7 +152,8 @@ def main():
   model = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.02)
   tx = optim.adamw(learning_rate=1e-5, b1=0.9, b2=0.95, eps=1e-8, weight_decay=0.1)
   tcfg = TrainingConfig(eval_every_n_steps=10**9, gradient_accumulation_steps=ga, max_grad_norm=1.0,
-                        pbar_description=None, max_inflight_computations=2 * ga)
+                        pbar_description=None, max_inflight_computations=2 * ga,
+                        data_sharding_axis=())   # every rank already holds only its share of the batch
   from tunix_b200.dist import fsdp
   model = fsdp.shard_model(model, mesh)     # flat bf16 params + fp32 grads, sharded optimizer state
   trainer = PeftTrainer(model, tx, tcfg)
@@ -252,6 +253,7 @@ def main():
                    "optimizer": "AdamW fp32 master/m/v, global-norm clip 1.0"},
         "model_tflops_per_gpu": fl / (ms_total / args.steps / 1e3) / 1e12 / world,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        "train_losses": [float(x) for x in trainer.metrics_logger.get_metric_history("", "loss", "train")[:args.warmup + args.steps]],
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
     }
     print(json.dumps(out))

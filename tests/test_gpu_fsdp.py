@@ -1,0 +1,37 @@
+"""Sharded-vs-unsharded equivalence of FSDP training on 2 GPUs, for both transports
+(NCCL collectives and the peer-memory kernels)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _run(nproc, out, transport, port):
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+  if nproc == 1:
+    cmd = [sys.executable, os.path.join(HERE, "_fsdp_worker.py"), "--out", out, "--transport", transport]
+  else:
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_fsdp_worker.py"),
+           "--out", out, "--transport", transport]
+  r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  return torch.load(out, weights_only=False)
+
+
+@pytest.mark.parametrize("transport", ["nccl", "p2p"])
+def test_fsdp2_matches_single_gpu(kernel_lib, tmp_path, transport):
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  ref = _run(1, str(tmp_path / "ref.pt"), "local", 0)
+  got = _run(2, str(tmp_path / f"{transport}.pt"), transport, 29611 if transport == "nccl" else 29612)
+  for n, p in ref["params"].items():
+    q = got["params"][n]
+    rel = (p - q).norm() / (p.norm() + 1e-6)
+    assert rel < 2e-2, (n, rel.item())
+  assert abs(ref["loss"][-1] - got["loss"][-1]) < 0.05

@@ -247,5 +247,14 @@ class GradSync:
       dist.all_reduce(g, group=self.group)
     dist.all_reduce(acc.denom, group=self.group)
 
+  def reduce_scalars(self, values):
+    """Sum of host floats over the data-parallel group (metrics path)."""
+    if self.world == 1:
+      return list(values)
+    dev = self.flat.device if self.flat is not None else ("cuda" if torch.cuda.is_available() else "cpu")
+    t = torch.tensor(list(values), dtype=torch.float64, device=dev)
+    dist.all_reduce(t, group=self.group)
+    return t.tolist()
+
   def reduce_norm_sq(self, sq: torch.Tensor) -> torch.Tensor:
     return sq    # gradients are already identical on every rank after `reduce`

@@ -86,6 +86,7 @@ class ModelConfig:
   dtype: torch.dtype = torch.float32
   family: str = "generic"
   max_position: int = 0                   # hint for the RoPE table (0 = grow on demand)
+  fused_layers: bool = True               # training fast path: one autograd node per layer
 
   @property
   def is_moe(self) -> bool:
@@ -338,6 +339,10 @@ class DecoderLayer(nn.Module):
     self.mlp = MoELayer(cfg, device) if cfg.is_moe else MLP(cfg, device)
 
   def forward(self, h, positions, cache, attn_mask, layer_name=""):
+    if self.cfg.fused_layers and torch.is_grad_enabled():
+      from ..ops import fused_layer
+      if fused_layer.eligible(self, h, cache, attn_mask):
+        return fused_layer.run(self, h, positions), None
     x = self.input_layernorm(h)
     a, new_cache = self.attn(x, positions, cache, attn_mask, layer_name)
     if self.post_attn_norm is not None:

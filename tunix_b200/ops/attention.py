@@ -1,21 +1,66 @@
-"""CUDA attention entry point used by `functional.attention`.
+"""CUDA attention entry points.
 
-Layout convention: q [B,T,N,H], k/v [B,S,K,H] (token-major, heads contiguous), which is what
-the fused qkv projection produces, so no transposes are materialised on the way in.
+Layout convention: q [B,T,N,H], k/v [B,S,K,H] (token-major, heads contiguous) - what the fused
+qkv projection produces, so q, k and v may be strided views of one buffer and no transposes are
+materialised on the way in.
+
+`flash_fwd` / `flash_bwd` are the explicit forward / backward pair used by hand-scheduled
+backward passes; `attention_cuda` is the autograd-facing call. The sm_100a kernels in `flash.py`
+are used when they cover the case, otherwise the library flash kernels behind
+`torch.ops.aten._scaled_dot_product_flash_attention`.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Any, Optional, Tuple
 
 import torch
 import torch.nn.functional as F
 
+from . import flash
+
+
+def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, scale: float) -> Tuple[torch.Tensor, Any]:
+  """Returns (o [B,T,N,H] contiguous, ctx for `flash_bwd`)."""
+  if flash.supported(q, k, v, None, causal):
+    return flash.forward(q, k, v, causal=causal, scale=scale)
+  qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+  rep = qt.shape[1] // kt.shape[1]
+  try:
+    res = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
+  except RuntimeError:
+    if rep == 1:
+      raise
+    kt, vt = kt.repeat_interleave(rep, dim=1), vt.repeat_interleave(rep, dim=1)
+    res = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
+    o, lse, cq, ck, mq, mk, seed, offset, _ = res
+    return o.transpose(1, 2).contiguous(), ("aten_rep", lse, cq, ck, mq, mk, seed, offset, causal, scale, rep)
+  o, lse, cq, ck, mq, mk, seed, offset, _ = res
+  return o.transpose(1, 2).contiguous(), ("aten", lse, cq, ck, mq, mk, seed, offset, causal, scale, 1)
+
+
+def flash_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, ctx: Any,
+              dq_out: torch.Tensor, dk_out: torch.Tensor, dv_out: torch.Tensor) -> None:
+  """Writes dq/dk/dv (token-major [B,T,heads,H], may be strided views) given do and the forward ctx."""
+  if ctx[0] == "tx":
+    flash.backward(do, q, k, v, o, ctx, dq_out, dk_out, dv_out)
+    return
+  kind, lse, cq, ck, mq, mk, seed, offset, causal, scale, rep = ctx
+  qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+  if kind == "aten_rep":
+    kt, vt = kt.repeat_interleave(rep, dim=1), vt.repeat_interleave(rep, dim=1)
+  dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+      do.transpose(1, 2), qt, kt, vt, o.transpose(1, 2), lse, cq, ck, mq, mk, 0.0, causal, seed, offset, scale=scale)
+  if kind == "aten_rep":
+    B, NK, S, H = dk.shape
+    dk = dk.view(B, NK // rep, rep, S, H).sum(2)
+    dv = dv.view(B, NK // rep, rep, S, H).sum(2)
+  dq_out.copy_(dq.transpose(1, 2))
+  dk_out.copy_(dk.transpose(1, 2))
+  dv_out.copy_(dv.transpose(1, 2))
+
 
 def attention_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: Optional[torch.Tensor],
                    causal: bool, scale: float) -> torch.Tensor:
-  """Dispatches to the flash kernels in this package when they cover the case, otherwise to
-  the library kernel behind `scaled_dot_product_attention`."""
-  from . import flash
   if flash.supported(q, k, v, mask, causal):
     return flash.flash_attention(q, k, v, causal=causal, scale=scale)
   qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)

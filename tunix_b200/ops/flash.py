@@ -8,5 +8,13 @@ def supported(q, k, v, mask, causal) -> bool:
   return False
 
 
+def forward(q, k, v, *, causal: bool, scale: float):
+  raise NotImplementedError
+
+
+def backward(do, q, k, v, o, ctx, dq_out, dk_out, dv_out):
+  raise NotImplementedError
+
+
 def flash_attention(q, k, v, *, causal: bool, scale: float):
   raise NotImplementedError

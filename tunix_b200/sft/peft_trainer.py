@@ -447,9 +447,23 @@ class PeftTrainer:
           v = [x.compute() for x in v]
       return op(to_np(v))
 
-    self._log_metrics(loss=metrics_buffer.loss, step=metrics_buffer.step,
+    self._log_metrics(loss=self._global_loss(metrics_buffer), step=metrics_buffer.step,
                       additional_metrics={k: apply_op(v, op) for k, (v, op) in
                                           metrics_buffer.additional_metrics.items()})
+
+  def _global_loss(self, metrics_buffer: MetricsBuffer) -> float:
+    """Loss of the step over all data-parallel ranks (each rank buffered its own share)."""
+    gs = self._grad_sync
+    if gs is None or getattr(gs, "world", 1) == 1:
+      return metrics_buffer.loss
+    losses = metrics_buffer.losses
+    if isinstance(losses[0], WeightedMetric):
+      total = sum(_to_float(v.unreduced_sum) for v in losses)
+      denom = sum(_to_float(v.denominator) for v in losses)
+      total, denom = gs.reduce_scalars([total, denom])
+      return _to_float(WeightedMetric(total, denom, losses[0].eps, losses[0].min_denom).compute())
+    (mean,) = gs.reduce_scalars([metrics_buffer.loss])
+    return mean / gs.world
 
   @contextlib.contextmanager
   def _switch_mode(self, mode: Mode):
