@@ -27,6 +27,9 @@ GEMM_SHAPES = [
     (4096, 6144, 4096),   # Llama-8B fused qkv
     (8, 128, 128),
     (2048, 1024, 4096),
+    (2304, 4608, 512),    # CTA-pair kernel, exact tiles
+    (2200, 4360, 264),    # CTA-pair kernel, ragged in M, N and K
+    (8192, 4096, 1024),
 ]
 
 
@@ -80,6 +83,21 @@ def test_gemm_strided_views(kernel_lib):
   ref = a.float() @ w.float().t()
   assert _rel_err(out_big[:, 128:384], ref) < 6e-3
   assert out_big[:, :128].abs().max().item() == 0 and out_big[:, 384:].abs().max().item() == 0
+
+
+def test_gemm_pair_matches_single_cta(kernel_lib):
+  """The 2-CTA kernel and the 1-CTA kernel accumulate in the same order: identical results."""
+  from tunix_b200.ops import _lib, kernels
+  lib = _lib.require()
+  a, b = _rand(4096, 2048, scale=0.5), _rand(4608, 2048, scale=0.5)
+  o_pair = kernels.gemm(a, b)
+  lib.tx_gemm_set_disable_pair(1)
+  try:
+    o_single = kernels.gemm(a, b)
+  finally:
+    lib.tx_gemm_set_disable_pair(0)
+  _lib.check_status()
+  assert torch.equal(o_pair, o_single)
 
 
 def test_gemm_deterministic(kernel_lib):

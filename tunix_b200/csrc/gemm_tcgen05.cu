@@ -22,8 +22,8 @@
 //
 // No cluster launch and no multicast copies are used, so the kernel is safe to run in
 // multi-GPU jobs, and its operands may live in peer memory.
+#include "gemm_common.cuh"
 #include "tx_host.h"
-#include "tx_ptx.cuh"
 
 namespace {
 
@@ -45,24 +45,10 @@ struct Cfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-struct GemmParams {
-  void* C;
-  long long ldc;
-  int M, N, K;
-  int c_fp32;      // 1: C is fp32, 0: C is bf16
-  int accumulate;  // 1: C += result, 0: C = result
-  float alpha;
-  int* status;
-};
+using txg::GemmParams;
 
 __device__ __forceinline__ void tile_coords(int t, int mb, int nb, int& pm, int& pn) {
-  const int per_group = GROUP_M * nb;
-  const int g = t / per_group;
-  const int first_m = g * GROUP_M;
-  const int gsize = min(mb - first_m, GROUP_M);
-  const int r = t - g * per_group;
-  pm = first_m + (r % gsize);
-  pn = r / gsize;
+  txg::tile_coords(t, mb, nb, GROUP_M, pm, pn);
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -211,51 +197,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
-        const int col = n0 + c;
-        if (row < p.M && col < p.N) {
-          if (p.c_fp32) {
-            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              if (col + j < p.N) {
-                float4 v = make_float4(__uint_as_float(r[j]) * p.alpha, __uint_as_float(r[j + 1]) * p.alpha,
-                                       __uint_as_float(r[j + 2]) * p.alpha, __uint_as_float(r[j + 3]) * p.alpha);
-                float4* d4 = reinterpret_cast<float4*>(dst + j);
-                if (p.accumulate) {
-                  const float4 o = *d4;
-                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                }
-                *d4 = v;
-              }
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col + j < p.N) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[j + e]) * p.alpha;
-                uint4* d4 = reinterpret_cast<uint4*>(dst + j);
-                if (p.accumulate) {
-                  const uint4 o = *d4;
-                  const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&o);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 of = __bfloat1622float2(o2[e]);
-                    f[2 * e] += of.x;
-                    f[2 * e + 1] += of.y;
-                  }
-                }
-                uint4 v;
-                __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) v2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
-                *d4 = v;
-              }
-            }
-          }
-        }
+        txg::store_row_chunk(p, row, n0 + c, r);
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
@@ -310,6 +252,10 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
 // Requirements: bf16 operands, 16-byte aligned bases, lda/ldb multiples of 8, N and ldc
 // multiples of 8 (4 for fp32 C). `status` is a device int32 that receives error bits.
 // `max_ctas` > 0 caps the grid (leaves SMs free for a concurrent copy/collective).
+static int g_disable_pair = 0;
+// Test hook: 1 forces the single-CTA kernels for every shape.
+extern "C" void tx_gemm_set_disable_pair(int v) { g_disable_pair = v; }
+
 extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                             long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, int accumulate,
                             float alpha, int* status, int max_ctas, cudaStream_t stream) {
@@ -319,6 +265,13 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
       (reinterpret_cast<uintptr_t>(C) & 15))
     return 3;
   GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status};
+  // Large problems: 256 x 256 tiles on CTA pairs (cta_group::2) halve the B traffic per SM.
+  {
+    const long long tiles_pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
+    const int pairs = txh::sm_count() / 2;
+    if (!g_disable_pair && M >= 256 && N >= 256 && tiles_pair >= pairs)
+      return tx_gemm_pair_launch(A, B, p, lda, ldb, a_mn, b_mn, max_ctas, stream);
+  }
   // Wide tiles unless that would leave most SMs idle.
   const long long tiles256 = static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256);
   const bool bn256 = tiles256 >= txh::sm_count() || (N % 256 == 0 && tiles256 * 2 > 3 * txh::sm_count());

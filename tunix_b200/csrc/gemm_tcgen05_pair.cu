@@ -1,0 +1,247 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2, one 256 x 256 output tile per pair.
+//
+// Two CTAs on neighbouring SMs form a cluster. Each stages its own half of the tile's operands -
+// 128 rows of A and 128 of the 256 B rows (N) - so per SM and k-block 32 KB arrive from L2 for
+// 128 x 256 x 64 MACs, two thirds of what the single-CTA 128 x 256 tile needs; at 148 SMs the
+// L2 -> shared-memory traffic is what limits the single-CTA kernel. The leader CTA (cluster
+// rank 0) issues the MMAs, which read both CTAs' shared memory and write 128 accumulator rows
+// into each CTA's TMEM. Each CTA drains its own TMEM half in its epilogue warps.
+//
+// Synchronisation (all mbarriers, all waits bounded):
+//   full[s]    leader only. The leader's producer arms it with the bytes of BOTH CTAs; both
+//              CTAs' TMA loads complete on it (cta_group::2 loads may signal the peer's barrier).
+//   empty[s]   one per CTA; tcgen05.commit multicast to both when the MMAs reading stage s retire.
+//   tfull[a]   one per CTA; commit multicast when accumulator a is complete.
+//   tempty[a]  leader only; one arrival per epilogue warp of either CTA (8) once a is drained.
+// No TMA load uses cluster multicast: every CTA fetches its own operand half.
+#include "gemm_common.cuh"
+#include "tx_host.h"
+
+namespace {
+
+using namespace tx;
+using txg::GemmParams;
+
+constexpr int BM_CTA = 128;     // rows of A (and accumulator rows) per CTA
+constexpr int BN = 256;         // tile width; each CTA stages BN / 2 rows of B
+constexpr int BN_CTA = BN / 2;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 8;
+constexpr int kStages = 6;
+constexpr int kABytes = BM_CTA * BK * 2;      // 16 KB
+constexpr int kBBytes = BN_CTA * BK * 2;      // 16 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kTmemCols = 2 * BN;             // two accumulators
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kStages * kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * kStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kStages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();          // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int mb = (p.M + 2 * BM_CTA - 1) / (2 * BM_CTA);
+  const int nb = (p.N + BN - 1) / BN;
+  const int num_tiles = mb * nb;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 8);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        int pm, pn;
+        txg::tile_coords(t, mb, nb, GROUP_M, pm, pn);
+        const int m0 = pm * 2 * BM_CTA + cta * BM_CTA;
+        const int n0 = pn * BN + cta * BN_CTA;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
+            atomicOr(p.status, kStatusWaitTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = map_to_cta(bar_full + 8 * stage, 0);
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+          if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM_CTA / 64; ++i)
+              tma_load_2d_pair(sa + i * (BK * 128), &map_a, m0 + i * 64, kb * BK, full_leader);
+          } else {
+            tma_load_2d_pair(sa, &map_a, kb * BK, m0, full_leader);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int i = 0; i < BN_CTA / 64; ++i)
+              tma_load_2d_pair(sb + i * (BK * 128), &map_b, n0 + i * 64, kb * BK, full_leader);
+          } else {
+            tma_load_2d_pair(sb, &map_b, kb * BK, n0, full_leader);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (cta == 0 && elect_one()) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM_CTA, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = pair; t < num_tiles && ok; t += num_pairs) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
+          atomicOr(p.status, kStatusWaitTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
+            atomicOr(p.status, kStatusWaitTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kABytes;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                                     : make_smem_desc_sw128(sb + k * 32, 16, 1024);
+            umma_bf16_pair(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(bar_empty + 8 * stage, 3);     // both CTAs may refill this stage
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(bar_tfull + 8 * acc, 3);         // both CTAs may drain this accumulator
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    const uint32_t tempty_leader0 = map_to_cta(bar_tempty, 0);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int t = pair; t < num_tiles; t += num_pairs) {
+      int pm, pn;
+      txg::tile_coords(t, mb, nb, GROUP_M, pm, pn);
+      const int row = pm * 2 * BM_CTA + cta * BM_CTA + quarter * 32 + lane;
+      const int n0 = pn * BN;
+      if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
+        atomicOr(p.status, kStatusWaitTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        txg::store_row_chunk(p, row, n0 + c, r);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  if (*abort_flag) __nanosleep(200000);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // nobody leaves while the peer may still touch its memory or barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <bool A_MN, bool B_MN>
+int launch(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb, int max_ctas,
+           cudaStream_t stream) {
+  CUtensorMap ma, mbm;
+  int rc;
+  if (A_MN) rc = txh::make_map_2d_bf16(&ma, A, p.K, p.M, lda, BK, 64);
+  else      rc = txh::make_map_2d_bf16(&ma, A, p.M, p.K, lda, BM_CTA, BK);
+  if (rc) return 100 + rc;
+  if (B_MN) rc = txh::make_map_2d_bf16(&mbm, B, p.K, p.N, ldb, BK, 64);
+  else      rc = txh::make_map_2d_bf16(&mbm, B, p.N, p.K, ldb, BN_CTA, BK);
+  if (rc) return 200 + rc;
+  auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return 300;
+    attr_set = true;
+  }
+  const int mb = (p.M + 2 * BM_CTA - 1) / (2 * BM_CTA), nb = (p.N + BN - 1) / BN;
+  int sms = txh::sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+  int pairs = mb * nb;
+  if (pairs > sms / 2) pairs = sms / 2;
+  if (pairs < 1) pairs = 1;
+  kern<<<2 * pairs, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+}  // namespace
+
+int tx_gemm_pair_launch(const void* A, const void* B, const txg::GemmParams& p, long long lda, long long ldb,
+                        int a_mn, int b_mn, int max_ctas, cudaStream_t stream) {
+  const int sel = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  switch (sel) {
+    case 0: return launch<false, false>(A, B, p, lda, ldb, max_ctas, stream);
+    case 1: return launch<false, true>(A, B, p, lda, ldb, max_ctas, stream);
+    case 2: return launch<true, false>(A, B, p, lda, ldb, max_ctas, stream);
+    default: return launch<true, true>(A, B, p, lda, ldb, max_ctas, stream);
+  }
+}
