@@ -1,0 +1,73 @@
+"""DAPO (https://arxiv.org/pdf/2503.14476): GRPO without a KL term (`beta=None`), asymmetric
+clipping (`epsilon_high=0.28`), token-mean aggregation, and overlong-response reward shaping
+(tunix/rl/grpo/dapo_learner.py:28-158)."""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Dict, List, Optional, Sequence
+
+from . import grpo_learner as grpo_lib
+
+
+@dataclasses.dataclass(kw_only=True)
+class DAPOConfig(grpo_lib.GRPOConfig):
+  algo_variant: str = "dapo"
+  advantage_estimator: str = "grpo"
+  policy_loss_fn: str = "grpo"
+  loss_agg_mode: str = "token-mean"
+  reward_manager: str = "sequence-level"
+  num_generations: int = 2
+  num_iterations: int = 1
+  beta: Optional[float] = None
+  epsilon: float = 0.2
+  epsilon_high: float = 0.28
+  dynamic_sampling: bool = True
+  overlong_buffer: Optional[Dict[str, Any]] = dataclasses.field(default_factory=lambda: {
+      "enable": True, "overlong_buffer_length": 4096, "overlong_buffer_penalty": 1.0, "max_response_length": 20480})
+
+  def __post_init__(self):
+    if self.beta is not None:
+      raise ValueError("DAPO does not support KL penalty, so beta must be None.")
+    if self.epsilon_high < self.epsilon:
+      raise ValueError("epsilon_high must be greater than or equal to epsilon.")
+    if self.overlong_buffer is not None and self.overlong_buffer.get("enable"):
+      b = self.overlong_buffer
+      missing = [k for k in ("overlong_buffer_length", "overlong_buffer_penalty", "max_response_length")
+                 if b.get(k) is None]
+      if missing:
+        raise ValueError(f"overlong_buffer is enabled but missing: {missing}")
+      if b["overlong_buffer_penalty"] < 0:
+        raise ValueError("overlong_buffer_penalty must be non-negative.")
+      if b["overlong_buffer_length"] <= 0:
+        raise ValueError("overlong_buffer_length must be positive.")
+      if b["max_response_length"] <= 0:
+        raise ValueError("max_response_length must be positive.")
+    super().__post_init__()
+
+
+def reward_shaping(prompts: List[str], completions: List[str], mode: Any = None,
+                   overlong_buffer: Optional[Dict[str, Any]] = None, **kwargs) -> List[float]:
+  """Soft penalty for responses that run into the last `overlong_buffer_length` of the budget:
+  `min(-(len - (max_len - buffer)) / buffer * penalty, 0)`."""
+  del prompts, mode, kwargs
+  if overlong_buffer is None:
+    raise ValueError("reward_shaping is called but with empty overlong_buffer.")
+  buf_len = overlong_buffer["overlong_buffer_length"]
+  penalty = overlong_buffer["overlong_buffer_penalty"]
+  expected = overlong_buffer["max_response_length"] - buf_len
+  return [min(-(len(c) - expected) / buf_len * penalty, 0) for c in completions]
+
+
+class DAPOLearner(grpo_lib.GRPOLearner):
+
+  def __init__(self, rl_engine=None, algo_config: DAPOConfig = None, reward_fns=None,
+               metric_fns: Optional[Sequence[Any]] = None, data_shuffle_seed: Optional[int] = None, rl_cluster=None):
+    fns = [reward_fns] if not isinstance(reward_fns, Sequence) else list(reward_fns)
+    if algo_config.overlong_buffer and algo_config.overlong_buffer["enable"]:
+      fns.append(reward_shaping)
+    super().__init__(rl_engine=rl_engine, algo_config=algo_config, reward_fns=fns, metric_fns=metric_fns,
+                     data_shuffle_seed=data_shuffle_seed, rl_cluster=rl_cluster)
+
+
+DapoConfig = DAPOConfig
+DapoLearner = DAPOLearner

@@ -257,6 +257,7 @@ class PeftTrainer:
     self._mini_batch_size = None
     self._grad_sync = None   # set by tunix_b200.dist when the model is sharded/replicated
     self._zero_norm = None
+    self._closing = False
     try:
       self._device = next(model.parameters()).device
     except StopIteration:
@@ -604,6 +605,7 @@ class PeftTrainer:
     self._write_train_metrics()
     if self._prev_buffered_train_metrics is not None:
       self._write_train_metrics()
+    self._closing = True     # metadata providers may distinguish the final save from in-loop saves
     self._save_last_checkpoint()
     self.checkpoint_manager.close()
     self.metrics_logger.close()
