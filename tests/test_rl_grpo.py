@@ -287,3 +287,26 @@ def test_pack_sequences_ffd_and_update_boundaries():
     list(rl_utils.pack_sequences(iter([[ex([4], [6])]]), max_token_budget=8, sequences_per_update=1))
   with pytest.raises(ValueError, match="mid-mini-batch"):
     list(rl_utils.pack_sequences(iter([[ex([1], [1])]]), max_token_budget=8, sequences_per_update=2))
+
+
+def test_ppo_end_to_end_with_critic():
+  from tunix_b200.rl.ppo import ppo_learner
+  actor, reference = toy_model(), toy_model()
+  critic = rl_utils.create_critic_model(toy_model(seed=1))
+  tc = RLTrainingConfig(actor_optimizer=optim.adamw(1e-2), critic_optimizer=optim.adamw(1e-2), eval_every_n_steps=100,
+                        max_steps=3, pbar_description=None)
+  rc = RolloutConfig(max_tokens_to_generate=8, max_prompt_length=8, kv_cache_size=32, temperature=1.0, top_p=1.0, seed=3)
+  cc = ClusterConfig(role_to_mesh={Role.ACTOR: None, Role.REFERENCE: None, Role.ROLLOUT: None, Role.CRITIC: None},
+                     rollout_engine="vanilla", training_config=tc, rollout_config=rc)
+  cl = rl_cluster.RLCluster(actor=actor, reference=reference, critic=critic, tokenizer=ToyTokenizer(), cluster_config=cc)
+  before = {n: p.clone() for n, p in cl.critic_trainer.model.named_parameters()}
+  cfg = ppo_learner.PPOConfig(entropy_coef=0.01, epsilon_c=3.0)
+  assert cfg.epsilon_low == cfg.epsilon_high == 0.2
+  with pytest.raises(ValueError):
+    ppo_learner.PPOLearner(rl_cluster=cl, algo_config=cfg, reward_fns=None)
+  ppo_learner.PPOLearner(rl_cluster=cl, algo_config=cfg, reward_fns=reward_len).train(prompts_ds(3))
+  assert cl.actor_trainer.train_steps == 3 and cl.critic_trainer.train_steps == 3
+  assert any(not torch.equal(p, before[n]) for n, p in cl.critic_trainer.model.named_parameters())
+  lg = cl._rl_metrics_logger
+  assert lg.metric_exists("advantages", "returns/mean", "train")
+  assert lg.metric_exists("", "vpred_mean", "train")
