@@ -385,3 +385,70 @@ extern "C" int tx_qknorm_rope_bwd(const void* x, const void* dy, void* dx, const
                        x_stride, dy_stride, dx_stride, eps, w_offset)));
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
+
+// ---- RMSNorm backward with library-owned scratch (contract in norm_static.h) -----------------
+#include <mutex>
+
+#include "norm_static.h"
+
+namespace {
+constexpr int kStaticMaxD = 4096;
+constexpr int kStaticMaxPartials = 148 * 2;   // upper bound of tx_rmsnorm_bwd_partials()
+constexpr int kStaticMaxDevices = 64;
+// One instance per device that loads this module. In host code the name below is only a
+// handle for the symbol look-up, never a device address.
+static __device__ __align__(256) float g_static_dw_partial[kStaticMaxPartials * kStaticMaxD];
+float* g_static_dw_ptr[kStaticMaxDevices] = {};
+std::mutex g_static_mu;
+
+// Device address of the scratch on the current device; looked up once per device.
+int static_scratch(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) return TX_STATIC_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_dw_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_dw_partial) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return TX_STATIC_ERR_SYMBOL;
+    }
+    g_static_dw_ptr[dev] = p;
+  }
+  *out = g_static_dw_ptr[dev];
+  return TX_STATIC_OK;
+}
+}  // namespace
+
+extern "C" int tx_rmsnorm_bwd_static_max_d(void) { return kStaticMaxD; }
+
+extern "C" const char* tx_rmsnorm_bwd_static_strerror(int code) {
+  switch (code) {
+    case TX_STATIC_OK: return "ok";
+    case TX_STATIC_ERR_BAD_SHAPE: return "tx_rmsnorm_bwd_static: D must be a multiple of 8 and T >= 0";
+    case TX_STATIC_ERR_TOO_LARGE:
+      return "tx_rmsnorm_bwd_static: D exceeds the built-in scratch (max 4096); use tx_rmsnorm_bwd with "
+             "caller-provided scratch";
+    case TX_STATIC_ERR_DEVICE: return "tx_rmsnorm_bwd_static: no current CUDA device, or its ordinal is >= 64";
+    case TX_STATIC_ERR_SYMBOL: return "tx_rmsnorm_bwd_static: address look-up of the scratch array failed";
+    case TX_STATIC_ERR_LAUNCH: return "tx_rmsnorm_bwd_static: kernel launch failed";
+    default: return "tx_rmsnorm_bwd_static: unknown code";
+  }
+}
+
+extern "C" int tx_rmsnorm_bwd_static(const void* x, const void* w, const void* dy, const float* rstd,
+                                     const void* dres, void* dx, float* dw, int dw_accumulate, int T, int D,
+                                     float eps, float w_offset, cudaStream_t stream) {
+  if (D <= 0 || D % 8 != 0 || T < 0) return TX_STATIC_ERR_BAD_SHAPE;
+  if (D > kStaticMaxD) return TX_STATIC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = static_scratch(&scratch);   // also on T == 0, so that a start-up call does the set-up
+  if (rc != TX_STATIC_OK) return rc;
+  if (T == 0) return TX_STATIC_OK;
+  const int grid = tx_rmsnorm_bwd_partials(T);   // <= kStaticMaxPartials rows of D <= kStaticMaxD floats
+  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(dy), rstd, static_cast<const __nv_bfloat16*>(dres),
+      static_cast<__nv_bfloat16*>(dx), scratch, T, D, eps, w_offset);
+  if (dw) colsum_partials_kernel<<<(D + 255) / 256, 256, 0, stream>>>(scratch, dw, grid, D, dw_accumulate);
+  return cudaGetLastError() == cudaSuccess ? TX_STATIC_OK : TX_STATIC_ERR_LAUNCH;
+}
