@@ -51,6 +51,7 @@ def _declare(lib):
       "tx_clip_scale": [P, P, F, P, P, P],
       "tx_cast_f32_bf16": [P, P, L, P],
       "tx_accum_bf16_f32": [P, P, L, F, P],
+      "tx_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, I, F, P, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
       "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],
   }

@@ -1,20 +1,81 @@
-"""Flash attention on the sm_100a kernels (forward and backward)."""
+"""Flash attention on the sm_100a kernels.
+
+Forward: `tx_flash_fwd` (tcgen05 / TMEM, head_dim 128, causal or full, GQA, strided q/k/v views
+of a fused projection). The backward still runs the library flash backward on the forward's
+output and log-sum-exp; its interface (`backward`) is the one the hand-scheduled layer
+backward calls, so a native backward drops in without touching callers.
+"""
 from __future__ import annotations
+
+import os
+from typing import Any, Tuple
 
 import torch
 
+from . import _lib
+
+_DISABLED = os.environ.get("TUNIX_B200_FLASH", "1") == "0"
+
+
+def _rows_ok(t: torch.Tensor) -> bool:
+  # [B, L, heads, H] view whose (B, L) flatten to rows of one stride and heads*H is contiguous
+  B, L, n, H = t.shape
+  sb, sl, sn, sh = t.stride()
+  return sh == 1 and sn == H and (B == 1 or sb == L * sl) and sl % 8 == 0 and t.data_ptr() % 16 == 0
+
 
 def supported(q, k, v, mask, causal) -> bool:
-  return False
+  if _DISABLED or mask is not None or not q.is_cuda or q.dtype != torch.bfloat16:
+    return False
+  if q.dim() != 4 or q.shape[-1] != 128 or k.shape[-1] != 128 or q.shape[2] % k.shape[2] != 0:
+    return False
+  if k.shape != v.shape or k.dtype != q.dtype or v.dtype != q.dtype:
+    return False
+  return _rows_ok(q) and _rows_ok(k) and _rows_ok(v) and _lib.available()
 
 
-def forward(q, k, v, *, causal: bool, scale: float):
-  raise NotImplementedError
+def forward(q, k, v, *, causal: bool, scale: float) -> Tuple[torch.Tensor, Any]:
+  """q [B,Lq,N,128], k/v [B,Lk,K,128] -> (o [B,Lq,N,128] contiguous, ctx)."""
+  B, Lq, N, H = q.shape
+  Lk, Kh = k.shape[1], k.shape[2]
+  o = torch.empty((B, Lq, N, H), dtype=q.dtype, device=q.device)
+  lse = torch.empty((B, N, Lq), dtype=torch.float32, device=q.device)
+  lib = _lib.require()
+  rc = lib.tx_flash_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), B, N, Kh, Lq, Lk,
+                        H, q.stride(1), k.stride(1), v.stride(1), N * H, int(causal), float(scale),
+                        _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_flash_fwd")
+  return o, ("tx", lse, causal, scale)
 
 
-def backward(do, q, k, v, o, ctx, dq_out, dk_out, dv_out):
-  raise NotImplementedError
+def backward(do, q, k, v, o, ctx, dq_out, dk_out, dv_out) -> None:
+  _, lse, causal, scale = ctx
+  B, Lq, N, H = q.shape
+  Lk = k.shape[1]
+  e = torch.empty(0, dtype=torch.long, device=q.device)
+  dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+      do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2), lse,
+      None, None, Lq, Lk, 0.0, causal, e, e, scale=scale)
+  dq_out.copy_(dq.transpose(1, 2))
+  dk_out.copy_(dk.transpose(1, 2))
+  dv_out.copy_(dv.transpose(1, 2))
+
+
+class _FlashFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, q, k, v, causal, scale):
+    o, c = forward(q, k, v, causal=causal, scale=scale)
+    ctx.save_for_backward(q, k, v, o, c[1])
+    ctx.causal, ctx.scale = causal, scale
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    q, k, v, o, lse = ctx.saved_tensors
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    backward(do.contiguous(), q, k, v, o, ("tx", lse, ctx.causal, ctx.scale), dq, dk, dv)
+    return dq, dk, dv, None, None
 
 
 def flash_attention(q, k, v, *, causal: bool, scale: float):
-  raise NotImplementedError
+  return _FlashFn.apply(q, k, v, causal, scale)
