@@ -1,0 +1,121 @@
+"""Naming, registry, safetensors round trips, LoRA-merged export, AutoModel."""
+import dataclasses
+import json
+import os
+
+import pytest
+import torch
+
+from tunix_b200.models import automodel, dummy_model_creator, lora, naming, registry, safetensors_io
+from tunix_b200.models import safetensors_loader, safetensors_saver
+from tunix_b200.models.transformer import Transformer
+
+
+def tiny(family_mod, preset, **kw):
+  cfg = getattr(family_mod.ModelConfig, preset)()
+  base = dict(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=4, head_dim=8, num_kv_heads=2)
+  if cfg.num_experts:
+    base.update(num_experts=4, num_experts_per_tok=2, moe_hidden_dim=16, hidden_dim=16)
+  base.update(kw)
+  return dataclasses.replace(cfg, **base)
+
+
+def test_naming_rules():
+  n = naming.ModelNaming(model_id="meta-llama/Llama-3.1-8B")
+  assert (n.model_name, n.model_family, n.model_version, n.model_config_category, n.model_config_id) == \
+      ("llama-3.1-8b", "llama3p1", "8b", "llama3", "llama3p1_8b")
+  assert naming.ModelNaming(model_id="google/gemma-2-2b-it").model_config_id == "gemma2_2b_it"
+  assert naming.ModelNaming(model_name="qwen2.5-0.5b").model_config_id == "qwen2p5_0p5b"
+  assert naming.ModelNaming(model_id="qwen3_30b_a3b").model_family == "qwen3"
+  with pytest.raises(ValueError):
+    naming.ModelNaming(model_id="acme/unknown-7b")
+  with pytest.raises(ValueError):
+    naming.ModelNaming(model_id="Qwen/Qwen3-8B", model_family="llama3")
+  with pytest.raises(ValueError):
+    naming.ModelNaming()
+
+
+def test_registry_covers_presets():
+  ids = registry.config_ids()
+  for want in ("llama3p1_8b", "qwen3_8b", "qwen3_30b_a3b", "gemma2_2b_it", "qwen2p5_0p5b"):
+    assert want in ids
+  assert registry.lookup("Qwen/Qwen3-8B").model_config_id == "qwen3_8b"
+  cfg = automodel.call_model_config("llama-3.1-8b")
+  assert cfg.num_layers == 32 and cfg.embed_dim == 4096 and cfg.vocab_size == 128256
+
+
+def test_safetensors_io_round_trip(tmp_path):
+  t = {"a": torch.randn(3, 4), "b": torch.arange(6, dtype=torch.int64).view(2, 3), "c": torch.randn(5).bfloat16(),
+       "e": torch.empty(0, 4)}
+  p = str(tmp_path / "x.safetensors")
+  safetensors_io.save_file(t, p, metadata={"format": "pt"})
+  f = safetensors_io.SafeTensorsFile(p)
+  assert sorted(f.keys()) == ["a", "b", "c", "e"] and f.metadata == {"format": "pt"}
+  for k in t:
+    assert torch.equal(f.get(k), t[k])
+  try:
+    import safetensors.torch as st
+    ref = st.load_file(p)
+    for k in t:
+      assert torch.equal(ref[k], t[k])
+  except ImportError:
+    pass
+
+
+@pytest.mark.parametrize("family,preset", [("llama3", "llama3p1_8b"), ("qwen3", "qwen3_8b"), ("qwen2", "qwen2p5_0p5b"),
+                                           ("gemma", "gemma2_2b"), ("qwen3", "qwen3_30b_a3b")])
+def test_hf_export_import_round_trip(tmp_path, family, preset):
+  import importlib
+  mod = importlib.import_module(f"tunix_b200.models.{family}.model")
+  cfg = tiny(mod, preset)
+  m = Transformer(cfg).init_weights(seed=3, scale=0.1)
+  out = safetensors_saver.save_lora_merged_model_as_safetensors(None, str(tmp_path), m)
+  keys = safetensors_io.SafeTensorsFile(out).keys()
+  assert "model.layers.0.self_attn.q_proj.weight" in keys and "model.embed_tokens.weight" in keys
+  if cfg.num_experts:
+    assert "model.layers.1.mlp.experts.3.down_proj.weight" in keys and "model.layers.0.mlp.gate.weight" in keys
+  m2 = Transformer(cfg).init_weights(seed=9, scale=0.1)
+  ignored = safetensors_loader.load_into_model(m2, str(tmp_path))
+  assert ignored == []
+  for (n1, p1), (n2, p2) in zip(m.named_parameters(), m2.named_parameters()):
+    assert n1 == n2 and torch.equal(p1, p2), n1
+  tok = torch.randint(0, 64, (2, 6))
+  pos = torch.arange(6)[None].expand(2, -1)
+  mask = torch.tril(torch.ones(6, 6, dtype=torch.bool))[None].expand(2, -1, -1)
+  torch.testing.assert_close(m(tok, pos, None, mask)[0], m2(tok, pos, None, mask)[0])
+
+
+def test_lora_merged_export_matches_adapter_forward(tmp_path):
+  from tunix_b200.models.llama3 import model as llama
+  cfg = tiny(llama, "llama3p2_1b")
+  m = Transformer(cfg).init_weights(seed=1, scale=0.1)
+  lora.apply_lora_to_model(m, rank=4, alpha=8.0, module_path=".*q_proj|.*v_proj|.*down_proj")
+  with torch.no_grad():
+    for n, p in m.named_parameters():
+      if getattr(p, "is_lora", False):
+        p.normal_(0, 0.1)
+  safetensors_saver.save_lora_merged_model_as_safetensors(None, str(tmp_path), m)
+  assert lora.is_lora_enabled(m)      # export leaves the adapters in place
+  plain = Transformer(cfg)
+  safetensors_loader.load_into_model(plain, str(tmp_path))
+  tok = torch.randint(0, 64, (2, 6))
+  pos = torch.arange(6)[None].expand(2, -1)
+  mask = torch.tril(torch.ones(6, 6, dtype=torch.bool))[None].expand(2, -1, -1)
+  torch.testing.assert_close(m(tok, pos, None, mask)[0], plain(tok, pos, None, mask)[0], rtol=1e-4, atol=1e-4)
+
+
+def test_automodel_dummy_and_local_path(tmp_path):
+  from tunix_b200.models.qwen3 import model as qwen3
+  cfg = tiny(qwen3, "qwen3_0p6b")
+  m, path = automodel.AutoModel.from_pretrained("Qwen/Qwen3-0.6B", model_source=automodel.ModelSource.DUMMY,
+                                                model_config=cfg, dtype=torch.float32, device="cpu")
+  assert path is None and isinstance(m, Transformer)
+  safetensors_saver.save_lora_merged_model_as_safetensors(None, str(tmp_path), m)
+  m2, path = automodel.AutoModel.from_pretrained("Qwen/Qwen3-0.6B", model_path=str(tmp_path), model_config=cfg,
+                                                 dtype=torch.float32, device="cpu")
+  assert path == str(tmp_path)
+  assert torch.equal(m.embedder.input_embedding, m2.embedder.input_embedding)
+  with pytest.raises(ValueError):
+    automodel.AutoModel.from_pretrained("Qwen/Qwen3-0.6B", model_source=automodel.ModelSource.GCS)
+  with pytest.raises(FileNotFoundError):
+    automodel.download_model("/nonexistent/dir", None, automodel.ModelSource.INTERNAL)
