@@ -59,18 +59,37 @@ def test_flash_large_logits_rescale_path(kernel_lib):
   torch.testing.assert_close(ctx[1], lse_ref, rtol=1e-3, atol=5e-3)
 
 
-def test_flash_autograd_matches_sdpa(kernel_lib):
-  from tunix_b200.ops import flash
+@pytest.mark.parametrize("B,Lq,Lk,N,Kh,causal", [(2, 256, 256, 4, 2, True), (1, 128, 128, 1, 1, True),
+                                                    (1, 200, 200, 4, 1, True), (1, 320, 320, 2, 2, False),
+                                                    (1, 100, 333, 2, 1, True), (1, 1024, 1024, 8, 2, True)])
+def test_flash_autograd_matches_reference(kernel_lib, B, Lq, Lk, N, Kh, causal):
+  from tunix_b200.ops import _lib, flash
   torch.manual_seed(2)
-  B, L, N, Kh, H = 2, 256, 4, 2, 128
-  q = torch.randn(B, L, N, H, device="cuda").bfloat16().requires_grad_()
-  k = torch.randn(B, L, Kh, H, device="cuda").bfloat16().requires_grad_()
-  v = torch.randn(B, L, Kh, H, device="cuda").bfloat16().requires_grad_()
-  o = flash.flash_attention(q, k, v, causal=True, scale=0.09)
+  H = 128
+  q = torch.randn(B, Lq, N, H, device="cuda").bfloat16().requires_grad_()
+  k = torch.randn(B, Lk, Kh, H, device="cuda").bfloat16().requires_grad_()
+  v = torch.randn(B, Lk, Kh, H, device="cuda").bfloat16().requires_grad_()
+  o = flash.flash_attention(q, k, v, causal=causal, scale=0.09)
   g = torch.randn_like(o)
   o.backward(g)
   qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
-  o_ref, _ = ref_attention(qf, kf, vf, True, 0.09)
+  _lib.check_status()
+  o_ref, _ = ref_attention(qf, kf, vf, causal, 0.09)
   o_ref.backward(g.float())
   for a, b in ((q.grad, qf.grad), (k.grad, kf.grad), (v.grad, vf.grad)):
     torch.testing.assert_close(a.float(), b, rtol=5e-2, atol=5e-2)
+
+
+def test_flash_backward_is_reproducible(kernel_lib):
+  from tunix_b200.ops import flash
+  torch.manual_seed(3)
+  q, k, v = (torch.randn(1, 512, n, 128, device="cuda").bfloat16().requires_grad_() for n in (4, 2, 2))
+  g = torch.randn(1, 512, 4, 128, device="cuda").bfloat16()
+  grads = []
+  for _ in range(2):
+    for t in (q, k, v):
+      t.grad = None
+    flash.flash_attention(q, k, v, causal=True, scale=0.09).backward(g)
+    grads.append([t.grad.clone() for t in (q, k, v)])
+  for a, b in zip(*grads):
+    assert torch.equal(a, b)

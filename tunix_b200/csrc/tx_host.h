@@ -15,7 +15,21 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
                                   CUtensorMapFloatOOBfill);
 
+// The driver entry point below needs a context that is current on the calling thread. A thread
+// that has only made runtime calls which do not touch the device (an autograd worker before its
+// first launch) may not have one yet; a launch-free runtime call binds the primary context.
+inline void bind_primary_context() {
+  thread_local bool bound = false;
+  if (!bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 inline EncodeTiledFn encode_fn() {
+  bind_primary_context();
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;

@@ -52,6 +52,7 @@ def _declare(lib):
       "tx_cast_f32_bf16": [P, P, L, P],
       "tx_accum_bf16_f32": [P, P, L, F, P],
       "tx_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, I, F, P, P],
+      "tx_flash_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, I, F, P, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
       "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],
   }

@@ -1,9 +1,8 @@
 """Flash attention on the sm_100a kernels.
 
 Forward: `tx_flash_fwd` (tcgen05 / TMEM, head_dim 128, causal or full, GQA, strided q/k/v views
-of a fused projection). The backward still runs the library flash backward on the forward's
-output and log-sum-exp; its interface (`backward`) is the one the hand-scheduled layer
-backward calls, so a native backward drops in without touching callers.
+of a fused projection). Backward: `tx_flash_bwd`, two tcgen05 kernels (dK/dV per key tile, dQ per
+query tile) with a fixed reduction order, so gradients are bitwise reproducible.
 """
 from __future__ import annotations
 
@@ -48,17 +47,37 @@ def forward(q, k, v, *, causal: bool, scale: float) -> Tuple[torch.Tensor, Any]:
   return o, ("tx", lse, causal, scale)
 
 
+_BWD_LIBRARY = os.environ.get("TUNIX_B200_FLASH_BWD", "1") == "0"
+
+
 def backward(do, q, k, v, o, ctx, dq_out, dk_out, dv_out) -> None:
+  """Writes dq/dk/dv ([B,L,heads,128], may be strided views of one fused gradient buffer)."""
   _, lse, causal, scale = ctx
   B, Lq, N, H = q.shape
-  Lk = k.shape[1]
-  e = torch.empty(0, dtype=torch.long, device=q.device)
-  dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-      do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2), lse,
-      None, None, Lq, Lk, 0.0, causal, e, e, scale=scale)
-  dq_out.copy_(dq.transpose(1, 2))
-  dk_out.copy_(dk.transpose(1, 2))
-  dv_out.copy_(dv.transpose(1, 2))
+  Lk, Kh = k.shape[1], k.shape[2]
+  if _BWD_LIBRARY:
+    e = torch.empty(0, dtype=torch.long, device=q.device)
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
+        do.transpose(1, 2), q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), o.transpose(1, 2), lse,
+        None, None, Lq, Lk, 0.0, causal, e, e, scale=scale)
+    dq_out.copy_(dq.transpose(1, 2))
+    dk_out.copy_(dk.transpose(1, 2))
+    dv_out.copy_(dv.transpose(1, 2))
+    return
+  if not _rows_ok(do):
+    do = do.contiguous()
+  outs = [t if _rows_ok(t) else torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (dq_out, dk_out, dv_out)]
+  delta = torch.empty((B, N, Lq), dtype=torch.float32, device=q.device)
+  lib = _lib.require()
+  rc = lib.tx_flash_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                        delta.data_ptr(), outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(), B, N, Kh, Lq,
+                        Lk, H, q.stride(1), k.stride(1), v.stride(1), o.stride(1), do.stride(1), outs[0].stride(1),
+                        outs[1].stride(1), outs[2].stride(1), int(causal), float(scale),
+                        _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_flash_bwd")
+  for dst, src in zip((dq_out, dk_out, dv_out), outs):
+    if dst is not src:
+      dst.copy_(src)
 
 
 class _FlashFn(torch.autograd.Function):

@@ -51,6 +51,22 @@ def main():
   _lib.check_status()
   print(json.dumps({"impl": "tx_flash_fwd", "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
                     "shape": [B, L, N, K, H], "causal": causal}))
+  o, ctx = flash.forward(q, k, v, causal=causal, scale=scale)
+  do = torch.randn_like(o)
+  dqkv = torch.empty_like(qkv)
+  dq, dk, dv = (dqkv[..., :N * H].view(B, L, N, H), dqkv[..., N * H:(N + K) * H].view(B, L, K, H),
+                dqkv[..., (N + K) * H:].view(B, L, K, H))
+  ms = _time(lambda: flash.backward(do, q, k, v, o, ctx, dq, dk, dv), a.iters, a.warmup)
+  _lib.check_status()
+  print(json.dumps({"impl": "tx_flash_bwd", "ms": round(ms, 4), "tflops": round(2.5 * flops / ms / 1e9, 1)}))
+  if not a.no_lib:
+    e = torch.empty(0, dtype=torch.long, device="cuda")
+    ot, dot, lse = o.transpose(1, 2), do.transpose(1, 2), ctx[1]
+    fnb = lambda: torch.ops.aten._scaled_dot_product_flash_attention_backward(
+        dot, q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), ot, lse, None, None, L, L, 0.0, causal, e, e,
+        scale=scale)
+    ms = _time(fnb, a.iters, a.warmup)
+    print(json.dumps({"impl": "library_flash_bwd", "ms": round(ms, 4), "tflops": round(2.5 * flops / ms / 1e9, 1)}))
   if not a.no_lib:
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     fn = lambda: torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
