@@ -110,6 +110,9 @@ def main():
     reference_arm(args)
     return
 
+  # micro-batches of 2 sequences need the allocator to grow segments in place: with fixed-size
+  # segments the ~150 GiB working set fragments and the step runs out of memory
+  os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
   import torch
   import torch.distributed as dist
   from tunix_b200 import optim
@@ -143,7 +146,7 @@ def main():
   remat = args.remat
   if remat == "auto":
     remat = "none"      # the fused decoder-layer node stores only what is expensive to rebuild
-  micro = args.micro_batch or min(per_gpu, (1 if remat == "none" else 4) if world == 1 else 2)
+  micro = args.micro_batch or min(per_gpu, 2 if remat == "none" else 4)
   ga = per_gpu // micro
   cfg = cfg.replace(dtype=torch.bfloat16, max_position=S,
                     remat_config=RematConfig.BLOCK if remat == "block" else RematConfig.NONE)
