@@ -51,11 +51,23 @@ class ConversationAgentBase(LLMBaseAgent):
   def _init_messages(self, system_prompt: str) -> None:
     self._messages = [{"role": "system", "content": system_prompt or ""}]
 
+  @staticmethod
+  def _text(value: Any) -> str:
+    """Dataset fields arrive as arrays of one element when a batch was split into examples."""
+    if hasattr(value, "shape") and getattr(value, "size", 0) == 1:
+      value = value.reshape(-1)[0]
+      value = value.item() if hasattr(value, "item") else value
+    if isinstance(value, (list, tuple)) and len(value) == 1:
+      value = value[0]
+    if isinstance(value, bytes):
+      value = value.decode("utf-8", errors="replace")
+    return "" if value is None else (value if isinstance(value, str) else str(value))
+
   def _observation_to_messages(self, observation: Any, reward: float, done: bool, info: Dict[str, Any]) -> None:
     if isinstance(observation, dict) and "prompts" in observation:
-      self._messages.append({"role": "user", "content": observation["prompts"] or ""})
+      self._messages.append({"role": "user", "content": self._text(observation["prompts"])})
     elif isinstance(observation, dict) and "question" in observation:
-      self._messages.append({"role": "user", "content": observation["question"] or ""})
+      self._messages.append({"role": "user", "content": self._text(observation["question"])})
     elif isinstance(observation, str):
       self._messages.append({"role": "user", "content": observation})
 

@@ -31,8 +31,9 @@ class ToolAgent(base_agent.ConversationAgentBase):
         for call_id, output in observation["tool_outputs"].items():
           self._messages.append({"role": "tool", "tool_call_id": call_id,
                                  "content": "Tool returned result: " + (output or "")})
-      elif "question" in observation:
-        self._messages.append({"role": "user", "content": observation["question"] or ""})
+      elif "question" in observation or "prompts" in observation:
+        key = "question" if "question" in observation else "prompts"
+        self._messages.append({"role": "user", "content": self._text(observation[key])})
       else:
         logging.warning("Unknown dict observation format: %s", observation)
     elif isinstance(observation, str):
