@@ -201,6 +201,9 @@ class Attention(nn.Module):
     else:
       self.q_norm = self.k_norm = None
 
+  def _forward_paged(self, q, k, v, cache, B, T):
+    return _paged_attention(self, q, k, v, cache, B, T)
+
   def _theta_scale(self) -> Tuple[float, float]:
     cfg = self.cfg
     if self.attn_type == AttentionType.LOCAL_SLIDING and cfg.local_rope_theta:
@@ -219,6 +222,9 @@ class Attention(nn.Module):
                          cfg.norm_eps, cfg.norm_offset, rscale, cfg.max_position)
     qkv = qkv.view(B, T, N + 2 * K, H)
     q, k, v = qkv[:, :, :N], qkv[:, :, N:N + K], qkv[:, :, N + K:]
+
+    if cache is not None and not isinstance(cache, dict):
+      return self._forward_paged(q, k, v, cache, B, T)
 
     new_cache = None
     if cache is not None:
@@ -241,6 +247,26 @@ class Attention(nn.Module):
                     softcap=cfg.attn_logits_soft_cap or 0.0)
     out = self.o_proj(o.reshape(B, T, N * H))
     return out, new_cache
+
+
+def _paged_attention(attn: "Attention", q, k, v, cache, B: int, T: int):
+  """Paged KV cache path (`rollout.paged_cache.PagedLayerCache`): store the new K/V rows in
+  their pages, then attend - within the prompt for a prefill, through the block tables for a
+  decode step."""
+  from ..ops import paged
+  cfg = attn.cfg
+  N, K, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+  paged.kv_page_write(k.reshape(B * T, K, H), v.reshape(B * T, K, H), cache.slots, cache.k_pages, cache.v_pages)
+  if cache.mode == "decode":
+    if T != 1:
+      raise ValueError("a paged decode step takes one token per sequence")
+    o = paged.paged_decode_attention(q.reshape(B, N, H), cache.k_pages, cache.v_pages, cache.block_tables,
+                                     cache.seq_lens, cfg.attn_scale, cache.num_splits, cache.max_len)
+    o = o.view(B, 1, N * H)
+  else:
+    o = F.attention(q, k, v, mask=None, causal=True, scale=cfg.attn_scale,
+                    softcap=cfg.attn_logits_soft_cap or 0.0).reshape(B, T, N * H)
+  return attn.o_proj(o), cache
 
 
 def _apply_sliding_window(mask, positions, S, window, cached):

@@ -53,6 +53,9 @@ def _declare(lib):
       "tx_accum_bf16_f32": [P, P, L, F, P],
       "tx_flash_fwd": [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, I, F, P, P],
       "tx_flash_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, I, F, P, P],
+      "tx_kv_page_write": [P, P, L, L, P, P, P, I, I, I, P],
+      "tx_paged_decode_attn": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
+      "tx_sample": [P, I, L, I, I, F, I, ctypes.c_ulonglong, P, L, P, I, P, P, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
       "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],
   }

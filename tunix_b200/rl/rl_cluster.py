@@ -128,7 +128,7 @@ class RLEngine:
                                        num_kv_heads=mcfg.num_kv_heads, head_dim=mcfg.head_dim)
       self._rollout = vanilla_rollout.VanillaRollout(self.rollout_actor, self.tokenizer, cache)
     elif engine == "native":
-      from ..rollout import native_rollout
+      from .rollout import native_rollout
       self._rollout = native_rollout.NativeRollout(self.rollout_actor, self.tokenizer, rc,
                                                    mesh=self.r2m.get(Role.ROLLOUT))
     elif engine == "vllm":
