@@ -76,6 +76,15 @@ def _coerce(schema_value: Any, value: Any, key: str) -> Any:
   """Types `value` like `schema_value` where a lossless conversion exists."""
   if value is None or schema_value is None:
     return value
+  try:
+    return _coerce_inner(schema_value, value, key)
+  except ValueError as e:
+    if "cannot turn" in str(e):
+      raise
+    raise ValueError(f"For key '{key}', cannot turn {value!r} into {type(schema_value).__name__}: {e}") from e
+
+
+def _coerce_inner(schema_value: Any, value: Any, key: str) -> Any:
   if isinstance(schema_value, bool):
     if isinstance(value, bool):
       return value
