@@ -150,6 +150,17 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: 
 
 # ------------------------------------------------------------------------------ qk-norm + rope
 _rope_tables = {}
+_position_bound = 0
+
+
+def set_position_bound(n: int) -> int:
+  """Declares that every position passed to `qk_norm_rope` is below `n` until further notice
+  (0 = unknown). With a bound the rotary table is sized once and the per-call device-to-host
+  read of `positions.max()` is skipped, which also makes the call capturable in a CUDA graph.
+  Returns the previous bound."""
+  global _position_bound
+  old, _position_bound = _position_bound, int(n)
+  return old
 
 
 def rope_table(head_dim: int, theta: float, max_pos: int, device, scale: float = 1.0) -> torch.Tensor:
@@ -198,8 +209,8 @@ def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_k: int,
   if _use_kernels(qkv) and head_dim in (64, 128, 256):
     q2 = qkv.reshape(-1, qkv.shape[-1]).contiguous()
     pos = positions.reshape(-1).to(torch.int32)
-    table = rope_table(head_dim, theta, max_pos or 4096, qkv.device, rope_scale)
-    if max_pos == 0 and table.shape[0] < 1 << 20:
+    table = rope_table(head_dim, theta, max_pos or _position_bound or 4096, qkv.device, rope_scale)
+    if max_pos == 0 and _position_bound == 0 and table.shape[0] < 1 << 20:
       # positions are data; make sure the table covers them (rare: only beyond 4096 tokens)
       need = int(pos.max().item()) + 1 if pos.numel() else 1
       if need > table.shape[0]:

@@ -277,6 +277,8 @@ class PagedEngine:
     """Generates up to `max_new_tokens` per prompt (token id lists, unpadded)."""
     was_training = self.model.training
     self.model.eval()
+    from ..ops import functional as F
+    old_bound = F.set_position_bound(self.cfg.max_seq_len)
     sampling = {"temperature": float(temperature), "greedy": bool(greedy or temperature == 0.0), "seed": int(seed),
                 "eos": set(int(e) for e in eos_ids),
                 "forbidden": torch.tensor(list(forbidden), dtype=torch.int32, device=self.device) if forbidden else None}
@@ -306,6 +308,7 @@ class PagedEngine:
       for s in running:                      # only on an error path
         self.cache.allocator.free(s.pages)
       self.model.train(was_training)
+      F.set_position_bound(old_bound)
     order = [results[i] for i in range(len(prompts))]
     return GenerationResult(tokens=[np.asarray(s.out, dtype=np.int64) for s in order],
                             logprobs=[np.asarray(s.lps, dtype=np.float32) for s in order] if return_logprobs else None,
