@@ -304,3 +304,61 @@ def test_manifest_validation():
   h.register_work_unit(peer_memory_handler.manifest_of(u2, {"w": torch.zeros(3, 2)})); h.attach(u2, {"w": torch.zeros(3, 2)})
   r = h.transfer([u1], [u2], req_id="x")
   assert not r.success and "shape mismatch" in r.message
+
+
+# ---- the whole loop in one process ---------------------------------------------------------------
+def test_rl_program_end_to_end_with_workers_and_weight_sync():
+  from tests.test_rl_grpo import ToyTokenizer, toy_model
+  from tunix_b200 import optim
+  from tunix_b200.common.configs import TrainingConfig
+  from tunix_b200.experimental.orchestrator import (algorithm_adapter, batch_assembly, orchestrator as orch_lib,
+                                                    rl_program)
+  from tunix_b200.experimental.rollout import manager as manager_lib, native_sampler_adapter
+  from tunix_b200.experimental.train import peft_trainer_v2
+  from tunix_b200.experimental.worker import inference_worker, rollout_worker, trainer_worker
+  from tunix_b200.rl import function_registry
+  from tunix_b200.rl.grpo.grpo_learner import GRPOConfig
+  from tunix_b200.rollout import EngineConfig
+
+  tok = ToyTokenizer()
+  actor, rollout_model, ref = toy_model(), toy_model(), toy_model()
+  handler = peer_memory_handler.InProcessHandler()
+  algo_cfg = GRPOConfig(num_generations=2, beta=0.04)
+  loss = function_registry.get_policy_loss_fn("grpo")
+
+  def make_trainer():
+    t = peft_trainer_v2.PeftTrainerV2(actor, optim.adamw(1e-2), TrainingConfig(eval_every_n_steps=100, pbar_description=None))
+    t.with_loss_fn(lambda model, train_example: loss(model, train_example.to_tensors(), algo_config=algo_cfg,
+                                                     pad_id=0, eos_id=2), has_aux=True)
+    t.with_gen_model_input_fn(lambda x: {"train_example": x})
+    return t
+  tw = trainer_worker.TrainerWorker(make_trainer, worker_id="t0", handler=handler)
+  sampler = native_sampler_adapter.NativeSamplerAdapter(rollout_model, tok, handler=handler, worker_id="r0",
+                                                        engine_config=EngineConfig(page_size=4, max_batch=8, max_seq_len=32))
+  rw = rollout_worker.RolloutWorker(lambda: manager_lib.RolloutManager(sampler=sampler, tokenizer=tok, chat_parser=None),
+                                    worker_id="r0")
+  iw = inference_worker.InferenceWorker({"reference": ref}, worker_id="i0")
+  co = wsc.WeightSyncCoordinator(handler, sources=[tw], destinations=[rw])
+  orch = orch_lib.ClusterOrchestrator(weight_sync_coordinator=co)
+  for w in (tw, rw, iw):
+    orch.register_worker(w)
+  before = {n: p.detach().clone() for n, p in rollout_model.named_parameters()}
+  algo = algorithm_adapter.GRPOAdapter(group_size=2, mini_batch_size=2, beta_kl=0.04)
+  prog = rl_program.StandardRLProgram(
+      algo, reward_fns=[lambda item: float(len(item.completion_tokens)) / 8.0 + 0.1 * item.pair_index],
+      assembler=batch_assembly.GRPOTrainExampleAssembler(batch_size=2, max_prompt_length=8, max_response_length=8, pad_id=0),
+      max_staleness=1)
+  ds = [{"prompt": f"alpha beta {w}", "generation_kwargs": {"max_generation_steps": 8, "temperature": 1.0, "seed": i}}
+        for i, w in enumerate(["gamma", "delta", "eps", "zeta", "eta", "theta"])]
+  with orch:
+    reports, overdue, bad = orch.poll_health()
+    assert {r.state for r in reports.values()} == {S.READY} and not overdue and not bad
+    orch.run_program(prog, ds, num_steps=2)
+  assert [r.policy_version for r in prog.history] == [1, 2] and prog.history[0].num_rollouts == 4
+  assert co.last_committed_version == 2 and sampler.policy_version == 2
+  assert tw.trainer.train_steps == 2
+  changed = [n for n, p in rollout_model.named_parameters() if not torch.equal(p, before[n])]
+  assert changed                                                     # the rollout model received the new weights
+  for n, p in rollout_model.named_parameters():
+    torch.testing.assert_close(p, dict(actor.named_parameters())[n])
+  assert all(w.state == S.STOPPED for w in (tw, rw, iw))

@@ -9,7 +9,10 @@ from typing import Any, Dict, List, Optional
 
 import numpy as np
 
+from ...common.datatypes import Role  # noqa: F401  (roles of the control plane are the cluster roles)
 from ...rl.agentic.agents import agent_types
+
+Trajectory = agent_types.Trajectory
 
 
 @dataclasses.dataclass(kw_only=True)
