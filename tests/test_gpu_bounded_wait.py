@@ -1,0 +1,39 @@
+"""A device-side wait that nothing satisfies ends by itself and reports through the status word."""
+
+import time
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_peer_barrier_gives_up_and_context_survives():
+  from tunix_b200.ops import _lib
+  from tunix_b200.dist import symm
+  lib = _lib.require()
+  dev = torch.device("cuda", 0)
+  # Two flag rows on one GPU stand in for two ranks; "rank 1" never arrives.
+  rows = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]
+  status = _lib.status_word(dev)
+  status.zero_()
+  torch.cuda.synchronize()
+  t0 = time.time()
+  rc = lib.tx_peer_barrier(symm._ptr_array([r.data_ptr() for r in rows]), 0, 2, 1, 300,
+                           status.data_ptr(), _lib.stream_ptr())
+  assert rc == 0
+  torch.cuda.synchronize()
+  waited = time.time() - t0
+  assert 0.25 < waited < 5.0
+  assert int(rows[1][0]) == 1          # our arrival was published to the peer's row
+  with pytest.raises(RuntimeError, match="0x10"):
+    _lib.check_status(dev)
+  _lib.check_status(dev)               # the word was cleared
+  # the context is still usable, and a barrier whose peer did arrive passes
+  rows[0][1] = 2
+  rc = lib.tx_peer_barrier(symm._ptr_array([r.data_ptr() for r in rows]), 0, 2, 2, 300,
+                           status.data_ptr(), _lib.stream_ptr())
+  assert rc == 0
+  torch.cuda.synchronize()
+  _lib.check_status(dev)
+  assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0

@@ -1,0 +1,138 @@
+"""Times the memory-bound kernels one at a time and prints achieved bandwidth.
+
+  python -m tunix_b200.ops.kernel_bench [--only rmsnorm_fwd,paged_decode] [--iters 10]
+
+Every case works on more bytes than the L2 holds, is warmed up, and is timed
+with CUDA events around `iters` back-to-back launches. "bytes" is the
+algorithmic traffic (each input read once, each output written once). One JSON
+line per kernel: name, shape, ms, GB/s, and the fraction of the measured copy
+bandwidth when a peaks file is found beside the package.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import kernels as K
+from . import paged
+
+
+def _time(fn, iters, warmup=3):
+  for _ in range(warmup):
+    fn()
+  torch.cuda.synchronize()
+  a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  a.record()
+  for _ in range(iters):
+    fn()
+  b.record()
+  torch.cuda.synchronize()
+  return a.elapsed_time(b) / iters
+
+
+def _peak_gbs():
+  here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+  try:
+    with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+      return float(json.load(f)["hbm_gbs"]), "measured"
+  except (OSError, KeyError, ValueError):
+    return 6650.0, "fallback"
+
+
+def cases(dev, small=False):
+  bf = torch.bfloat16
+  T, D, F, V = (4096 if small else 16384), 4096, 14336, 128256
+  out = {}
+
+  def rms_fwd():
+    x = torch.randn(T, D, device=dev, dtype=bf); r = torch.randn_like(x)
+    w = torch.ones(D, device=dev, dtype=bf)
+    return (lambda: K.rmsnorm_fwd(x, w, 1e-6, 0.0, r), 4 * T * D * 2, f"T={T} D={D} +residual")
+  out["rmsnorm_fwd"] = rms_fwd
+
+  def rms_bwd():
+    x = torch.randn(T, D, device=dev, dtype=bf); dy = torch.randn_like(x); dres = torch.randn_like(x)
+    w = torch.ones(D, device=dev, dtype=bf)
+    _, _, rstd = K.rmsnorm_fwd(x, w, 1e-6)
+    return (lambda: K.rmsnorm_bwd(x, w, dy, rstd, 1e-6, 0.0, dres), 4 * T * D * 2, f"T={T} D={D} +dres")
+  out["rmsnorm_bwd"] = rms_bwd
+
+  def glu_f():
+    gu = torch.randn(T, 2 * F, device=dev, dtype=bf)
+    return (lambda: K.glu_fwd(gu, False), 3 * T * F * 2, f"T={T} F={F} silu")
+  out["glu_fwd"] = glu_f
+
+  def glu_b():
+    gu = torch.randn(T, 2 * F, device=dev, dtype=bf); do = torch.randn(T, F, device=dev, dtype=bf)
+    return (lambda: K.glu_bwd(gu, do, False), 5 * T * F * 2, f"T={T} F={F} silu")
+  out["glu_bwd"] = glu_b
+
+  def lp_f():
+    t = 1024 if small else 4096
+    lg = torch.randn(t, V, device=dev, dtype=bf); tg = torch.randint(0, V, (t,), device=dev)
+    return (lambda: K.logprob_fwd(lg, tg), t * V * 2, f"T={t} V={V} bf16 logits")
+  out["logprob_fwd"] = lp_f
+
+  def lp_b():
+    t = 1024 if small else 4096
+    lg = torch.randn(t, V, device=dev, dtype=bf); tg = torch.randint(0, V, (t,), device=dev)
+    logp, lse, _ = K.logprob_fwd(lg, tg)
+    g = torch.ones(t, device=dev); o = torch.empty_like(lg)
+    return (lambda: K.logprob_bwd(lg, tg, lse, None, g, None, out=o), 2 * t * V * 2, f"T={t} V={V}")
+  out["logprob_bwd"] = lp_b
+
+  def adamw():
+    n = (64 if small else 256) << 20
+    master = torch.randn(n, device=dev); m = torch.zeros(n, device=dev); v = torch.zeros(n, device=dev)
+    g = torch.randn(n, device=dev); p = torch.empty(n, device=dev, dtype=bf)
+    return (lambda: K.adamw_step(master, m, v, g, p, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                                 step=3), n * (4 * 4 * 2 + 2), f"n={n} fp32 grad, zeroed in place")
+  out["adamw"] = adamw
+
+  def decode():
+    B, N, Kh, H, page, L = (128 if small else 512), 32, 8, 128, 16, 640
+    blocks = (L + page - 1) // page
+    P = B * blocks
+    kp = torch.randn(P, page, Kh, H, device=dev, dtype=bf); vp = torch.randn_like(kp)
+    bt = torch.randperm(P, device=dev, dtype=torch.int32).view(B, blocks).contiguous()
+    lens = torch.full((B,), L, device=dev, dtype=torch.int32)
+    q = torch.randn(B, N, H, device=dev, dtype=bf)
+    return (lambda: paged.paged_decode_attention(q, kp, vp, bt, lens, H ** -0.5, max_len=L),
+            2 * B * L * Kh * H * 2 + 2 * B * N * H * 2, f"B={B} N={N} Kh={Kh} H={H} len={L} page={page}")
+  out["paged_decode"] = decode
+
+  def sample():
+    B, Vq = 512, 151936
+    lg = torch.randn(B, Vq, device=dev, dtype=bf)
+    return (lambda: paged.sample(lg, 1.0, False, seed=1, step=2), B * Vq * 2, f"B={B} V={Vq} bf16")
+  out["sample"] = sample
+  return out
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--only", default="")
+  ap.add_argument("--iters", type=int, default=10)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--small", action="store_true", help="about a quarter of the bytes (for profiler captures)")
+  a = ap.parse_args()
+  dev = torch.device("cuda", 0)
+  peak, how = _peak_gbs()
+  table = cases(dev, a.small)
+  names = [n for n in a.only.split(",") if n] or list(table)
+  for name in names:
+    fn, nbytes, shape = table[name]()
+    ms = _time(fn, a.iters, a.warmup)
+    gbs = nbytes / ms / 1e6
+    print(json.dumps({"kernel": name, "shape": shape, "ms": round(ms, 4), "GB_s": round(gbs, 1),
+                      f"frac_of_{how}_copy": round(gbs / peak, 3)}), flush=True)
+    del fn
+    torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+  main()

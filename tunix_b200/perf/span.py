@@ -40,6 +40,10 @@ class SpanGroup:
     return f"SpanGroup({self.name}, {self.begin:.6f}, {self.end:.6f}, inner={len(self.inner)})"
 
   @property
+  def ended(self) -> bool:
+    return self.end != float("inf")
+
+  @property
   def duration(self) -> float:
     return self.end - self.begin
 
