@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 def test_peer_barrier_gives_up_and_context_survives():
   from tunix_b200.ops import _lib
   from tunix_b200.dist import symm
-  lib = _lib.require()
+  lib = symm._declare()     # pointer-typed signatures: an undeclared ctypes call would truncate addresses
   dev = torch.device("cuda", 0)
   # Two flag rows on one GPU stand in for two ranks; "rank 1" never arrives.
   rows = [torch.zeros(16, dtype=torch.int32, device=dev) for _ in range(2)]

@@ -36,6 +36,42 @@ def test_paged_decode_attention(kernel_lib, H, N, Kh, page, splits):
   torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("N,Kh,page", [(32, 8, 8), (32, 8, 64), (32, 2, 16), (4, 4, 32)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_paged_decode_tensor_core_kernel(kernel_lib, N, Kh, page, splits):
+  """tcgen05 kernel: page sizes 8..64, groups up to 16 heads, unused block-table entries poisoned."""
+  from tunix_b200.ops import _lib, paged
+  torch.manual_seed(4)
+  H = 128
+  assert paged.tc_supported(H, page, N // Kh)
+  lens = [1, 63, 64, 65, 700, 129, 2048]
+  kp, vp, bt, sl = make_cache(len(lens), lens, page, Kh, H, "cuda")
+  for b, n in enumerate(lens):
+    bt[b, (n + page - 1) // page:] = -1          # entries past the sequence must never be dereferenced
+  q = torch.randn(len(lens), N, H, device="cuda").bfloat16()
+  scale = 1 / math.sqrt(H)
+  out = paged.paged_decode_attention(q, kp, vp, bt, sl, scale, num_splits=splits)
+  _lib.check_status()
+  bt_ref = bt.clamp(min=0)
+  ref = paged.paged_decode_attention_ref(q, kp, vp, bt_ref, sl, scale)
+  torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_paged_decode_simt_kernel_still_matches(kernel_lib, monkeypatch):
+  from tunix_b200.ops import paged
+  monkeypatch.setenv("TUNIX_B200_DECODE_TC", "0")
+  torch.manual_seed(5)
+  H, N, Kh, page = 128, 32, 8, 16
+  assert not paged.tc_supported(H, page, N // Kh)
+  lens = [5, 400, 1025]
+  kp, vp, bt, sl = make_cache(len(lens), lens, page, Kh, H, "cuda")
+  q = torch.randn(len(lens), N, H, device="cuda").bfloat16()
+  for splits in (1, 4):
+    out = paged.paged_decode_attention(q, kp, vp, bt, sl, 1 / math.sqrt(H), num_splits=splits)
+    ref = paged.paged_decode_attention_ref(q, kp, vp, bt, sl, 1 / math.sqrt(H))
+    torch.testing.assert_close(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_kv_page_write(kernel_lib):
   from tunix_b200.ops import paged
   torch.manual_seed(1)

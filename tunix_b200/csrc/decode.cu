@@ -339,6 +339,23 @@ extern "C" int tx_kv_page_write(const void* k_new, const void* v_new, long long 
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 
+// Merges the per-split partial results (ws_o unnormalised fp32 sums relative to ws_ml's max, ws_ml = (max in
+// log2 units, sum)) into out [B, N*H] bf16. Used by the tensor-core decode kernel, which writes the same layout.
+extern "C" int tx_paged_decode_combine(const float* ws_o, const float* ws_ml, int num_splits, void* out,
+                                       long long ldo, int B, int N, int H, cudaStream_t s) {
+  if (B <= 0) return 0;
+  if (!ws_o || !ws_ml || num_splits < 1) return 1;
+  dim3 g2(N, B);
+  auto* op = static_cast<__nv_bfloat16*>(out);
+  switch (H) {
+    case 64: paged_decode_combine_kernel<64><<<g2, 64, 0, s>>>(ws_o, ws_ml, num_splits, op, ldo, N); break;
+    case 128: paged_decode_combine_kernel<128><<<g2, 128, 0, s>>>(ws_o, ws_ml, num_splits, op, ldo, N); break;
+    case 256: paged_decode_combine_kernel<256><<<g2, 256, 0, s>>>(ws_o, ws_ml, num_splits, op, ldo, N); break;
+    default: return 1;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
 // Workspace for num_splits > 1: ws_o [B*N*splits*H] floats, ws_ml [B*N*splits*2] floats.
 extern "C" int tx_paged_decode_attn(const void* q, long long ldq, const void* k_pages, const void* v_pages,
                                     const int* block_tables, int max_blocks, const int* seq_lens, int B, int N, int Kh,

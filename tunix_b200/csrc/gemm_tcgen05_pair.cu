@@ -34,16 +34,19 @@ constexpr int kABytes = BM_CTA * BK * 2;      // 16 KB
 constexpr int kBBytes = BN_CTA * BK * 2;      // 16 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;             // two accumulators
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kRedBytes = 32 * 128;            // one [32 rows x 32 fp32] swizzled box
+constexpr int kRedBufBytes = 4 * 2 * kRedBytes; // per epilogue warp: two boxes (double buffer)
+constexpr int kSmemBytes = kStages * kStageBytes + kRedBufBytes + 1024 + 256;
 
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const GemmParams p) {
+                      const __grid_constant__ CUtensorMap map_c, const GemmParams p, const int red_epilogue) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kStages * kStageBytes);
+  const uint32_t red_base = smem_base + kStages * kStageBytes;      // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kStages * kStageBytes + kRedBufBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_tfull = bar_empty + 8 * kStages;
@@ -182,18 +185,50 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (red_epilogue) {
+        // fp32 C += tile: each warp stages a [32 x 32] box in shared memory (128-byte swizzle) and hands it
+        // to the TMA unit as a reduce-add, so C is never read into the SM and the adds run in L2.
+        const int row0 = pm * 2 * BM_CTA + cta * BM_CTA + quarter * 32;
+        const uint32_t my_red = red_base + quarter * (2 * kRedBytes);
+        uint8_t* my_red_gen = smem_gen + kStages * kStageBytes + quarter * (2 * kRedBytes);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c, r);
-        tmem_ld_wait();
-        txg::store_row_chunk(p, row, n0 + c, r);
+        for (int c = 0; c < BN; c += 32) {
+          const int buf = (c >> 5) & 1;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<1>();      // the box issued two chunks ago has been read
+          __syncwarp();
+          uint8_t* rowp = my_red_gen + buf * kRedBytes + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = make_float4(__uint_as_float(r[4 * j]) * p.alpha, __uint_as_float(r[4 * j + 1]) * p.alpha,
+                                         __uint_as_float(r[4 * j + 2]) * p.alpha,
+                                         __uint_as_float(r[4 * j + 3]) * p.alpha);
+            *reinterpret_cast<float4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M && n0 + c < p.N) {
+            tma_reduce_add_2d(&map_c, my_red + buf * kRedBytes, n0 + c, row0);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          txg::store_row_chunk(p, row, n0 + c, r);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (red_epilogue && lane == 0) tma_store_wait<0>();   // every reduce has landed before shared memory goes away
   }
 
   if (*abort_flag) __nanosleep(200000);
@@ -217,6 +252,13 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   if (B_MN) rc = txh::make_map_2d_bf16(&mbm, B, p.K, p.N, ldb, BK, 64);
   else      rc = txh::make_map_2d_bf16(&mbm, B, p.N, p.K, ldb, BN_CTA, BK);
   if (rc) return 200 + rc;
+  // fp32 accumulation into C (gradient accumulation of weight gradients) goes through TMA reduce-add.
+  CUtensorMap mc = ma;
+  int red = 0;
+  if (p.c_fp32 && p.accumulate && p.ldc % 4 == 0 && reinterpret_cast<uintptr_t>(p.C) % 16 == 0) {
+    if (txh::make_map_2d_f32(&mc, p.C, p.M, p.N, p.ldc, 32) == 0) red = 1;
+    else mc = ma;
+  }
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -229,7 +271,7 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   int pairs = mb * nb;
   if (pairs > sms / 2) pairs = sms / 2;
   if (pairs < 1) pairs = 1;
-  kern<<<2 * pairs, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, p);
+  kern<<<2 * pairs, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, mc, p, red);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 

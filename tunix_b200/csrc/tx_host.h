@@ -60,6 +60,22 @@ inline int make_map_2d_bf16(CUtensorMap* map, const void* base, uint64_t rows, u
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// 2-D fp32 tensor map over a row-major [rows, cols] matrix (row stride `ld` elements, a multiple of 4);
+// box = [box_rows, 32 columns] = 128-byte rows, 128-byte swizzle.
+inline int make_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                           uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {32, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
+}
+
 // 3-D bf16 tensor map: dims (innermost first) d0, d1, d2 with byte strides s1, s2.
 inline int make_map_3d_bf16(CUtensorMap* map, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                             uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1,

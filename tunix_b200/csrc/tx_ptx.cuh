@@ -128,6 +128,15 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sm
                : "memory");
 }
 
+// Adds a shared-memory tile into global memory (element type and swizzle from the tensor map);
+// out-of-range parts of the box are dropped. Coordinates must be non-negative and x a multiple of 16 bytes.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(smem_src), "r"(x), "r"(y)
+               : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {

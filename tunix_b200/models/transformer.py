@@ -427,12 +427,18 @@ class Transformer(nn.Module):
         "attention_mask": torch.ones(B, 1, L, dtype=torch.bool, device=dev),
     }
 
-  def compute_final_logits(self, hidden: torch.Tensor) -> torch.Tensor:
-    """lm_head (or tied `h E^T`) in fp32, with the final soft-cap when configured."""
-    logits = F.linear(hidden, self.head_weight()).float()
+  def compute_final_logits(self, hidden: torch.Tensor, as_float: bool = True) -> torch.Tensor:
+    """lm_head (or tied `h E^T`) in fp32, with the final soft-cap when configured.
+
+    `as_float=False` returns the GEMM's own dtype when no soft-cap applies: the sampler kernel
+    reads bf16 rows directly, which saves a pass over [B, V] per decode step."""
+    logits = F.linear(hidden, self.head_weight())
     cap = self.config.final_logit_softcap
     if cap:
+      logits = logits.float()
       logits = torch.tanh(logits / cap) * cap
+    elif as_float:
+      logits = logits.float()
     return logits
 
   def _stack(self, h, positions, cache, attn_mask):

@@ -55,6 +55,13 @@ def _declare(lib):
       "tx_flash_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, I, F, P, P],
       "tx_kv_page_write": [P, P, L, L, P, P, P, I, I, I, P],
       "tx_paged_decode_attn": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
+      "tx_paged_decode_attn_tc": [P, L, P, P, P, I, P, I, I, I, I, I, L, F, I, P, P, P, L, P, P],
+      "tx_paged_decode_combine": [P, P, I, P, L, I, I, I, P],
+      "tx_peer_barrier": [ctypes.POINTER(P), I, I, I, L, P, P],
+      "tx_reduce_scatter_grid": [],
+      "tx_reduce_scatter_sum_f32": [ctypes.POINTER(P), P, L, L, I, I, P, P],
+      "tx_adamw_allgather": [P, P, P, P, ctypes.POINTER(P), L, L, F, F, F, F, F, F, F, P, I, I, P],
+      "tx_peer_copy_2d": [P, P, L, L, L, L, P],
       "tx_sample": [P, I, L, I, I, F, I, ctypes.c_ulonglong, P, L, P, I, P, P, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
       "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],

@@ -93,17 +93,21 @@ def cases(dev, small=False):
                                  step=3), n * (4 * 4 * 2 + 2), f"n={n} fp32 grad, zeroed in place")
   out["adamw"] = adamw
 
-  def decode():
-    B, N, Kh, H, page, L = (128 if small else 512), 32, 8, 128, 16, 640
-    blocks = (L + page - 1) // page
-    P = B * blocks
-    kp = torch.randn(P, page, Kh, H, device=dev, dtype=bf); vp = torch.randn_like(kp)
-    bt = torch.randperm(P, device=dev, dtype=torch.int32).view(B, blocks).contiguous()
-    lens = torch.full((B,), L, device=dev, dtype=torch.int32)
-    q = torch.randn(B, N, H, device=dev, dtype=bf)
-    return (lambda: paged.paged_decode_attention(q, kp, vp, bt, lens, H ** -0.5, max_len=L),
-            2 * B * L * Kh * H * 2 + 2 * B * N * H * 2, f"B={B} N={N} Kh={Kh} H={H} len={L} page={page}")
-  out["paged_decode"] = decode
+  def make_decode(page, L=640):
+    def decode():
+      B, N, Kh, H = (128 if small else 512), 32, 8, 128
+      blocks = (L + page - 1) // page
+      P = B * blocks
+      kp = torch.randn(P, page, Kh, H, device=dev, dtype=bf); vp = torch.randn_like(kp)
+      bt = torch.randperm(P, device=dev, dtype=torch.int32).view(B, blocks).contiguous()
+      lens = torch.full((B,), L, device=dev, dtype=torch.int32)
+      q = torch.randn(B, N, H, device=dev, dtype=bf)
+      return (lambda: paged.paged_decode_attention(q, kp, vp, bt, lens, H ** -0.5, max_len=L),
+              2 * B * L * Kh * H * 2 + 2 * B * N * H * 2, f"B={B} N={N} Kh={Kh} H={H} len={L} page={page}")
+    return decode
+  out["paged_decode"] = make_decode(16)
+  out["paged_decode_p64"] = make_decode(64)
+  out["paged_decode_p64_len1000"] = make_decode(64, 1000)
 
   def sample():
     B, Vq = 512, 151936

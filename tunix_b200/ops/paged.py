@@ -9,6 +9,7 @@ int32 page ids per sequence; `seq_lens` [B] int32; `slots` [T] int64 = page * pa
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -79,13 +80,21 @@ def choose_splits(batch: int, kv_heads: int, max_len: int, sm_count: int = 148) 
   return int(max(1, min(want, max_len // 256, 32)))
 
 
+def tc_supported(head_dim: int, page_size: int, group: int) -> bool:
+  """Shapes the tensor-core decode kernel covers; TUNIX_B200_DECODE_TC=0 forces the SIMT kernel."""
+  return (head_dim == 128 and page_size in (8, 16, 32, 64) and 1 <= group <= 32
+          and os.environ.get("TUNIX_B200_DECODE_TC", "1") != "0")
+
+
 def paged_decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                            seq_lens: torch.Tensor, scale: float, num_splits: Optional[int] = None,
                            max_len: Optional[int] = None) -> torch.Tensor:
   """q [B, N, H] -> [B, N, H]: each row attends to the `seq_lens[b]` cached tokens of its pages."""
   B, N, H = q.shape
   P, page, Kh, _ = k_pages.shape
-  if not _use_kernels(q, k_pages) or H not in (64, 128, 256) or N // Kh > 8 or q.stride(2) != 1 or q.stride(1) != H:
+  tc = tc_supported(H, page, N // Kh)
+  if (not _use_kernels(q, k_pages) or H not in (64, 128, 256) or (N // Kh > 8 and not tc) or q.stride(2) != 1
+      or q.stride(1) != H):
     return paged_decode_attention_ref(q, k_pages, v_pages, block_tables, seq_lens, scale)
   if num_splits is None:
     num_splits = choose_splits(B, Kh, max_len if max_len is not None else block_tables.shape[1] * page)
@@ -93,7 +102,20 @@ def paged_decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
   ws_o = ws_ml = None
   if num_splits > 1:
     ws_o, ws_ml = _workspace(q.device, B * N * num_splits * H, B * N * num_splits * 2)
-  rc = _lib.require().tx_paged_decode_attn(
+  lib = _lib.require()
+  if tc and k_pages.is_contiguous() and v_pages.is_contiguous():
+    rc = lib.tx_paged_decode_attn_tc(
+        q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
+        block_tables.stride(0), seq_lens.data_ptr(), B, N, Kh, H, page, P, float(scale), int(num_splits),
+        ws_o.data_ptr() if ws_o is not None else None, ws_ml.data_ptr() if ws_ml is not None else None,
+        out.data_ptr(), out.stride(0), _lib.status_word(q.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "tx_paged_decode_attn_tc")
+    if num_splits > 1:
+      _lib.check_rc(lib.tx_paged_decode_combine(ws_o.data_ptr(), ws_ml.data_ptr(), int(num_splits), out.data_ptr(),
+                                                out.stride(0), B, N, H, _lib.stream_ptr()),
+                    "tx_paged_decode_combine")
+    return out
+  rc = lib.tx_paged_decode_attn(
       q.data_ptr(), q.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), block_tables.data_ptr(),
       block_tables.stride(0), seq_lens.data_ptr(), B, N, Kh, H, page, float(scale), int(num_splits),
       ws_o.data_ptr() if ws_o is not None else None, ws_ml.data_ptr() if ws_ml is not None else None, out.data_ptr(),

@@ -29,13 +29,14 @@ def main():
   ap.add_argument("--max-batch", type=int, default=512)
   ap.add_argument("--no-graphs", action="store_true")
   ap.add_argument("--warmup-tokens", type=int, default=8)
+  ap.add_argument("--page-size", type=int, default=16)
   a = ap.parse_args()
   cfg = automodel.call_model_config(a.model)
   if a.layers:
     import dataclasses
     cfg = dataclasses.replace(cfg, num_layers=a.layers)
   model = dummy_model_creator.create_dummy_model(Transformer, cfg, dtype=torch.bfloat16, device="cuda").eval()
-  eng = PagedEngine(model, EngineConfig(page_size=16, max_batch=a.max_batch, max_seq_len=a.prompt_len + a.new_tokens + 16,
+  eng = PagedEngine(model, EngineConfig(page_size=a.page_size, max_batch=a.max_batch, max_seq_len=a.prompt_len + a.new_tokens + 16,
                                         use_cuda_graphs=not a.no_graphs))
   rng = np.random.default_rng(0)
   prompts = [rng.integers(0, cfg.vocab_size, size=a.prompt_len).tolist() for _ in range(a.prompts)]
@@ -52,7 +53,7 @@ def main():
   print(json.dumps({"metric": "rollout generated tokens/s", "value": round(n / ms * 1e3, 1), "ms": round(ms, 1),
                     "generated": n, "decode_steps": res.steps, "ms_per_decode_step": round(ms / max(res.steps, 1), 3),
                     "sequences": len(prompts), "model": a.model, "layers": cfg.num_layers,
-                    "cuda_graphs": not a.no_graphs, "kv_cache_gb": round(eng.cache.bytes() / 2 ** 30, 1),
+                    "cuda_graphs": not a.no_graphs, "page_size": a.page_size, "kv_cache_gb": round(eng.cache.bytes() / 2 ** 30, 1),
                     "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))
 
 

@@ -103,7 +103,7 @@ class PagedEngine:
     hidden, _ = self.model(tokens, positions, caches, None, skip_lm_head=True)
     for s in group:
       s.length = L
-    return self.model.compute_final_logits(hidden[:, -1])
+    return self.model.compute_final_logits(hidden[:, -1], as_float=False)
 
   # ---- decode --------------------------------------------------------------------------------
   def _bucket(self, n: int) -> int:
@@ -128,7 +128,7 @@ class PagedEngine:
     caches = self.cache.layer_caches(st["slots"], st["block_tables"], st["seq_lens"], "decode", self._num_splits,
                                      self.cfg.max_seq_len)
     hidden, _ = self.model(st["tokens"], st["positions"], caches, None, skip_lm_head=True)
-    logits = self.model.compute_final_logits(hidden[:, -1])
+    logits = self.model.compute_final_logits(hidden[:, -1], as_float=False)
     return paged.sample(logits, temperature=sampling["temperature"], greedy=sampling["greedy"], seed=sampling["seed"],
                         step=0, step_tensor=self._step_counter, forbidden=sampling["forbidden"])
 
