@@ -141,10 +141,18 @@ class FlatParamStore:
     elif self.symm is not None:
       self.symm.reduce_scatter_sum(self.flat_grad, self.grad_shard, self.rank)
       g = self.grad_shard
-    else:
+    elif self.device.type == "cuda":
       dist.reduce_scatter_tensor(self.grad_shard, self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
       g = self.grad_shard
-    kernels.sumsq(g, ss, accumulate=False)
+    else:
+      # gloo (CPU ranks in tests) has no reduce-scatter: all-reduce and keep this rank's slice
+      dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
+      self.grad_shard.copy_(self.flat_grad[self.shard])
+      g = self.grad_shard
+    if self.device.type == "cuda":
+      kernels.sumsq(g, ss, accumulate=False)
+    else:
+      ss.copy_(g.double().pow(2).sum().float().reshape(1))
     if self.world > 1:
       pack = self._buf("pack", 2)
       pack[0:1].copy_(ss)
@@ -155,7 +163,14 @@ class FlatParamStore:
     inv = self._buf("inv")
     torch.where(d == 0, torch.zeros_like(d), 1.0 / torch.where(d == 0, torch.ones_like(d), d), out=inv)
     norm, scale = self._buf("norm"), self._buf("scale")
-    kernels.clip_scale(ss, inv, max_grad_norm or 0.0, norm, scale)
+    if self.device.type == "cuda":
+      kernels.clip_scale(ss, inv, max_grad_norm or 0.0, norm, scale)
+    else:
+      # norm of the mean gradient; scale = 1/denom, times max_norm/norm when clipping applies
+      norm.copy_(ss.sqrt() * inv)
+      scale.copy_(inv)
+      if max_grad_norm and float(norm) > max_grad_norm:
+        scale.mul_(max_grad_norm / (float(norm) + 1e-6))
     inner = getattr(tx, "inner", tx)
     if self.world > 1 and self.symm is not None:
       self.symm.adamw_allgather(inner, state, g, self.flat_param, self.shard, scale)

@@ -57,7 +57,10 @@ def main(argv=None):
     row["tx_tn"] = fl / timeit(lambda: kernels.gemm(x, w)) / 1e9
     row["tx_nn"] = fl / timeit(lambda: kernels.gemm(x, wt, b_mn=True)) / 1e9
     row["tx_nt"] = fl / timeit(lambda: kernels.gemm(xt, wt, a_mn=True, b_mn=True)) / 1e9
+    acc = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+    row["tx_nt_acc_f32"] = fl / timeit(lambda: kernels.gemm(xt, wt, a_mn=True, b_mn=True, out=acc, accumulate=True)) / 1e9
     if not a.no_cublas:
+      row["cublas_nt_acc_f32"] = fl / timeit(lambda: acc.add_(torch.matmul(xt.t(), wt))) / 1e9
       row["cublas_tn"] = fl / timeit(lambda: torch.matmul(x, w.t())) / 1e9
       row["cublas_nt"] = fl / timeit(lambda: torch.matmul(xt.t(), wt)) / 1e9
     _lib.check_status()

@@ -161,6 +161,17 @@ def adamw_step(master, m, v, grad, param_bf16, *, lr, beta1, beta2, eps, weight_
   n = master.numel()
   bc1 = 1.0 - beta1 ** step
   bc2 = 1.0 - beta2 ** step
+  if not master.is_cuda:      # the same update in plain PyTorch (CPU ranks of the multi-process tests)
+    g = grad.float() * (float(grad_scale) if grad_scale is not None else 1.0)
+    m.mul_(beta1).add_(g, alpha=1.0 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1.0 - beta2)
+    upd = (m / bc1) / ((v / bc2).sqrt() + eps) + weight_decay * master
+    master.sub_(lr * upd)
+    if param_bf16 is not None:
+      param_bf16.copy_(master)
+    if zero_grad:
+      grad.zero_()
+    return
   _lib.check_rc(_lib.require().tx_adamw(master.data_ptr(), m.data_ptr(), v.data_ptr(), grad.data_ptr(),
                                         _p(param_bf16), n, float(lr), float(beta1), float(beta2), float(eps),
                                         float(weight_decay), float(bc1), float(bc2), _p(grad_scale),

@@ -164,11 +164,26 @@ class RLEngine:
     actor_cfg = copy.copy(tc)
     if root:
       actor_cfg.checkpoint_root_directory = f"{root}/actor"
+    # An actor mesh of several ranks trains data-parallel with sharded optimizer state: parameters move into
+    # a flat store whose bf16 replica stays resident on every rank, so a rollout engine that shares the module
+    # reads each update in place and `sync_weights` has nothing to copy.
+    actor_mesh = self.r2m.get(Role.ACTOR)
+    actor_sync = None
+    if actor_mesh is not None and getattr(actor_mesh, "size", 1) > 1 and getattr(actor_mesh, "contains_me", True):
+      import torch.distributed as torch_dist
+      if torch_dist.is_available() and torch_dist.is_initialized():
+        from ..dist import fsdp
+        axis = "fsdp" if "fsdp" in actor_mesh.axis_names else actor_mesh.axis_names[0]
+        if not hasattr(self.train_actor, "flat_store"):
+          fsdp.shard_model(self.train_actor, actor_mesh, axis)
+        actor_sync = fsdp.GradSync(self.train_actor, actor_mesh, axis)
     self._actor_trainer = rl_trainer.Trainer(
         model=self.train_actor, optimizer=tc.actor_optimizer, training_config=_as_training_config(actor_cfg),
         custom_checkpoint_metadata_fn=lambda: {
             "global_step": self.global_steps + (0 if self._actor_trainer._closing else 1), "role": "actor"},
         metrics_logger=self._rl_metrics_logger, perf_tracer=self._perf, perf_tracer_v2=self._perf_v2)
+    if actor_sync is not None:
+      self._actor_trainer.with_grad_sync(actor_sync)
     del self.train_actor
     self._maybe_offload_model_to_cpu(self._actor_trainer.model, Role.ACTOR)
     if self.critic is not None:
@@ -308,6 +323,7 @@ class RLEngine:
 
   def update_actor(self, train_ds, eval_ds, skip_jit=False):
     self._maybe_load_model_from_cpu(self.actor_trainer.model, Role.ACTOR)
+    self._anchor_ready()       # the snapshot of the old weights is complete before they change
     with self._perf.span_group("actor_training"):
       self.actor_trainer.train(train_ds, eval_ds, skip_jit)
     self._maybe_offload_model_to_cpu(self.actor_trainer.model, Role.ACTOR)
@@ -437,6 +453,7 @@ class RLEngine:
     p, c = self._place(prompt_tokens, model), self._place(completion_tokens, model)
     s, sp = self._place(segment_ids, model), self._place(segment_positions, model)
     outs = []
+    self._anchor_ready(host=True)
     with _swapped_params(model, self._anchor_policy_state):
       for sl in rl_utils.chunk_slices_by_size(B, mb):
         outs.append(common.compute_per_token_logps(
@@ -452,17 +469,47 @@ class RLEngine:
     lora = sft_utils.is_lora_enabled(model)
     params = {n: p for n, p in model.named_parameters() if (getattr(p, "is_lora", False) or not lora)}
     self.rollout.update_params(params, ("lora",) if lora else None)
-    pin = torch.cuda.is_available()
-    anchor = {}
-    for n, p in params.items():
-      t = torch.empty(p.shape, dtype=p.dtype, device="cpu", pin_memory=pin and p.is_cuda)
-      t.copy_(p.detach(), non_blocking=True)
-      anchor[n] = t
-    if torch.cuda.is_available():
-      torch.cuda.synchronize()
-    self._anchor_policy_state = anchor
+    self._snapshot_anchor(params)
     gc.collect()
     self.global_steps += 1
+
+  def _snapshot_anchor(self, params: Mapping[str, torch.Tensor]) -> None:
+    """Copies the start-of-step weights to pinned host buffers that are allocated once and reused.
+
+    On a GPU the copy runs on a side stream so the rollout that follows overlaps it; whoever changes
+    the weights next (`train`) or reads the snapshot first waits for it through `_anchor_ready`."""
+    bufs = self._anchor_policy_state or {}
+    cuda = any(p.is_cuda for p in params.values())
+    if not cuda:
+      self._anchor_policy_state = {n: p.detach().clone() for n, p in params.items()}
+      self._anchor_event = None
+      return
+    if getattr(self, "_anchor_stream", None) is None:
+      self._anchor_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    side = self._anchor_stream
+    side.wait_stream(main)
+    out = {}
+    with torch.cuda.stream(side):
+      for n, p in params.items():
+        t = bufs.get(n)
+        if t is None or t.shape != p.shape or t.dtype != p.dtype:
+          t = torch.empty(p.shape, dtype=p.dtype, device="cpu", pin_memory=True)
+        t.copy_(p.detach(), non_blocking=True)
+        out[n] = t
+      ev = torch.cuda.Event()
+      ev.record(side)
+    self._anchor_policy_state = out
+    self._anchor_event = ev
+
+  def _anchor_ready(self, host: bool = False) -> None:
+    ev = getattr(self, "_anchor_event", None)
+    if ev is None:
+      return
+    if host:
+      ev.synchronize()
+    else:
+      torch.cuda.current_stream().wait_event(ev)
 
   def get_values(self, prompt_tokens, completion_tokens, pad_id: int, eos_id: int):
     m = self.inference_worker.get_model("critic")
