@@ -38,6 +38,14 @@ def parse_args():
   ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
   ap.add_argument("--remat", default="auto", choices=["auto", "none", "block"])
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--workload", default="sft", choices=["sft", "grpo"],
+                  help="sft: Llama-3.1-8B full-weight SFT (default, the headline); grpo: Qwen3-8B GRPO step")
+  ap.add_argument("--grpo-prompts", type=int, default=64)
+  ap.add_argument("--grpo-generations", type=int, default=8)
+  ap.add_argument("--grpo-prompt-len", type=int, default=256)
+  ap.add_argument("--grpo-new-tokens", type=int, default=768)
+  ap.add_argument("--grpo-train-micro", type=int, default=1, help="prompts (x generations) per training micro-step")
+  ap.add_argument("--grpo-rollout-batch", type=int, default=512, help="sequences decoded together per rank")
   return ap.parse_args()
 
 
@@ -108,6 +116,10 @@ def main():
   args = parse_args()
   if args.impl == "reference":
     reference_arm(args)
+    return
+  if args.workload == "grpo":
+    from tunix_b200.rl import grpo_bench
+    grpo_bench.run(args, ClockSampler)
     return
 
   # micro-batches of 2 sequences need the allocator to grow segments in place: with fixed-size

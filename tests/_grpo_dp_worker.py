@@ -25,6 +25,7 @@ def main():
   from tunix_b200.rl import rl_cluster
   from tunix_b200.rl.grpo.grpo_learner import GRPOConfig, GRPOLearner
   from tests.test_rl_grpo import ToyTokenizer, prompts_ds, reward_len, toy_model
+  from tunix_b200.ops import _lib
 
   world = int(os.environ.get("WORLD_SIZE", "1"))
   rank = int(os.environ.get("RANK", "0"))
@@ -37,9 +38,16 @@ def main():
   dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if cuda else torch.device("cpu")
   if cuda:
     torch.cuda.set_device(dev)
-  kw = dict(dtype=torch.bfloat16) if cuda else {}
-  actor = toy_model(0, **kw).to(dev)
-  reference = toy_model(0, **kw).to(dev)
+  if cuda:
+    # large enough for every sm_100a kernel (head_dim 128 flash / paged decode, tcgen05 GEMM tiles)
+    from tunix_b200.models.transformer import ModelConfig, Transformer
+    mc = ModelConfig(num_layers=2, vocab_size=512, embed_dim=512, hidden_dim=1024, num_heads=4, head_dim=128,
+                     num_kv_heads=2, dtype=torch.bfloat16, max_position=64)
+    actor = Transformer(mc, device=dev).init_weights(seed=0, scale=0.05)
+    reference = Transformer(mc, device=dev).init_weights(seed=0, scale=0.05)
+  else:
+    actor = toy_model(0).to(dev)
+    reference = toy_model(0).to(dev)
   tc = RLTrainingConfig(actor_optimizer=optim.adamw(1e-2), eval_every_n_steps=100, max_steps=a.steps,
                         pbar_description=None, max_grad_norm=1.0)
   rc = RolloutConfig(max_tokens_to_generate=8, max_prompt_length=8, kv_cache_size=32, temperature=1.0, top_p=1.0,
@@ -55,6 +63,9 @@ def main():
   # every rank trains on its own prompts
   batches = list(prompts_ds(a.steps * world, batch=4))[rank::world]
   learner.train(batches)
+  if cuda:
+    torch.cuda.synchronize()
+    _lib.check_status()
   params = {n: p.detach().float().cpu() for n, p in cluster.actor_trainer.model.named_parameters()}
   moved = sum(float((params[n] - before[n]).abs().sum()) for n in params)
   checksum = torch.tensor([sum(float(p.double().sum()) for p in params.values())], dtype=torch.float64)

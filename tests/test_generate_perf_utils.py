@@ -157,3 +157,49 @@ def test_sanitize_and_trajectory_logger(tmp_path):
   assert files and any(f.endswith(".csv") for f in files)
   text = open(os.path.join(tmp_path, [f for f in files if f.endswith(".csv")][0])).read()
   assert "prompt" in text and "q" in text
+
+
+def test_math_grading_and_reward():
+  from tunix_b200.utils import math_rewards, math_utils
+  cases = [("\\frac{1}{2}", "0.5", True), ("1/2", "\\frac12", True), ("3", "3.0", True), ("(1,2)", "(1, 2)", True),
+           ("[1,2]", "(1,2)", False), ("2\\sqrt{3}", "\\sqrt{12}", True), ("10\\%", "10", True), ("x+1", "1+x", True),
+           ("1,000", "1000", True), ("5 \\text{ cm}", "5", True), ("7", "8", False),
+           ("\\frac{2}{4}", "\\frac{1}{2}", False), ("\\pi/2", "\\frac{\\pi}{2}", True),
+           ("0.\\overline{3}", "\\frac{1}{3}", True), ("(-\\infty,1]\\cup[2,3)", "[2,3)\\cup(-\\infty,1]", True),
+           ("\\frac{x+1}{2}", "(1+x)/2", True), ("7 \\frac{3}{4}", "31/4", True), ("-3", "3", False)]
+  for given, truth, want in cases:
+    assert math_rewards.is_correct(given, truth) == want, (given, truth)
+  assert math_utils.extract_answer("first \\boxed{1}, then \\boxed{\\frac{3}{4}}.") == "\\frac{3}{4}"
+  assert math_utils.extract_answer("no box here") is None
+  assert math_utils.last_boxed_only_string("\\boxed{a{b}c} tail") == "\\boxed{a{b}c}"
+  got = math_rewards.math_reward(["p"] * 4, ["<think>hm \\boxed{1}</think> thus \\boxed{42}", "no box", "\\boxed{41}",
+                                             ""], ["42", "1", ["40", "\\boxed{41}"], "3"])
+  assert got == [1.0, 0.0, 1.0, 0.0]
+
+
+def test_diffusion_batch_contract():
+  from tunix_b200 import diffusion
+  t = torch.tensor([[1, 2, -1], [3, 0, 5]])
+  w = torch.tensor([[1.0, 1.0, 0.0], [0.5, 0.0, 1.0]])
+  b = diffusion.DiffusionTokenBatch.create(model_inputs={"noisy": torch.zeros(2, 3, dtype=torch.long),
+                                                          "t": np.zeros((2,), np.float32)},
+                                           target_ids=t, loss_weights=w)
+  with pytest.raises(ValueError, match="active target_ids"):
+    diffusion.DiffusionTokenBatch.create(model_inputs={"x": torch.zeros(2, 3)}, target_ids=t,
+                                         loss_weights=torch.ones(2, 3))
+  with pytest.raises(ValueError, match="batch size"):
+    diffusion.DiffusionTokenBatch.create(model_inputs={"x": torch.zeros(3, 3)}, target_ids=t, loss_weights=w)
+  with pytest.raises(TypeError, match="integer"):
+    diffusion.DiffusionTokenBatch.create(model_inputs={"x": torch.zeros(2, 3)}, target_ids=t.float(), loss_weights=w)
+  with pytest.raises(ValueError, match="nonnegative"):
+    diffusion.DiffusionTokenBatch.create(model_inputs={"x": torch.zeros(2, 3)}, target_ids=t, loss_weights=-w)
+  emb = torch.nn.Embedding(8, 7)
+  fn = lambda model, inputs: model(inputs["noisy"])
+  logits = diffusion.compute_diffusion_logits(emb, b, fn)
+  assert logits.shape == (2, 3, 7)
+  with pytest.raises(ValueError, match="align"):
+    diffusion.compute_diffusion_logits(emb, b, lambda m, i: m(i["noisy"])[:, :2])
+  loss, denom = diffusion.masked_token_loss(emb, b, fn)
+  assert float(denom) == 3.5 and torch.isfinite(loss)
+  loss.backward()
+  assert emb.weight.grad is not None

@@ -35,3 +35,19 @@ def test_fsdp2_matches_single_gpu(kernel_lib, tmp_path, transport):
     rel = (p - q).norm() / (p.norm() + 1e-6)
     assert rel < 2e-2, (n, rel.item())
   assert abs(ref["loss"][-1] - got["loss"][-1]) < 0.05
+
+
+def test_grpo_data_parallel_two_gpus(kernel_lib, tmp_path):
+  """GRPO through RLCluster on 2 GPUs: sharded actor state, rollout on the trainer's replica."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  out = str(tmp_path / "grpo.pt")
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29613", os.path.join(HERE, "_grpo_dp_worker.py"), "--out", out,
+         "--device", "cuda"]
+  r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  got = torch.load(out, weights_only=False)
+  assert got["steps"] == 2 and got["moved"] > 0
+  assert abs(got["checksums"][0] - got["checksums"][1]) < 1e-6 * max(1.0, abs(got["checksums"][0]))

@@ -21,9 +21,15 @@ from .. import common
 from . import base_rollout, vanilla_rollout
 
 
+DEFAULT_MAX_BATCH = 512      # sequences decoded together; lower it when the KV cache must stay small
+DEFAULT_PAGE_SIZE = 64       # one TMA box per 64-key tile in the decode kernel
+
+
 class NativeRollout(base_rollout.BaseRollout):
   def __init__(self, model: torch.nn.Module, tokenizer: Any, rollout_config: base_rollout.RolloutConfig, mesh=None,
-               page_size: int = 16, max_batch: int = 512):
+               page_size: Optional[int] = None, max_batch: Optional[int] = None):
+    page_size = page_size or DEFAULT_PAGE_SIZE
+    max_batch = max_batch or DEFAULT_MAX_BATCH
     self._model = model
     self._tokenizer = tokenizer if isinstance(tokenizer, tok_adapter.TokenizerAdapter) else \
         tok_adapter.TokenizerAdapter(tokenizer)
