@@ -203,3 +203,64 @@ def test_diffusion_batch_contract():
   assert float(denom) == 3.5 and torch.isfinite(loss)
   loss.backward()
   assert emb.weight.grad is not None
+
+
+def test_perf_v2_timelines_tracer_and_writer(tmp_path):
+  import threading
+  from tunix_b200.perf import experimental as pv2
+  from tunix_b200.perf.experimental import constants, timeline_utils
+  from tunix_b200.perf.experimental.timeline import Span
+
+  tl = pv2.Timeline("host-1", 0.0)
+  a = tl.start_span("outer", 1.0, tags={constants.STEP: 1})
+  b = tl.start_span("inner", 2.0)
+  assert b.parent_id == a.id
+  tl.stop_span(3.0)
+  with pytest.raises(ValueError, match="before it began"):
+    tl.stop_span(0.5)
+  tl.start_span("dangling", 4.0)
+  tl.commit_step()                       # the open spans are purged, the finished one is kept
+  assert [s.name for s in tl.committed_steps[0].values()] == ["inner"]
+  with pytest.raises(ValueError, match="no more spans"):
+    tl.stop_span(9.0)
+
+  def mk(i, name, b, e):
+    s = Span(name=name, begin=b, id=i)
+    s.end = e
+    return s
+  active, queued = timeline_utils.sequentialize_overlapping_spans(
+      {0: mk(0, "a", 0.0, 4.0), 1: mk(1, "b", 1.0, 6.0), 2: mk(2, "c", 2.0, 3.0), 3: mk(3, "d", 7.0, 8.0)})
+  assert (active[0].begin, active[0].end) == (0.0, 4.0)
+  assert (active[1].begin, active[1].end) == (4.0, 6.0) and (queued[1].begin, queued[1].end) == (1.0, 4.0)
+  assert 2 not in active and (queued[2].begin, queued[2].end) == (2.0, 3.0)
+  assert 3 in active and 3 not in queued
+
+  done = threading.Event()
+
+  class Work:
+    def synchronize(self):
+      assert done.wait(5)
+
+  with pv2.PerfMetricsExport(trace_dir=str(tmp_path), role_to_devices={"actor": [0], "rollout": [0, 1]}) as exp:
+    tr = pv2.PerfTracer(devices=[0, 1], export_fn=exp.export_metrics)
+    for step in range(2):
+      with tr.span(constants.ROLLOUT, devices=[0, 1], tags={constants.STEP: step}) as wl:
+        wl.async_end(Work())
+      with tr.span(constants.PEFT_TRAIN, devices=[0], tags={constants.STEP: step}):
+        time.sleep(0.002)
+      done.set()
+      assert tr.export() == {}
+    assert set(tr.all_devices) == {"cuda0", "cuda1"}
+    tls = tr._get_timelines()
+    assert len(tls["cuda0"].committed_steps) == 2
+    names = [s.name for s in tls["cuda0"].committed_steps[0].values()]
+    assert constants.ROLLOUT in names
+  doc = json.load(open(exp.writer.path))
+  ev = [e for e in doc["traceEvents"] if e["ph"] == "X"]
+  assert any(e["name"].startswith("rollout [step=0") for e in ev)
+  procs = {e["args"]["name"] for e in doc["traceEvents"] if e.get("name") == "process_name"}
+  assert "host" in procs and "actor/rollout" in procs and "rollout" in procs
+  noop = pv2.NoopTracer()
+  with noop.span("x", devices=[0]) as wl:
+    wl.async_end(None)
+  assert noop.export() == {}
