@@ -104,7 +104,24 @@ def require():
   return lib
 
 
+_HOME_DEVICE = None    # one process drives one GPU: the device current when the first kernel is launched
+
+
+def bind_thread() -> None:
+  """Makes this host thread use the process's GPU.
+
+  The CUDA current device is per thread and starts at 0, so a helper thread of rank r (a rollout
+  producer, an asyncio loop) would otherwise launch on GPU 0 with pointers that live on GPU r."""
+  global _HOME_DEVICE
+  cur = torch.cuda.current_device()
+  if _HOME_DEVICE is None:
+    _HOME_DEVICE = cur
+  elif cur != _HOME_DEVICE:
+    torch.cuda.set_device(_HOME_DEVICE)
+
+
 def stream_ptr() -> int:
+  bind_thread()
   return torch.cuda.current_stream().cuda_stream
 
 

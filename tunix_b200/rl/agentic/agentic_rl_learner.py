@@ -150,10 +150,20 @@ class AgenticRLLearner(abc.ABC, Generic[TConfig]):
     # the rollout side lives on its own event loop thread
     ready: "queue.Queue" = queue.Queue()
 
+    try:
+      home = next(self.rl_engine.actor_trainer.model.parameters()).device
+    except (StopIteration, AttributeError):
+      home = None
+
+    def bind():     # helper threads start on CUDA device 0; they must use this rank's GPU
+      if home is not None and home.type == "cuda":
+        torch.cuda.set_device(home)
+
     def run_loop():
+      bind()
       loop = asyncio.new_event_loop()
       asyncio.set_event_loop(loop)
-      loop.set_default_executor(ThreadPoolExecutor(max_workers=algo_config.max_concurrency + 1))
+      loop.set_default_executor(ThreadPoolExecutor(max_workers=algo_config.max_concurrency + 1, initializer=bind))
       ready.put(loop)
       loop.run_forever()
     self._loop_thread = threading.Thread(target=run_loop, daemon=True, name="agentic-rollout-loop")

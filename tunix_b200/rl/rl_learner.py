@@ -45,6 +45,20 @@ def _repeat_tree(example: TrainingInputT, n: int) -> TrainingInputT:
   return out
 
 
+
+def sft_utils_device(model) -> Optional[torch.device]:
+  try:
+    return next(model.parameters()).device
+  except StopIteration:
+    return None
+
+
+def _bind_producer_thread(device) -> None:
+  """The rollout producer thread launches kernels: it must use the trainer's GPU, not device 0."""
+  if device is not None and device.type == "cuda":
+    torch.cuda.set_device(device)
+
+
 class RLLearner(abc.ABC):
 
   def __init__(self, rl_engine: Optional[rl_engine_lib.RLEngine] = None, algo_config: Any = None,
@@ -73,7 +87,8 @@ class RLLearner(abc.ABC):
                                                                self.rl_engine.rollout.model())
     r2m = self.rl_engine.cluster_config.role_to_mesh
     self.can_enable_async_rollout = r2m.get(Role.ACTOR) != r2m.get(Role.ROLLOUT)
-    self.executor = futures.ThreadPoolExecutor(max_workers=1)
+    self.executor = futures.ThreadPoolExecutor(max_workers=1, initializer=_bind_producer_thread,
+                                               initargs=(sft_utils_device(self.rl_engine.actor_trainer.model),))
     self._last_iter_step = self.rl_engine.actor_trainer.iter_steps
     self._rollout_micro_batch_size = self._training_config.rollout_micro_batch_size
     self._compute_logps_micro_batch_size = self._training_config.compute_logps_micro_batch_size
