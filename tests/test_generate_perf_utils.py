@@ -264,3 +264,48 @@ def test_perf_v2_timelines_tracer_and_writer(tmp_path):
   with noop.span("x", devices=[0]) as wl:
     wl.async_end(None)
   assert noop.export() == {}
+
+
+def test_image_and_audio_processors():
+  import types as pytypes
+  from tunix_b200.processors import audio_processor as ap, image_processor as ip
+  cfg = pytypes.SimpleNamespace(image_height=8, image_width=12, image_channels=3, image_mean=(127.5,) * 3,
+                                image_std=(127.5,) * 3)
+  proc = ip.ImageProcessor(cfg)
+  rng = np.random.default_rng(0)
+  img = rng.integers(0, 255, (20, 30, 3), dtype=np.uint8)
+  out = proc([[img, img], None, img])
+  assert len(out) == 3 and all(len(s) == 2 for s in out)
+  assert out[0][0].shape == (8, 12, 3) and out[0][0].min() >= -1 and out[0][0].max() <= 1
+  assert not out[1][0].any() and not out[2][1].any()
+  # variable resolution: sides are multiples of pool*patch and patches fit the budget
+  th, tw = ip.get_target_dimensions(480, 640, 16, 90, 3)
+  assert th % 48 == 0 and tw % 48 == 0 and (th // 16) * (tw // 16) <= 90
+  assert ip.get_target_dimensions(4, 4000, 16, 90, 3)[0] == 48
+  patches, xy = ip.patchify(np.arange(2 * 4 * 6 * 3, dtype=np.float32).reshape(2, 4, 6, 3), 2)
+  assert patches.shape == (2, 6, 12) and xy.shape == (2, 6, 2) and xy[0, 4].tolist() == [1, 1]
+  assert patches[0, 1, :3].tolist() == [6.0, 7.0, 8.0]          # second patch starts at pixel (0, 2)
+  toks = np.array([[5, 258880, 7, 258880]])
+  exp = ip.add_variable_extra_tokens_for_images(toks, soft_token_counts=[2, 1])
+  assert exp[0].tolist() == [5, 108, 255999, -2, -2, 258882, 108, 7, 108, 255999, -2, 258882, 108]
+  enc = pytypes.SimpleNamespace(config=pytypes.SimpleNamespace(patch_size=16, num_mm_tokens_per_image=4,
+                                                               pooling_kernel_size=3))
+  big = rng.integers(0, 255, (200, 300, 3), dtype=np.uint8)
+  (P, XY), new_tokens = ip.process_gemma4_inputs([[big], []], [np.array([1, 258880]), np.array([2, 3])], enc, 0)
+  assert P.shape[0] == 2 and P.shape[2] == 768 and XY.shape[:2] == P.shape[:2]
+  assert (XY[1] == -1).all() and len(new_tokens[0]) == len(new_tokens[1])
+  n_soft = int((new_tokens[0] == -2).sum())
+  assert 1 <= n_soft <= 4
+
+  tok = pytypes.SimpleNamespace(sample_rate=16000, get_num_soft_tokens=lambda n: n // 640)
+  a1, a2 = np.ones(6400, np.float32), np.ones(3200, np.float32)
+  audio, new_tokens = ap.process_gemma4_inputs([a1, [a2, a1], []],
+                                               [np.array([1, 258881]), np.array([258881, 9, 258881]), np.array([4])],
+                                               tok, max_audio_length=8000, max_audio_clips=2)
+  assert audio.waveforms.shape == (3, 2, 8000) and audio.lengths.tolist() == [[6400, 0], [3200, 6400], [0, 0]]
+  assert audio.soft_token_counts == ((10,), (5, 10), ())
+  assert int((new_tokens[1] == ap.AUDIO_SOFT_TOKEN_PLACEHOLDER).sum()) == 15
+  with pytest.raises(ValueError, match="more clips"):
+    ap.process_gemma4_inputs([[a1, a1, a1]], [np.array([258881] * 3)], tok, max_audio_clips=2)
+  with pytest.raises(ValueError, match="placeholders"):
+    ap.process_gemma4_inputs([a1], [np.array([1, 2])], tok)
