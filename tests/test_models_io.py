@@ -119,3 +119,41 @@ def test_automodel_dummy_and_local_path(tmp_path):
     automodel.AutoModel.from_pretrained("Qwen/Qwen3-0.6B", model_source=automodel.ModelSource.GCS)
   with pytest.raises(FileNotFoundError):
     automodel.download_model("/nonexistent/dir", None, automodel.ModelSource.INTERNAL)
+
+
+def test_mapping_config_matches_hf_export(tmp_path):
+  """The declarative mapping reproduces the exporter's names and tensors, dense and MoE."""
+  from tunix_b200.generate import mappings
+  from tunix_b200.models import safetensors_saver
+  from tunix_b200.models.transformer import ModelConfig, Transformer
+  for moe in (False, True):
+    kw = dict(num_experts=4, num_experts_per_tok=2, moe_hidden_dim=16) if moe else {}
+    cfg = ModelConfig(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=4, head_dim=8,
+                      num_kv_heads=2, use_qk_norm=True, **kw)
+    model = Transformer(cfg).init_weights(seed=0)
+    want = safetensors_saver.to_hf_state(model)
+    mc = mappings.MappingConfig.build(model=model)
+    got = mappings.apply(mc, {n: p.detach() for n, p in model.named_parameters()})
+    assert set(got) == set(want)
+    for k in want:
+      assert torch.equal(got[k], want[k]), k
+  again = mappings.MappingConfig.build(mapping_obj={"to_hf_mappings": lambda: {"a": ("b", None)}})
+  assert again.to_hf_mappings == {"a": ("b", None)}
+  assert mappings.MappingConfig.build(mapping_obj=again) is again
+  with pytest.raises(KeyError):
+    mappings.apply(again, {"zzz": torch.zeros(1)})
+
+
+def test_script_utils_datasets(tmp_path):
+  import json
+  from tunix_b200.utils import script_utils
+  recs = [{"question": f"q{i}", "answer": f"blah #### {i}"} for i in range(10)]
+  (tmp_path / "train.jsonl").write_text("\n".join(json.dumps(r) for r in recs))
+  tr, ev = script_utils.get_train_and_eval_datasets(
+      str(tmp_path), "train", seed=1, system_prompt="SYS ", batch_size=2, num_batches=4, train_fraction=0.5,
+      num_epochs=2, answer_extractor=lambda s: s.split("####")[1].strip())
+  tb, eb = list(tr), list(ev)
+  assert len(tb) == 4 and len(eb) == 4            # 2 batches x 2 epochs each
+  assert tb[0]["prompts"][0].startswith("SYS q") and tb[0]["answer"][0].isdigit()
+  with script_utils.profile_and_capture_log("t", enable_profile=False):
+    pass
