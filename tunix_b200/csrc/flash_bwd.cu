@@ -40,6 +40,10 @@ struct BwdParams {
   int B, N, Kh, Lq, Lk, causal;
   float scale, scale_log2;
   int* status;
+  // Packed sequences (optional, Lq == Lk): first / last token index of each token's segment, [B, Lq].
+  // Key k is visible to query q when seg_lo[q] <= k <= (causal ? q : seg_hi[q]).
+  const int* seg_lo;
+  const int* seg_hi;
 };
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -116,7 +120,7 @@ constexpr int kKBytes = kKeys * kHD * 2;       // 32 KiB, two [128 x 64] sub-til
 constexpr int kQBytes = kQT * kHD * 2;         // 16 KiB, two [64 x 64] sub-tiles
 constexpr int kPBytes = kKeys * kQT * 2;       // 16 KiB
 constexpr int kTileBytes = 2 * kKBytes + 4 * kQBytes + 2 * kPBytes;   // 163840
-constexpr int kVecBytes = 2 * 2 * kQT * 4;     // lse and delta, two buffers
+constexpr int kVecBytes = 4 * 2 * kQT * 4;     // lse, delta, segment lo and hi; two buffers each
 constexpr int kSmemBytes = kTileBytes + kVecBytes + 256 + 1024;
 constexpr int kTmemCols = 512;                 // [S^T dP^T] x 2 | dK | dV
 }  // namespace dkv
@@ -136,6 +140,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t sPT = sDO + 2 * kQBytes, sDST = sPT + kPBytes;
   float* sLse = reinterpret_cast<float*>(gen + kTileBytes);       // [2][64]
   float* sDelta = sLse + 2 * kQT;                                  // [2][64]
+  int* sLo = reinterpret_cast<int*>(sDelta + 2 * kQT);             // [2][64]
+  int* sHi = sLo + 2 * kQT;                                        // [2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kTileBytes + kVecBytes);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_kv = bar0;
@@ -151,9 +157,16 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const int g = p.N / p.Kh;
   const int off = p.Lk - p.Lq;
   const int nqt = (p.Lq + kQT - 1) / kQT;
-  int i_start = 0;
+  int i_start = 0, i_end = nqt;
   if (p.causal) i_start = max(0, k0 - off) / kQT;
-  const int per_head = max(0, nqt - i_start);
+  const bool packed = p.seg_lo != nullptr;
+  if (packed) {
+    const long long rb = static_cast<long long>(b) * p.Lq;
+    // queries past the segment of this tile's last key see none of its keys
+    i_end = min(nqt, p.seg_hi[rb + min(k0 + kKeys, p.Lk) - 1] / kQT + 1);
+    if (!p.causal) i_start = p.seg_lo[rb + k0] / kQT;
+  }
+  const int per_head = max(0, i_end - i_start);
   const int n_it = per_head * g;
 
   if (threadIdx.x == 0) {
@@ -274,8 +287,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (t128 < 64) {
           float v = qi < p.Lq ? p.lse[idx] : INFINITY;
           sLse[st * kQT + c] = (v == -INFINITY) ? INFINITY : v * kLog2e;
+          sLo[st * kQT + c] = (packed && qi < p.Lq) ? p.seg_lo[static_cast<long long>(b) * p.Lq + qi] : 0;
         } else {
           sDelta[st * kQT + c] = qi < p.Lq ? p.delta[idx] : 0.f;
+          sHi[st * kQT + c] = (packed && qi < p.Lq) ? p.seg_hi[static_cast<long long>(b) * p.Lq + qi] : p.Lk - 1;
         }
       }
       // the 128 row threads meet on a bounded barrier (a hardware bar.sync could not time out)
@@ -286,7 +301,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       if (!ok) break;
       tc_fence_after();
       uint32_t pk[32], dk_[32];
-      const bool need_mask = (p.causal && k0 + kKeys - 1 > q0 + off) || (k0 + kKeys > p.Lk);
+      const bool need_mask = packed || (p.causal && k0 + kKeys - 1 > q0 + off) || (k0 + kKeys > p.Lk);
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint32_t ts[32], td[32];
@@ -300,7 +315,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
           for (int e = 0; e < 2; ++e) {
             const int c = half * 32 + i + e;
             float pe = exp2f(__uint_as_float(ts[i + e]) * p.scale_log2 - sLse[st * kQT + c]);
-            if (need_mask && ((p.causal && kj > q0 + c + off) || kj >= p.Lk)) pe = 0.f;
+            if (need_mask && ((p.causal && kj > q0 + c + off) || kj >= p.Lk || kj < sLo[st * kQT + c] ||
+                              kj > sHi[st * kQT + c]))
+              pe = 0.f;
             pv[e] = pe;
             dv[e] = pe * (__uint_as_float(td[i + e]) - sDelta[st * kQT + c]);
           }
@@ -383,7 +400,13 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int off = p.Lk - p.Lq;
   int kv_end = p.Lk;
   if (p.causal) kv_end = min(p.Lk, q0 + kBM + off);
-  const int n_tiles = kv_end > 0 ? (kv_end + kBN - 1) / kBN : 0;
+  int j0 = 0;
+  if (p.seg_lo != nullptr) {
+    const long long rb = static_cast<long long>(b) * p.Lq;
+    j0 = p.seg_lo[rb + q0] / kBN;
+    if (!p.causal) kv_end = min(p.Lk, p.seg_hi[rb + min(q0 + kBM, p.Lq) - 1] + 1);
+  }
+  const int n_tiles = kv_end > j0 * kBN ? (kv_end + kBN - 1) / kBN - j0 : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -422,7 +445,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tma_load_2d(sDO + kBM * 128, &map_do, h * kHD + 64, qrow, bar_q);
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
-        const int krow = b * p.Lk + j * kBN;
+        const int krow = b * p.Lk + (j0 + j) * kBN;
         if (!mbar_wait(bar_kvempty + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag)) {
           atomicOr(p.status, kStatusWaitTimeoutProducer);
           break;
@@ -491,15 +514,20 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       lse2 = (v == -INFINITY) ? INFINITY : v * kLog2e;
       delta = p.delta[idx];
     }
+    int row_lo = 0, row_hi = p.Lk - 1;
+    if (p.seg_lo != nullptr && qi < p.Lq) {
+      row_lo = p.seg_lo[static_cast<long long>(b) * p.Lq + qi];
+      row_hi = p.seg_hi[static_cast<long long>(b) * p.Lq + qi];
+    }
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * st, (j >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      const int k0 = j * kBN;
-      const int limit = p.causal ? min(qi + off, p.Lk - 1) : p.Lk - 1;
-      const bool need_mask = k0 + kBN - 1 > limit;
+      const int k0 = (j0 + j) * kBN;
+      const int limit = p.causal ? min(qi + off, row_hi) : row_hi;
+      const bool need_mask = k0 + kBN - 1 > limit || k0 < row_lo;
       uint32_t dsk[32];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -513,7 +541,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             float pe = exp2f(__uint_as_float(ts[i + e]) * p.scale_log2 - lse2);
-            if (need_mask && k0 + half * 32 + i + e > limit) pe = 0.f;
+            if (need_mask && (k0 + half * 32 + i + e > limit || k0 + half * 32 + i + e < row_lo)) pe = 0.f;
             dv[e] = pe * (__uint_as_float(td[i + e]) - delta);
           }
           dsk[half * 16 + (i >> 1)] = pack2(dv[0], dv[1]);
@@ -556,7 +584,16 @@ extern "C" int tx_flash_bwd(const void* q, const void* k, const void* v, const v
                             const float* lse, float* delta, void* dq_out, void* dk_out, void* dv_out, int B, int N,
                             int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk, long long ldv,
                             long long ldo, long long lddo, long long lddq, long long lddk, long long lddv,
-                            int causal, float scale, int* status, cudaStream_t stream) {
+                            int causal, float scale, int* status, cudaStream_t stream);
+
+// As tx_flash_bwd for packed rows (seg_lo / seg_hi int32 [B, Lq], both or neither; need Lq == Lk).
+extern "C" int tx_flash_bwd_seg(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                const float* lse, float* delta, void* dq_out, void* dk_out, void* dv_out, int B,
+                                int N, int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk,
+                                long long ldv, long long ldo, long long lddo, long long lddq, long long lddk,
+                                long long lddv, int causal, float scale, const int* seg_lo, const int* seg_hi,
+                                int* status, cudaStream_t stream) {
+  if ((seg_lo == nullptr) != (seg_hi == nullptr) || (seg_lo != nullptr && Lq != Lk)) return 1;
   if (head_dim != kHD || B <= 0 || N <= 0 || Kh <= 0 || N % Kh != 0 || Lq <= 0 || Lk <= 0) return 1;
   if ((ldq | ldk | ldv | ldo | lddo | lddq | lddk | lddv) % 8 != 0) return 1;
   const uint64_t rq = static_cast<uint64_t>(B) * Lq, rk = static_cast<uint64_t>(B) * Lk;
@@ -590,6 +627,8 @@ extern "C" int tx_flash_bwd(const void* q, const void* k, const void* v, const v
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.status = status;
+  p.seg_lo = seg_lo;
+  p.seg_hi = seg_hi;
   p.out0 = static_cast<__nv_bfloat16*>(dk_out);
   p.out1 = static_cast<__nv_bfloat16*>(dv_out);
   p.ld0 = lddk;
@@ -603,4 +642,13 @@ extern "C" int tx_flash_bwd(const void* q, const void* k, const void* v, const v
   dim3 gq((Lq + dq::kBM - 1) / dq::kBM, N, B);
   flash_bwd_dq_kernel<<<gq, kThreads, dq::kSmemBytes, stream>>>(q128, do128, k64, v64, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+extern "C" int tx_flash_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                            const float* lse, float* delta, void* dq_out, void* dk_out, void* dv_out, int B, int N,
+                            int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk, long long ldv,
+                            long long ldo, long long lddo, long long lddq, long long lddk, long long lddv,
+                            int causal, float scale, int* status, cudaStream_t stream) {
+  return tx_flash_bwd_seg(q, k, v, o, d_o, lse, delta, dq_out, dk_out, dv_out, B, N, Kh, Lq, Lk, head_dim, ldq, ldk,
+                          ldv, ldo, lddo, lddq, lddk, lddv, causal, scale, nullptr, nullptr, status, stream);
 }

@@ -48,6 +48,10 @@ struct FlashParams {
   int causal;
   float scale_log2;   // softmax scale * log2(e)
   int* status;
+  // Packed sequences (optional, need Lq == Lk): per token the first and last index of its segment.
+  // Key k is visible to query q when seg_lo[q] <= k <= (causal ? q : seg_hi[q]).
+  const int* seg_lo;
+  const int* seg_hi;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -89,7 +93,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
   const int off = p.Lk - p.Lq;
   int kv_end = p.Lk;
   if (p.causal) kv_end = min(p.Lk, q0 + kBM + off);
-  const int n_tiles = kv_end > 0 ? (kv_end + kBN - 1) / kBN : 0;
+  int j0 = 0;                                   // first key tile any row of this CTA can see
+  if (p.seg_lo != nullptr) {
+    const long long rb = static_cast<long long>(b) * p.Lq;
+    j0 = p.seg_lo[rb + q0] / kBN;               // seg_lo is non-decreasing along the sequence
+    if (!p.causal) kv_end = min(p.Lk, p.seg_hi[rb + min(q0 + kBM, p.Lq) - 1] + 1);
+  }
+  const int n_tiles = kv_end > j0 * kBN ? (kv_end + kBN - 1) / kBN - j0 : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -128,7 +138,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       for (int j = 0; j < n_tiles; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int krow = b * p.Lk + j * kBN;
+        const int krow = b * p.Lk + (j0 + j) * kBN;
         if (!mbar_wait(bar_kempty + 8 * st, ph ^ 1, abort_flag)) {
           atomicOr(p.status, kStatusWaitTimeoutProducer);
           break;
@@ -199,6 +209,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    int row_lo = 0, row_hi = p.Lk - 1;            // this row's segment (whole sequence without packing)
+    if (p.seg_lo != nullptr && qi < p.Lq) {
+      row_lo = p.seg_lo[static_cast<long long>(b) * p.Lq + qi];
+      row_hi = p.seg_hi[static_cast<long long>(b) * p.Lq + qi];
+    }
     for (int j = 0; j < n_tiles; ++j) {
       const int st = j & 1;
       // every decision that guards a warp-collective TMEM access is made warp-uniform
@@ -219,12 +234,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(bar_sempty + 8 * st);
-      const int k0 = j * kBN;
-      const int limit = p.causal ? min(qi + off, p.Lk - 1) : p.Lk - 1;   // last visible key
+      const int k0 = (j0 + j) * kBN;
+      const int limit = p.causal ? min(qi + off, row_hi) : row_hi;       // last visible key
       if (k0 + kBN - 1 > limit) {
 #pragma unroll
         for (int i = 0; i < kBN; ++i)
           if (k0 + i > limit) s[i] = -INFINITY;
+      }
+      if (k0 < row_lo) {                                                 // keys of earlier segments
+#pragma unroll
+        for (int i = 0; i < kBN; ++i)
+          if (k0 + i < row_lo) s[i] = -INFINITY;
       }
       float mt = s[0];
 #pragma unroll
@@ -325,7 +345,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
 // Returns 0, 1 for an unsupported shape, 3xx for a tensor-map failure, 400 for a refused launch.
 extern "C" int tx_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N,
                             int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk, long long ldv,
-                            long long ldo, int causal, float scale, int* status, cudaStream_t stream) {
+                            long long ldo, int causal, float scale, int* status, cudaStream_t stream);
+
+// As tx_flash_fwd, for packed rows: seg_lo / seg_hi are int32 [B, Lq] (first / last token index of each
+// token's segment, both nullptr for unpacked rows); they need Lq == Lk.
+extern "C" int tx_flash_fwd_seg(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N,
+                                int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk, long long ldv,
+                                long long ldo, int causal, float scale, const int* seg_lo, const int* seg_hi,
+                                int* status, cudaStream_t stream) {
+  if ((seg_lo == nullptr) != (seg_hi == nullptr) || (seg_lo != nullptr && Lq != Lk)) return 1;
   if (head_dim != kHD || B <= 0 || N <= 0 || Kh <= 0 || N % Kh != 0 || Lq <= 0 || Lk <= 0) return 1;
   if ((ldq | ldk | ldv | ldo) % 8 != 0) return 1;
   CUtensorMap mq, mk, mv;
@@ -348,7 +376,16 @@ extern "C" int tx_flash_fwd(const void* q, const void* k, const void* v, void* o
   p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.seg_lo = seg_lo;
+  p.seg_hi = seg_hi;
   dim3 grid((Lq + kBM - 1) / kBM, N, B);
   flash_fwd_kernel<<<grid, kThreads, kSmemBytes, stream>>>(mq, mk, mv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+extern "C" int tx_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int N,
+                            int Kh, int Lq, int Lk, int head_dim, long long ldq, long long ldk, long long ldv,
+                            long long ldo, int causal, float scale, int* status, cudaStream_t stream) {
+  return tx_flash_fwd_seg(q, k, v, o, lse, B, N, Kh, Lq, Lk, head_dim, ldq, ldk, ldv, ldo, causal, scale, nullptr,
+                          nullptr, status, stream);
 }

@@ -240,6 +240,9 @@ class Attention(nn.Module):
 
     mask = attn_mask
     causal = mask is None and cache is None
+    if mask is not None and not isinstance(mask, torch.Tensor) and (
+        cache is not None or (self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size)):
+      mask = mask.dense()
     if self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size:
       mask = _apply_sliding_window(mask, positions, k.shape[1], cfg.sliding_window_size, cache is not None)
       causal = False
@@ -368,7 +371,7 @@ class DecoderLayer(nn.Module):
     if self.cfg.fused_layers and torch.is_grad_enabled():
       from ..ops import fused_layer
       if fused_layer.eligible(self, h, cache, attn_mask):
-        return fused_layer.run(self, h, positions), None
+        return fused_layer.run(self, h, positions, attn_mask), None
     x = self.input_layernorm(h)
     a, new_cache = self.attn(x, positions, cache, attn_mask, layer_name)
     if self.post_attn_norm is not None:
@@ -462,11 +465,9 @@ class Transformer(nn.Module):
     if positions is None:
       positions = torch.arange(L, device=input_tokens.device)[None].expand(B, L)
     if segment_ids is not None:
-      seg = segment_ids
-      same = seg[:, :, None] == seg[:, None, :]
-      tri = torch.ones(L, L, dtype=torch.bool, device=seg.device).tril()[None]
-      seg_mask = same & tri & (seg[:, :, None] != 0)
-      attention_mask = seg_mask if attention_mask is None else (attention_mask & seg_mask)
+      from ..ops import attention as attn_ops
+      seg_mask = attn_ops.SegmentMask(segment_ids)      # symbolic: the flash kernels take segment bounds
+      attention_mask = seg_mask if attention_mask is None else (attention_mask & seg_mask.dense())
     h = self.embedder.encode(input_tokens)
     if cfg.remat_config == RematConfig.DECODER and torch.is_grad_enabled() and cache is None:
       h = torch_ckpt.checkpoint(lambda hh: self._stack(hh, positions, None, attention_mask)[0], h, use_reentrant=False)

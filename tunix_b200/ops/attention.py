@@ -19,10 +19,41 @@ import torch.nn.functional as F
 from . import flash
 
 
-def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, scale: float) -> Tuple[torch.Tensor, Any]:
-  """Returns (o [B,T,N,H] contiguous, ctx for `flash_bwd`)."""
+class SegmentMask:
+  """Causal attention restricted to contiguous segments of packed rows, kept symbolic.
+
+  It travels where a dense [B, T, S] mask would; the sm_100a kernels consume the (first, last)
+  bounds directly, every other path asks for `dense()` (built once). Query rows of padding
+  (segment id 0) see nothing in the dense form and only themselves in the kernels; both are
+  excluded from losses."""
+
+  def __init__(self, segment_ids: torch.Tensor):
+    self.segment_ids = segment_ids
+    self._dense = None
+    self._bounds = None
+
+  def bounds(self):
+    if self._bounds is None:
+      self._bounds = flash.segment_bounds(self.segment_ids)
+    return self._bounds
+
+  def dense(self) -> torch.Tensor:
+    if self._dense is None:
+      seg = self.segment_ids
+      L = seg.shape[1]
+      tri = torch.ones(L, L, dtype=torch.bool, device=seg.device).tril()[None]
+      self._dense = (seg[:, :, None] == seg[:, None, :]) & tri & (seg[:, :, None] != 0)
+    return self._dense
+
+
+def flash_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool, scale: float,
+              segments=None) -> Tuple[torch.Tensor, Any]:
+  """Returns (o [B,T,N,H] contiguous, ctx for `flash_bwd`). `segments`: bounds of a `SegmentMask`
+  (only with the sm_100a kernel; callers check `flash.supported` first)."""
   if flash.supported(q, k, v, None, causal):
-    return flash.forward(q, k, v, causal=causal, scale=scale)
+    return flash.forward(q, k, v, causal=causal, scale=scale, segments=segments)
+  if segments is not None:
+    raise ValueError("packed segments need the sm_100a flash kernel (bf16, head_dim 128)")
   qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
   rep = qt.shape[1] // kt.shape[1]
   try:
@@ -61,6 +92,11 @@ def flash_bwd(do: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
 
 def attention_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: Optional[torch.Tensor],
                    causal: bool, scale: float) -> torch.Tensor:
+  if isinstance(mask, SegmentMask):
+    if q.shape[1] == k.shape[1] and flash.supported(q, k, v, None, True):
+      lo, hi = mask.bounds()
+      return flash._FlashFn.apply(q, k, v, True, scale, lo, hi)
+    mask = mask.dense()
   if flash.supported(q, k, v, mask, causal):
     return flash.flash_attention(q, k, v, causal=causal, scale=scale)
   qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)

@@ -289,6 +289,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: Option
   if q.is_cuda and q.dtype in (bf16, torch.float16) and softcap == 0.0:
     from . import attention as _attn
     return _attn.attention_cuda(q, k, v, mask=mask, causal=causal, scale=scale)
+  if mask is not None and not isinstance(mask, torch.Tensor):
+    mask = mask.dense()          # a symbolic segment mask
   if mask is None and causal:
     T, S = q.shape[1], k.shape[1]
     mask = torch.ones(T, S, dtype=torch.bool, device=q.device).tril(S - T)[None].expand(q.shape[0], T, S)

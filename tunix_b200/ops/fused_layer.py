@@ -19,6 +19,7 @@ from typing import Optional
 import torch
 
 from . import attention as attn_ops
+from . import flash as flash_lib
 from . import kernels
 
 bf16 = torch.bfloat16
@@ -48,7 +49,8 @@ def _vec_grad(dw_fp32: torch.Tensor, w: torch.Tensor):
 class DecoderLayerFn(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, h, positions, table, w_in, w_qkv, w_o, w_post, w_gu, w_d, wq_norm, wk_norm, cfg):
+  def forward(ctx, h, positions, table, w_in, w_qkv, w_o, w_post, w_gu, w_d, wq_norm, wk_norm, cfg,
+              segments=None):
     B, T, D = h.shape
     N, K, H = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
     eps, off = cfg.norm_eps, cfg.norm_offset
@@ -62,7 +64,7 @@ class DecoderLayerFn(torch.autograd.Function):
       qkv_pre = None
     q4 = qkv.view(B, T, N + 2 * K, H)
     o, attn_ctx = attn_ops.flash_fwd(q4[:, :, :N], q4[:, :, N:N + K], q4[:, :, N + K:], causal=True,
-                                     scale=cfg.attn_scale)
+                                     scale=cfg.attn_scale, segments=segments)
     o2 = o.reshape(B * T, N * H)
     a = kernels.gemm(o2, w_o)
     x2, h_mid, rstd2 = kernels.rmsnorm_fwd(a, w_post, eps, off, residual=h2d)
@@ -135,14 +137,18 @@ class DecoderLayerFn(torch.autograd.Function):
     dh, dw_in = kernels.rmsnorm_bwd(h2d, w_in, dx1, rstd1, eps, off, dres=dh_mid, dw_out=mg,
                                     dw_accumulate=mg is not None)
     g_win = None if mg is not None else dw_in.to(w_in.dtype)
-    return (dh.view(B, T, D), None, None, g_win, g_wqkv, g_wo, g_wpost, g_wgu, g_wd, g_wq, g_wk, None)
+    return (dh.view(B, T, D), None, None, g_win, g_wqkv, g_wo, g_wpost, g_wgu, g_wd, g_wq, g_wk, None, None)
 
 
 def eligible(layer, h: torch.Tensor, cache, attn_mask) -> bool:
   """True when `layer` (a models.transformer.DecoderLayer) can run as the fused node."""
   cfg = layer.cfg
-  if not (h.is_cuda and h.dtype == bf16 and cache is None and attn_mask is None):
+  if not (h.is_cuda and h.dtype == bf16 and cache is None):
     return False
+  if attn_mask is not None:
+    # packed rows run fused when the flash kernel takes the segment bounds (head_dim 128)
+    if not (isinstance(attn_mask, attn_ops.SegmentMask) and cfg.head_dim == 128 and flash_lib._DISABLED is False):
+      return False
   if cfg.is_moe or cfg.qkv_bias or cfg.use_post_attn_norm or cfg.use_post_ffw_norm or cfg.attn_logits_soft_cap:
     return False
   if cfg.sliding_window_size and layer.attn.attn_type.name == "LOCAL_SLIDING":
@@ -158,7 +164,7 @@ def eligible(layer, h: torch.Tensor, cache, attn_mask) -> bool:
   return True
 
 
-def run(layer, h: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+def run(layer, h: torch.Tensor, positions: torch.Tensor, attn_mask=None) -> torch.Tensor:
   from .functional import rope_table
   cfg = layer.cfg
   a, m = layer.attn, layer.mlp
@@ -169,4 +175,5 @@ def run(layer, h: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
   wq = a.q_norm.w if a.q_norm is not None else None
   wk = a.k_norm.w if a.k_norm is not None else None
   return DecoderLayerFn.apply(h.contiguous(), pos, table, layer.input_layernorm.w, a.qkv_proj.w, a.o_proj.w,
-                              layer.post_attention_layernorm.w, m.gate_up_proj.w, m.down_proj.w, wq, wk, cfg)
+                              layer.post_attention_layernorm.w, m.gate_up_proj.w, m.down_proj.w, wq, wk, cfg,
+                              attn_mask.bounds() if attn_mask is not None else None)
