@@ -2,7 +2,7 @@
 //
 //   C[M,N] (+)= alpha * A[M,K] * B[N,K]^T        (fp32 accumulation in TMEM)
 //
-// One persistent CTA per SM walks output tiles of 128 x BN (BN = 256 or 128).
+// One persistent CTA per SM walks output tiles of 128 x BN (BN = 256, 128 or 64).
 // Warp roles inside a CTA (192 threads):
 //   warp 0     : TMA producer - one elected lane issues cp.async.bulk.tensor loads into a
 //                ring of 128-byte-swizzled shared-memory stages.
@@ -37,7 +37,7 @@ constexpr int GROUP_M = 8;      // tile-order swizzle: 8 row-blocks share their 
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -271,6 +271,17 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
     const int pairs = txh::sm_count() / 2;
     if (!g_disable_pair && M >= 256 && N >= 256 && tiles_pair >= pairs)
       return tx_gemm_pair_launch(A, B, p, lda, ldb, a_mn, b_mn, max_ctas, stream);
+  }
+  const int sel0 = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  // Skinny problems (decode: M <= 128 rows against a large weight) are bound by streaming B once.
+  // Narrow 64-column tiles put 2-4x as many CTAs on that stream, which is what fills HBM.
+  if (M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
+    switch (sel0) {
+      case 0: return launch<64, false, false>(A, B, p, lda, ldb, stream, max_ctas);
+      case 1: return launch<64, false, true>(A, B, p, lda, ldb, stream, max_ctas);
+      case 2: return launch<64, true, false>(A, B, p, lda, ldb, stream, max_ctas);
+      default: return launch<64, true, true>(A, B, p, lda, ldb, stream, max_ctas);
+    }
   }
   // Wide tiles unless that would leave most SMs idle.
   const long long tiles256 = static_cast<long long>((M + BM - 1) / BM) * ((N + 255) / 256);
