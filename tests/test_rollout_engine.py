@@ -114,3 +114,25 @@ def test_native_rollout_in_grpo_cluster():
   ml = cluster.actor_trainer.metrics_logger
   pre = cluster.actor_trainer.metrics_prefix
   assert all(np.isfinite(ml.get_metric_history(pre, "loss", "train")))
+
+
+def test_top_k_and_top_p_in_the_paged_engine():
+  """top_k=1 is greedy; top-k draws stay inside the k best tokens; log-probs are those of the full distribution."""
+  from tests.test_rl_grpo import toy_model
+  from tunix_b200.rollout import EngineConfig, PagedEngine
+  model = toy_model(0)
+  eng = PagedEngine(model, EngineConfig(page_size=4, max_batch=4, max_seq_len=32, use_cuda_graphs=False))
+  prompts = [[5, 6, 7], [9, 10, 11, 12], [3, 4]]
+  greedy = eng.generate(prompts, 6, greedy=True, eos_ids=[63])
+  k1 = eng.generate(prompts, 6, temperature=1.0, top_k=1, seed=4, eos_ids=[63])
+  assert [list(t) for t in greedy.tokens] == [list(t) for t in k1.tokens]
+  out = eng.generate(prompts, 6, temperature=1.3, top_k=3, top_p=0.9, seed=5, eos_ids=[63])
+  for p, toks, lps in zip(prompts, out.tokens, out.logprobs):
+    ids = list(p)
+    for t, lp in zip(toks, lps):
+      full = torch.tensor([ids])
+      logits, _ = model(full, torch.arange(len(ids))[None], None, None)
+      z = logits[0, -1].float() / 1.3
+      assert int(t) in torch.topk(z, 3).indices.tolist()
+      np.testing.assert_allclose(float(torch.log_softmax(z, -1)[int(t)]), float(lp), atol=2e-4)
+      ids.append(int(t))

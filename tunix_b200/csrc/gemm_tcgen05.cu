@@ -73,8 +73,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int mb = (p.M + BM - 1) / BM;
   const int nb = (p.N + BN - 1) / BN;
-  const int num_tiles = mb * nb;
+  const int ks = p.k_splits > 1 ? p.k_splits : 1;
+  const int num_tiles = mb * nb * ks;            // work items: (tile, K range)
   const int num_kb = (p.K + BK - 1) / BK;
+  const int kb_per = (num_kb + ks - 1) / ks;     // the host picks ks so that no range is empty
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -107,9 +109,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
         int pm, pn;
-        tile_coords(t, mb, nb, pm, pn);
+        tile_coords(t / ks, mb, nb, pm, pn);
         const int m0 = pm * BM, n0 = pn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (t % ks) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             atomicOr(p.status, kStatusWaitTimeoutProducer);
             ok = false;
@@ -151,7 +154,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = (t % ks) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
             atomicOr(p.status, kStatusWaitTimeoutMma);
             ok = false;
@@ -166,7 +170,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                      : make_smem_desc_sw128(sa + k * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(sb + k * 2048, BK * 128, 1024)
                                      : make_smem_desc_sw128(sb + k * 32, 16, 1024);
-            umma_bf16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_bf16(tmem_d, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * stage);
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
@@ -183,7 +187,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t acc_phase = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int pm, pn;
-      tile_coords(t, mb, nb, pm, pn);
+      tile_coords(t / ks, mb, nb, pm, pn);
       const int row = pm * BM + quarter * 32 + lane;
       const int n0 = pn * BN;
       if (!mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag)) {
@@ -236,7 +240,7 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
     attr_set = true;
   }
   const int mb = (p.M + BM - 1) / BM, nb = (p.N + BN - 1) / BN;
-  int grid = mb * nb;
+  int grid = mb * nb * (p.k_splits > 1 ? p.k_splits : 1);
   int sms = txh::sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   if (grid > sms) grid = sms;
@@ -252,6 +256,40 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
 // Requirements: bf16 operands, 16-byte aligned bases, lda/ldb multiples of 8, N and ldc
 // multiples of 8 (4 for fp32 C). `status` is a device int32 that receives error bits.
 // `max_ctas` > 0 caps the grid (leaves SMs free for a concurrent copy/collective).
+// Scratch of the split-K path: fp32 partial sums of one skinny GEMM at a time (M <= 128, M * N floats).
+// One buffer per device; launches that use it must be ordered on one stream.
+constexpr long long kSplitWsFloats = 128LL * 32768;
+static __device__ __align__(256) float g_splitk_ws[kSplitWsFloats];
+
+__global__ void splitk_finish_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ c, long long ldc,
+                                     int M, int N) {
+  const long long n4 = static_cast<long long>(M) * (N / 4);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / (N / 4)), q = static_cast<int>(i % (N / 4));
+    const float4 v = reinterpret_cast<const float4*>(ws + static_cast<long long>(r) * N)[q];
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(c + static_cast<long long>(r) * ldc) + 2 * q;
+    o[0] = __floats2bfloat162_rn(v.x, v.y);
+    o[1] = __floats2bfloat162_rn(v.z, v.w);
+  }
+}
+
+// The scratch address of the current device, looked up once per device (the lookup is not something to do
+// inside a stream capture; `tx_gemm_warmup` lets callers force it early).
+static float* splitk_workspace() {
+  static float* cache[16] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  if (cache[dev] == nullptr) {
+    float* ws = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ws), g_splitk_ws) != cudaSuccess) return nullptr;
+    cache[dev] = ws;
+  }
+  return cache[dev];
+}
+
+extern "C" int tx_gemm_warmup() { return splitk_workspace() != nullptr ? 0 : 300; }
+
 static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
 extern "C" void tx_gemm_set_disable_pair(int v) { g_disable_pair = v; }
@@ -264,7 +302,7 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return 3;
-  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status};
+  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1};
   // Large problems: 256 x 256 tiles on CTA pairs (cta_group::2) halve the B traffic per SM.
   {
     const long long tiles_pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
@@ -276,6 +314,31 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   // Skinny problems (decode: M <= 128 rows against a large weight) are bound by streaming B once.
   // Narrow 64-column tiles put 2-4x as many CTAs on that stream, which is what fills HBM.
   if (M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
+    // Too few tiles to fill the GPU: split K over several CTAs per tile, sum the fp32 partials with
+    // vector atomics in a scratch buffer, then round to bf16.
+    const int tiles = (N + 63) / 64, num_kb = (K + BK - 1) / BK;
+    int ks = (2 * txh::sm_count()) / tiles;
+    if (ks > 8) ks = 8;
+    if (ks > num_kb / 8) ks = num_kb / 8;
+    while (ks > 1 && (ks - 1) * ((num_kb + ks - 1) / ks) >= num_kb) --ks;     // no empty K range
+    if (ks > 1 && !c_fp32 && !accumulate && (N & 3) == 0 && static_cast<long long>(M) * N <= kSplitWsFloats) {
+      float* ws = splitk_workspace();
+      if (ws == nullptr) return 300;
+      if (cudaMemsetAsync(ws, 0, sizeof(float) * static_cast<size_t>(M) * N, stream) != cudaSuccess) return 400;
+      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks};
+      int rc;
+      switch (sel0) {
+        case 0: rc = launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        case 1: rc = launch<64, false, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        case 2: rc = launch<64, true, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        default: rc = launch<64, true, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
+      }
+      if (rc) return rc;
+      const long long n4 = static_cast<long long>(M) * (N / 4);
+      const int blocks = static_cast<int>(n4 / 256 + 1 < 592 ? n4 / 256 + 1 : 592);
+      splitk_finish_kernel<<<blocks, 256, 0, stream>>>(ws, static_cast<__nv_bfloat16*>(C), ldc, M, N);
+      return cudaGetLastError() == cudaSuccess ? 0 : 400;
+    }
     switch (sel0) {
       case 0: return launch<64, false, false>(A, B, p, lda, ldb, stream, max_ctas);
       case 1: return launch<64, false, true>(A, B, p, lda, ldb, stream, max_ctas);

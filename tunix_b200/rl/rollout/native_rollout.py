@@ -2,7 +2,7 @@
 
 Same contract as the other engines (tunix/rl/rollout/base_rollout.py:35-103): prompts are
 tokenised (BOS de-duplicated), truncated on the left to `max_prompt_length`, generated with
-temperature sampling (top-p 1, no top-k: those fall back to the contiguous-cache sampler),
+temperature sampling with optional top-k / top-p,
 and returned with left-padded prompt ids and per-token log-probs of the sampled tokens.
 Weights are the rollout model's own parameters, so `update_params` is an in-place copy (or a
 no-op when trainer and rollout share parameters) and the KV cache needs no rebuild.
@@ -56,8 +56,7 @@ class NativeRollout(base_rollout.BaseRollout):
 
   def generate(self, prompts: List[str], rollout_config: base_rollout.RolloutConfig, **kwargs):
     rc = rollout_config
-    needs_filter = (rc.top_p is not None and rc.top_p < 1.0) or bool(rc.top_k)
-    if self._engine is None or (needs_filter and rc.temperature):
+    if self._engine is None:
       fb = self._fallback or vanilla_rollout.VanillaRollout(
           self._model, self._tokenizer, base_rollout.CacheConfig(
               cache_size=rc.kv_cache_size, num_layers=self._model.config.num_layers,
@@ -70,7 +69,7 @@ class NativeRollout(base_rollout.BaseRollout):
     eos = list(rc.eos_tokens) if rc.eos_tokens else [self.eos_id()]
     res = self._engine.generate(ids, rc.max_tokens_to_generate, temperature=rc.temperature or 0.0,
                                 greedy=not rc.temperature, seed=rc.seed or 0, eos_ids=eos,
-                                return_logprobs=True)
+                                return_logprobs=True, top_k=rc.top_k, top_p=rc.top_p)
     tokens, lps = [], []
     for t, l in zip(res.tokens, res.logprobs):
       if len(t) and int(t[-1]) in eos:        # the EOS ends the completion and is not part of it

@@ -129,8 +129,32 @@ class PagedEngine:
                                      self.cfg.max_seq_len)
     hidden, _ = self.model(st["tokens"], st["positions"], caches, None, skip_lm_head=True)
     logits = self.model.compute_final_logits(hidden[:, -1], as_float=False)
-    return paged.sample(logits, temperature=sampling["temperature"], greedy=sampling["greedy"], seed=sampling["seed"],
-                        step=0, step_tensor=self._step_counter, forbidden=sampling["forbidden"])
+    return self._sample(logits, sampling)
+
+  def _sample(self, logits: torch.Tensor, sampling: Dict[str, Any]):
+    """Greedy / temperature sampling in one kernel; with top-k or top-p the candidates are cut first
+    (device-side, capturable) and the kernel draws among them. The returned log-prob is that of the token
+    under the full tempered distribution, as the trainer recomputes it."""
+    top_k, top_p = sampling.get("top_k"), sampling.get("top_p")
+    filtered = (top_k is not None and top_k > 0) or (top_p is not None and top_p < 1.0)
+    if sampling["greedy"] or not filtered:
+      return paged.sample(logits, temperature=sampling["temperature"], greedy=sampling["greedy"],
+                          seed=sampling["seed"], step=0, step_tensor=self._step_counter,
+                          forbidden=sampling["forbidden"])
+    T = sampling["temperature"]
+    z = logits.float() / T
+    if sampling["forbidden"] is not None:
+      z = z.index_fill(1, sampling["forbidden"].long(), float("-inf"))
+    k = z.shape[-1] if not top_k or top_k <= 0 else min(int(top_k), z.shape[-1])
+    zs, idx = torch.topk(z, k, dim=-1)
+    if top_p is not None and top_p < 1.0:
+      ps = torch.softmax(zs, dim=-1)
+      zs = torch.where(torch.cumsum(ps, dim=-1) - ps > top_p, torch.full_like(zs, float("-inf")), zs)
+    pick, _ = paged.sample(zs.contiguous(), temperature=1.0, greedy=False, seed=sampling["seed"], step=0,
+                           step_tensor=self._step_counter, want_logprobs=False)
+    tok = idx.gather(-1, pick[:, None]).squeeze(-1)
+    lp = z.gather(-1, tok[:, None]).squeeze(-1) - torch.logsumexp(z, dim=-1)
+    return tok, lp
 
   @torch.no_grad()
   def _decode_step(self, running: List[_Seq], sampling: Dict[str, Any]) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -150,7 +174,8 @@ class PagedEngine:
       lens[i] = s.length + 1
     for name, arr in (("tokens", tok), ("positions", pos), ("slots", slots), ("block_tables", bt), ("seq_lens", lens)):
       st[name].copy_(torch.from_numpy(arr), non_blocking=True)
-    key = (bucket, sampling["greedy"], sampling["temperature"], sampling["seed"], id(sampling["forbidden"]))
+    key = (bucket, sampling["greedy"], sampling["temperature"], sampling["seed"], id(sampling["forbidden"]),
+           sampling.get("top_k"), sampling.get("top_p"))
     use_graph = self.cfg.use_cuda_graphs and self.device.type == "cuda"
     if not use_graph:
       out = self._decode_body(st, sampling)
@@ -240,9 +265,7 @@ class PagedEngine:
           logits = logits[torch.tensor(rows, device=logits.device)]
         else:
           seqs = leaders
-        tok, lp = paged.sample(logits.contiguous(), temperature=sampling["temperature"], greedy=sampling["greedy"],
-                               seed=sampling["seed"], step=0, step_tensor=self._step_counter,
-                               forbidden=sampling["forbidden"])
+        tok, lp = self._sample(logits.contiguous(), sampling)
         self._step_counter += 1
         self._append(seqs, tok, lp, sampling, results)
 
@@ -273,14 +296,16 @@ class PagedEngine:
   @torch.no_grad()
   def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int, *, temperature: float = 1.0,
                greedy: bool = False, seed: int = 0, eos_ids: Sequence[int] = (), forbidden: Sequence[int] = (),
-               return_logprobs: bool = True) -> GenerationResult:
-    """Generates up to `max_new_tokens` per prompt (token id lists, unpadded)."""
+               return_logprobs: bool = True, top_k: Optional[int] = None,
+               top_p: Optional[float] = None) -> GenerationResult:
+    """Generates up to `max_new_tokens` per prompt (token id lists, unpadded). `top_k` / `top_p` restrict
+    the candidates as the dense sampler does (top-p over the top-k sorted distribution)."""
     was_training = self.model.training
     self.model.eval()
     from ..ops import functional as F
     old_bound = F.set_position_bound(self.cfg.max_seq_len)
     sampling = {"temperature": float(temperature), "greedy": bool(greedy or temperature == 0.0), "seed": int(seed),
-                "eos": set(int(e) for e in eos_ids),
+                "eos": set(int(e) for e in eos_ids), "top_k": top_k, "top_p": top_p,
                 "forbidden": torch.tensor(list(forbidden), dtype=torch.int32, device=self.device) if forbidden else None}
     self._step_counter.zero_()
     waiting: Deque[_Seq] = deque(_Seq(i, tuple(int(t) for t in p), int(max_new_tokens)) for i, p in enumerate(prompts))
