@@ -31,7 +31,7 @@ GEMM_SHAPES = [
     (2200, 4360, 264),    # CTA-pair kernel, ragged in M, N and K
     (8192, 4096, 1024),
     (64, 512, 4096),      # skinny: 64-column tiles, K split 8 ways, fp32 atomics + rounding pass
-    (33, 264, 1104),      # skinny and ragged, K split 2 ways
+    (40, 264, 1104),      # skinny and ragged, K split 2 ways
     (128, 4096, 12288),   # decode down-projection
 ]
 
