@@ -120,6 +120,18 @@ def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: 
   tree_md: Dict[str, Any] = {}
   arr_md: List[Dict[str, Any]] = []
   shard_md: Dict[str, str] = {}
+  # array chunks go through the native writer pool (temp file + rename on worker threads)
+  from ..runtime import native
+  writer = native.AsyncWriter(threads=8)
+  try:
+    _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md)
+    writer.wait()
+  finally:
+    writer.close()
+  _write_tree_metadata(directory, process_index, tree_md, arr_md, shard_md)
+
+
+def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md) -> None:
   for key, t in tree.items():
     if not isinstance(t, torch.Tensor):
       t = torch.as_tensor(t)
@@ -133,7 +145,7 @@ def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: 
     }
     _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
     chunk_name = ".".join("0" for _ in shape) if shape else "0"
-    _write_file(os.path.join(pdir, chunk_name), data)
+    writer.submit(os.path.join(pdir, chunk_name), data)
     tree_md[key_to_str(key)] = {
         "key_metadata": [{"key": str(k), "key_type": 1 if isinstance(k, int) else 2} for k in key],
         "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, "write_shape": shape},
@@ -142,6 +154,9 @@ def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: 
                                       "ext_metadata": None}})
     desc = (sharding_desc or {}).get(key) or {"sharding_type": "SingleDeviceSharding", "device_str": "cuda:0"}
     shard_md[base64.b64encode(name.encode()).decode()] = json.dumps(desc)
+
+
+def _write_tree_metadata(directory, process_index, tree_md, arr_md, shard_md) -> None:
   if process_index == 0:
     _write_file(os.path.join(directory, "_METADATA"), json.dumps({
         "tree_metadata": tree_md, "use_zarr3": False, "store_array_data_equal_to_fill_value": True,
