@@ -54,6 +54,20 @@ def test_gemm_layouts(kernel_lib, M, N, K, a_mn, b_mn):
   torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K) * 0.25)
 
 
+def test_skinny_gemm_scratch_is_left_clean(kernel_lib):
+  """Decode-shaped GEMMs share one zero-filled scratch: interleaved shapes and repeats must not leak."""
+  from tunix_b200.ops import _lib, kernels
+  torch.manual_seed(7)
+  shapes = [(64, 4096, 4096), (100, 1024, 2048), (8, 6144, 4096), (128, 4096, 12288), (64, 4096, 4096), (1, 512, 1024)]
+  for rep in range(2):
+    for M, N, K in shapes:
+      a, b = _rand(M, K, scale=0.5), _rand(N, K, scale=0.5)
+      out = kernels.gemm(a, b)
+      ref = a.float() @ b.float().t()
+      assert _rel_err(out, ref) < 6e-3, (M, N, K, rep, _rel_err(out, ref))
+  _lib.check_status()
+
+
 def test_gemm_fp32_accumulate(kernel_lib):
   from tunix_b200.ops import _lib, kernels
   torch.manual_seed(1)
