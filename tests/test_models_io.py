@@ -157,3 +157,43 @@ def test_script_utils_datasets(tmp_path):
   assert tb[0]["prompts"][0].startswith("SYS q") and tb[0]["answer"][0].isdigit()
   with script_utils.profile_and_capture_log("t", enable_profile=False):
     pass
+
+
+def test_gemma3_vision_tower_and_multimodal_merge():
+  from tunix_b200.models.gemma3 import vision
+  from tunix_b200.models.transformer import ModelConfig, Transformer
+  torch.manual_seed(0)
+  vc = vision.SigLIPConfig(image_height=28, image_width=28, patch_size=(7, 7), width=32, depth=2, mlp_dim=64,
+                           num_heads=4, num_mm_tokens_per_image_prepool=16, num_mm_tokens_per_image=4)
+  tower = vision.SigLiP(vc)
+  imgs = torch.randn(2, 3, 28, 28, 3)
+  soft = tower(imgs)
+  assert soft.shape == (2, 3, 4, 32) and not soft.requires_grad
+  # the exit layer averages 2x2 windows of the 4x4 patch grid
+  grid = torch.arange(16.0).view(1, 16, 1)
+  assert vision.VisionExit(4)(grid).flatten().tolist() == [2.5, 4.5, 10.5, 12.5]
+
+  cfg = ModelConfig(num_layers=2, vocab_size=256, embed_dim=32, hidden_dim=64, num_heads=4, head_dim=8, num_kv_heads=2)
+  mm = vision.Gemma3Multimodal(Transformer(cfg).init_weights(seed=0, scale=0.2), vc)
+  with torch.no_grad():
+    mm.mm_input_projection.normal_(0, 0.2)
+    mm.mm_soft_embedding_norm.w.fill_(1.0)
+    mm.vision_encoder.siglip_encoder.pos_embedding.normal_(0, 0.02)
+  ph = vc.soft_token_placeholder
+  toks = torch.tensor([[5, ph, ph, ph, ph, 9, 10, ph, ph, ph, ph, 11], [7, 8, ph, ph, ph, ph, 12, 13, 14, 15, 16, 17]])
+  images = torch.randn(2, 2, 28, 28, 3)
+  logits, _ = mm(toks, images=images)
+  assert logits.shape == (2, 12, 256) and torch.isfinite(logits).all()
+  mask = vision.multimodal_attention_mask(toks, ph, 4)
+  assert mask[0, 1, 4] and mask[0, 4, 1]                     # inside one image: both directions
+  assert not mask[0, 1, 7] and mask[0, 7, 1]                 # across images: causal only
+  assert not mask[0, 0, 1]
+  # changing the second image changes only what follows it; the text-only path ignores images
+  images2 = images.clone()
+  images2[0, 1] += 1.0
+  logits2, _ = mm(toks, images=images2)
+  assert torch.allclose(logits[0, :7], logits2[0, :7], atol=1e-5) and not torch.allclose(logits[0, 7:], logits2[0, 7:])
+  assert torch.allclose(logits[1], logits2[1], atol=1e-5)
+  emb = vision.merge_embeddings(torch.zeros(1, 5, 2), torch.arange(8.0).view(1, 2, 2, 2),
+                                torch.tensor([[False, True, True, False, True]]))
+  assert emb[0].tolist() == [[0, 0], [0, 1], [2, 3], [0, 0], [4, 5]]

@@ -459,7 +459,10 @@ class Transformer(nn.Module):
     return h, new_cache
 
   def forward(self, input_tokens, positions=None, cache: Optional[Cache] = None, attention_mask=None,
-              output_hidden_states: bool = False, segment_ids=None, skip_lm_head: bool = False):
+              output_hidden_states: bool = False, segment_ids=None, skip_lm_head: bool = False,
+              input_embeddings: Optional[torch.Tensor] = None):
+    """`input_embeddings` [B, L, D] replaces the embedding lookup (multimodal models merge image or audio
+    soft tokens into the text embeddings first); `input_tokens` then only gives the shape."""
     cfg = self.config
     B, L = input_tokens.shape
     if positions is None:
@@ -468,7 +471,7 @@ class Transformer(nn.Module):
       from ..ops import attention as attn_ops
       seg_mask = attn_ops.SegmentMask(segment_ids)      # symbolic: the flash kernels take segment bounds
       attention_mask = seg_mask if attention_mask is None else (attention_mask & seg_mask.dense())
-    h = self.embedder.encode(input_tokens)
+    h = self.embedder.encode(input_tokens) if input_embeddings is None else input_embeddings
     if cfg.remat_config == RematConfig.DECODER and torch.is_grad_enabled() and cache is None:
       h = torch_ckpt.checkpoint(lambda hh: self._stack(hh, positions, None, attention_mask)[0], h, use_reentrant=False)
       new_cache = None
