@@ -226,10 +226,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           if (row < p.M) {
             __nv_bfloat16* cdst = reinterpret_cast<__nv_bfloat16*>(p.C);
             const int b_end = min(p.N, n0 + BN);
-            for (int b = n0; b < b_end; ++b) {
-              float* w = p.ws + b * ldw + row;
-              cdst[static_cast<long long>(b) * p.ldc + row] = __float2bfloat16_rn(__ldcg(w));
-              *w = 0.f;
+            // 16 independent L2 reads in flight per lane, then the stores: the loop is latency-bound otherwise
+#pragma unroll 1
+            for (int b0 = n0; b0 < b_end; b0 += 16) {
+              float v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                v[j] = (b0 + j < b_end) ? __ldcg(p.ws + (b0 + j) * ldw + row) : 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (b0 + j < b_end) {
+                  cdst[static_cast<long long>(b0 + j) * p.ldc + row] = __float2bfloat16_rn(v[j]);
+                  p.ws[(b0 + j) * ldw + row] = 0.f;
+                }
+              }
             }
           }
           __syncwarp();
