@@ -14,11 +14,8 @@ struct GemmParams {
   int accumulate;  // 1: C += result, 0: C = result
   float alpha;
   int* status;
-  int k_splits;    // > 1 (or swapped != 0): every tile is computed by k_splits CTAs over disjoint K ranges that add
-                   // their fp32 partials into `ws`; the last one to arrive rounds the sum into C (single-CTA kernel)
-  int swapped;     // the kernel computes C^T: its rows are C's columns (weights as the M operand of a skinny GEMM)
-  float* ws;       // zero-filled fp32 scratch [rows of C][cols of C]; left zero-filled again
-  int* ws_count;   // zero-filled arrival counters, 4 per tile; left zero-filled again
+  int k_splits;    // > 1: every tile is computed by k_splits CTAs over disjoint K ranges; C must then be a zeroed
+                   // fp32 buffer and the epilogue adds into it atomically (single-CTA kernel only)
 };
 
 // Walks tiles so that `group_m` consecutive row-blocks share their B tiles while they are hot in L2.
@@ -35,6 +32,18 @@ __device__ __forceinline__ void tile_coords(int t, int mb, int nb, int group_m, 
 // r[0..31]: accumulator columns [col, col + 32) of row `row`.
 __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col, const uint32_t (&r)[32]) {
   if (row >= p.M || col >= p.N) return;
+  if (p.k_splits > 1) {
+    float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      if (col + j < p.N)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j),
+                     "f"(__uint_as_float(r[j]) * p.alpha), "f"(__uint_as_float(r[j + 1]) * p.alpha),
+                     "f"(__uint_as_float(r[j + 2]) * p.alpha), "f"(__uint_as_float(r[j + 3]) * p.alpha)
+                     : "memory");
+    }
+    return;
+  }
   if (p.c_fp32) {
     float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
 #pragma unroll

@@ -196,57 +196,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      if (p.ws != nullptr) {
-        // Split-K / swapped epilogue. Kernel rows are C's columns: lane `row` owns column `row` of C, the tile's
-        // columns are rows b of C. Partials are added into ws[b][row]; lanes of a warp hit consecutive addresses.
-        const long long ldw = p.M;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(taddr + c, r);
-          tmem_ld_wait();
-          if (row < p.M) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int b = n0 + c + j;
-              if (b < p.N) atomicAdd(p.ws + b * ldw + row, __uint_as_float(r[j]) * p.alpha);
-            }
-          }
-        }
-        tc_fence_before();
-        mbar_arrive(bar_tempty + 8 * acc);            // the accumulator is free; the rest is global memory only
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) last = atomicAdd(p.ws_count + (t / ks) * 4 + quarter, 1) == ks - 1;
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {                                    // every K range of these 32 columns has been added
-          __threadfence();
-          if (row < p.M) {
-            __nv_bfloat16* cdst = reinterpret_cast<__nv_bfloat16*>(p.C);
-            const int b_end = min(p.N, n0 + BN);
-            // 16 independent L2 reads in flight per lane, then the stores: the loop is latency-bound otherwise
-#pragma unroll 1
-            for (int b0 = n0; b0 < b_end; b0 += 16) {
-              float v[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                v[j] = (b0 + j < b_end) ? __ldcg(p.ws + (b0 + j) * ldw + row) : 0.f;
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (b0 + j < b_end) {
-                  cdst[static_cast<long long>(b0 + j) * p.ldc + row] = __float2bfloat16_rn(v[j]);
-                  p.ws[(b0 + j) * ldw + row] = 0.f;
-                }
-              }
-            }
-          }
-          __syncwarp();
-          if (lane == 0) p.ws_count[(t / ks) * 4 + quarter] = 0;
-        }
-        continue;
-      }
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -307,39 +256,39 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
 // Requirements: bf16 operands, 16-byte aligned bases, lda/ldb multiples of 8, N and ldc
 // multiples of 8 (4 for fp32 C). `status` is a device int32 that receives error bits.
 // `max_ctas` > 0 caps the grid (leaves SMs free for a concurrent copy/collective).
-// Scratch of the skinny-GEMM path: fp32 partial sums (M <= 128 rows of C, M * N floats) and arrival counters.
-// Both start zero-filled (static storage) and every launch leaves them zero-filled. One set per device;
-// launches that use it must be ordered on one stream.
+// Scratch of the split-K path: fp32 partial sums of one skinny GEMM at a time (M <= 128, M * N floats).
+// One buffer per device; launches that use it must be ordered on one stream.
 constexpr long long kSplitWsFloats = 128LL * 32768;
-constexpr int kSplitCounters = 4096;
 static __device__ __align__(256) float g_splitk_ws[kSplitWsFloats];
-static __device__ int g_splitk_cnt[kSplitCounters];
 
-// Addresses on the current device, looked up once per device (not something to do inside a stream capture;
-// `tx_gemm_warmup` forces it early).
-static bool splitk_workspace(float** ws, int** cnt) {
-  static float* ws_cache[16] = {nullptr};
-  static int* cnt_cache[16] = {nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return false;
-  if (ws_cache[dev] == nullptr) {
-    float* w = nullptr;
-    int* c = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&w), g_splitk_ws) != cudaSuccess) return false;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&c), g_splitk_cnt) != cudaSuccess) return false;
-    cnt_cache[dev] = c;
-    ws_cache[dev] = w;
+__global__ void splitk_finish_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ c, long long ldc,
+                                     int M, int N) {
+  const long long n4 = static_cast<long long>(M) * (N / 4);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(i / (N / 4)), q = static_cast<int>(i % (N / 4));
+    const float4 v = reinterpret_cast<const float4*>(ws + static_cast<long long>(r) * N)[q];
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(c + static_cast<long long>(r) * ldc) + 2 * q;
+    o[0] = __floats2bfloat162_rn(v.x, v.y);
+    o[1] = __floats2bfloat162_rn(v.z, v.w);
   }
-  *ws = ws_cache[dev];
-  *cnt = cnt_cache[dev];
-  return true;
 }
 
-extern "C" int tx_gemm_warmup() {
-  float* w;
-  int* c;
-  return splitk_workspace(&w, &c) ? 0 : 300;
+// The scratch address of the current device, looked up once per device (the lookup is not something to do
+// inside a stream capture; `tx_gemm_warmup` lets callers force it early).
+static float* splitk_workspace() {
+  static float* cache[16] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  if (cache[dev] == nullptr) {
+    float* ws = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ws), g_splitk_ws) != cudaSuccess) return nullptr;
+    cache[dev] = ws;
+  }
+  return cache[dev];
 }
+
+extern "C" int tx_gemm_warmup() { return splitk_workspace() != nullptr ? 0 : 300; }
 
 static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
@@ -353,7 +302,7 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return 3;
-  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1, 0, nullptr, nullptr};
+  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1};
   // Large problems: 256 x 256 tiles on CTA pairs (cta_group::2) halve the B traffic per SM.
   {
     const long long tiles_pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
@@ -365,23 +314,30 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   // Skinny problems (decode: M <= 128 rows against a large weight) are bound by streaming B once.
   // Narrow 64-column tiles put 2-4x as many CTAs on that stream, which is what fills HBM.
   if (M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
-    // Weights become the M operand (C^T = W X^T): 128 weight rows per tile against the whole batch as one
-    // 64- or 128-column tile, so two thirds of what a CTA stages is weight bytes. K is split over enough CTAs
-    // to fill the GPU; partial sums meet in a zero-filled scratch and the last CTA to arrive rounds them to bf16.
-    const int tiles = (N + BM - 1) / BM, num_kb = (K + BK - 1) / BK;
-    int ks = (2 * txh::sm_count() + tiles - 1) / tiles;
-    if (ks > 16) ks = 16;
-    if (ks > num_kb / 4) ks = num_kb / 4;
-    if (ks < 1) ks = 1;
+    // Too few tiles to fill the GPU: split K over several CTAs per tile, sum the fp32 partials with
+    // vector atomics in a scratch buffer, then round to bf16.
+    const int tiles = (N + 63) / 64, num_kb = (K + BK - 1) / BK;
+    int ks = tiles < 96 ? (2 * txh::sm_count()) / tiles : 1;     // measured: splitting only pays when few tiles exist
+    if (ks > 8) ks = 8;
+    if (ks > num_kb / 8) ks = num_kb / 8;
     while (ks > 1 && (ks - 1) * ((num_kb + ks - 1) / ks) >= num_kb) --ks;     // no empty K range
-    float* ws = nullptr;
-    int* cnt = nullptr;
-    if (sel0 == 0 && !c_fp32 && !accumulate && static_cast<long long>(M) * N <= kSplitWsFloats &&
-        tiles * 4 <= kSplitCounters && splitk_workspace(&ws, &cnt)) {
-      // kernel view: M' = N (weight rows), N' = M (batch), A' = B, B' = A
-      GemmParams ps{C, ldc, N, M, K, 0, 0, alpha, status, ks, 1, ws, cnt};
-      return M <= 64 ? launch<64, false, false>(B, A, ps, ldb, lda, stream, max_ctas)
-                     : launch<128, false, false>(B, A, ps, ldb, lda, stream, max_ctas);
+    if (ks > 1 && !c_fp32 && !accumulate && (N & 3) == 0 && static_cast<long long>(M) * N <= kSplitWsFloats) {
+      float* ws = splitk_workspace();
+      if (ws == nullptr) return 300;
+      if (cudaMemsetAsync(ws, 0, sizeof(float) * static_cast<size_t>(M) * N, stream) != cudaSuccess) return 400;
+      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks};
+      int rc;
+      switch (sel0) {
+        case 0: rc = launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        case 1: rc = launch<64, false, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        case 2: rc = launch<64, true, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        default: rc = launch<64, true, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
+      }
+      if (rc) return rc;
+      const long long n4 = static_cast<long long>(M) * (N / 4);
+      const int blocks = static_cast<int>(n4 / 256 + 1 < 592 ? n4 / 256 + 1 : 592);
+      splitk_finish_kernel<<<blocks, 256, 0, stream>>>(ws, static_cast<__nv_bfloat16*>(C), ldc, M, N);
+      return cudaGetLastError() == cudaSuccess ? 0 : 400;
     }
     switch (sel0) {
       case 0: return launch<64, false, false>(A, B, p, lda, ldb, stream, max_ctas);
