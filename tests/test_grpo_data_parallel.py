@@ -20,3 +20,15 @@ def test_grpo_two_ranks_cpu(tmp_path):
   assert got["moved"] > 0                                   # the actor was trained
   assert abs(got["checksums"][0] - got["checksums"][1]) < 1e-6 * max(1.0, abs(got["checksums"][0]))
   assert all(l == l for l in got["loss"])                   # no NaN
+
+
+def test_moe_expert_parallel_two_ranks_cpu(tmp_path):
+  """Dispatch / grouped MLP / combine over 2 ranks equals the single-rank layer, forward and backward."""
+  out = str(tmp_path / "ep.pt")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29651", os.path.join(HERE, "_moe_ep_worker.py"), "--out", out]
+  r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2"), capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["shape"][0] == 2
+    assert res["fwd"] < 1e-5 and res["dx"] < 1e-4 and res["dw"] < 1e-4, res
