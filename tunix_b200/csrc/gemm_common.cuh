@@ -16,6 +16,8 @@ struct GemmParams {
   int* status;
   int k_splits;    // > 1: every tile is computed by k_splits CTAs over disjoint K ranges; C must then be a zeroed
                    // fp32 buffer and the epilogue adds into it atomically (single-CTA kernel only)
+  int K2;          // > 0: a second operand pair (A2 [M,K2], B2 [N,K2], same layouts) is accumulated after the first:
+                   // C = A B^T + A2 B2^T in one pass (fused low-rank adapters); 0 otherwise
 };
 
 // Walks tiles so that `group_m` consecutive row-blocks share their B tiles while they are hot in L2.
@@ -91,5 +93,6 @@ __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, in
 }  // namespace txg
 
 // Implemented in gemm_tcgen05_pair.cu: the 2-CTA (256 x 256 tile per CTA pair) variant.
-int tx_gemm_pair_launch(const void* A, const void* B, const txg::GemmParams& p, long long lda, long long ldb,
-                        int a_mn, int b_mn, int max_ctas, cudaStream_t stream);
+int tx_gemm_pair_launch(const void* A, const void* B, const void* A2, const void* B2, const txg::GemmParams& p,
+                        long long lda, long long ldb, long long lda2, long long ldb2, int a_mn, int b_mn, int max_ctas,
+                        cudaStream_t stream);

@@ -54,6 +54,7 @@ __device__ __forceinline__ void tile_coords(int t, int mb, int nb, int& pm, int&
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                  const GemmParams p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -75,7 +76,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int nb = (p.N + BN - 1) / BN;
   const int ks = p.k_splits > 1 ? p.k_splits : 1;
   const int num_tiles = mb * nb * ks;            // work items: (tile, K range)
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb1 = (p.K + BK - 1) / BK;
+  const int num_kb = num_kb1 + (p.K2 > 0 ? (p.K2 + BK - 1) / BK : 0);   // k-blocks of both operand pairs
   const int kb_per = (num_kb + ks - 1) / ks;     // the host picks ks so that no range is empty
 
   if (threadIdx.x == 0) {
@@ -122,17 +124,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const uint32_t sa = smem_base + stage * C::kStageBytes;
           const uint32_t sb = sa + C::kABytes;
           mbar_expect_tx(full, C::kStageBytes);
+          const bool second = kb >= num_kb1;                 // the low-rank pair follows the main pair
+          const CUtensorMap* ma = second ? &map_a2 : &map_a;
+          const CUtensorMap* mbp = second ? &map_b2 : &map_b;
+          const int kc = (second ? kb - num_kb1 : kb) * BK;
           if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), &map_a, m0 + i * 64, kb * BK, full);
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + i * 64, kc, full);
           } else {
-            tma_load_2d(sa, &map_a, kb * BK, m0, full);
+            tma_load_2d(sa, ma, kc, m0, full);
           }
           if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), &map_b, n0 + i * 64, kb * BK, full);
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * (BK * 128), mbp, n0 + i * 64, kc, full);
           } else {
-            tma_load_2d(sb, &map_b, kb * BK, n0, full);
+            tma_load_2d(sb, mbp, kc, n0, full);
           }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
@@ -222,7 +228,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb,
-           cudaStream_t stream, int max_ctas) {
+           cudaStream_t stream, int max_ctas, const void* A2 = nullptr, const void* B2 = nullptr, long long lda2 = 0,
+           long long ldb2 = 0) {
   using C = Cfg<BN>;
   CUtensorMap ma, mbm;
   int rc;
@@ -232,6 +239,15 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   if (B_MN) rc = txh::make_map_2d_bf16(&mbm, B, p.K, p.N, ldb, BK, 64);
   else      rc = txh::make_map_2d_bf16(&mbm, B, p.N, p.K, ldb, BN, BK);
   if (rc) return 200 + rc;
+  CUtensorMap ma2 = ma, mb2 = mbm;
+  if (p.K2 > 0) {
+    if (A_MN) rc = txh::make_map_2d_bf16(&ma2, A2, p.K2, p.M, lda2, BK, 64);
+    else      rc = txh::make_map_2d_bf16(&ma2, A2, p.M, p.K2, lda2, BM, BK);
+    if (rc) return 100 + rc;
+    if (B_MN) rc = txh::make_map_2d_bf16(&mb2, B2, p.K2, p.N, ldb2, BK, 64);
+    else      rc = txh::make_map_2d_bf16(&mb2, B2, p.N, p.K2, ldb2, BN, BK);
+    if (rc) return 200 + rc;
+  }
   static bool attr_set = false;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!attr_set) {
@@ -244,7 +260,7 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   int sms = txh::sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
   if (grid > sms) grid = sms;
-  kern<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mbm, p);
+  kern<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(ma, mbm, ma2, mb2, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 
@@ -294,26 +310,32 @@ static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
 extern "C" void tx_gemm_set_disable_pair(int v) { g_disable_pair = v; }
 
-extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
-                            long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, int accumulate,
-                            float alpha, int* status, int max_ctas, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0) return 1;
+// C = alpha * (A B^T + A2 B2^T): the second pair (K2 columns, same layouts as the first; K2 == 0 for none)
+// is accumulated in the same pass - fused low-rank adapters. lda2 / ldb2 multiples of 8.
+extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, const void* B2, void* C, int M, int N,
+                                 int K, int K2, long long lda, long long ldb, long long lda2, long long ldb2,
+                                 long long ldc, int a_mn, int b_mn, int c_fp32, int accumulate, float alpha,
+                                 int* status, int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K2 < 0) return 1;
+  if (K2 > 0 && (!A2 || !B2 || (lda2 & 7) || (ldb2 & 7) || (reinterpret_cast<uintptr_t>(A2) & 15) ||
+                 (reinterpret_cast<uintptr_t>(B2) & 15)))
+    return 2;
   if ((lda & 7) || (ldb & 7) || (N & 7) || (ldc & 3)) return 2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return 3;
-  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1};
+  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1, K2};
   // Large problems: 256 x 256 tiles on CTA pairs (cta_group::2) halve the B traffic per SM.
   {
     const long long tiles_pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
     const int pairs = txh::sm_count() / 2;
     if (!g_disable_pair && M >= 256 && N >= 256 && tiles_pair >= pairs)
-      return tx_gemm_pair_launch(A, B, p, lda, ldb, a_mn, b_mn, max_ctas, stream);
+      return tx_gemm_pair_launch(A, B, A2, B2, p, lda, ldb, lda2, ldb2, a_mn, b_mn, max_ctas, stream);
   }
   const int sel0 = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   // Skinny problems (decode: M <= 128 rows against a large weight) are bound by streaming B once.
   // Narrow 64-column tiles put 2-4x as many CTAs on that stream, which is what fills HBM.
-  if (M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
+  if (K2 == 0 && M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
     // Too few tiles to fill the GPU: split K over several CTAs per tile, sum the fp32 partials with
     // vector atomics in a scratch buffer, then round to bf16.
     const int tiles = (N + 63) / 64, num_kb = (K + BK - 1) / BK;
@@ -325,7 +347,7 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
       float* ws = splitk_workspace();
       if (ws == nullptr) return 300;
       if (cudaMemsetAsync(ws, 0, sizeof(float) * static_cast<size_t>(M) * N, stream) != cudaSuccess) return 400;
-      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks};
+      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks, 0};
       int rc;
       switch (sel0) {
         case 0: rc = launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
@@ -352,16 +374,23 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
   const int sel = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   if (bn256 || tiles256 >= 96) {
     switch (sel) {
-      case 0: return launch<256, false, false>(A, B, p, lda, ldb, stream, max_ctas);
-      case 1: return launch<256, false, true>(A, B, p, lda, ldb, stream, max_ctas);
-      case 2: return launch<256, true, false>(A, B, p, lda, ldb, stream, max_ctas);
-      default: return launch<256, true, true>(A, B, p, lda, ldb, stream, max_ctas);
+      case 0: return launch<256, false, false>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+      case 1: return launch<256, false, true>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+      case 2: return launch<256, true, false>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+      default: return launch<256, true, true>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
     }
   }
   switch (sel) {
-    case 0: return launch<128, false, false>(A, B, p, lda, ldb, stream, max_ctas);
-    case 1: return launch<128, false, true>(A, B, p, lda, ldb, stream, max_ctas);
-    case 2: return launch<128, true, false>(A, B, p, lda, ldb, stream, max_ctas);
-    default: return launch<128, true, true>(A, B, p, lda, ldb, stream, max_ctas);
+    case 0: return launch<128, false, false>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+    case 1: return launch<128, false, true>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+    case 2: return launch<128, true, false>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
+    default: return launch<128, true, true>(A, B, p, lda, ldb, stream, max_ctas, A2, B2, lda2, ldb2);
   }
+}
+
+extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                            long long ldb, long long ldc, int a_mn, int b_mn, int c_fp32, int accumulate,
+                            float alpha, int* status, int max_ctas, cudaStream_t stream) {
+  return tx_gemm_bf16_dual(A, B, nullptr, nullptr, C, M, N, K, 0, lda, ldb, 0, 0, ldc, a_mn, b_mn, c_fp32, accumulate,
+                           alpha, status, max_ctas, stream);
 }

@@ -41,6 +41,7 @@ constexpr int kSmemBytes = kStages * kStageBytes + kRedBufBytes + 1024 + 256;
 template <bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                       const __grid_constant__ CUtensorMap map_c, const GemmParams p, const int red_epilogue) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -62,7 +63,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int mb = (p.M + 2 * BM_CTA - 1) / (2 * BM_CTA);
   const int nb = (p.N + BN - 1) / BN;
   const int num_tiles = mb * nb;
-  const int num_kb = (p.K + BK - 1) / BK;
+  const int num_kb1 = (p.K + BK - 1) / BK;
+  const int num_kb = num_kb1 + (p.K2 > 0 ? (p.K2 + BK - 1) / BK : 0);   // k-blocks of both operand pairs
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -109,19 +111,23 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kABytes;
           if (cta == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * kStageBytes);
+          const bool second = kb >= num_kb1;                 // the low-rank pair follows the main pair
+          const CUtensorMap* ma = second ? &map_a2 : &map_a;
+          const CUtensorMap* mbp = second ? &map_b2 : &map_b;
+          const int kc = (second ? kb - num_kb1 : kb) * BK;
           if (A_MN) {
 #pragma unroll
             for (int i = 0; i < BM_CTA / 64; ++i)
-              tma_load_2d_pair(sa + i * (BK * 128), &map_a, m0 + i * 64, kb * BK, full_leader);
+              tma_load_2d_pair(sa + i * (BK * 128), ma, m0 + i * 64, kc, full_leader);
           } else {
-            tma_load_2d_pair(sa, &map_a, kb * BK, m0, full_leader);
+            tma_load_2d_pair(sa, ma, kc, m0, full_leader);
           }
           if (B_MN) {
 #pragma unroll
             for (int i = 0; i < BN_CTA / 64; ++i)
-              tma_load_2d_pair(sb + i * (BK * 128), &map_b, n0 + i * 64, kb * BK, full_leader);
+              tma_load_2d_pair(sb + i * (BK * 128), mbp, n0 + i * 64, kc, full_leader);
           } else {
-            tma_load_2d_pair(sb, &map_b, kb * BK, n0, full_leader);
+            tma_load_2d_pair(sb, mbp, kc, n0, full_leader);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -242,8 +248,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }
 
 template <bool A_MN, bool B_MN>
-int launch(const void* A, const void* B, const GemmParams& p, long long lda, long long ldb, int max_ctas,
-           cudaStream_t stream) {
+int launch(const void* A, const void* B, const void* A2, const void* B2, const GemmParams& p, long long lda,
+           long long ldb, long long lda2, long long ldb2, int max_ctas, cudaStream_t stream) {
   CUtensorMap ma, mbm;
   int rc;
   if (A_MN) rc = txh::make_map_2d_bf16(&ma, A, p.K, p.M, lda, BK, 64);
@@ -252,6 +258,15 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   if (B_MN) rc = txh::make_map_2d_bf16(&mbm, B, p.K, p.N, ldb, BK, 64);
   else      rc = txh::make_map_2d_bf16(&mbm, B, p.N, p.K, ldb, BN_CTA, BK);
   if (rc) return 200 + rc;
+  CUtensorMap ma2 = ma, mb2 = mbm;
+  if (p.K2 > 0) {
+    if (A_MN) rc = txh::make_map_2d_bf16(&ma2, A2, p.K2, p.M, lda2, BK, 64);
+    else      rc = txh::make_map_2d_bf16(&ma2, A2, p.M, p.K2, lda2, BM_CTA, BK);
+    if (rc) return 100 + rc;
+    if (B_MN) rc = txh::make_map_2d_bf16(&mb2, B2, p.K2, p.N, ldb2, BK, 64);
+    else      rc = txh::make_map_2d_bf16(&mb2, B2, p.N, p.K2, ldb2, BN_CTA, BK);
+    if (rc) return 200 + rc;
+  }
   // fp32 accumulation into C (gradient accumulation of weight gradients) goes through TMA reduce-add.
   CUtensorMap mc = ma;
   int red = 0;
@@ -271,19 +286,20 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
   int pairs = mb * nb;
   if (pairs > sms / 2) pairs = sms / 2;
   if (pairs < 1) pairs = 1;
-  kern<<<2 * pairs, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, mc, p, red);
+  kern<<<2 * pairs, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, ma2, mb2, mc, p, red);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 
 }  // namespace
 
-int tx_gemm_pair_launch(const void* A, const void* B, const txg::GemmParams& p, long long lda, long long ldb,
-                        int a_mn, int b_mn, int max_ctas, cudaStream_t stream) {
+int tx_gemm_pair_launch(const void* A, const void* B, const void* A2, const void* B2, const txg::GemmParams& p,
+                        long long lda, long long ldb, long long lda2, long long ldb2, int a_mn, int b_mn, int max_ctas,
+                        cudaStream_t stream) {
   const int sel = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
   switch (sel) {
-    case 0: return launch<false, false>(A, B, p, lda, ldb, max_ctas, stream);
-    case 1: return launch<false, true>(A, B, p, lda, ldb, max_ctas, stream);
-    case 2: return launch<true, false>(A, B, p, lda, ldb, max_ctas, stream);
-    default: return launch<true, true>(A, B, p, lda, ldb, max_ctas, stream);
+    case 0: return launch<false, false>(A, B, A2, B2, p, lda, ldb, lda2, ldb2, max_ctas, stream);
+    case 1: return launch<false, true>(A, B, A2, B2, p, lda, ldb, lda2, ldb2, max_ctas, stream);
+    case 2: return launch<true, false>(A, B, A2, B2, p, lda, ldb, lda2, ldb2, max_ctas, stream);
+    default: return launch<true, true>(A, B, A2, B2, p, lda, ldb, lda2, ldb2, max_ctas, stream);
   }
 }

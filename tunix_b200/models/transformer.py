@@ -160,7 +160,19 @@ class Linear(nn.Module):
     self.lora_b[key] = b
     self.lora_scale[key] = alpha / rank
 
+  def _adapters(self):
+    out = []
+    for key, a in self.lora_a.items():
+      lo, hi = self.slices["" if key == "w" else key]
+      out.append((a, self.lora_b[key], self.lora_scale[key], lo, hi))
+    return out
+
   def forward(self, x):
+    if len(self.lora_a) and self.quant is None and self.b is None and x.is_cuda:
+      from ..ops import lora as lora_ops
+      adapters = self._adapters()
+      if lora_ops.supported(x.reshape(-1, x.shape[-1]), self.w, adapters):
+        return lora_ops.fused_lora_linear(x, self.w, adapters)      # adapter folded into the base GEMM
     y = F.linear(x, self.weight(), self.b)
     if len(self.lora_a):
       for key, a in self.lora_a.items():

@@ -55,6 +55,7 @@ def _declare(lib):
       "tx_flash_bwd": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, I, F, P, P],
       "tx_flash_fwd_seg": [P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, I, F, P, P, P, P],
       "tx_flash_bwd_seg": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, L, L, L, L, L, L, L, L, I, F, P, P, P, P],
+      "tx_gemm_bf16_dual": [P, P, P, P, P, I, I, I, I, L, L, L, L, L, I, I, I, I, F, P, I, P],
       "tx_kv_page_write": [P, P, L, L, P, P, P, I, I, I, P],
       "tx_paged_decode_attn": [P, L, P, P, P, I, P, I, I, I, I, I, F, I, P, P, P, L, P],
       "tx_paged_decode_attn_tc": [P, L, P, P, P, I, P, I, I, I, I, I, L, F, I, P, P, P, L, P, P],
