@@ -36,6 +36,9 @@ def _rules(gemma_norms: bool) -> List[Tuple[re.Pattern, str]]:
       (lay + r"mlp\.down_proj\.weight$", r"layers.\1.mlp.down_proj.w"),
       (lay + r"mlp\.gate\.weight$", r"layers.\1.mlp.router.w"),
       (lay + r"mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$", r"layers.\1.mlp.experts.\2.\3"),
+      # experts already stacked ([E, 2F, D] gate-then-up and [E, D, F]), as newer exports store them
+      (lay + r"mlp\.experts\.gate_up_proj$", r"layers.\1.mlp.gate_up_proj"),
+      (lay + r"mlp\.experts\.down_proj$", r"layers.\1.mlp.down_proj"),
   ]
   if gemma_norms:
     rules += [(lay + r"post_attention_layernorm\.weight$", r"layers.\1.post_attn_norm.w"),
