@@ -32,3 +32,14 @@ def test_moe_expert_parallel_two_ranks_cpu(tmp_path):
   for res in torch.load(out, weights_only=False):
     assert res["shape"][0] == 2
     assert res["fwd"] < 1e-5 and res["dx"] < 1e-4 and res["dw"] < 1e-4, res
+
+
+def test_tensor_parallel_two_ranks_cpu(tmp_path):
+  """Head- and hidden-sharded decoder equals the full model: logits, replicated and sharded gradients."""
+  out = str(tmp_path / "tp.pt")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29661", os.path.join(HERE, "_tp_worker.py"), "--out", out]
+  r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2"), capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["fwd"] < 1e-4 and res["d_embed"] < 1e-5 and res["d_norm"] < 1e-5 and res["d_down"] < 1e-5, res

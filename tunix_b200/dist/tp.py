@@ -1,0 +1,130 @@
+"""Megatron-style tensor parallelism for the decoder (dense layers).
+
+`shard_model_tp(model, mesh, axis="tp")` returns this rank's slice of the model: query and kv
+heads are split over the ranks of `axis` (rows of the fused qkv projection, columns of the
+output projection), the MLP's hidden units likewise (rows of gate and of up, columns of down).
+Embedding, norms and lm_head stay replicated. The two partial sums per layer (after `o_proj`
+and after `down_proj`) are all-reduced; gradients flowing back into the replicated activations
+are all-reduced where the forward was an identity (the f / g pair of Megatron-LM). The KV
+cache (dense or paged) shrinks with the local kv-head count without further changes, and a
+rollout engine on each rank samples identical tokens because the all-reduced logits are
+bitwise equal on all ranks and sampling is keyed by (seed, step, row).
+
+Reference behaviour: the `'tp'` mesh axis on heads and FFN hidden units
+(tunix/models/qwen3/model.py:111-134); here the collectives are explicit NCCL all-reduces.
+"""
+from __future__ import annotations
+
+import copy
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class _CopyToRegion(torch.autograd.Function):
+  """Identity forward, all-reduce of the gradient backward (entry of a column-parallel layer)."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    ctx.group = group
+    return x
+
+  @staticmethod
+  def backward(ctx, g):
+    g = g.contiguous()
+    dist.all_reduce(g, group=ctx.group)
+    return g, None
+
+
+class _ReduceFromRegion(torch.autograd.Function):
+  """All-reduce forward, identity backward (exit of a row-parallel layer)."""
+
+  @staticmethod
+  def forward(ctx, x, group):
+    x = x.contiguous()
+    dist.all_reduce(x, group=group)
+    return x
+
+  @staticmethod
+  def backward(ctx, g):
+    return g, None
+
+
+class _ColumnEntry(torch.nn.Module):
+
+  def __init__(self, inner: torch.nn.Module, group):
+    super().__init__()
+    self.inner, self.group = inner, group
+
+  def forward(self, x, *a, **k):
+    return self.inner(_CopyToRegion.apply(x, self.group), *a, **k)
+
+  def __getattr__(self, name):
+    try:
+      return super().__getattr__(name)
+    except AttributeError:
+      return getattr(super().__getattr__("inner"), name)
+
+
+class _RowExit(_ColumnEntry):
+
+  def forward(self, x, *a, **k):
+    return _ReduceFromRegion.apply(self.inner(x, *a, **k), self.group)
+
+
+def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
+  """Takes rank r's share of every row section (sizes in `sections`) of w."""
+  parts, off = [], 0
+  for n in sections:
+    per = n // tp
+    parts.append(w[off + r * per: off + (r + 1) * per])
+    off += n
+  return torch.cat(parts, dim=0).clone()
+
+
+def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp") -> torch.nn.Module:
+  """Builds this rank's tensor-parallel slice from a full (replicated) model and returns it."""
+  from ..models.transformer import Transformer
+  tp, r = mesh.axis_size(axis), mesh.axis_index(axis)
+  if tp == 1:
+    return model
+  group = mesh.group(axis)
+  cfg = model.config
+  if cfg.is_moe:
+    raise NotImplementedError("tensor parallelism covers dense layers; shard experts with dist.moe")
+  N, K, H, Fh = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.hidden_dim
+  if N % tp or K % tp or Fh % tp:
+    raise ValueError(f"heads {N}/{K} and hidden {Fh} must divide by tp={tp}")
+  # q_pre_attn scaling depends on the full head geometry: freeze it before the head counts change
+  local = cfg.replace(num_heads=N // tp, num_kv_heads=K // tp, hidden_dim=Fh // tp,
+                      query_pre_attn_scalar=cfg.query_pre_attn_scalar)
+  dev = next(model.parameters()).device
+  out = Transformer(local, device=dev)
+  src = dict(model.named_parameters())
+  with torch.no_grad():
+    for name, p in out.named_parameters():
+      w = src[name].data
+      if name.endswith("attn.qkv_proj.w") or name.endswith("attn.qkv_proj.b"):
+        p.copy_(_slice_rows(w, (N * H, K * H, K * H), tp, r))
+      elif name.endswith("attn.o_proj.w"):
+        per = N * H // tp
+        p.copy_(w[:, r * per:(r + 1) * per])
+      elif name.endswith("mlp.gate_up_proj.w"):
+        p.copy_(_slice_rows(w, (Fh, Fh), tp, r))
+      elif name.endswith("mlp.down_proj.w"):
+        per = Fh // tp
+        p.copy_(w[:, r * per:(r + 1) * per])
+      else:
+        p.copy_(w)
+  for layer in out.layers:
+    layer.attn.qkv_proj = _ColumnEntry(layer.attn.qkv_proj, group)
+    layer.attn.o_proj = _RowExit(layer.attn.o_proj, group)
+    layer.mlp.gate_up_proj = _ColumnEntry(layer.mlp.gate_up_proj, group)
+    layer.mlp.down_proj = _RowExit(layer.mlp.down_proj, group)
+  # the fused decoder-layer node bypasses the wrapped projections
+  out.config = local.replace(fused_layers=False)
+  for layer in out.layers:
+    layer.cfg = out.config
+  out.tp_group, out.tp_size, out.tp_rank = group, tp, r
+  return out
