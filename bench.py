@@ -38,8 +38,13 @@ def parse_args():
   ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
   ap.add_argument("--remat", default="auto", choices=["auto", "none", "block"])
   ap.add_argument("--no-e2e", action="store_true")
-  ap.add_argument("--workload", default="sft", choices=["sft", "grpo"],
-                  help="sft: Llama-3.1-8B full-weight SFT (default, the headline); grpo: Qwen3-8B GRPO step")
+  ap.add_argument("--workload", default="sft", choices=["sft", "grpo", "dpo"],
+                  help="sft: Llama-3.1-8B full-weight SFT (default, the headline); grpo: Qwen3-8B GRPO step; "
+                       "dpo: Qwen3-4B DPO with LoRA")
+  ap.add_argument("--dpo-pairs", type=int, default=32)
+  ap.add_argument("--dpo-prompt-len", type=int, default=512)
+  ap.add_argument("--dpo-response-len", type=int, default=512)
+  ap.add_argument("--dpo-micro", type=int, default=4, help="pairs per micro-step per GPU")
   ap.add_argument("--grpo-prompts", type=int, default=64)
   ap.add_argument("--grpo-generations", type=int, default=8)
   ap.add_argument("--grpo-prompt-len", type=int, default=256)
@@ -116,6 +121,10 @@ def main():
   args = parse_args()
   if args.impl == "reference":
     reference_arm(args)
+    return
+  if args.workload == "dpo":
+    from tunix_b200.sft.dpo import dpo_bench
+    dpo_bench.run(args, ClockSampler)
     return
   if args.workload == "grpo":
     from tunix_b200.rl import grpo_bench

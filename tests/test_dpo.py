@@ -86,3 +86,38 @@ def test_orpo_trains_without_reference_and_tokenised_input():
   assert l[-1] < l[0]
   with pytest.raises(ValueError):
     tr._prepare_inputs({"foo": 1})
+
+
+def test_reference_with_adapters_off_shares_the_backbone():
+  """DPO with a LoRA policy and `ReferenceWithAdaptersOff`: at zero adapter output policy == reference, so the
+  first loss is log 2; adapters train, the backbone does not, and the reference ignores the adapters."""
+  import numpy as np
+  from tunix_b200 import optim
+  from tunix_b200.models import lora
+  from tunix_b200.models.transformer import ModelConfig, Transformer
+  from tunix_b200.sft.dpo import dpo_trainer as dpo
+  torch.manual_seed(0)
+  cfg = ModelConfig(num_layers=2, vocab_size=64, embed_dim=32, hidden_dim=64, num_heads=4, head_dim=8, num_kv_heads=2)
+  model = Transformer(cfg).init_weights(seed=0, scale=0.3)
+  lora.apply_lora_to_model(model, rank=4, alpha=8.0)
+  ref = dpo.ReferenceWithAdaptersOff(model)
+  assert not list(ref.parameters())
+  g = torch.Generator().manual_seed(1)
+  ti = dpo.TrainingInput(prompt_ids=torch.randint(1, 64, (4, 6), generator=g), prompt_mask=torch.ones(4, 6),
+                         chosen_ids=torch.randint(1, 64, (4, 5), generator=g), chosen_mask=torch.ones(4, 5),
+                         rejected_ids=torch.randint(1, 64, (4, 5), generator=g), rejected_mask=torch.ones(4, 5))
+  tc = dpo.DPOTrainingConfig(eval_every_n_steps=100, max_steps=6, pbar_description=None, beta=0.5)
+  tr = dpo.DPOTrainer(model, ref, optim.adamw(5e-2), tc)
+  base = {n: p.clone() for n, p in model.named_parameters() if "lora" not in n}
+  tr.train([ti] * 6)
+  losses = tr.metrics_logger.get_metric_history("", "loss", "train")
+  np.testing.assert_allclose(losses[0], np.log(2.0), rtol=1e-4)
+  assert losses[-1] < losses[0]
+  for n, p in model.named_parameters():
+    if "lora" not in n:
+      assert torch.equal(p, base[n])
+  toks = torch.randint(1, 64, (2, 7), generator=g)
+  with_adapters, _ = model(toks, None, None, None)
+  without, _ = ref(toks, None, None, None)
+  assert not torch.allclose(with_adapters, without)
+  assert all(v != 0 for m in model.modules() if hasattr(m, "lora_scale") for v in m.lora_scale.values())

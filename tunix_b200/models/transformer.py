@@ -167,8 +167,14 @@ class Linear(nn.Module):
       out.append((a, self.lora_b[key], self.lora_scale[key], lo, hi))
     return out
 
+  def _lora_active(self) -> bool:
+    # adapters whose scale was zeroed (reference pass over a shared backbone) cost nothing
+    return len(self.lora_a) > 0 and any(v != 0 for v in self.lora_scale.values())
+
   def forward(self, x):
-    if len(self.lora_a) and self.quant is None and self.b is None and x.is_cuda:
+    if not self._lora_active():
+      return F.linear(x, self.weight(), self.b)
+    if self.quant is None and self.b is None and x.is_cuda:
       from ..ops import lora as lora_ops
       adapters = self._adapters()
       if lora_ops.supported(x.reshape(-1, x.shape[-1]), self.w, adapters):

@@ -63,6 +63,34 @@ class TrainExample:
   full_mask: Optional[torch.Tensor] = None
 
 
+class ReferenceWithAdaptersOff(torch.nn.Module):
+  """The frozen reference of a LoRA policy: the same module with every adapter's scale set to zero for the
+  duration of the call, so no second copy of the backbone is held."""
+
+  def __init__(self, model: torch.nn.Module):
+    super().__init__()
+    object.__setattr__(self, "_policy", model)      # not registered: its parameters stay the policy's
+
+  @property
+  def config(self):
+    return self._policy.config
+
+  def forward(self, *args, **kwargs):
+    saved = []
+    for mod in self._policy.modules():
+      sc = getattr(mod, "lora_scale", None)
+      if isinstance(sc, dict) and sc:
+        saved.append((mod, dict(sc)))
+        for k in sc:
+          sc[k] = 0.0
+    try:
+      with torch.no_grad():
+        return self._policy(*args, **kwargs)
+    finally:
+      for mod, sc in saved:
+        mod.lora_scale.update(sc)
+
+
 @dataclasses.dataclass(kw_only=True)
 class DPOTrainingConfig(TrainingConfig):
   algorithm: str = "dpo"            # "dpo" or "orpo"
@@ -238,7 +266,8 @@ class DPOTrainer(peft_trainer.PeftTrainer):
     images = ti.images
     if images is not None:
       images = torch.cat([t(images), t(images)], 0)
-    attn = sft_utils.make_causal_attn_mask(mask)
+    # rows without padding need no explicit mask: the plain causal path runs on the flash kernels
+    attn = None if bool(mask.bool().all()) else sft_utils.make_causal_attn_mask(mask)
     positions = sft_utils.build_positions_from_mask(mask)
     keep = comp_ids.shape[1]
     rc = rr = None
