@@ -204,3 +204,28 @@ def test_orchestrator_groups_and_propagates_failure():
   assert sorted(i.pair_index for b in batches for i in b) == list(range(6))
   with pytest.raises(RuntimeError, match="reward exploded"):
     asyncio.run(run(fail_at=3))
+
+
+def test_frozenlake_environment_and_oracle():
+  from tunix_b200.examples import frozenlake
+  from tunix_b200.examples.frozenlake import env as fl
+  for seed in range(5):
+    e = frozenlake.FrozenLakeEnv({"size": 5, "p_hole": 0.3, "seed": seed}, max_steps=20)
+    obs, _ = e.reset()
+    assert "P" in obs["question"] and "G" in obs["question"]
+    path = fl.shortest_path_moves(e)
+    assert path
+    reward = done = None
+    for mv in path:
+      obs, reward, done, info = e.step(f"I think ```{mv.capitalize()}```")
+      assert info["valid"]
+    assert done and reward == 1.0
+  e = frozenlake.FrozenLakeEnv.from_dict({"size": 3, "seed": 1, "max_steps": 2})
+  e.reset()
+  _, r, d, info = e.step("no idea")
+  assert not info["valid"] and r == 0.0 and not d
+  _, r, d, _ = e.step("left")
+  assert d                                  # step budget reached
+  assert fl.parse_move("first Up, then ```Down```") == "down"
+  agent = frozenlake.FrozenLakeAgent()
+  assert "frozen lake" in agent.system_prompt
