@@ -11,10 +11,13 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--out", required=True)
+  ap.add_argument("--device", default="cpu")
   a = ap.parse_args()
   import torch.distributed as dist
   from tunix_b200.dist import mesh as mesh_lib, tp as tp_lib
   from tunix_b200.models.transformer import ModelConfig, Transformer
+  if a.device == "cuda":
+    return main_cuda(a)
   mesh_lib.init_distributed("gloo", timeout_s=120)
   world, rank = dist.get_world_size(), dist.get_rank()
   mesh = mesh_lib.create_mesh((world,), ("tp",))
@@ -40,6 +43,48 @@ def main():
   res["d_down"] = float((gfull - pp["layers.1.mlp.down_proj.inner.w"].grad).abs().max())
   # decoding with a KV cache works on the slice too (fewer kv heads per rank)
   from tunix_b200.generate import utils as gen_utils  # noqa: F401
+  allres = [None] * world
+  dist.all_gather_object(allres, res)
+  if rank == 0:
+    torch.save(allres, a.out)
+  dist.barrier()
+  dist.destroy_process_group()
+
+
+def main_cuda(a):
+  """2 GPUs: the row-parallel exits run the GEMM with the all-reduce epilogue over peer memory."""
+  import torch.distributed as dist
+  from tunix_b200.dist import mesh as mesh_lib, tp as tp_lib
+  from tunix_b200.models.transformer import ModelConfig, Transformer
+  from tunix_b200.ops import _lib
+  local = int(os.environ.get("LOCAL_RANK", "0"))
+  torch.cuda.set_device(local)
+  dev = torch.device("cuda", local)
+  mesh_lib.init_distributed("nccl", timeout_s=120)
+  world, rank = dist.get_world_size(), dist.get_rank()
+  mesh = mesh_lib.create_mesh((world,), ("tp",))
+  cfg = ModelConfig(num_layers=2, vocab_size=512, embed_dim=512, hidden_dim=1024, num_heads=4, head_dim=128,
+                    num_kv_heads=2, dtype=torch.bfloat16, max_position=64)
+  full = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.05)
+  part = tp_lib.shard_model_tp(full, mesh, fused_max_rows=64)
+  assert isinstance(part.layers[0].attn.o_proj, tp_lib.FusedRowExit)
+  torch.manual_seed(5)
+  res = {}
+  with torch.no_grad():
+    for i, L in enumerate((16, 32, 8)):                  # repeated calls reuse the sum buffers
+      toks = torch.randint(0, 512, (2, L), device=dev)
+      pos = torch.arange(L, device=dev)[None].expand(2, L)
+      want, _ = full(toks, pos, None, None)
+      got, _ = part(toks, pos, None, None)
+      res[f"fwd{i}"] = float((want.float() - got.float()).abs().max() / want.float().abs().max())
+  torch.cuda.synchronize()
+  _lib.check_status()
+  # with gradients enabled the exits fall back to GEMM + all-reduce
+  toks = torch.randint(0, 512, (2, 16), device=dev)
+  pos = torch.arange(16, device=dev)[None].expand(2, 16)
+  got, _ = part(toks, pos, None, None)
+  got.float().pow(2).mean().backward()
+  res["grad_ok"] = all(p.grad is not None for n, p in part.named_parameters() if "inner.w" in n)
   allres = [None] * world
   dist.all_gather_object(allres, res)
   if rank == 0:

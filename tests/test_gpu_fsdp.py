@@ -51,3 +51,18 @@ def test_grpo_data_parallel_two_gpus(kernel_lib, tmp_path):
   got = torch.load(out, weights_only=False)
   assert got["steps"] == 2 and got["moved"] > 0
   assert abs(got["checksums"][0] - got["checksums"][1]) < 1e-6 * max(1.0, abs(got["checksums"][0]))
+
+
+def test_tensor_parallel_fused_allreduce_two_gpus(kernel_lib, tmp_path):
+  """TP=2 decoder whose row-parallel exits add their GEMM tiles into both ranks' buffers over NVLink."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  out = str(tmp_path / "tp.pt")
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29614", os.path.join(HERE, "_tp_worker.py"), "--out", out, "--device", "cuda"]
+  r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["grad_ok"]
+    assert max(res["fwd0"], res["fwd1"], res["fwd2"]) < 3e-2, res

@@ -18,6 +18,9 @@ struct GemmParams {
                    // fp32 buffer and the epilogue adds into it atomically (single-CTA kernel only)
   int K2;          // > 0: a second operand pair (A2 [M,K2], B2 [N,K2], same layouts) is accumulated after the first:
                    // C = A B^T + A2 B2^T in one pass (fused low-rank adapters); 0 otherwise
+  int n_red;       // > 0: all-reduce epilogue - the tile is added (fp32 vector atomics) into each of the n_red
+  float* red_dst[8];   // zero-filled [M, N] buffers, one per rank of a tensor-parallel group (peer-mapped memory),
+                       // so after every rank's GEMM each buffer holds the full sum (single-CTA kernel only)
 };
 
 // Walks tiles so that `group_m` consecutive row-blocks share their B tiles while they are hot in L2.
@@ -34,15 +37,26 @@ __device__ __forceinline__ void tile_coords(int t, int mb, int nb, int group_m, 
 // r[0..31]: accumulator columns [col, col + 32) of row `row`.
 __device__ __forceinline__ void store_row_chunk(const GemmParams& p, int row, int col, const uint32_t (&r)[32]) {
   if (row >= p.M || col >= p.N) return;
-  if (p.k_splits > 1) {
-    float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col;
+  if (p.k_splits > 1 || p.n_red > 0) {
+    const int nd = p.n_red > 0 ? p.n_red : 1;
+    for (int d = 0; d < nd; ++d) {
+      float* base = p.n_red > 0 ? p.red_dst[d] : reinterpret_cast<float*>(p.C);
+      float* dst = base + static_cast<long long>(row) * p.ldc + col;
+      if (p.n_red > 0) {
+        // peer-mapped destinations: plain scalar fp32 atomics, which NVLink carries natively
 #pragma unroll
-    for (int j = 0; j < 32; j += 4) {
-      if (col + j < p.N)
-        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j),
-                     "f"(__uint_as_float(r[j]) * p.alpha), "f"(__uint_as_float(r[j + 1]) * p.alpha),
-                     "f"(__uint_as_float(r[j + 2]) * p.alpha), "f"(__uint_as_float(r[j + 3]) * p.alpha)
-                     : "memory");
+        for (int j = 0; j < 32; ++j)
+          if (col + j < p.N) atomicAdd(dst + j, __uint_as_float(r[j]) * p.alpha);
+        continue;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        if (col + j < p.N)
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + j),
+                       "f"(__uint_as_float(r[j]) * p.alpha), "f"(__uint_as_float(r[j + 1]) * p.alpha),
+                       "f"(__uint_as_float(r[j + 2]) * p.alpha), "f"(__uint_as_float(r[j + 3]) * p.alpha)
+                       : "memory");
+      }
     }
     return;
   }

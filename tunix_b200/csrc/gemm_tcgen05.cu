@@ -324,7 +324,7 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
       (reinterpret_cast<uintptr_t>(C) & 15))
     return 3;
-  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1, K2};
+  GemmParams p{C, ldc, M, N, K, c_fp32, accumulate, alpha, status, 1, K2, 0, {nullptr}};
   // Large problems: 256 x 256 tiles on CTA pairs (cta_group::2) halve the B traffic per SM.
   {
     const long long tiles_pair = static_cast<long long>((M + 255) / 256) * ((N + 255) / 256);
@@ -347,7 +347,7 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
       float* ws = splitk_workspace();
       if (ws == nullptr) return 300;
       if (cudaMemsetAsync(ws, 0, sizeof(float) * static_cast<size_t>(M) * N, stream) != cudaSuccess) return 400;
-      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks, 0};
+      GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks, 0, 0, {nullptr}};
       int rc;
       switch (sel0) {
         case 0: rc = launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
@@ -393,4 +393,47 @@ extern "C" int tx_gemm_bf16(const void* A, const void* B, void* C, int M, int N,
                             float alpha, int* status, int max_ctas, cudaStream_t stream) {
   return tx_gemm_bf16_dual(A, B, nullptr, nullptr, C, M, N, K, 0, lda, ldb, 0, 0, ldc, a_mn, b_mn, c_fp32, accumulate,
                            alpha, status, max_ctas, stream);
+}
+
+// Rounds a fp32 [M, N] sum buffer (row stride N) to bf16 C (row stride ldc). N a multiple of 4.
+extern "C" int tx_f32_sum_to_bf16(const float* ws, void* C, long long ldc, int M, int N, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (N & 3) return 1;
+  const long long n4 = static_cast<long long>(M) * (N / 4);
+  const int blocks = static_cast<int>(n4 / 256 + 1 < 592 ? n4 / 256 + 1 : 592);
+  splitk_finish_kernel<<<blocks, 256, 0, stream>>>(ws, static_cast<__nv_bfloat16*>(C), ldc, M, N);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+// Row-parallel linear of a tensor-parallel group with the all-reduce fused into the GEMM epilogue:
+// every rank computes its partial product A B^T (its shard of K) and adds each output tile, with fp32 vector
+// atomics over NVLink, into the zero-filled [M, N] fp32 buffer of every rank (`dst[i]`, i < n_peers, peer-mapped
+// pointers, own buffer included). Once all ranks' kernels have finished (a barrier the caller provides) every
+// buffer holds the full sum. Plain peer stores only: no multicast. M x N x K in the caller's usual layouts.
+extern "C" int tx_gemm_bf16_allreduce(const void* A, const void* B, void* const* dst, int n_peers, int M, int N, int K,
+                                      long long lda, long long ldb, int a_mn, int b_mn, float alpha, int* status,
+                                      cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || n_peers < 1 || n_peers > 8 || !dst) return 1;
+  if ((lda & 7) || (ldb & 7) || (N & 7)) return 2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return 3;
+  GemmParams p{nullptr, N, M, N, K, 1, 0, alpha, status, 1, 0, n_peers, {nullptr}};
+  for (int i = 0; i < n_peers; ++i) {
+    if (!dst[i] || (reinterpret_cast<uintptr_t>(dst[i]) & 15)) return 3;
+    p.red_dst[i] = static_cast<float*>(dst[i]);
+  }
+  const int sel = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (M <= BM) {
+    switch (sel) {
+      case 0: return launch<64, false, false>(A, B, p, lda, ldb, stream, 0);
+      case 1: return launch<64, false, true>(A, B, p, lda, ldb, stream, 0);
+      case 2: return launch<64, true, false>(A, B, p, lda, ldb, stream, 0);
+      default: return launch<64, true, true>(A, B, p, lda, ldb, stream, 0);
+    }
+  }
+  switch (sel) {
+    case 0: return launch<256, false, false>(A, B, p, lda, ldb, stream, 0);
+    case 1: return launch<256, false, true>(A, B, p, lda, ldb, stream, 0);
+    case 2: return launch<256, true, false>(A, B, p, lda, ldb, stream, 0);
+    default: return launch<256, true, true>(A, B, p, lda, ldb, stream, 0);
+  }
 }

@@ -73,6 +73,57 @@ class _RowExit(_ColumnEntry):
     return _ReduceFromRegion.apply(self.inner(x, *a, **k), self.group)
 
 
+class FusedRowExit(torch.nn.Module):
+  """Row-parallel projection whose all-reduce runs inside the GEMM epilogue (inference path).
+
+  Every rank owns a zero-filled fp32 [max_rows, out] buffer in peer-mapped memory. A call zeroes the rows it
+  needs, meets the other ranks at a device-side barrier, runs `tx_gemm_bf16_allreduce` - each output tile is
+  added with fp32 atomics over NVLink into every rank's buffer - meets them again, and rounds its buffer to
+  bf16. Two bounded barriers and three launches replace GEMM + NCCL all-reduce. With gradients enabled,
+  on the CPU, or for rows beyond `max_rows` the call falls back to GEMM + all-reduce."""
+
+  def __init__(self, inner: torch.nn.Module, group, symm, max_rows: int):
+    super().__init__()
+    self.inner, self.group, self.symm, self.max_rows = inner, group, symm, int(max_rows)
+    self.out_dim = inner.out_dim
+    name = f"tp_sum_{id(self)}"
+    self.buf = symm.alloc(name, self.max_rows * self.out_dim, torch.float32)
+    self._name = name
+
+  def __getattr__(self, name):
+    try:
+      return super().__getattr__(name)
+    except AttributeError:
+      return getattr(super().__getattr__("inner"), name)
+
+  def forward(self, x):
+    lin = self.inner
+    x2 = x.reshape(-1, x.shape[-1])
+    M = x2.shape[0]
+    fused = (not torch.is_grad_enabled() and x2.is_cuda and x2.dtype == torch.bfloat16 and M <= self.max_rows
+             and M % 8 == 0 and lin.b is None and lin.quant is None and not len(lin.lora_a)
+             and x2.stride(1) == 1 and x2.data_ptr() % 16 == 0)
+    if not fused:
+      return _ReduceFromRegion.apply(lin(x), self.group)
+    from ..ops import _lib
+    from . import symm as symm_lib
+    lib = _lib.require()
+    N = self.out_dim
+    ws = self.buf[:M * N]
+    ws.zero_()
+    self.symm.barrier()                      # every rank's buffer is clean before anybody adds into it
+    ptrs = symm_lib._ptr_array(self.symm.peer_ptrs[self._name])
+    rc = lib.tx_gemm_bf16_allreduce(x2.data_ptr(), lin.w.data_ptr(), ptrs, self.symm.world, M, N, x2.shape[1],
+                                    x2.stride(0), lin.w.stride(0), 0, 0, 1.0,
+                                    _lib.status_word(x2.device).data_ptr(), _lib.stream_ptr())
+    _lib.check_rc(rc, "tx_gemm_bf16_allreduce")
+    self.symm.barrier()                      # every rank's partial sums have landed
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=x2.device)
+    _lib.check_rc(lib.tx_f32_sum_to_bf16(ws.data_ptr(), out.data_ptr(), N, M, N, _lib.stream_ptr()),
+                  "tx_f32_sum_to_bf16")
+    return out.view(*x.shape[:-1], N)
+
+
 def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
   """Takes rank r's share of every row section (sizes in `sections`) of w."""
   parts, off = [], 0
@@ -83,8 +134,10 @@ def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
   return torch.cat(parts, dim=0).clone()
 
 
-def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp") -> torch.nn.Module:
-  """Builds this rank's tensor-parallel slice from a full (replicated) model and returns it."""
+def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_rows: int = 0) -> torch.nn.Module:
+  """Builds this rank's tensor-parallel slice from a full (replicated) model and returns it.
+  `fused_max_rows > 0` (CUDA ranks on one NVLink domain) makes the two exits of every layer `FusedRowExit`s
+  for up to that many token rows per call (decode and chunked prefill of a rollout engine)."""
   from ..models.transformer import Transformer
   tp, r = mesh.axis_size(axis), mesh.axis_index(axis)
   if tp == 1:
@@ -117,11 +170,26 @@ def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp") -> torch.nn.M
         p.copy_(w[:, r * per:(r + 1) * per])
       else:
         p.copy_(w)
+  symm = None
+  if fused_max_rows > 0 and dev.type == "cuda":
+    from . import symm as symm_lib
+    symm = symm_lib.SymmetricBuffers(group, dev)
   for layer in out.layers:
     layer.attn.qkv_proj = _ColumnEntry(layer.attn.qkv_proj, group)
-    layer.attn.o_proj = _RowExit(layer.attn.o_proj, group)
     layer.mlp.gate_up_proj = _ColumnEntry(layer.mlp.gate_up_proj, group)
-    layer.mlp.down_proj = _RowExit(layer.mlp.down_proj, group)
+    if symm is not None:
+      layer.attn.o_proj = FusedRowExit(layer.attn.o_proj, group, symm, fused_max_rows)
+      layer.mlp.down_proj = FusedRowExit(layer.mlp.down_proj, group, symm, fused_max_rows)
+    else:
+      layer.attn.o_proj = _RowExit(layer.attn.o_proj, group)
+      layer.mlp.down_proj = _RowExit(layer.mlp.down_proj, group)
+  if symm is not None:
+    symm.rendezvous()
+    for layer in out.layers:
+      layer.attn.o_proj.buf.zero_()
+      layer.mlp.down_proj.buf.zero_()
+    torch.cuda.synchronize(dev)
+    dist.barrier(group=group)
   # the fused decoder-layer node bypasses the wrapped projections
   out.config = local.replace(fused_layers=False)
   for layer in out.layers:
