@@ -309,3 +309,53 @@ def test_image_and_audio_processors():
     ap.process_gemma4_inputs([[a1, a1, a1]], [np.array([258881] * 3)], tok, max_audio_clips=2)
   with pytest.raises(ValueError, match="placeholders"):
     ap.process_gemma4_inputs([a1], [np.array([1, 2])], tok)
+
+
+def test_vllm_sampler_adapter_with_a_fake_engine():
+  """Everything around the engine: config mapping, HF config export, tokenisation and padding, the batching
+  driver thread, output assembly (EOS stripping, log-probs) and HF-named weight sync."""
+  import types as pytypes
+  from tunix_b200.common.configs import RolloutConfig
+  from tunix_b200.generate import vllm_sampler as vs
+  model = toy_model(0)
+  rc = RolloutConfig(max_tokens_to_generate=4, max_prompt_length=6, kv_cache_size=32, temperature=0.7, top_k=5,
+                     rollout_vllm_server_mode=True, rollout_vllm_server_mode_submission_threshold=2,
+                     rollout_vllm_server_mode_submission_timeout_s=0.2, rollout_vllm_hbm_utilization=0.3)
+  cfg = vs.VllmConfig.from_rollout_config(rc)
+  assert cfg.server_mode and cfg.max_model_len == 32 and cfg.hbm_utilization == 0.3
+  args = cfg.engine_args("/some/dir")
+  assert args["load_format"] == "dummy" and args["gpu_memory_utilization"] == 0.3
+  hf = vs.hf_config_dict(model.config)
+  assert hf["num_key_value_heads"] == 2 and hf["architectures"][0].endswith("ForCausalLM")
+
+  class FakeLLM:
+    def __init__(self):
+      self.calls, self.loaded = [], None
+    def generate(self, prompts, params, use_tqdm=False):
+      self.calls.append(len(prompts))
+      outs = []
+      for p in prompts:
+        ids = p["prompt_token_ids"]
+        toks = [ids[-1] + 1, ids[-1] + 2, 2]            # ends with EOS (2)
+        lps = [{t: pytypes.SimpleNamespace(logprob=-0.5 * (k + 1))} for k, t in enumerate(toks)]
+        outs.append(pytypes.SimpleNamespace(outputs=[pytypes.SimpleNamespace(token_ids=toks, logprobs=lps)]))
+      return outs
+    def load_weights(self, weights):
+      self.loaded = dict(weights)
+
+  llm = FakeLLM()
+  s = vs.VllmSampler(ToyTokenizer(), cfg, model=model, llm=llm)
+  assert "model.layers.0.self_attn.q_proj.weight" in llm.loaded and "lm_head.weight" in llm.loaded
+  import threading
+  results = {}
+  def ask(i):
+    results[i] = s([f"alpha beta {i}", "gamma"], 4, max_prompt_length=6, temperature=0.7, return_logprobs=True)
+  ts = [threading.Thread(target=ask, args=(i,)) for i in range(2)]
+  [t.start() for t in ts]
+  [t.join() for t in ts]
+  assert sum(llm.calls) == 4 and len(llm.calls) <= 2      # the driver merged or serialised the two requests
+  out = results[0]
+  assert out.padded_prompt_tokens.shape == (2, 6) and out.padded_prompt_tokens[1, 0] == 0
+  assert all(len(t) == 2 for t in out.tokens)             # the EOS was stripped
+  assert out.logprobs[0] == [-0.5, -1.0]
+  s.close()
