@@ -360,6 +360,11 @@ class MoELayer(nn.Module):
       from ..dist import moe as dist_moe
       y = dist_moe.ep_forward(self, x2, topv, topi)
       return y.view(B, T, D)
+    from ..ops import moe as moe_ops
+    if moe_ops.grouped_supported(x2, self.gate_up_proj) and moe_ops.grouped_supported(x2, self.down_proj):
+      # one grouped tensor-core launch per projection, routing kept on the device
+      y = moe_ops.moe_forward_padded(x2, topv, topi, self.gate_up_proj, self.down_proj, cfg.activation)
+      return y.view(B, T, D)
     k = cfg.num_experts_per_tok
     flat_e = topi.reshape(-1)
     order = torch.argsort(flat_e, stable=True)

@@ -1,14 +1,26 @@
-"""Grouped expert MLP: rows sorted by expert, one GEMM chain per expert over its row range.
+"""Grouped expert MLP for mixture-of-experts layers.
 
-`grouped_mlp(xs, counts, gate_up [E,2F,D], down [E,D,F])` is the single-rank form of the
-reference's three grouped matmuls (tunix/models/qwen3/model.py:975-995)."""
+Two forms of the reference's three grouped matmuls (tunix/models/qwen3/model.py:975-995):
+
+* `grouped_mlp(xs, counts, ...)`: rows sorted by expert, a Python loop of dense GEMM chains, one per
+  expert (CPU, odd shapes, and the host-counted expert-parallel path).
+* `padded_layout` + `grouped_mlp_padded`: the CUDA path. Every expert's rows are placed in a block
+  padded with zero rows to a multiple of 128, the placement is computed on the device (no host
+  round trip for the counts), and each of gate|up, down and their gradients is ONE launch of the
+  grouped tcgen05 GEMM (`csrc/gemm_grouped.cu`) over all experts.
+"""
 from __future__ import annotations
 
-from typing import List
+import dataclasses
+from typing import List, Optional
 
 import torch
 
+from . import _lib
 from . import functional as F
+
+bf16 = torch.bfloat16
+TILE = 128
 
 
 def grouped_mlp(xs: torch.Tensor, counts: List[int], gate_up: torch.Tensor, down: torch.Tensor, kind: str,
@@ -25,3 +37,128 @@ def grouped_mlp(xs: torch.Tensor, counts: List[int], gate_up: torch.Tensor, down
   if not outs:
     return xs.new_zeros(xs.shape)
   return torch.cat(outs, dim=0)
+
+
+# ------------------------------------------------------------------------------ padded layout
+@dataclasses.dataclass
+class PaddedLayout:
+  """Where each routed row lives in the expert-major, 128-row-padded buffer."""
+  rows: int                  # static size of the buffer: a bound that holds for any routing
+  dest: torch.Tensor         # [n] int64: buffer row of routed row i (i = token * k + slot)
+  offsets: torch.Tensor      # [E + 1] int32: first buffer row of each expert (multiples of 128)
+  tile_expert: torch.Tensor  # [rows / 128] int32: expert of each row tile, -1 past the last block
+  num_experts: int
+
+
+def padded_rows(n: int, num_experts: int) -> int:
+  """Buffer rows that fit n routed rows however they fall on the experts."""
+  return (n + num_experts * (TILE - 1) + TILE - 1) // TILE * TILE
+
+
+def padded_layout(expert_ids: torch.Tensor, num_experts: int, counts: Optional[torch.Tensor] = None,
+                  rank_in_expert: Optional[torch.Tensor] = None) -> PaddedLayout:
+  """expert_ids [n]: expert of every routed row. All device-side; nothing is read back."""
+  n = expert_ids.numel()
+  E = num_experts
+  ids = expert_ids.reshape(-1).long()
+  if counts is None:
+    counts = torch.bincount(ids, minlength=E)
+  padded = (counts + (TILE - 1)) // TILE * TILE
+  offsets = torch.zeros(E + 1, dtype=torch.long, device=ids.device)
+  offsets[1:] = torch.cumsum(padded, 0)
+  if rank_in_expert is None:
+    order = torch.argsort(ids, stable=True)
+    start = torch.cumsum(counts, 0) - counts                     # first sorted position of each expert
+    rank_sorted = torch.arange(n, device=ids.device) - start[ids[order]]
+    rank_in_expert = torch.empty_like(rank_sorted).index_copy_(0, order, rank_sorted)
+  dest = offsets[ids] + rank_in_expert
+  rows = padded_rows(n, E)
+  tile_start = torch.arange(rows // TILE, device=ids.device) * TILE
+  te = torch.searchsorted(offsets[1:].contiguous(), tile_start, right=True)
+  te = torch.where(tile_start < offsets[E], te, torch.full_like(te, -1))
+  return PaddedLayout(rows, dest, offsets.int(), te.int(), E)
+
+
+def grouped_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+  """bf16 CUDA operands whose shapes the grouped kernel takes (`w` is [E, N, K])."""
+  if not (x.is_cuda and x.dtype == bf16 and w.dtype == bf16 and w.dim() == 3 and w.is_contiguous()):
+    return False
+  _, N, K = w.shape
+  return N % 64 == 0 and K % 8 == 0 and _lib.available()
+
+
+def _call(mode, a, b, c, lay: PaddedLayout, N, K, E, accumulate=False):
+  lib = _lib.require()
+  rc = lib.tx_gemm_grouped_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), lay.tile_expert.data_ptr(),
+                                lay.offsets.data_ptr(), mode, lay.rows, N, K, E, a.stride(0),
+                                b.stride(-2), c.stride(-2), int(c.dtype == torch.float32), int(accumulate), 1.0,
+                                _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, f"tx_gemm_grouped_bf16(mode={mode},R={lay.rows},N={N},K={K},E={E})")
+  return c
+
+
+class _GroupedLinear(torch.autograd.Function):
+  """y[r] = x[r] @ w[expert(r)]^T over the padded layout."""
+
+  @staticmethod
+  def forward(ctx, x, w, lay, first_expert):
+    E_all, N, K = w.shape
+    E = lay.num_experts
+    wv = w[first_expert:first_expert + E]
+    y = torch.zeros((lay.rows, N), dtype=bf16, device=x.device)     # rows of unused tiles stay zero
+    _call(0, x, wv, y, lay, N, K, E)
+    ctx.save_for_backward(x, w)
+    ctx.lay, ctx.first = lay, first_expert
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    x, w = ctx.saved_tensors
+    lay, first = ctx.lay, ctx.first
+    E_all, N, K = w.shape
+    E = lay.num_experts
+    dy = dy.contiguous()
+    wv = w[first:first + E]
+    dx = None
+    if ctx.needs_input_grad[0]:
+      # rows of unused tiles are never gathered; zero-fill so that they stay finite
+      dx = torch.zeros((lay.rows, K), dtype=bf16, device=dy.device)
+      _call(1, dy, wv, dx, lay, N, K, E)
+    dw = None
+    if ctx.needs_input_grad[1]:
+      mg = getattr(w, "main_grad", None)
+      if mg is not None:
+        _call(2, dy, x, mg[first:first + E], lay, N, K, E, accumulate=True)
+      else:
+        dw = torch.zeros_like(w)
+        _call(2, dy, x, dw[first:first + E], lay, N, K, E)
+    return dx, dw, None, None
+
+
+def grouped_linear(x: torch.Tensor, w: torch.Tensor, lay: PaddedLayout, first_expert: int = 0) -> torch.Tensor:
+  return _GroupedLinear.apply(x.contiguous(), w, lay, first_expert)
+
+
+def grouped_mlp_padded(x_pad: torch.Tensor, lay: PaddedLayout, gate_up: torch.Tensor, down: torch.Tensor, kind: str,
+                       first_expert: int = 0) -> torch.Tensor:
+  """x_pad [lay.rows, D] (padding rows zero) -> [lay.rows, D]; three grouped launches forward."""
+  gu = grouped_linear(x_pad, gate_up, lay, first_expert)
+  return grouped_linear(F.glu(gu, kind), down, lay, first_expert)
+
+
+def scatter_rows(x2: torch.Tensor, token_of_row: torch.Tensor, lay: PaddedLayout) -> torch.Tensor:
+  """Places token rows into the padded buffer (zero elsewhere); differentiable."""
+  buf = torch.zeros((lay.rows, x2.shape[1]), dtype=x2.dtype, device=x2.device)
+  return buf.index_copy(0, lay.dest, x2.index_select(0, token_of_row))
+
+
+def moe_forward_padded(x2: torch.Tensor, topv: torch.Tensor, topi: torch.Tensor, gate_up: torch.Tensor,
+                       down: torch.Tensor, kind: str) -> torch.Tensor:
+  """Single-rank routed MLP: x2 [T, D], topv/topi [T, k] -> [T, D]."""
+  T, k = topi.shape
+  E = gate_up.shape[0]
+  lay = padded_layout(topi.reshape(-1), E)
+  tok = torch.arange(T, device=x2.device).repeat_interleave(k)
+  y_pad = grouped_mlp_padded(scatter_rows(x2, tok, lay), lay, gate_up, down, kind)
+  ys = y_pad.index_select(0, lay.dest) * topv.reshape(-1, 1).to(y_pad.dtype)
+  return ys.view(T, k, -1).sum(1)
