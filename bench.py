@@ -31,14 +31,16 @@ def parse_args():
   ap.add_argument("--steps", type=int, default=2)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--model", default="llama3p1_8b")
+  ap.add_argument("--model", default=None, help="default: llama3p1_8b (sft), qwen3_30b_a3b (moe)")
   ap.add_argument("--seq-len", type=int, default=4096)
-  ap.add_argument("--global-batch", type=int, default=64)
+  ap.add_argument("--global-batch", type=int, default=0, help="default: 64 (sft), 32 (moe)")
+  ap.add_argument("--moe-capacity-factor", type=float, default=1.5,
+                  help="expert-parallel receive buffer, in multiples of a rank's own routed rows (overflow is an error)")
   ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-step per GPU (0 = auto)")
   ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
   ap.add_argument("--remat", default="auto", choices=["auto", "none", "block"])
   ap.add_argument("--no-e2e", action="store_true")
-  ap.add_argument("--workload", default="sft", choices=["sft", "grpo", "dpo"],
+  ap.add_argument("--workload", default="sft", choices=["sft", "grpo", "dpo", "moe"],
                   help="sft: Llama-3.1-8B full-weight SFT (default, the headline); grpo: Qwen3-8B GRPO step; "
                        "dpo: Qwen3-4B DPO with LoRA")
   ap.add_argument("--dpo-pairs", type=int, default=32)
@@ -159,7 +161,18 @@ def main():
     mesh = mesh_lib.create_mesh((world,), ("fsdp",))
     mesh_lib.set_current_mesh(mesh)
 
-  cfg = getattr(llama.ModelConfig, args.model)()
+  moe = args.workload == "moe"
+  args.model = args.model or ("qwen3_30b_a3b" if moe else "llama3p1_8b")
+  args.global_batch = args.global_batch or (32 if moe else 64)
+  if moe:
+    from tunix_b200.models.qwen3 import model as qwen3
+    cfg = getattr(qwen3.ModelConfig, args.model)()
+    full_layers = cfg.num_layers
+    if not args.layers and world < 8:
+      # the 30B model's optimizer state needs all 8 GPUs; fewer GPUs run proportionally fewer layers (flagged below)
+      args.layers = max(1, cfg.num_layers * world // 8)
+  else:
+    cfg = getattr(llama.ModelConfig, args.model)()
   if args.layers:
     cfg = cfg.replace(num_layers=args.layers)
   S, GB = args.seq_len, args.global_batch
@@ -179,6 +192,12 @@ def main():
                         pbar_description=None, max_inflight_computations=2 * ga,
                         data_sharding_axis=())   # every rank already holds only its share of the batch
   from tunix_b200.dist import fsdp
+  if moe and world > 1:
+    from tunix_b200.dist import moe as dist_moe
+    dist_moe.shard_experts(model, mesh)      # experts split over the ranks, tokens exchanged over peer memory
+    for mod in model.modules():
+      if hasattr(mod, "ep_group"):
+        mod.ep_capacity_factor = args.moe_capacity_factor
   model = fsdp.shard_model(model, mesh)     # flat bf16 params + fp32 grads, sharded optimizer state
   trainer = PeftTrainer(model, tx, tcfg)
   trainer.with_grad_sync(fsdp.GradSync(model, mesh))
@@ -265,16 +284,23 @@ def main():
 
   if rank == 0:
     fl = flops_lib.train_flops_per_token(cfg, S) * tokens_per_step
+    metric = "SFT tokens/s (Llama-3.1-8B full-weight, bf16 + fp32 master AdamW, seq 4096, global batch 64)"
+    if moe:
+      metric = (f"SFT tokens/s (Qwen3-30B-A3B MoE full-weight, expert parallel over {world} GPU(s), bf16 + fp32 master "
+                f"AdamW, seq {S}, global batch {GB})")
     out = {
-        "metric": "SFT tokens/s (Llama-3.1-8B full-weight, bf16 + fp32 master AdamW, seq 4096, global batch 64)",
+        "metric": metric,
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "ours",
         "config": {"model": args.model, "layers": cfg.num_layers, "global_batch": GB, "seq_len": S,
-                   "parallelism": f"fsdp{world}", "micro_batch_per_gpu": micro, "grad_accum": ga, "remat": remat,
+                   "parallelism": f"ep{world}+fsdp{world}" if moe else f"fsdp{world}", "micro_batch_per_gpu": micro, "grad_accum": ga, "remat": remat,
                    "l2": "inputs larger than L2: each step streams >100 GB of weights, gradients and optimizer state",
                    "optimizer": "AdamW fp32 master/m/v, global-norm clip 1.0"},
+        **({"moe": {"full_model_layers": full_layers, "layers_run": cfg.num_layers,
+                    "reduced": cfg.num_layers != full_layers, "experts": cfg.num_experts,
+                    "top_k": cfg.num_experts_per_tok, "capacity_factor": args.moe_capacity_factor}} if moe else {}),
         "model_tflops_per_gpu": fl / (ms_total / args.steps / 1e3) / 1e12 / world,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "train_losses": [float(x) for x in trainer.metrics_logger.get_metric_history("", "loss", "train")[:args.warmup + args.steps]],

@@ -66,3 +66,21 @@ def test_tensor_parallel_fused_allreduce_two_gpus(kernel_lib, tmp_path):
   for res in torch.load(out, weights_only=False):
     assert res["grad_ok"]
     assert max(res["fwd0"], res["fwd1"], res["fwd2"]) < 3e-2, res
+
+
+def test_moe_expert_parallel_peer_memory_two_gpus(kernel_lib, tmp_path):
+  """Expert parallelism with our dispatch / combine kernels over NVLink peer memory and the grouped tcgen05 GEMM:
+  outputs, input gradients, router and expert-weight gradients equal the unsharded layer on every rank."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  out = str(tmp_path / "ep.pt")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29615", os.path.join(HERE, "_moe_ep_worker.py"), "--out", out, "--device", "cuda"]
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+  r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["peer"], "the peer-memory path was not taken"
+    for rnd in (0, 1):
+      assert res[f"fwd{rnd}"] < 3e-2 and res[f"dx{rnd}"] < 3e-2, res
+      assert res[f"dw{rnd}"] < 3e-2 and res[f"dwd{rnd}"] < 3e-2 and res[f"drouter{rnd}"] < 5e-2, res

@@ -32,6 +32,8 @@ def test_moe_expert_parallel_two_ranks_cpu(tmp_path):
   for res in torch.load(out, weights_only=False):
     assert res["shape"][0] == 2
     assert res["fwd"] < 1e-5 and res["dx"] < 1e-4 and res["dw"] < 1e-4, res
+    # AdamW over the rank-local expert region + the sharded router equals the single-rank update
+    assert res["local_region"] > 0 and res["opt"] < 1e-5 and res["norm"] < 1e-4, res
 
 
 def test_tensor_parallel_two_ranks_cpu(tmp_path):
@@ -43,3 +45,15 @@ def test_tensor_parallel_two_ranks_cpu(tmp_path):
   assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
   for res in torch.load(out, weights_only=False):
     assert res["fwd"] < 1e-4 and res["d_embed"] < 1e-5 and res["d_norm"] < 1e-5 and res["d_down"] < 1e-5, res
+
+
+def test_sequence_parallel_two_ranks_cpu(tmp_path):
+  """Rows split along the sequence over 2 ranks (all-gathered K/V, causal prefix) give the full model's logits
+  and, after the gradient reduction over the axis, its parameter gradients."""
+  out = str(tmp_path / "sp.pt")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29671", os.path.join(HERE, "_sp_worker.py"), "--out", out]
+  r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2"), capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["fwd"] < 1e-4 and res["grads"] < 1e-4, res

@@ -51,7 +51,10 @@ class FlatParamStore:
     self.group = mesh.group(axis) if mesh is not None else None
     self.world = mesh.axis_size(axis) if mesh is not None else 1
     self.rank = mesh.axis_index(axis) if mesh is not None else 0
-    params = [(n, p) for n, p in model.named_parameters() if p.requires_grad or not only_trainable]
+    every = [(n, p) for n, p in model.named_parameters() if p.requires_grad or not only_trainable]
+    # expert-parallel parameters differ per rank: they get a rank-local region (no reduction, whole optimizer state)
+    local = [(n, p) for n, p in every if getattr(p, "is_expert_parallel", False)]
+    params = [(n, p) for n, p in every if not getattr(p, "is_expert_parallel", False)]
     if not params:
       raise ValueError("model has no trainable parameters")
     dev = params[0][1].device
@@ -97,6 +100,26 @@ class FlatParamStore:
         p.data = view
         p.main_grad = self.flat_grad[o:o + p.numel()].view(p.shape)
     self.params = dict(params)
+    self.local_names = [n for n, _ in local]
+    self.local_shapes = {n: tuple(p.shape) for n, p in local}
+    self.local_offsets: Dict[str, int] = {}
+    off = 0
+    for n, p in local:
+      self.local_offsets[n] = off
+      off += (p.numel() + 7) // 8 * 8
+    self.local_numel = off
+    self.local_param = self.local_grad = None
+    if local:
+      self.local_param = torch.zeros(off, dtype=dtype, device=dev)
+      self.local_grad = torch.zeros(off, dtype=torch.float32, device=dev)
+      with torch.no_grad():
+        for n, p in local:
+          o = self.local_offsets[n]
+          view = self.local_param[o:o + p.numel()].view(p.shape)
+          view.copy_(p.data)
+          p.data = view
+          p.main_grad = self.local_grad[o:o + p.numel()].view(p.shape)
+      self.params.update(dict(local))
     lo = self.rank * self.shard_numel
     self.shard = slice(lo, lo + self.shard_numel)
     self._scratch: Dict[str, torch.Tensor] = {}
@@ -114,6 +137,9 @@ class FlatParamStore:
         "mu": {"flat": torch.zeros_like(master)},
         "nu": {"flat": torch.zeros_like(master)},
     }
+    if self.local_param is not None:
+      lm = self.local_param.float()
+      st["master"]["local"], st["mu"]["local"], st["nu"]["local"] = lm, torch.zeros_like(lm), torch.zeros_like(lm)
     if getattr(tx, "exposes_hyperparams", False):
       from .. import optim
       st["hyperparams"] = {"learning_rate": torch.tensor(optim._lr_at(tx._lr, 0), dtype=torch.float32)}
@@ -153,6 +179,12 @@ class FlatParamStore:
       kernels.sumsq(g, ss, accumulate=False)
     else:
       ss.copy_(g.double().pow(2).sum().float().reshape(1))
+    if self.local_grad is not None:
+      # every rank's expert gradients are distinct, so their squares simply join the sum over ranks
+      if self.device.type == "cuda":
+        kernels.sumsq(self.local_grad, ss, accumulate=True)
+      else:
+        ss.add_(self.local_grad.double().pow(2).sum().float())
     if self.world > 1:
       pack = self._buf("pack", 2)
       pack[0:1].copy_(ss)
@@ -172,6 +204,8 @@ class FlatParamStore:
       if max_grad_norm and float(norm) > max_grad_norm:
         scale.mul_(max_grad_norm / (float(norm) + 1e-6))
     inner = getattr(tx, "inner", tx)
+    if self.local_grad is not None:
+      self._local_update(inner, state, scale)
     if self.world > 1 and self.symm is not None:
       self.symm.adamw_allgather(inner, state, g, self.flat_param, self.shard, scale)
     else:
@@ -181,6 +215,16 @@ class FlatParamStore:
         dist.all_gather_into_tensor(self.flat_param, self.flat_param[self.shard], group=self.group)
     self.flat_grad.zero_()
     return norm[0].clone()
+
+  def _local_update(self, inner, state, scale: torch.Tensor) -> None:
+    """AdamW over the rank-local (expert-parallel) region; same step count and schedule as the sharded part,
+    whose update follows and advances the count."""
+    from .. import optim
+    from ..ops import kernels
+    count = int(state["count"]) + 1
+    kernels.adamw_step(state["master"]["local"], state["mu"]["local"], state["nu"]["local"], self.local_grad,
+                       self.local_param, lr=optim._lr_at(inner._lr, count - 1), beta1=inner.b1, beta2=inner.b2,
+                       eps=inner.eps, weight_decay=inner.weight_decay, step=count, grad_scale=scale, zero_grad=True)
 
   # ---- checkpoint support ---------------------------------------------------------------------
   def full_state_tensor(self, shard_tensor: torch.Tensor) -> torch.Tensor:
@@ -203,6 +247,10 @@ class FlatParamStore:
     out: Dict[str, Any] = {"count": state["count"]}
     for k in ("mu", "nu", "master"):
       out[k] = self.unflatten(self.full_state_tensor(state[k]["flat"]))
+      if "local" in state[k]:          # this rank's experts only
+        for n in self.local_names:
+          o = self.local_offsets[n]
+          out[k][n] = state[k]["local"][o:o + int(math.prod(self.local_shapes[n]))].view(self.local_shapes[n])
     if "hyperparams" in state:
       out["hyperparams"] = state["hyperparams"]
     return out
@@ -218,6 +266,11 @@ class FlatParamStore:
           o = self.offsets[n]
           full[o:o + t.numel()].copy_(t.reshape(-1).to(self.device, torch.float32))
       state[k]["flat"].copy_(full[self.shard])
+      if "local" in state[k]:
+        for n, t in tree[k].items():
+          if n in self.local_offsets:
+            o = self.local_offsets[n]
+            state[k]["local"][o:o + t.numel()].copy_(t.reshape(-1).to(self.device, torch.float32))
     if "count" in tree:
       state["count"] = torch.as_tensor(tree["count"]).to(torch.int32).reshape(())
 
@@ -225,6 +278,8 @@ class FlatParamStore:
   def refresh_master_from_params(self, state: Dict[str, Any]) -> None:
     """After parameters were loaded into the bf16 buffer (checkpoint restore, weight import)."""
     state["master"]["flat"].copy_(self.flat_param[self.shard].float())
+    if "local" in state["master"]:
+      state["master"]["local"].copy_(self.local_param.float())
 
 
 def shard_model(model: torch.nn.Module, mesh: Optional[mesh_lib.Mesh] = None, axis: str = "fsdp",

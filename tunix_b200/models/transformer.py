@@ -256,6 +256,13 @@ class Attention(nn.Module):
       new_cache = {"k": ck, "v": cv, "end_index": end + T}
       k, v = ck, cv
 
+    sp_group = getattr(self, "sp_group", None)
+    if sp_group is not None:
+      if cache is not None or attn_mask is not None:
+        raise NotImplementedError("sequence parallelism covers causal training / scoring without a KV cache")
+      from ..dist import sp as sp_lib
+      k, v = sp_lib.causal_prefix(k, v, sp_group, T)    # keys [0, (rank + 1) T); our queries are its last T rows
+
     mask = attn_mask
     causal = mask is None and cache is None
     if mask is not None and not isinstance(mask, torch.Tensor) and (

@@ -145,6 +145,8 @@ def eligible(layer, h: torch.Tensor, cache, attn_mask) -> bool:
   cfg = layer.cfg
   if not (h.is_cuda and h.dtype == bf16 and cache is None):
     return False
+  if getattr(layer.attn, "sp_group", None) is not None or getattr(layer.attn, "tp_group", None) is not None:
+    return False
   if attn_mask is not None:
     # packed rows run fused when the flash kernel takes the segment bounds (head_dim 128)
     if not (isinstance(attn_mask, attn_ops.SegmentMask) and cfg.head_dim == 128 and flash_lib._DISABLED is False):

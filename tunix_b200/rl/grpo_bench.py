@@ -69,7 +69,7 @@ def run(args, ClockSampler) -> None:
     mesh = mesh_lib.create_mesh((world,), ("fsdp",))
     mesh_lib.set_current_mesh(mesh)
 
-  model_name = args.model if args.model != "llama3p1_8b" else "qwen3_8b"
+  model_name = args.model or "qwen3_8b"
   cfg = automodel.call_model_config(model_name)
   if args.layers:
     import dataclasses

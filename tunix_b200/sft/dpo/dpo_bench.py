@@ -35,7 +35,7 @@ def run(args, ClockSampler) -> None:
     mesh_lib.init_distributed("nccl")
     mesh = mesh_lib.create_mesh((world,), ("fsdp",))
     mesh_lib.set_current_mesh(mesh)
-  name = args.model if args.model != "llama3p1_8b" else "qwen3_4b"
+  name = args.model or "qwen3_4b"
   cfg = automodel.call_model_config(name)
   if args.layers:
     import dataclasses
