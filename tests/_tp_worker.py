@@ -41,8 +41,27 @@ def main():
   per = cfg.hidden_dim // world
   gfull = fp["layers.1.mlp.down_proj.w"].grad[:, rank * per:(rank + 1) * per]
   res["d_down"] = float((gfull - pp["layers.1.mlp.down_proj.inner.w"].grad).abs().max())
-  # decoding with a KV cache works on the slice too (fewer kv heads per rank)
-  from tunix_b200.generate import utils as gen_utils  # noqa: F401
+  # vocabulary-parallel head: log-probs and entropy from three numbers per token, full logits all-gathered
+  from tunix_b200.ops import functional as Fn
+  full2 = Transformer(cfg).init_weights(seed=0, scale=0.3)
+  part2 = tp_lib.shard_model_tp(full2, mesh, shard_vocab=True)
+  assert part2.lm_head.w.shape[0] == cfg.vocab_size // world
+  got2, _ = part2(toks, pos, None, None)
+  res["vp_logits"] = float((want - got2).abs().max())
+  tg = torch.randint(0, 64, (2, 10))
+  hf, _ = full2(toks, pos, None, None, skip_lm_head=True)
+  hp, _ = part2(toks, pos, None, None, skip_lm_head=True)
+  lp_f, en_f = Fn.linear_logprob(hf, full2.head_weight(), tg, temperature=0.7, want_entropy=True)
+  lp_p, en_p = Fn.linear_logprob(hp, part2.head_weight(), tg, temperature=0.7, want_entropy=True)
+  res["vp_logp"] = float((lp_f - lp_p).abs().max())
+  res["vp_ent"] = float((en_f - en_p).abs().max())
+  wgt = torch.randn(2, 10)
+  ((lp_f * wgt).sum() + 0.3 * en_f.sum()).backward()
+  ((lp_p * wgt).sum() + 0.3 * en_p.sum()).backward()
+  f2, p2 = dict(full2.named_parameters()), dict(part2.named_parameters())
+  per_v = cfg.vocab_size // world
+  res["vp_dhead"] = float((f2["lm_head.w"].grad[rank * per_v:(rank + 1) * per_v] - p2["lm_head.w"].grad).abs().max())
+  res["vp_dembed"] = float((f2["embedder.input_embedding"].grad - p2["embedder.input_embedding"].grad).abs().max())
   allres = [None] * world
   dist.all_gather_object(allres, res)
   if rank == 0:
@@ -85,6 +104,27 @@ def main_cuda(a):
   got, _ = part(toks, pos, None, None)
   got.float().pow(2).mean().backward()
   res["grad_ok"] = all(p.grad is not None for n, p in part.named_parameters() if "inner.w" in n)
+  # vocabulary-parallel head on the kernels: per-token log-probs / entropy against the unsharded head
+  from tunix_b200.ops import functional as Fn
+  h = (torch.randn(48, 512, device=dev) * 0.5).to(torch.bfloat16)
+  dist.broadcast(h, src=0)
+  tg = torch.randint(0, 512, (48,), device=dev)
+  dist.broadcast(tg, src=0)
+  w_full = full.head_weight().detach().clone().requires_grad_()
+  per_v = 512 // world
+  w_part = w_full.detach()[rank * per_v:(rank + 1) * per_v].clone().requires_grad_()
+  w_part.vocab_parallel = (mesh.group("tp"), rank * per_v)
+  hf = h.clone().requires_grad_()
+  hp = h.clone().requires_grad_()
+  lp_f, en_f = Fn.linear_logprob(hf, w_full, tg, temperature=0.8, want_entropy=True)
+  lp_p, en_p = Fn.linear_logprob(hp, w_part, tg, temperature=0.8, want_entropy=True)
+  (lp_f.sum() + 0.5 * en_f.sum()).backward()
+  (lp_p.sum() + 0.5 * en_p.sum()).backward()
+  res["vp_logp"] = float((lp_f - lp_p).abs().max())
+  res["vp_ent"] = float((en_f - en_p).abs().max())
+  res["vp_dh"] = float((hf.grad.float() - hp.grad.float()).abs().max() / (hf.grad.float().abs().max() + 1e-6))
+  res["vp_dw"] = float((w_full.grad.float()[rank * per_v:(rank + 1) * per_v] - w_part.grad.float()).abs().max()
+                       / (w_full.grad.float().abs().max() + 1e-6))
   allres = [None] * world
   dist.all_gather_object(allres, res)
   if rank == 0:

@@ -66,6 +66,7 @@ def test_tensor_parallel_fused_allreduce_two_gpus(kernel_lib, tmp_path):
   for res in torch.load(out, weights_only=False):
     assert res["grad_ok"]
     assert max(res["fwd0"], res["fwd1"], res["fwd2"]) < 3e-2, res
+    assert res["vp_logp"] < 2e-2 and res["vp_ent"] < 2e-2 and res["vp_dh"] < 3e-2 and res["vp_dw"] < 3e-2, res
 
 
 def test_moe_expert_parallel_peer_memory_two_gpus(kernel_lib, tmp_path):

@@ -45,6 +45,9 @@ def test_tensor_parallel_two_ranks_cpu(tmp_path):
   assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
   for res in torch.load(out, weights_only=False):
     assert res["fwd"] < 1e-4 and res["d_embed"] < 1e-5 and res["d_norm"] < 1e-5 and res["d_down"] < 1e-5, res
+    # vocabulary-parallel lm_head: logits, log-probs, entropy and their gradients equal the unsharded head
+    assert res["vp_logits"] < 1e-4 and res["vp_logp"] < 1e-4 and res["vp_ent"] < 1e-4, res
+    assert res["vp_dhead"] < 1e-4 and res["vp_dembed"] < 1e-4, res
 
 
 def test_sequence_parallel_two_ranks_cpu(tmp_path):

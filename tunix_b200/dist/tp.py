@@ -134,8 +134,11 @@ def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
   return torch.cat(parts, dim=0).clone()
 
 
-def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_rows: int = 0) -> torch.nn.Module:
+def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_rows: int = 0,
+                   shard_vocab: bool = False) -> torch.nn.Module:
   """Builds this rank's tensor-parallel slice from a full (replicated) model and returns it.
+  `shard_vocab` also splits an untied lm_head by vocabulary rows: log-probs then go through
+  `ops.vocab_parallel` (three numbers per token cross the ranks), full logits are all-gathered.
   `fused_max_rows > 0` (CUDA ranks on one NVLink domain) makes the two exits of every layer `FusedRowExit`s
   for up to that many token rows per call (decode and chunked prefill of a rollout engine)."""
   from ..models.transformer import Transformer
@@ -195,4 +198,9 @@ def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_row
   for layer in out.layers:
     layer.cfg = out.config
   out.tp_group, out.tp_size, out.tp_rank = group, tp, r
+  if shard_vocab and out.lm_head is not None and cfg.vocab_size % tp == 0:
+    per = cfg.vocab_size // tp
+    with torch.no_grad():
+      out.lm_head.w.data = out.lm_head.w.data[r * per:(r + 1) * per].clone()
+    out.lm_head.w.vocab_parallel = (group, r * per)
   return out

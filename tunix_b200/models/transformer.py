@@ -465,7 +465,14 @@ class Transformer(nn.Module):
 
     `as_float=False` returns the GEMM's own dtype when no soft-cap applies: the sampler kernel
     reads bf16 rows directly, which saves a pass over [B, V] per decode step."""
-    logits = F.linear(hidden, self.head_weight())
+    w = self.head_weight()
+    logits = F.linear(hidden, w)
+    vp = getattr(w, "vocab_parallel", None)
+    if vp is not None:       # vocabulary-parallel head: every rank computed its slice of the logits
+      import torch.distributed as dist
+      parts = [torch.empty_like(logits) for _ in range(dist.get_world_size(vp[0]))]
+      dist.all_gather(parts, logits.contiguous(), group=vp[0])
+      logits = torch.cat(parts, dim=-1)
     cap = self.config.final_logit_softcap
     if cap:
       logits = logits.float()

@@ -371,6 +371,10 @@ def linear_logprob(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Te
   hidden [..., D], weight [V, D], targets [...] -> (logp [...], entropy [...] or None), fp32.
   Shared by the trainer, the reference policy and the rollout sampler so that log-probs agree.
   """
+  vp = getattr(weight, "vocab_parallel", None)
+  if vp is not None:        # (group, first vocabulary row of this rank's slice): see ops/vocab_parallel.py
+    from . import vocab_parallel
+    return vocab_parallel.linear_logprob(hidden, weight, targets, vp[0], vp[1], temperature, softcap, want_entropy)
   lead = targets.shape
   D = hidden.shape[-1]
   V = weight.shape[0]
