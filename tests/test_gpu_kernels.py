@@ -332,3 +332,32 @@ def test_fused_lora_linear_matches_unfused(kernel_lib, multi):
   for i, (g, w) in enumerate(zip(got, want)):
     err = (g - w).norm() / (w.norm() + 1e-6)
     assert err < 2e-2, (i, err.item())
+
+
+@pytest.mark.parametrize("world,rank", [(1, 0), (2, 0), (2, 1), (4, 2)])
+def test_gemm_with_fused_allgather_of_sharded_weight(kernel_lib, world, rank):
+  """The all-gather-into-GEMM kernel with every "rank's" shard on this one GPU (a single launch: the copy warps
+  and the tensor-core warps of the same kernel hand slabs over through counters)."""
+  from tunix_b200.ops import _lib, kernels
+  torch.manual_seed(11)
+  M, K, N = 384, 256, 128 * world * 3
+  a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+  w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / K ** 0.5
+  shards = [w[r * (N // world):(r + 1) * (N // world)].clone() for r in range(world)]
+  stage = torch.full((N, K), float("nan"), device="cuda", dtype=torch.bfloat16)
+  cnt = torch.empty(N // 128, device="cuda", dtype=torch.int32)
+  for _ in range(2):                                   # a second call reuses the scratch
+    c = kernels.gemm_allgather_b(a, [s.data_ptr() for s in shards], rank, N // world, stage, cnt)
+  torch.cuda.synchronize()
+  _lib.check_status(torch.device("cuda"))
+  ref = a.float() @ w.float().t()
+  assert torch.allclose(c.float(), ref, atol=3e-2, rtol=3e-2)
+  # the staging buffer holds exactly the remote shards; the local rows were read in place
+  per = N // world
+  for r in range(world):
+    blk = stage[r * per:(r + 1) * per]
+    if r == rank:
+      assert bool(torch.isnan(blk.float()).all())
+    else:
+      assert torch.equal(blk, shards[r])
+  assert int(cnt.min()) == int(cnt.max()) or world > 1

@@ -6,7 +6,8 @@ For a flat model of `--params` parameters it times, per optimizer step and per r
 reduce-scatter (pull the own shard of every peer's fp32 gradient and sum it, with the partial sums
 of squares for the global norm), the fused AdamW + all-gather (update the own shard and store the
 new bf16 values into every rank's replica), the GEMM with an all-reduce epilogue for a decode-sized
-row-parallel projection, and the NCCL collectives that move the same bytes. CUDA events around
+row-parallel projection, the GEMM that all-gathers its row-sharded weight inside the kernel, and the NCCL
+collectives that move the same bytes. CUDA events around
 `--iters` repetitions after warm-up, max over ranks. Bandwidth = bytes that cross NVLink per rank
 and direction divided by the time; the roofline is the measured peer-copy bandwidth.
 """
@@ -41,6 +42,7 @@ def main():
   ap.add_argument("--params", type=float, default=2e9)
   ap.add_argument("--iters", type=int, default=5)
   ap.add_argument("--link-gbs", type=float, default=770.0, help="measured peer-copy bandwidth per direction")
+  ap.add_argument("--gemm-tflops", type=float, default=1674.5, help="measured cuBLAS bf16 burst rate")
   a = ap.parse_args()
   from tunix_b200 import optim
   from tunix_b200.dist import mesh as mesh_lib, symm as symm_lib
@@ -113,6 +115,46 @@ def main():
   err = float((y.float() - ref).abs().max() / ref.abs().max())
   rows.append({"op": f"gemm + all-reduce epilogue M={M} N={N} K={K}/rank", "ms": ms_f, "rel_err_vs_nccl": err})
   rows.append({"op": "library linear + nccl all_reduce (same shape)", "ms": ms_p})
+  # all-gather fused into the consuming GEMM: Llama-3.1-8B gate|up half (N 14336, K 4096) on 8192 tokens, the
+  # weight row-sharded over the ranks. Roofline: the slower of the GEMM at the measured cuBLAS rate and the
+  # remote shards over the link.
+  from tunix_b200.ops import kernels
+  Mg, Ng, Kg = 8192, 14336, 4096
+  if Ng % (128 * world) == 0:
+    per = Ng // world
+    wsh = sb.alloc("wshard", per * Kg, torch.bfloat16).view(per, Kg)
+    sb.rendezvous()
+    wsh.copy_((torch.randn(per, Kg, device=dev) * 0.02).bfloat16())
+    xa = torch.randn(Mg, Kg, device=dev).bfloat16()
+    stage = torch.empty(Ng, Kg, dtype=torch.bfloat16, device=dev)
+    cnt = torch.empty(Ng // 128, dtype=torch.int32, device=dev)
+    cg = torch.empty(Mg, Ng, dtype=torch.bfloat16, device=dev)
+    wfull = torch.empty(Ng, Kg, dtype=torch.bfloat16, device=dev)
+    ptrs = sb.peer_ptrs["wshard"]
+    sb.barrier()
+
+    def fused_ag():
+      kernels.gemm_allgather_b(xa, ptrs, rank, per, stage, cnt, out=cg)
+
+    def plain_ag():
+      dist.all_gather_into_tensor(wfull, wsh)
+      kernels.gemm(xa, wfull, out=cg)
+
+    def gemm_only():
+      kernels.gemm(xa, wfull, out=cg)
+    ms_f = _time(fused_ag, 10)
+    got = cg.float().clone()
+    ms_p = _time(plain_ag, 10)
+    err = float((got - cg.float()).abs().max() / cg.float().abs().max())
+    ms_g = _time(gemm_only, 10)
+    fl = 2.0 * Mg * Ng * Kg
+    link = (world - 1) * per * Kg * 2
+    t_roof = max(fl / (a.gemm_tflops * 1e12), link / (a.link_gbs * 1e9)) * 1e3
+    rows.append({"op": f"all-gather fused into GEMM M={Mg} N={Ng} K={Kg}", "ms": ms_f, "tflops": fl / ms_f / 1e9,
+                 "nvlink_GB_s": link / ms_f / 1e6, "roofline_ms": t_roof, "frac_of_roofline": t_roof / ms_f,
+                 "rel_err_vs_nccl_path": err})
+    rows.append({"op": "nccl all_gather + tcgen05 GEMM (same shape)", "ms": ms_p, "tflops": fl / ms_p / 1e9})
+    rows.append({"op": "tcgen05 GEMM alone on the gathered weight", "ms": ms_g, "tflops": fl / ms_g / 1e9})
   _lib.check_status()
   if rank == 0:
     for r in rows:

@@ -59,6 +59,7 @@ def _declare(lib):
       "tx_gemm_grouped_bf16": [P, P, P, P, P, I, I, I, I, I, L, L, L, I, I, F, P, P],
       "tx_moe_dispatch_rows": [P, L, P, I, P, P, P, ctypes.POINTER(P), I, L, I, L, P, P],
       "tx_moe_combine_rows": [ctypes.POINTER(P), I, P, P, P, I, P, L, P, L, I, L, P, P],
+      "tx_gemm_bf16_allgather_b": [P, ctypes.POINTER(P), I, I, P, P, P, I, I, I, L, L, L, I, I, F, L, P, P],
       "tx_gemm_bf16_allreduce": [P, P, ctypes.POINTER(P), I, I, I, I, L, L, I, I, F, P, P],
       "tx_f32_sum_to_bf16": [P, P, L, I, I, P],
       "tx_kv_page_write": [P, P, L, L, P, P, P, I, I, I, P],

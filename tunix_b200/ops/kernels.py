@@ -240,3 +240,26 @@ def rope_table(max_pos: int, head_dim: int, theta: float, device, scale: float =
   inv = 1.0 / (theta ** (torch.arange(half, dtype=torch.float64) * 2.0 / head_dim))
   ang = torch.arange(max_pos, dtype=torch.float64)[:, None] / scale * inv[None, :]
   return torch.cat([ang.cos(), ang.sin()], dim=-1).to(torch.float32).to(device)
+
+
+def gemm_allgather_b(a: torch.Tensor, shard_ptrs, rank: int, shard_rows: int, stage: torch.Tensor,
+                     slab_count: torch.Tensor, *, ldb: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                     out_dtype: torch.dtype = bf16, accumulate: bool = False, alpha: float = 1.0,
+                     wait_limit_ms: int = 2000) -> torch.Tensor:
+  """C = a @ W^T with W [N, K] row-sharded over len(shard_ptrs) ranks: the all-gather of W runs inside the GEMM
+  kernel (`csrc/gemm_allgather.cu`). `shard_ptrs[r]` is the device address of rank r's [shard_rows, K] block
+  (peer-mapped; entry `rank` is local), `stage` a local [N, K] bf16 scratch and `slab_count` an int32 [N / 128]
+  scratch. Every rank's shard must be final before any rank calls this."""
+  import ctypes
+  M, K = a.shape
+  world = len(shard_ptrs)
+  N = shard_rows * world
+  if out is None:
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+  arr = (ctypes.c_void_p * world)(*[int(x) for x in shard_ptrs])
+  rc = _lib.require().tx_gemm_bf16_allgather_b(
+      a.data_ptr(), arr, world, rank, stage.data_ptr(), slab_count.data_ptr(), out.data_ptr(), M, N, K, a.stride(0),
+      int(ldb or K), out.stride(0), int(out.dtype == torch.float32), int(accumulate), float(alpha), int(wait_limit_ms),
+      _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, f"tx_gemm_bf16_allgather_b(M={M},N={N},K={K},world={world})")
+  return out
