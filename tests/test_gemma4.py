@@ -1,0 +1,95 @@
+"""Gemma 4 text decoder: layer pattern, KV sharing, per-layer inputs, partial RoPE, MoE branch, cache."""
+import torch
+
+from tunix_b200.models.gemma4 import AttentionType, Gemma4, ModelConfig, kv_sharing_pattern
+from tunix_b200.models.gemma4 import model as g4
+
+
+def tiny(**kw):
+  base = dict(num_layers=7, num_embed=64, embed_dim=32, hidden_dim=48, num_heads=4, head_dim=8, num_kv_heads=2,
+              sliding_window_size=4, per_layer_input_dim=6, frac_shared_layers=4.0 / 7, global_key_size=16,
+              num_global_kv_heads=1, k_eq_v_global=True, override_kv_shared_ffw_hidden=64,
+              attention_pattern=(AttentionType.LOCAL_SLIDING, AttentionType.LOCAL_SLIDING, AttentionType.GLOBAL))
+  base.update(kw)
+  return ModelConfig(**base)
+
+
+def test_presets_and_sharing_pattern():
+  c = ModelConfig.gemma4_e2b()
+  types = c.attention_types()
+  assert len(types) == 35 and types[4] == AttentionType.GLOBAL and types[3] == AttentionType.LOCAL_SLIDING
+  pat = kv_sharing_pattern(35, 20.0 / 35, types)
+  assert pat[:15] == list(range(15))
+  assert all(pat[i] == (14 if types[i] == AttentionType.GLOBAL else 13) for i in range(15, 35))
+  assert types[14] == AttentionType.GLOBAL and types[13] == AttentionType.LOCAL_SLIDING
+  assert ModelConfig.gemma4_26b_a4b_it().num_experts == 128 and ModelConfig.gemma4_31b().num_global_kv_heads == 4
+
+
+def test_structure_of_shared_and_global_layers():
+  m = Gemma4(tiny())
+  # pattern L L G | L L G L: three unshared layers, the four after them reuse layer 2 (global) or 1 (local)
+  assert m.kv_sharing == [0, 1, 2, 1, 1, 2, 1]
+  for i in range(3, 7):
+    assert m.layers[i].attn.k_proj is None
+    assert m.layers[i].mlp.down_proj.shape[1] == 64          # wider MLP on shared layers
+  glob = m.layers[2].attn
+  assert glob.head_dim == 16 and glob.num_kv_heads == 1 and glob.v_proj is None       # k == v on global layers
+  assert m.layers[0].attn.head_dim == 8 and m.layers[0].attn.v_proj is not None
+
+
+def test_partial_rope_rotates_only_the_leading_pairs():
+  x = torch.randn(1, 5, 2, 16)
+  pos = torch.arange(5)[None]
+  y = g4.partial_rope(x, pos, 10000.0, 1.0, 0.25)          # 2 of 8 pairs rotate
+  assert torch.allclose(y[..., 2:8], x[..., 2:8]) and torch.allclose(y[..., 10:], x[..., 10:])
+  assert not torch.allclose(y[0, 1:, :, :2], x[0, 1:, :, :2])
+  assert torch.allclose(y[0, 0], x[0, 0])                   # position 0 is the identity
+  full = g4.partial_rope(x, pos, 10000.0, 1.0, 1.0)
+  assert torch.allclose(full.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+
+
+def test_cached_decode_matches_full_forward_and_gradients_flow():
+  torch.manual_seed(0)
+  for moe in (False, True):
+    kw = dict(enable_moe=True, num_experts=4, num_experts_per_tok=2, expert_dim=24) if moe else {}
+    m = Gemma4(tiny(**kw)).init_weights(seed=1, scale=0.2)
+    toks = torch.randint(0, 64, (2, 9))
+    full, _ = m(toks)
+    assert full.shape == (2, 9, 64) and float(full.abs().max()) <= 30.0
+    # prefill 5 tokens into a cache, then 4 single-token steps
+    cache = m.init_cache(2, 16)
+    assert set(cache) == {"layer_0", "layer_1", "layer_2"}
+    pos = torch.arange(9)[None].expand(2, 9)
+    out, cache = m(toks[:, :5], pos[:, :5], cache, None)
+    steps = [out]
+    for t in range(5, 9):
+      o, cache = m(toks[:, t:t + 1], pos[:, t:t + 1], cache, None)
+      steps.append(o)
+    assert torch.allclose(torch.cat(steps, 1), full, atol=2e-4), float((torch.cat(steps, 1) - full).abs().max())
+    full.square().mean().backward()
+    missing = [n for n, p in m.named_parameters() if p.grad is None]
+    assert not missing, missing
+
+
+def test_sliding_window_limits_what_a_local_layer_sees():
+  torch.manual_seed(1)
+  cfg = tiny(num_layers=1, frac_shared_layers=0.0, per_layer_input_dim=0,
+             attention_pattern=(AttentionType.LOCAL_SLIDING,), sliding_window_size=3)
+  m = Gemma4(cfg).init_weights(seed=2, scale=0.3)
+  a = torch.randint(0, 64, (1, 8))
+  b = a.clone()
+  b[0, 0] = (a[0, 0] + 1) % 64                 # differs only at position 0
+  ya, _ = m(a)
+  yb, _ = m(b)
+  assert not torch.allclose(ya[0, 2], yb[0, 2])     # position 2 still sees position 0 (window 3)
+  assert torch.allclose(ya[0, 3:], yb[0, 3:], atol=1e-6)   # positions >= 3 do not
+
+
+def test_automodel_builds_a_random_gemma4():
+  from tunix_b200.models import automodel
+  cfg = tiny()
+  m, path = automodel.AutoModel.from_pretrained("google/gemma-4-e2b-it", model_source=automodel.ModelSource.DUMMY,
+                                                model_config=cfg, dtype=torch.float32, device="cpu")
+  assert isinstance(m, Gemma4) and path is None
+  logits, _ = m(torch.randint(0, 64, (1, 5)))
+  assert logits.shape == (1, 5, 64) and bool(torch.isfinite(logits).all())

@@ -130,7 +130,8 @@ constexpr int kKeys = 128, kQT = 64;
 constexpr int kKBytes = kKeys * kHD * 2;       // 32 KiB, two [128 x 64] sub-tiles
 constexpr int kQBytes = kQT * kHD * 2;         // 16 KiB, two [64 x 64] sub-tiles
 constexpr int kPBytes = kKeys * kQT * 2;       // 16 KiB
-constexpr int kTileBytes = 2 * kKBytes + 4 * kQBytes + 2 * kPBytes;   // 163840
+constexpr int kQStages = 3;                    // Q / dO ring: a tile is requested two iterations ahead of its use
+constexpr int kTileBytes = 2 * kKBytes + 2 * kQStages * kQBytes + 2 * kPBytes;   // 196608
 constexpr int kVecBytes = 4 * 2 * kQT * 4;     // lse, delta, segment lo and hi; two buffers each
 constexpr int kSmemBytes = kTileBytes + kVecBytes + 256 + 1024;
 constexpr int kTmemCols = 512;                 // [S^T dP^T] x 2 | dK | dV
@@ -146,9 +147,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
   const uint32_t sK = base, sV = sK + kKBytes;
-  const uint32_t sQ = sV + kKBytes;            // 2 stages
-  const uint32_t sDO = sQ + 2 * kQBytes;       // 2 stages
-  const uint32_t sPT = sDO + 2 * kQBytes, sDST = sPT + kPBytes;
+  const uint32_t sQ = sV + kKBytes;            // kQStages stages
+  const uint32_t sDO = sQ + kQStages * kQBytes;
+  const uint32_t sPT = sDO + kQStages * kQBytes, sDST = sPT + kPBytes;
   float* sLse = reinterpret_cast<float*>(gen + kTileBytes);       // [2][64]
   float* sDelta = sLse + 2 * kQT;                                  // [2][64]
   int* sLo = reinterpret_cast<int*>(sDelta + 2 * kQT);             // [2][64]
@@ -156,10 +157,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kTileBytes + kVecBytes);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_kv = bar0;
-  const uint32_t bar_qfull = bar0 + 8, bar_qempty = bar0 + 24;
-  const uint32_t bar_sfull = bar0 + 40, bar_sempty = bar0 + 56;
-  const uint32_t bar_pfull = bar0 + 72, bar_pdone = bar0 + 80, bar_vec = bar0 + 88;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  const uint32_t bar_qfull = bar0 + 8, bar_qempty = bar0 + 40;      // up to 4 stages each
+  const uint32_t bar_sfull = bar0 + 72, bar_sempty = bar0 + 88;
+  const uint32_t bar_pfull = bar0 + 104, bar_pdone = bar0 + 112, bar_vec = bar0 + 120;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -183,9 +184,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_kv, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kQStages; ++s) {
       mbar_init(bar_qfull + 8 * s, 1);
       mbar_init(bar_qempty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sfull + 8 * s, 1);
       mbar_init(bar_sempty + 8 * s, 256);
     }
@@ -217,10 +220,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tma_load_2d(sV, &map_v, kvh * kHD, krow, bar_kv);
       tma_load_2d(sV + kKeys * 128, &map_v, kvh * kHD + 64, krow, bar_kv);
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
+        const int st = it % kQStages;
         const int h = kvh * g + it / per_head;
         const int qrow = b * p.Lq + (i_start + it % per_head) * kQT;
-        if (!mbar_wait(bar_qempty + 8 * st, ((it >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(bar_qempty + 8 * st, ((it / kQStages) & 1) ^ 1, abort_flag)) {
           atomicOr(p.status, kStatusWaitTimeoutProducer);
           break;
         }
@@ -238,12 +241,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       constexpr uint32_t idesc_d = make_idesc_bf16(kKeys, kHD, false, true);
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
       auto issue_sdp = [&](int it) -> bool {
-        const int st = it & 1;
+        const int st = it & 1, qs = it % kQStages;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(bar_qfull + 8 * st, ph, abort_flag)) return false;
+        if (!mbar_wait(bar_qfull + 8 * qs, (it / kQStages) & 1, abort_flag)) return false;
         if (!mbar_wait(bar_sempty + 8 * st, ph ^ 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sq = sQ + st * kQBytes, sdo = sDO + st * kQBytes;
+        const uint32_t sq = sQ + qs * kQBytes, sdo = sDO + qs * kQBytes;
 #pragma unroll
         for (int k = 0; k < kHD / 16; ++k) {
           const uint32_t sub = k >> 2, kk = k & 3;
@@ -263,7 +266,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       for (int it = 0; it < n_it && ok; ++it) {
         if (it + 1 < n_it) ok = issue_sdp(it + 1);
         if (!ok) break;
-        const int st = it & 1;
+        const int st = it % kQStages;
         if (!mbar_wait(bar_pfull, it & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sq = sQ + st * kQBytes, sdo = sDO + st * kQBytes;
@@ -377,7 +380,8 @@ constexpr int kBM = 128, kBN = 64;
 constexpr int kQBytes = kBM * kHD * 2;         // 32 KiB
 constexpr int kKVBytes = kBN * kHD * 2;        // 16 KiB
 constexpr int kDSBytes = kBM * kBN * 2;        // 16 KiB
-constexpr int kTileBytes = 2 * kQBytes + 4 * kKVBytes + kDSBytes;   // 147456
+constexpr int kKVStages = 4;                   // K / V ring: a tile is requested three iterations ahead of its use
+constexpr int kTileBytes = 2 * kQBytes + 2 * kKVStages * kKVBytes + kDSBytes;   // 212992
 constexpr int kSmemBytes = kTileBytes + 256 + 1024;
 constexpr int kTmemCols = 512;                 // [S dP] x 2 | dQ
 }  // namespace dq
@@ -392,16 +396,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
   const uint32_t sQ = base, sDO = sQ + kQBytes;
-  const uint32_t sK = sDO + kQBytes;            // 2 stages
-  const uint32_t sV = sK + 2 * kKVBytes;        // 2 stages
-  const uint32_t sDS = sV + 2 * kKVBytes;
+  const uint32_t sK = sDO + kQBytes;            // kKVStages stages
+  const uint32_t sV = sK + kKVStages * kKVBytes;
+  const uint32_t sDS = sV + kKVStages * kKVBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(gen + kTileBytes);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t bar_q = bar0;
-  const uint32_t bar_kvfull = bar0 + 8, bar_kvempty = bar0 + 24;
-  const uint32_t bar_sfull = bar0 + 40, bar_sempty = bar0 + 56;
-  const uint32_t bar_dsfull = bar0 + 72, bar_dsdone = bar0 + 80;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  const uint32_t bar_kvfull = bar0 + 8, bar_kvempty = bar0 + 40;    // up to 4 stages each
+  const uint32_t bar_sfull = bar0 + 72, bar_sempty = bar0 + 88;
+  const uint32_t bar_dsfull = bar0 + 104, bar_dsdone = bar0 + 112;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -424,9 +428,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kKVStages; ++s) {
       mbar_init(bar_kvfull + 8 * s, 1);
       mbar_init(bar_kvempty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sfull + 8 * s, 1);
       mbar_init(bar_sempty + 8 * s, 256);
     }
@@ -457,9 +463,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tma_load_2d(sDO, &map_do, h * kHD, qrow, bar_q);
       tma_load_2d(sDO + kBM * 128, &map_do, h * kHD + 64, qrow, bar_q);
       for (int j = 0; j < n_tiles; ++j) {
-        const int st = j & 1;
+        const int st = j % kKVStages;
         const int krow = b * p.Lk + (j0 + j) * kBN;
-        if (!mbar_wait(bar_kvempty + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(bar_kvempty + 8 * st, ((j / kKVStages) & 1) ^ 1, abort_flag)) {
           atomicOr(p.status, kStatusWaitTimeoutProducer);
           break;
         }
@@ -477,12 +483,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_d = make_idesc_bf16(kBM, kHD, false, true);
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       auto issue_sdp = [&](int j) -> bool {
-        const int st = j & 1;
+        const int st = j & 1, ks = j % kKVStages;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(bar_kvfull + 8 * st, ph, abort_flag)) return false;
+        if (!mbar_wait(bar_kvfull + 8 * ks, (j / kKVStages) & 1, abort_flag)) return false;
         if (!mbar_wait(bar_sempty + 8 * st, ph ^ 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t sk = sK + st * kKVBytes, sv = sV + st * kKVBytes;
+        const uint32_t sk = sK + ks * kKVBytes, sv = sV + ks * kKVBytes;
 #pragma unroll
         for (int k = 0; k < kHD / 16; ++k) {
           const uint32_t sub = k >> 2, kk = k & 3;
@@ -502,7 +508,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) ok = issue_sdp(j + 1);
         if (!ok) break;
-        const int st = j & 1;
+        const int st = j % kKVStages;
         if (!mbar_wait(bar_dsfull, j & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sk = sK + st * kKVBytes;

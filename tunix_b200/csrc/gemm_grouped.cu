@@ -35,7 +35,9 @@ constexpr int kABytes = BM * BK * 2;
 constexpr int kBBytes = BN * BK * 2;
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kTmemCols = 2 * BN;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+constexpr int kRedBytes = 32 * 128;             // one [32 rows x 32 fp32] swizzled box of the reduce-add epilogue
+constexpr int kRedBufBytes = 4 * 2 * kRedBytes; // per epilogue warp: two boxes (double buffer)
+constexpr int kSmemBytes = kStages * kStageBytes + kRedBufBytes + 1024 + 256;
 
 struct GroupedParams {
   GemmParams g;            // C, ldc, M/N/K = extents of the tile grid and of the reduction (modes 0/1)
@@ -43,6 +45,7 @@ struct GroupedParams {
   const int* offsets;      // mode 2
   int num_experts;
   int estride;             // rows per expert in the stacked operand (B in modes 0/1, C in mode 2)
+  int red_epilogue;        // mode 2 with fp32 accumulation: C += tile through TMA reduce-adds (C is never read)
 };
 
 // One unit of work: an output tile and the K range that produces it.
@@ -82,11 +85,12 @@ __device__ __forceinline__ bool decode_item(const GroupedParams& p, int t, int m
 template <bool A_MN, bool B_MN, int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const GroupedParams p) {
+                    const __grid_constant__ CUtensorMap map_c, const GroupedParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kStages * kStageBytes);
+  const uint32_t red_base = smem_base + kStages * kStageBytes;      // 1024-byte aligned
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + kStages * kStageBytes + kRedBufBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kStages;
   const uint32_t bar_tfull = bar_empty + 8 * kStages;
@@ -221,17 +225,49 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (MODE == 2 && p.red_epilogue) {
+        // each warp stages [32 x 32] fp32 boxes (128-byte swizzle) and hands them to the TMA unit as reduce-adds:
+        // coalesced, and the adds run in L2. A warp's 32 rows lie inside one expert (M is a multiple of 32).
+        const int row0 = it.m0 + quarter * 32;
+        const uint32_t my_red = red_base + quarter * (2 * kRedBytes);
+        uint8_t* my_red_gen = smem_gen + kStages * kStageBytes + quarter * (2 * kRedBytes);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c, r);
-        tmem_ld_wait();
-        if (local_row < p.g.M) txg::store_row_chunk(g, it.c_row + local_row, it.n0 + c, r);
+        for (int c = 0; c < BN; c += 32) {
+          const int buf = (c >> 5) & 1;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<1>();      // the box issued two chunks ago has been read
+          __syncwarp();
+          uint8_t* rowp = my_red_gen + buf * kRedBytes + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 v = make_float4(__uint_as_float(r[4 * j]) * p.g.alpha, __uint_as_float(r[4 * j + 1]) * p.g.alpha,
+                                         __uint_as_float(r[4 * j + 2]) * p.g.alpha,
+                                         __uint_as_float(r[4 * j + 3]) * p.g.alpha);
+            *reinterpret_cast<float4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.g.M && it.n0 + c < p.g.N) {
+            tma_reduce_add_2d(&map_c, my_red + buf * kRedBytes, it.n0 + c, it.c_row + row0);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (local_row < p.g.M) txg::store_row_chunk(g, it.c_row + local_row, it.n0 + c, r);
+        }
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (MODE == 2 && p.red_epilogue && lane == 0) tma_store_wait<0>();   // reduces have landed before smem goes away
   }
 
   if (*abort_flag) __nanosleep(200000);
@@ -244,7 +280,8 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 }
 
 template <bool A_MN, bool B_MN, int MODE>
-int launch(const CUtensorMap& ma, const CUtensorMap& mbm, const GroupedParams& p, cudaStream_t stream) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mbm, const CUtensorMap& mc, const GroupedParams& p,
+           cudaStream_t stream) {
   static bool attr_set = false;
   auto kern = gemm_grouped_kernel<A_MN, B_MN, MODE>;
   if (!attr_set) {
@@ -255,7 +292,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mbm, const GroupedParams& p
   const long long mb = (p.g.M + BM - 1) / BM, nb = (p.g.N + BN - 1) / BN;
   long long items = (MODE == 2 ? p.num_experts : 1) * mb * nb;
   int grid = static_cast<int>(items < txh::sm_count() ? items : txh::sm_count());
-  kern<<<grid, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, p);
+  kern<<<grid, NUM_THREADS, kSmemBytes, stream>>>(ma, mbm, mc, p);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 
@@ -291,7 +328,7 @@ extern "C" int tx_gemm_grouped_bf16(const void* A, const void* B, void* C, const
     if (rc) return 100 + rc;
     rc = txh::make_map_2d_bf16(&mbm, B, static_cast<uint64_t>(E) * N, K, ldb, BN, BK);
     if (rc) return 200 + rc;
-    return launch<false, false, 0>(ma, mbm, p, stream);
+    return launch<false, false, 0>(ma, mbm, ma, p, stream);
   }
   if (mode == 1) {
     p.g.M = R; p.g.N = K; p.g.K = N; p.estride = N;
@@ -299,12 +336,18 @@ extern "C" int tx_gemm_grouped_bf16(const void* A, const void* B, void* C, const
     if (rc) return 100 + rc;
     rc = txh::make_map_2d_bf16(&mbm, B, static_cast<uint64_t>(E) * N, K, ldb, BK, 64);
     if (rc) return 200 + rc;
-    return launch<false, true, 1>(ma, mbm, p, stream);
+    return launch<false, true, 1>(ma, mbm, ma, p, stream);
   }
   p.g.M = N; p.g.N = K; p.g.K = 0; p.estride = N;
   rc = txh::make_map_2d_bf16(&ma, A, R, N, lda, BK, 64);
   if (rc) return 100 + rc;
   rc = txh::make_map_2d_bf16(&mbm, B, R, K, ldb, BK, 64);
   if (rc) return 200 + rc;
-  return launch<true, true, 2>(ma, mbm, p, stream);
+  CUtensorMap mc = ma;
+  if (c_fp32 && accumulate && (N % 32) == 0) {
+    rc = txh::make_map_2d_f32(&mc, C, static_cast<uint64_t>(E) * N, K, ldc, 32);
+    if (rc) return 300 + rc;
+    p.red_epilogue = 1;
+  }
+  return launch<true, true, 2>(ma, mbm, mc, p, stream);
 }

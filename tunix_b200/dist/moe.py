@@ -299,7 +299,7 @@ def ep_forward_peer(layer, x2: torch.Tensor, topv: torch.Tensor, topi: torch.Ten
   per = E // ep
   T, D = x2.shape
   flat_e = topi.reshape(-1)
-  counts = torch.bincount(flat_e, minlength=E)
+  counts = moe_ops.count_rows(flat_e, E)
   table = torch.empty((ep, E), dtype=counts.dtype, device=counts.device)
   dist.all_gather_into_tensor(table, counts, group=group)
   ws = peer_workspace(group, x2.device, T * k, D, ep, per, getattr(layer, "ep_capacity_factor", None))

@@ -97,8 +97,16 @@ class AutoModel:
     n = naming.ModelNaming(model_id=model_id)
     cfg = kwargs.pop("model_config", None) or call_model_config(n.model_name)
     device = device or ("cuda" if torch.cuda.is_available() else "cpu")
+    model_cls = Transformer
+    if n.model_config_category == "gemma4":
+      from .gemma4 import Gemma4
+      model_cls = Gemma4
+      if model_source not in (ModelSource.DUMMY,):
+        raise NotImplementedError("Gemma 4 weights: only random initialisation (model_source=DUMMY) is wired up; "
+                                  "the safetensors key map of this family is not written yet")
+      cfg = cfg.replace(dtype=dtype) if dtype is not None else cfg
     if model_source == ModelSource.DUMMY:
-      model = dummy_model_creator.create_dummy_model(Transformer, cfg, mesh, dtype=dtype, device=device,
+      model = dummy_model_creator.create_dummy_model(model_cls, cfg, mesh, dtype=dtype, device=device,
                                                      random_seed=kwargs.pop("rng_seed", 0))
       resolved = None
     else:

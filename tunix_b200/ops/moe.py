@@ -55,6 +55,12 @@ def padded_rows(n: int, num_experts: int) -> int:
   return (n + num_experts * (TILE - 1) + TILE - 1) // TILE * TILE
 
 
+def count_rows(ids: torch.Tensor, num_experts: int) -> torch.Tensor:
+  """Rows per expert without the device-to-host read that `torch.bincount` does to size its result."""
+  return torch.zeros(num_experts, dtype=torch.long, device=ids.device).scatter_add_(
+      0, ids.reshape(-1).long(), torch.ones(ids.numel(), dtype=torch.long, device=ids.device))
+
+
 def padded_layout(expert_ids: torch.Tensor, num_experts: int, counts: Optional[torch.Tensor] = None,
                   rank_in_expert: Optional[torch.Tensor] = None) -> PaddedLayout:
   """expert_ids [n]: expert of every routed row. All device-side; nothing is read back."""
@@ -62,7 +68,7 @@ def padded_layout(expert_ids: torch.Tensor, num_experts: int, counts: Optional[t
   E = num_experts
   ids = expert_ids.reshape(-1).long()
   if counts is None:
-    counts = torch.bincount(ids, minlength=E)
+    counts = count_rows(ids, E)
   padded = (counts + (TILE - 1)) // TILE * TILE
   offsets = torch.zeros(E + 1, dtype=torch.long, device=ids.device)
   offsets[1:] = torch.cumsum(padded, 0)
