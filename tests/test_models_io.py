@@ -197,3 +197,15 @@ def test_gemma3_vision_tower_and_multimodal_merge():
   emb = vision.merge_embeddings(torch.zeros(1, 5, 2), torch.arange(8.0).view(1, 2, 2, 2),
                                 torch.tensor([[False, True, True, False, True]]))
   assert emb[0].tolist() == [[0, 0], [0, 1], [2, 3], [0, 0], [4, 5]]
+
+
+def test_oss_download_helpers_fail_clearly_offline(tmp_path, monkeypatch):
+  import pytest
+  from tunix_b200.oss import utils as oss
+  assert oss.pathways_available() is False
+  assert oss.load_file_from_gcs(str(tmp_path)) == str(tmp_path)          # local paths pass through
+  monkeypatch.setenv("HF_HUB_OFFLINE", "1")
+  with pytest.raises(FileNotFoundError, match="local directory"):
+    oss.hf_pipeline("some-org/definitely-not-cached-model", str(tmp_path / "dl"))
+  with pytest.raises(FileNotFoundError, match="local directory"):
+    oss.load_file_from_gcs("gs://no-such-bucket-tunix-b200/ckpt", str(tmp_path / "gcs"))
