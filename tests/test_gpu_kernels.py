@@ -361,3 +361,19 @@ def test_gemm_with_fused_allgather_of_sharded_weight(kernel_lib, world, rank):
     else:
       assert torch.equal(blk, shards[r])
   assert int(cnt.min()) == int(cnt.max()) or world > 1
+
+
+def test_deterministic_mode_makes_skinny_gemms_bitwise_reproducible(kernel_lib):
+  from tunix_b200.ops import _lib, kernels
+  torch.manual_seed(12)
+  a = torch.randn(64, 12288, device="cuda", dtype=torch.bfloat16)
+  w = torch.randn(4096, 12288, device="cuda", dtype=torch.bfloat16) / 110.0
+  ref = a.float() @ w.float().t()
+  _lib.set_deterministic(True)
+  try:
+    outs = [kernels.gemm(a, w).clone() for _ in range(4)]
+  finally:
+    _lib.set_deterministic(False)
+  assert all(torch.equal(outs[0], o) for o in outs[1:])
+  assert torch.allclose(outs[0].float(), ref, atol=5e-2, rtol=3e-2)
+  assert torch.allclose(kernels.gemm(a, w).float(), ref, atol=5e-2, rtol=3e-2)       # split-K path back on

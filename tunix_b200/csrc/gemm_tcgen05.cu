@@ -306,6 +306,11 @@ static float* splitk_workspace() {
 
 extern "C" int tx_gemm_warmup() { return splitk_workspace() != nullptr ? 0 : 300; }
 
+static int g_deterministic = 0;
+// 1: no split-K (its partial sums meet through fp32 atomics, whose order varies from run to run); every product
+// is then reduced in one fixed order and repeated launches give identical bits.
+extern "C" void tx_gemm_set_deterministic(int v) { g_deterministic = v; }
+
 static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
 extern "C" void tx_gemm_set_disable_pair(int v) { g_disable_pair = v; }
@@ -342,6 +347,7 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
     int ks = tiles < 96 ? (2 * txh::sm_count()) / tiles : 1;     // measured: splitting only pays when few tiles exist
     if (ks > 8) ks = 8;
     if (ks > num_kb / 8) ks = num_kb / 8;
+    if (g_deterministic) ks = 1;
     while (ks > 1 && (ks - 1) * ((num_kb + ks - 1) / ks) >= num_kb) --ks;     // no empty K range
     if (ks > 1 && !c_fp32 && !accumulate && (N & 3) == 0 && static_cast<long long>(M) * N <= kSplitWsFloats) {
       float* ws = splitk_workspace();

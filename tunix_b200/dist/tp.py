@@ -100,7 +100,8 @@ class FusedRowExit(torch.nn.Module):
     lin = self.inner
     x2 = x.reshape(-1, x.shape[-1])
     M = x2.shape[0]
-    fused = (not torch.is_grad_enabled() and x2.is_cuda and x2.dtype == torch.bfloat16 and M <= self.max_rows
+    from ..ops import _lib as _lib0
+    fused = (not _lib0.deterministic() and not torch.is_grad_enabled() and x2.is_cuda and x2.dtype == torch.bfloat16 and M <= self.max_rows
              and M % 8 == 0 and lin.b is None and lin.quant is None and not len(lin.lora_a)
              and x2.stride(1) == 1 and x2.data_ptr() % 16 == 0)
     if not fused:

@@ -101,7 +101,29 @@ def load():
   with _LOCK:
     if _LIB is None and _LIB_PATH.exists():
       _LIB = _declare(ctypes.CDLL(str(_LIB_PATH), mode=ctypes.RTLD_GLOBAL))
+      if _DETERMINISTIC and hasattr(_LIB, "tx_gemm_set_deterministic"):
+        _LIB.tx_gemm_set_deterministic(1)
   return _LIB
+
+
+_DETERMINISTIC = os.environ.get("TUNIX_B200_DETERMINISTIC", "0") == "1"
+
+
+def deterministic() -> bool:
+  return _DETERMINISTIC
+
+
+def set_deterministic(flag: bool) -> None:
+  """Bitwise-reproducible mode (also `TUNIX_B200_DETERMINISTIC=1`): products whose partial sums would meet through
+  floating-point atomics take their single-pass form - no split-K in skinny GEMMs, and tensor-parallel exits
+  all-reduce through the collective library instead of the atomic-add epilogue. Flash attention (fixed reduction
+  order), the log-prob kernels, the grouped expert GEMMs and the Philox sampler are reproducible in either mode;
+  the embedding gradient (a scatter of fp32 atomic adds over repeated tokens) is the remaining exception."""
+  global _DETERMINISTIC
+  _DETERMINISTIC = bool(flag)
+  lib = load()
+  if lib is not None and hasattr(lib, "tx_gemm_set_deterministic"):
+    lib.tx_gemm_set_deterministic(int(_DETERMINISTIC))
 
 
 def require():
