@@ -118,7 +118,7 @@ def set_deterministic(flag: bool) -> None:
   floating-point atomics take their single-pass form - no split-K in skinny GEMMs, and tensor-parallel exits
   all-reduce through the collective library instead of the atomic-add epilogue. Flash attention (fixed reduction
   order), the log-prob kernels, the grouped expert GEMMs and the Philox sampler are reproducible in either mode;
-  the embedding gradient (a scatter of fp32 atomic adds over repeated tokens) is the remaining exception."""
+  the embedding gradient switches from fp32 atomic adds to a sorted accumulation."""
   global _DETERMINISTIC
   _DETERMINISTIC = bool(flag)
   lib = load()

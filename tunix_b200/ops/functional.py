@@ -264,6 +264,12 @@ class _EmbeddingFn(torch.autograd.Function):
   def backward(ctx, dout):
     (ids,) = ctx.saved_tensors
     mg = _main_grad(ctx.holder)
+    from . import _lib
+    if _lib.deterministic():
+      # sorted accumulation (index_put_ with accumulate sorts the indices on CUDA) instead of fp32 atomics
+      g = mg if mg is not None else torch.zeros(ctx.shape, dtype=torch.float32, device=dout.device)
+      g.index_put_((ids.long(),), dout.float() * ctx.scale, accumulate=True)
+      return None, (None if mg is not None else g.to(dout.dtype)), None, None
     if mg is not None:
       kernels.embedding_bwd(ids, dout.contiguous(), mg, ctx.scale)
       return None, None, None, None
