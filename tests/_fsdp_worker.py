@@ -43,7 +43,7 @@ def main():
   if cuda:
     model = fsdp.shard_model(model, mesh, transport=a.transport)
   tc = TrainingConfig(eval_every_n_steps=100, gradient_accumulation_steps=2, max_grad_norm=1.0, pbar_description=None)
-  tr = PeftTrainer(model, optim.adamw(1e-2, weight_decay=0.01), tc)
+  tr = PeftTrainer(model, optim.adamw(2e-3, weight_decay=0.01), tc)
   tr.with_grad_sync(fsdp.GradSync(model, mesh))
   g = torch.Generator().manual_seed(7)
   data = []

@@ -334,13 +334,13 @@ def test_fused_lora_linear_matches_unfused(kernel_lib, multi):
     assert err < 2e-2, (i, err.item())
 
 
-@pytest.mark.parametrize("world,rank", [(1, 0), (2, 0), (2, 1), (4, 2)])
-def test_gemm_with_fused_allgather_of_sharded_weight(kernel_lib, world, rank):
+@pytest.mark.parametrize("world,rank,slab", [(1, 0, 128), (2, 0, 128), (2, 1, 256), (4, 2, 128), (4, 3, 256)])
+def test_gemm_with_fused_allgather_of_sharded_weight(kernel_lib, world, rank, slab):
   """The all-gather-into-GEMM kernel with every "rank's" shard on this one GPU (a single launch: the copy warps
   and the tensor-core warps of the same kernel hand slabs over through counters)."""
   from tunix_b200.ops import _lib, kernels
   torch.manual_seed(11)
-  M, K, N = 384, 256, 128 * world * 3
+  M, K, N = 384, 256, (128 * world * 3 if slab == 128 else 256 * world * 2)   # the kernel picks 256-row slabs when it can
   a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
   w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / K ** 0.5
   shards = [w[r * (N // world):(r + 1) * (N // world)].clone() for r in range(world)]

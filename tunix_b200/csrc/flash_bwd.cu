@@ -14,8 +14,10 @@
 //         S = Q K^T, dP = dO V^T, dS = P * (dP - delta), dQ += dS K.
 //
 // delta[b,h,i] = sum_d dO[i,d] * O[i,d] comes from flash_bwd_delta_kernel. Roles inside a CTA
-// are those of the forward kernel: warp 0 TMA producer, warp 1 MMA issuer, warps 2..5 one
-// thread per TMEM lane. Every wait is bounded and reports through the status word.
+// are those of the forward kernel: warp 0 TMA producer, warp 1 MMA issuer; the elementwise work
+// between the two product pairs has no row reduction (lse and delta are inputs), so it is split
+// over 8 warps: warps 2..5 take columns 0..31 of their TMEM lanes, warps 6..9 columns 32..63.
+// Every wait is bounded and reports through the status word.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -28,7 +30,7 @@ namespace {
 using namespace tx;
 
 constexpr int kHD = 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // warp 0 producer, warp 1 MMA issuer, warps 2..9 elementwise (two per TMEM lane quarter)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct BwdParams {
@@ -60,11 +62,20 @@ __device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint
         make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
 }
 
-// TMEM accumulator [128 lanes x 128 cols] -> bf16 rows in global memory, scaled.
+// Half a row: 32 bf16 (16 packed words) into 16-byte chunks [4 ch, 4 ch + 4) of row r.
+__device__ __forceinline__ void store_half_row_sw128(uint8_t* tile, int r, int ch, const uint32_t (&pk)[16]) {
+  uint8_t* row = tile + r * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<uint4*>(row + (((ch * 4 + c) ^ (r & 7)) << 4)) =
+        make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+}
+
+// TMEM accumulator columns [c0, c1) of [128 lanes x 128 cols] -> bf16 rows in global memory, scaled.
 __device__ __forceinline__ void store_acc_rows(uint32_t taddr, __nv_bfloat16* row_ptr, bool in_range, float mul,
-                                               bool have_data) {
+                                               bool have_data, int c0 = 0, int c1 = kHD) {
 #pragma unroll 1
-  for (int c = 0; c < kHD; c += 32) {
+  for (int c = c0; c < c1; c += 32) {
     uint32_t t[32];
     if (have_data) {
       tmem_ld_32x32b_x32(taddr + c, t);
@@ -179,11 +190,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sfull + 8 * s, 1);
-      mbar_init(bar_sempty + 8 * s, 128);
+      mbar_init(bar_sempty + 8 * s, 256);
     }
-    mbar_init(bar_pfull, 128);
+    mbar_init(bar_pfull, 256);
     mbar_init(bar_pdone, 1);
-    mbar_init(bar_vec, 128);
+    mbar_init(bar_vec, 256);
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -275,7 +286,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;           // key row in the tile == TMEM lane
-    const int t128 = threadIdx.x - 64;           // 0..127 among the compute threads
+    const int ch = (warp - 2) >> 2;              // which 32 of the 64 query columns this thread handles
+    const int t256 = threadIdx.x - 64;           // 0..255 among the compute threads
     const int kj = k0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
@@ -284,39 +296,40 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       const int h = kvh * g + it / per_head;
       const int q0 = (i_start + it % per_head) * kQT;
       {
-        const int c = t128 & 63;
+        const int c = t256 & 63, which = t256 >> 6;
         const int qi = q0 + c;
         const long long idx = (static_cast<long long>(b) * p.N + h) * p.Lq + qi;
-        if (t128 < 64) {
+        if (which == 0) {
           float v = qi < p.Lq ? p.lse[idx] : INFINITY;
           sLse[st * kQT + c] = (v == -INFINITY) ? INFINITY : v * kLog2e;
+        } else if (which == 1) {
           sLo[st * kQT + c] = (packed && qi < p.Lq) ? p.seg_lo[static_cast<long long>(b) * p.Lq + qi] : 0;
-        } else {
+        } else if (which == 2) {
           sDelta[st * kQT + c] = qi < p.Lq ? p.delta[idx] : 0.f;
+        } else {
           sHi[st * kQT + c] = (packed && qi < p.Lq) ? p.seg_hi[static_cast<long long>(b) * p.Lq + qi] : p.Lk - 1;
         }
       }
-      // the 128 row threads meet on a bounded barrier (a hardware bar.sync could not time out)
+      // the 256 elementwise threads meet on a bounded barrier (a hardware bar.sync could not time out)
       mbar_arrive(bar_vec);
       ok = __all_sync(0xffffffffu, mbar_wait(bar_vec, it & 1, abort_flag));
       if (!ok) break;
       ok = __all_sync(0xffffffffu, mbar_wait(bar_sfull + 8 * st, (it >> 1) & 1, abort_flag));
       if (!ok) break;
       tc_fence_after();
-      uint32_t pk[32], dk_[32];
+      uint32_t pk[16], dk_[16];
       const bool need_mask = packed || (p.causal && k0 + kKeys - 1 > q0 + off) || (k0 + kKeys > p.Lk);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t ts[32], td[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + half * 32, ts);
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + 64 + half * 32, td);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + ch * 32, ts);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + 64 + ch * 32, td);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           float pv[2], dv[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int c = half * 32 + i + e;
+            const int c = ch * 32 + i + e;
             float pe = exp2f(__uint_as_float(ts[i + e]) * p.scale_log2 - sLse[st * kQT + c]);
             if (need_mask && ((p.causal && kj > q0 + c + off) || kj >= p.Lk || kj < sLo[st * kQT + c] ||
                               kj > sHi[st * kQT + c]))
@@ -324,8 +337,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             pv[e] = pe;
             dv[e] = pe * (__uint_as_float(td[i + e]) - sDelta[st * kQT + c]);
           }
-          pk[half * 16 + (i >> 1)] = pack2(pv[0], pv[1]);
-          dk_[half * 16 + (i >> 1)] = pack2(dv[0], dv[1]);
+          pk[i >> 1] = pack2(pv[0], pv[1]);
+          dk_[i >> 1] = pack2(dv[0], dv[1]);
         }
       }
       tc_fence_before();
@@ -334,8 +347,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         ok = __all_sync(0xffffffffu, mbar_wait(bar_pdone, (it - 1) & 1, abort_flag));
         if (!ok) break;
       }
-      store_row_sw128(gen + (sPT - base), r, pk);
-      store_row_sw128(gen + (sDST - base), r, dk_);
+      store_half_row_sw128(gen + (sPT - base), r, ch, pk);
+      store_half_row_sw128(gen + (sDST - base), r, ch, dk_);
       fence_proxy_async_smem();
       mbar_arrive(bar_pfull);
     }
@@ -345,8 +358,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       tc_fence_after();
       const bool in_range = kj < p.Lk;
       const long long row = static_cast<long long>(b) * p.Lk + (in_range ? kj : 0);
-      store_acc_rows(tmem_dk + lane_addr, p.out0 + row * p.ld0 + kvh * kHD, in_range, p.scale, n_it > 0);
-      store_acc_rows(tmem_dv + lane_addr, p.out1 + row * p.ld1 + kvh * kHD, in_range, 1.f, n_it > 0);
+      if (ch == 0) store_acc_rows(tmem_dk + lane_addr, p.out0 + row * p.ld0 + kvh * kHD, in_range, p.scale, n_it > 0);
+      else         store_acc_rows(tmem_dv + lane_addr, p.out1 + row * p.ld1 + kvh * kHD, in_range, 1.f, n_it > 0);
     }
   }
 
@@ -421,9 +434,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_sfull + 8 * s, 1);
-      mbar_init(bar_sempty + 8 * s, 128);
+      mbar_init(bar_sempty + 8 * s, 256);
     }
-    mbar_init(bar_dsfull, 128);
+    mbar_init(bar_dsfull, 256);
     mbar_init(bar_dsdone, 1);
     mbar_fence_init();
   }
@@ -511,6 +524,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
+    const int ch = (warp - 2) >> 2;              // which 32 of the 64 key columns this thread handles
     const int qi = q0 + r;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float lse2 = INFINITY, delta = 0.f;
@@ -534,12 +548,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int k0 = (j0 + j) * kBN;
       const int limit = p.causal ? min(qi + off, row_hi) : row_hi;
       const bool need_mask = k0 + kBN - 1 > limit || k0 < row_lo;
-      uint32_t dsk[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      uint32_t dsk[16];
+      {
         uint32_t ts[32], td[32];
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + half * 32, ts);
-        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + 64 + half * 32, td);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + ch * 32, ts);
+        tmem_ld_32x32b_x32(tmem_base + lane_addr + st * 128 + 64 + ch * 32, td);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -547,10 +560,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             float pe = exp2f(__uint_as_float(ts[i + e]) * p.scale_log2 - lse2);
-            if (need_mask && (k0 + half * 32 + i + e > limit || k0 + half * 32 + i + e < row_lo)) pe = 0.f;
+            if (need_mask && (k0 + ch * 32 + i + e > limit || k0 + ch * 32 + i + e < row_lo)) pe = 0.f;
             dv[e] = pe * (__uint_as_float(td[i + e]) - delta);
           }
-          dsk[half * 16 + (i >> 1)] = pack2(dv[0], dv[1]);
+          dsk[i >> 1] = pack2(dv[0], dv[1]);
         }
       }
       tc_fence_before();
@@ -559,7 +572,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = __all_sync(0xffffffffu, mbar_wait(bar_dsdone, (j - 1) & 1, abort_flag));
         if (!ok) break;
       }
-      store_row_sw128(gen + (sDS - base), r, dsk);
+      store_half_row_sw128(gen + (sDS - base), r, ch, dsk);
       fence_proxy_async_smem();
       mbar_arrive(bar_dsfull);
     }
@@ -569,7 +582,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_after();
       const bool in_range = qi < p.Lq;
       const long long row = static_cast<long long>(b) * p.Lq + (in_range ? qi : 0);
-      store_acc_rows(tmem_dq + lane_addr, p.out0 + row * p.ld0 + h * kHD, in_range, p.scale, n_tiles > 0);
+      store_acc_rows(tmem_dq + lane_addr, p.out0 + row * p.ld0 + h * kHD, in_range, p.scale, n_tiles > 0, ch * 64,
+                     ch * 64 + 64);
     }
   }
 

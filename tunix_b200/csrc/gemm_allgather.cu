@@ -3,13 +3,13 @@
 //   C[M, N] = A[M, K] * W[N, K]^T     with W row-sharded over `world` ranks: rank r holds W[r N/world : (r+1) N/world]
 //
 // No separate all-gather runs and the full W is never needed before the kernel starts. One launch does both:
-//   * warps 6..9 of every CTA are copy warps. Together, all CTAs pull the remote shards 128 rows (one "slab" =
-//     one column of output tiles) at a time with plain 16-byte peer loads into a local staging buffer; every CTA
+//   * warps 6..9 of every CTA are copy warps. Together, all CTAs pull the remote shards one "slab" (256 or 128
+//     rows = one column of output tiles) at a time with plain 16-byte peer loads into a local staging buffer; every CTA
 //     copies its 1/grid share of EACH slab, so slabs complete one after another at the full link rate, in the
 //     order in which the tensor-core side will need them. A per-slab counter in global memory counts the CTAs
 //     that have finished their share.
 //   * warp 0 (TMA producer), warp 1 (tcgen05.mma issuer) and warps 2..5 (epilogue) are the persistent GEMM of
-//     gemm_tcgen05.cu with 128 x 128 tiles. Tiles are walked slab by slab starting with this rank's OWN rows
+//     gemm_tcgen05.cu with 128 x 256 (or 128 x 128) tiles. Tiles are walked slab by slab starting with this rank's OWN rows
 //     (read in place, no copy, no wait), then the next rank's, and so on around the ring, so each rank starts on
 //     a different peer. Before the first TMA load of a remote slab the producer waits (bounded) until the slab's
 //     counter has reached the grid size.
@@ -24,18 +24,23 @@ using namespace tx;
 using txg::GemmParams;
 
 constexpr int BM = 128;
-constexpr int BN = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 320;
 constexpr int COPY_THREADS = 128;
-constexpr int kStages = 6;
 constexpr int kABytes = BM * BK * 2;
-constexpr int kBBytes = BN * BK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kTmemCols = 2 * BN;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
 constexpr int kMaxPeers = 8;
+
+// Tile width BN = slab height: 256 (4 stages of 48 KB, both TMEM accumulators fill the 512 columns) when the
+// shards divide into 256-row slabs, else 128 (6 stages of 32 KB).
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
 
 struct GatherParams {
   GemmParams g;
@@ -54,9 +59,13 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_allgather_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_own,
                       const __grid_constant__ CUtensorMap map_stage, const GatherParams p) {
+  constexpr int kStages = Cfg<BN>::kStages;
+  constexpr int kStageBytes = Cfg<BN>::kStageBytes;
+  constexpr int kTmemCols = Cfg<BN>::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -264,16 +273,40 @@ gemm_allgather_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }  // namespace
 
 // shards[r]: rank r's rows of W (bf16, row stride ldb), peer-mapped; shards[rank] is local. stage: local [N, K] bf16
-// scratch; slab_count: local int32 [N / 128] scratch (this call zeroes it on `stream`). A [M, K] (stride lda),
+// scratch; slab_count: local int32 [N / 128] scratch (N / 256 entries are used with 256-row slabs) (this call zeroes it on `stream`). A [M, K] (stride lda),
 // C [M, N] bf16 or fp32 (stride ldc). Needs N % (128 * world) == 0, K % 64 == 0, world <= 8.
 // Every rank of the group must have finished writing its shard before any rank launches (a barrier the caller
 // provides), and must not overwrite it before all ranks' kernels have finished.
+template <int BN>
+static int launch_gather(const void* A, void* const* shards, void* stage, GatherParams& p, int M, int N, int K,
+                         long long lda, long long ldb, int world, int rank, cudaStream_t stream) {
+  CUtensorMap ma, mown, mstage;
+  int rc = txh::make_map_2d_bf16(&ma, A, M, K, lda, BM, BK);
+  if (rc) return 100 + rc;
+  rc = txh::make_map_2d_bf16(&mown, shards[rank], N / world, K, ldb, BN, BK);
+  if (rc) return 200 + rc;
+  rc = txh::make_map_2d_bf16(&mstage, stage, N, K, K, BN, BK);
+  if (rc) return 200 + rc;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_allgather_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             Cfg<BN>::kSmemBytes) != cudaSuccess)
+      return 300;
+    attr_set = true;
+  }
+  if (cudaMemsetAsync(p.slab_count, 0, sizeof(int) * (N / BN), stream) != cudaSuccess) return 400;
+  const long long tiles = static_cast<long long>((M + BM - 1) / BM) * (N / BN);
+  const int grid = static_cast<int>(tiles < txh::sm_count() ? tiles : txh::sm_count());
+  gemm_allgather_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::kSmemBytes, stream>>>(ma, mown, mstage, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
 extern "C" int tx_gemm_bf16_allgather_b(const void* A, void* const* shards, int world, int rank, void* stage,
                                         int* slab_count, void* C, int M, int N, int K, long long lda, long long ldb,
                                         long long ldc, int c_fp32, int accumulate, float alpha, long long wait_limit_ms,
                                         int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return 1;
-  if ((N % (BN * world)) || (K % BK) || (lda & 7) || (ldb & 7) || (ldc & 3)) return 2;
+  if ((N % (128 * world)) || (K % BK) || (lda & 7) || (ldb & 7) || (ldc & 3)) return 2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
       (reinterpret_cast<uintptr_t>(stage) & 15))
     return 3;
@@ -289,23 +322,6 @@ extern "C" int tx_gemm_bf16_allgather_b(const void* A, void* const* shards, int 
   p.world = world;
   p.rank = rank;
   p.wait_limit_ns = static_cast<unsigned long long>(wait_limit_ms > 0 ? wait_limit_ms : 2000) * 1000000ull;
-  CUtensorMap ma, mown, mstage;
-  int rc = txh::make_map_2d_bf16(&ma, A, M, K, lda, BM, BK);
-  if (rc) return 100 + rc;
-  rc = txh::make_map_2d_bf16(&mown, shards[rank], N / world, K, ldb, BN, BK);
-  if (rc) return 200 + rc;
-  rc = txh::make_map_2d_bf16(&mstage, stage, N, K, K, BN, BK);
-  if (rc) return 200 + rc;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_allgather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
-        cudaSuccess)
-      return 300;
-    attr_set = true;
-  }
-  if (cudaMemsetAsync(slab_count, 0, sizeof(int) * (N / BN), stream) != cudaSuccess) return 400;
-  const long long tiles = static_cast<long long>((M + BM - 1) / BM) * (N / BN);
-  const int grid = static_cast<int>(tiles < txh::sm_count() ? tiles : txh::sm_count());
-  gemm_allgather_kernel<<<grid, NUM_THREADS, kSmemBytes, stream>>>(ma, mown, mstage, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+  if (N % (256 * world) == 0) return launch_gather<256>(A, shards, stage, p, M, N, K, lda, ldb, world, rank, stream);
+  return launch_gather<128>(A, shards, stage, p, M, N, K, lda, ldb, world, rank, stream);
 }

@@ -111,11 +111,13 @@ def run(args, ClockSampler) -> None:
       dist.barrier()
       torch.cuda.synchronize()
 
-  gen_counter = {"n": 0}
+  gen_counter = {"n": 0, "rollout_s": 0.0}
   orig_generate = cluster.rollout.generate
 
   def counting_generate(prompts, rollout_config, **kw):
-    out = orig_generate(prompts, rollout_config, **kw)
+    t_in = time.perf_counter()
+    out = orig_generate(prompts, rollout_config, **kw)       # returns host-side ids: the rollout has finished
+    gen_counter["rollout_s"] += time.perf_counter() - t_in
     gen_counter["n"] += int(sum(len(t) for t in out.tokens))
     return out
   cluster.rollout.generate = counting_generate
@@ -137,6 +139,7 @@ def run(args, ClockSampler) -> None:
       if i == args.warmup:
         sync()
         marks["gen0"] = gen_counter["n"]
+        marks["rollout0"] = gen_counter["rollout_s"]
         marks["launch0"] = _lib.launch_calls
         marks["t0"] = time.perf_counter()
         if rank == 0:
@@ -174,6 +177,9 @@ def run(args, ClockSampler) -> None:
                    "weight_sync": "none needed: rollout reads the trainer's bf16 replica in place",
                    "l2": "inputs larger than L2: every decode step streams the 16 GB weights and the KV cache"},
         "generated_tokens_per_step": gen / args.steps,
+        "phases_rank0": {"rollout_s_per_step": (gen_counter["rollout_s"] - marks["rollout0"]) / args.steps,
+                         "scoring_and_update_s_per_step": (wall - (gen_counter["rollout_s"] - marks["rollout0"]))
+                         / args.steps},
         "clocks": clocks,
         "e2e": {"value": gen / wall, "unit": "tokens/s",
                 "h2d_bytes_per_step": P * PL * 8 + P * G * (PL + NEW) * 8 * 3,
