@@ -158,12 +158,86 @@ def scatter_rows(x2: torch.Tensor, token_of_row: torch.Tensor, lay: PaddedLayout
   return buf.index_copy(0, lay.dest, x2.index_select(0, token_of_row))
 
 
+# Single-rank dispatch / combine on the row kernels of `csrc/moe_dispatch.cu` (the same kernels the expert-parallel
+# path runs over peer memory, here with one "rank" whose buffer is local): one pass over the routed rows each way
+# instead of index_select + index_copy and index_select + multiply + sum.
+def _row_ptrs(buf: torch.Tensor):
+  import ctypes
+  return (ctypes.c_void_p * 1)(buf.data_ptr())
+
+
+def _dispatch_rows(src: torch.Tensor, k: int, scale: Optional[torch.Tensor], dest32: torch.Tensor, zero_rank: torch.Tensor,
+                   rows: int) -> torch.Tensor:
+  D = src.shape[1]
+  buf = torch.zeros((rows, D), dtype=bf16, device=src.device)
+  rc = _lib.require().tx_moe_dispatch_rows(src.data_ptr(), src.stride(0), None, k,
+                                           scale.data_ptr() if scale is not None else None, zero_rank.data_ptr(),
+                                           dest32.data_ptr(), _row_ptrs(buf), 1, dest32.numel(), D, rows,
+                                           _lib.status_word(src.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_moe_dispatch_rows")
+  return buf
+
+
+def _combine_rows(buf: torch.Tensor, weights: Optional[torch.Tensor], k: int, T: int, dest32: torch.Tensor,
+                  zero_rank: torch.Tensor, keep_rows: bool):
+  D = buf.shape[1]
+  out = torch.empty((T, D), dtype=bf16, device=buf.device)
+  gathered = torch.empty((T * k, D), dtype=bf16, device=buf.device) if keep_rows else None
+  rc = _lib.require().tx_moe_combine_rows(_row_ptrs(buf), 1, zero_rank.data_ptr(), dest32.data_ptr(),
+                                          weights.data_ptr() if weights is not None else None, k, out.data_ptr(),
+                                          out.stride(0), gathered.data_ptr() if gathered is not None else None, T, D,
+                                          buf.shape[0], _lib.status_word(buf.device).data_ptr(), _lib.stream_ptr())
+  _lib.check_rc(rc, "tx_moe_combine_rows")
+  return out, gathered
+
+
+class _LocalDispatch(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, x2, dest32, zero_rank, rows, k):
+    ctx.save_for_backward(dest32, zero_rank)
+    ctx.k, ctx.T = k, x2.shape[0]
+    return _dispatch_rows(x2, k, None, dest32, zero_rank, rows)
+
+  @staticmethod
+  def backward(ctx, dbuf):
+    dest32, zero_rank = ctx.saved_tensors
+    dx, _ = _combine_rows(dbuf.contiguous(), None, ctx.k, ctx.T, dest32, zero_rank, keep_rows=False)
+    return dx, None, None, None, None
+
+
+class _LocalCombine(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, y_pad, topv, dest32, zero_rank):
+    T, k = topv.shape
+    w = topv.reshape(-1).float().contiguous()
+    out, gathered = _combine_rows(y_pad, w, k, T, dest32, zero_rank, keep_rows=True)
+    ctx.save_for_backward(gathered, w, dest32, zero_rank)
+    ctx.shape, ctx.rows = (T, k), y_pad.shape[0]
+    return out
+
+  @staticmethod
+  def backward(ctx, dout):
+    gathered, w, dest32, zero_rank = ctx.saved_tensors
+    T, k = ctx.shape
+    dout = dout.contiguous()
+    dtopv = torch.einsum("tkd,td->tk", gathered.view(T, k, -1).float(), dout.float())
+    return _dispatch_rows(dout, k, w, dest32, zero_rank, ctx.rows), dtopv, None, None
+
+
 def moe_forward_padded(x2: torch.Tensor, topv: torch.Tensor, topi: torch.Tensor, gate_up: torch.Tensor,
                        down: torch.Tensor, kind: str) -> torch.Tensor:
   """Single-rank routed MLP: x2 [T, D], topv/topi [T, k] -> [T, D]."""
   T, k = topi.shape
   E = gate_up.shape[0]
   lay = padded_layout(topi.reshape(-1), E)
+  if x2.shape[1] % 8 == 0 and k <= 16:
+    dest32 = lay.dest.int()
+    zero_rank = torch.zeros_like(dest32)
+    x_pad = _LocalDispatch.apply(x2.contiguous(), dest32, zero_rank, lay.rows, k)
+    y_pad = grouped_mlp_padded(x_pad, lay, gate_up, down, kind)
+    return _LocalCombine.apply(y_pad, topv.float(), dest32, zero_rank)
   tok = torch.arange(T, device=x2.device).repeat_interleave(k)
   y_pad = grouped_mlp_padded(scatter_rows(x2, tok, lay), lay, gate_up, down, kind)
   ys = y_pad.index_select(0, lay.dest) * topv.reshape(-1, 1).to(y_pad.dtype)
