@@ -180,7 +180,7 @@ def main():
   remat = args.remat
   if remat == "auto":
     remat = "none"      # the fused decoder-layer node stores only what is expensive to rebuild
-  micro = args.micro_batch or min(per_gpu, 2 if remat == "none" else 4)
+  micro = args.micro_batch or min(per_gpu, 1 if moe else (2 if remat == "none" else 4))   # MoE keeps routed-row buffers per layer
   ga = per_gpu // micro
   cfg = cfg.replace(dtype=torch.bfloat16, max_position=S,
                     remat_config=RematConfig.BLOCK if remat == "block" else RematConfig.NONE)
