@@ -37,7 +37,7 @@ constexpr int GROUP_M = 8;      // tile-order swizzle: 8 row-blocks share their 
 
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : (BN == 64 ? 8 : 10));
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -311,6 +311,15 @@ static int g_deterministic = 0;
 // is then reduced in one fixed order and repeated launches give identical bits.
 extern "C" void tx_gemm_set_deterministic(int v) { g_deterministic = v; }
 
+// Skinny-GEMM policy knobs (decode shapes, M <= 128): tile width 64 or 32 for the plain K-major product, and the
+// tile count below which K is split over several CTAs. Settable for measurements; the defaults are the measured best.
+static int g_skinny_bn32 = 0;
+static int g_split_limit = 96;
+extern "C" void tx_gemm_set_tuning(int skinny_bn32, int split_limit) {
+  g_skinny_bn32 = skinny_bn32;
+  if (split_limit > 0) g_split_limit = split_limit;
+}
+
 static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
 extern "C" void tx_gemm_set_disable_pair(int v) { g_disable_pair = v; }
@@ -343,8 +352,9 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
   if (K2 == 0 && M <= BM && static_cast<long long>((N + 127) / 128) < 2LL * txh::sm_count()) {
     // Too few tiles to fill the GPU: split K over several CTAs per tile, sum the fp32 partials with
     // vector atomics in a scratch buffer, then round to bf16.
-    const int tiles = (N + 63) / 64, num_kb = (K + BK - 1) / BK;
-    int ks = tiles < 96 ? (2 * txh::sm_count()) / tiles : 1;     // measured: splitting only pays when few tiles exist
+    const bool bn32 = g_skinny_bn32 && sel0 == 0;                // 32-column tiles: twice as many CTAs on the stream
+    const int tiles = bn32 ? (N + 31) / 32 : (N + 63) / 64, num_kb = (K + BK - 1) / BK;
+    int ks = tiles < g_split_limit ? (2 * txh::sm_count()) / tiles : 1;   // splitting only pays when few tiles exist
     if (ks > 8) ks = 8;
     if (ks > num_kb / 8) ks = num_kb / 8;
     if (g_deterministic) ks = 1;
@@ -356,7 +366,8 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
       GemmParams ps{ws, N, M, N, K, 1, 0, alpha, status, ks, 0, 0, {nullptr}};
       int rc;
       switch (sel0) {
-        case 0: rc = launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
+        case 0: rc = bn32 ? launch<32, false, false>(A, B, ps, lda, ldb, stream, max_ctas)
+                          : launch<64, false, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
         case 1: rc = launch<64, false, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
         case 2: rc = launch<64, true, false>(A, B, ps, lda, ldb, stream, max_ctas); break;
         default: rc = launch<64, true, true>(A, B, ps, lda, ldb, stream, max_ctas); break;
@@ -368,7 +379,8 @@ extern "C" int tx_gemm_bf16_dual(const void* A, const void* B, const void* A2, c
       return cudaGetLastError() == cudaSuccess ? 0 : 400;
     }
     switch (sel0) {
-      case 0: return launch<64, false, false>(A, B, p, lda, ldb, stream, max_ctas);
+      case 0: return bn32 ? launch<32, false, false>(A, B, p, lda, ldb, stream, max_ctas)
+                          : launch<64, false, false>(A, B, p, lda, ldb, stream, max_ctas);
       case 1: return launch<64, false, true>(A, B, p, lda, ldb, stream, max_ctas);
       case 2: return launch<64, true, false>(A, B, p, lda, ldb, stream, max_ctas);
       default: return launch<64, true, true>(A, B, p, lda, ldb, stream, max_ctas);
