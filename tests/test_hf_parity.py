@@ -126,3 +126,40 @@ def test_gemma3_text_parity_local_global_rope():
       if "norm" in n:
         p.normal_(0, 0.2)
   _compare(m, _ours("gemma3", hf, sliding_window_size=8), atol=5e-4)
+
+
+def test_gemma3_multimodal_parity_vision_tower_projector_and_merge():
+  """SigLIP tower + average pooling + soft-embedding norm + projector + merge into the text embeddings, against
+  Hugging Face `Gemma3ForConditionalGeneration` with the same random weights (plain causal mask on both sides)."""
+  from transformers import Gemma3Config, Gemma3ForConditionalGeneration, Gemma3TextConfig, SiglipVisionConfig
+  from tunix_b200.models.gemma3 import vision as vis
+  tc = Gemma3TextConfig(**_tiny(head_dim=16, query_pre_attn_scalar=16, sliding_window=32, rope_theta=1000000.0,
+                                rope_local_base_freq=10000.0, hidden_activation="gelu_pytorch_tanh",
+                                attn_implementation="eager"))
+  vc = SiglipVisionConfig(hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=2,
+                          image_size=28, patch_size=7, num_channels=3, attn_implementation="eager")
+  cfg = Gemma3Config(text_config=tc, vision_config=vc, mm_tokens_per_image=4, image_token_index=5, boi_token_index=6,
+                     eoi_token_index=7, attn_implementation="eager")
+  torch.manual_seed(9)
+  hf = Gemma3ForConditionalGeneration(cfg).eval().float()
+  with torch.no_grad():
+    for n, p in hf.named_parameters():
+      if "norm" in n and p.dim() == 1:
+        p.normal_(0, 0.2) if "vision" not in n else p.add_(torch.randn_like(p) * 0.1)
+  ours_text = Transformer(_ours("gemma3", tc, sliding_window_size=32))
+  vcfg = vis.SigLIPConfig(num_mm_tokens_per_image_prepool=16, num_mm_tokens_per_image=4, image_height=28, image_width=28,
+                          soft_token_placeholder=5, patch_size=(7, 7), width=32, depth=2, mlp_dim=48, num_heads=2)
+  model = vis.Gemma3Multimodal(ours_text, vcfg, dtype=torch.float32).eval()
+  unused = vis.load_hf_multimodal_state(model, hf.state_dict().items())
+  assert all("head." in u or "rotary" in u or "inv_freq" in u for u in unused), unused
+  toks = torch.randint(8, 128, (2, 20))
+  toks[:, 3:7] = 5                                       # one image of 4 soft tokens per row
+  pixels = torch.randn(2, 3, 28, 28)
+  L = toks.shape[1]
+  causal = torch.ones(L, L, dtype=torch.bool).tril()[None].expand(2, L, L)
+  with torch.no_grad():
+    want = hf(input_ids=toks, pixel_values=pixels).logits.float()
+    got, _ = model(toks, torch.arange(L)[None].expand(2, L), None, causal,
+                   images=pixels.permute(0, 2, 3, 1)[:, None])      # [B, N=1, H, W, C]
+  err = (got.float() - want).abs().max().item()
+  assert err < 5e-4 * max(1.0, want.abs().max().item()), err

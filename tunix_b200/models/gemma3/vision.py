@@ -185,3 +185,95 @@ class Gemma3Multimodal(nn.Module):
     if attention_mask is None and cache is None:
       attention_mask = multimodal_attention_mask(input_tokens, ph, self.vision_config.num_mm_tokens_per_image)
     return self.text(input_tokens, positions, cache, attention_mask, input_embeddings=merged, **kw)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Hugging Face checkpoint import (Gemma3ForConditionalGeneration: SigLIP tower + projector + text decoder)
+_VISION_PREFIXES = ("model.vision_tower.vision_model.", "vision_tower.vision_model.")
+_PROJ_PREFIXES = ("model.multi_modal_projector.", "multi_modal_projector.")
+_TEXT_PREFIXES = ("model.language_model.", "language_model.model.")
+
+
+def _strip(key: str, prefixes) -> Optional[str]:
+  for p in prefixes:
+    if key.startswith(p):
+      return key[len(p):]
+  return None
+
+
+def convert_hf_multimodal_state(tensors) -> Tuple[dict, dict, list]:
+  """Splits a Hugging Face multimodal state dict into (vision + projector tensors under this module's
+  parameter names, text tensors under the names of a text-only Gemma 3 checkpoint, unused keys).
+
+  q/k/v projections of a SigLIP layer are fused row-wise into `attn.qkv`; the projector matrix is stored by
+  HF as [vision width, text width] and used as `x @ W`, here as a [text, vision] `linear` weight; the
+  attention-pooling head of the SigLIP checkpoint is not part of Gemma 3 and is reported as unused."""
+  import re
+  vis, text, unused, qkv = {}, {}, [], {}
+  for key, t in tensors:
+    v = _strip(key, _VISION_PREFIXES)
+    if v is not None:
+      if v.startswith("head."):
+        unused.append(key)
+      elif v == "embeddings.patch_embedding.weight":
+        vis["vision_encoder.siglip_encoder.embedding.weight"] = t
+      elif v == "embeddings.patch_embedding.bias":
+        vis["vision_encoder.siglip_encoder.embedding.bias"] = t
+      elif v == "embeddings.position_embedding.weight":
+        vis["vision_encoder.siglip_encoder.pos_embedding"] = t[None]
+      elif v.startswith("post_layernorm."):
+        vis["vision_encoder.siglip_encoder.encoder_norm." + v.split(".", 1)[1]] = t
+      else:
+        m = re.match(r"encoder\.layers\.(\d+)\.(.+)\.(weight|bias)$", v)
+        if not m:
+          unused.append(key)
+          continue
+        i, name, kind = m.group(1), m.group(2), m.group(3)
+        base = f"vision_encoder.siglip_encoder.blocks.{i}."
+        simple = {"layer_norm1": "ln1", "layer_norm2": "ln2", "mlp.fc1": "fc1", "mlp.fc2": "fc2",
+                  "self_attn.out_proj": "attn.out"}
+        if name in simple:
+          vis[base + simple[name] + "." + kind] = t
+        elif name in ("self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"):
+          qkv.setdefault((i, kind), {})[name[-6]] = t
+        else:
+          unused.append(key)
+      continue
+    pj = _strip(key, _PROJ_PREFIXES)
+    if pj is not None:
+      if pj == "mm_input_projection_weight":
+        vis["mm_input_projection"] = t.t().contiguous()
+      elif pj == "mm_soft_emb_norm.weight":
+        vis["mm_soft_embedding_norm.w"] = t
+      else:
+        unused.append(key)
+      continue
+    tx = _strip(key, _TEXT_PREFIXES)
+    if tx is not None:
+      text["model." + tx] = t
+    else:
+      text[key] = t                     # lm_head.weight and text-only checkpoints pass through
+  for (i, kind), parts in qkv.items():
+    vis[f"vision_encoder.siglip_encoder.blocks.{i}.attn.qkv.{kind}"] = torch.cat([parts["q"], parts["k"], parts["v"]], 0)
+  return vis, text, unused
+
+
+def load_hf_multimodal_state(model: "Gemma3Multimodal", tensors) -> list:
+  """Copies a Hugging Face `Gemma3ForConditionalGeneration` state dict into `model`; returns the unused keys."""
+  from .. import safetensors_loader
+  vis, text, unused = convert_hf_multimodal_state(tensors)
+  tstate, unmatched = safetensors_loader.convert_state(text.items(), gemma_norms=True)
+  own = dict(model.named_parameters())
+  with torch.no_grad():
+    for n, t in vis.items():
+      if n not in own:
+        raise KeyError(f"checkpoint tensor maps to {n!r}, which this model does not have")
+      if tuple(own[n].shape) != tuple(t.shape):
+        raise ValueError(f"{n}: checkpoint {tuple(t.shape)} vs model {tuple(own[n].shape)}")
+      own[n].copy_(t)
+    for n, p in model.text.named_parameters():
+      if n in tstate:
+        p.copy_(tstate[n])
+      elif not (n == "lm_head.w" and model.config.weight_tying):
+        raise KeyError(f"{n} missing from the checkpoint")
+  return unused + list(unmatched)
