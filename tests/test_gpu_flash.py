@@ -165,3 +165,22 @@ def test_packed_model_forward_matches_separate_sequences(kernel_lib):
         torch.testing.assert_close(logits[0, off:off + n].float(), alone[0].float(), rtol=5e-2, atol=5e-2)
         off += n
   _lib.check_status()
+
+
+def test_flash_packed_qkv_gradient_buffer_matches_separate_tensors(kernel_lib):
+  """Attention straight from the fused [B, L, N + 2K, H] projection output: same output and the same gradient as the
+  three-tensor form, with dq | dk | dv written into one buffer."""
+  from tunix_b200.ops import flash
+  torch.manual_seed(21)
+  B, L, N, K, H = 2, 320, 8, 2, 128
+  qkv = (torch.randn(B, L, N + 2 * K, H, device="cuda") * 0.5).to(torch.bfloat16)
+  a = qkv.clone().requires_grad_()
+  b = qkv.clone().requires_grad_()
+  assert flash.packed_supported(a, N, K)
+  oa = flash.flash_attention_packed(a, N, K, causal=True, scale=H ** -0.5)
+  ob = flash.flash_attention(b[:, :, :N], b[:, :, N:N + K], b[:, :, N + K:], causal=True, scale=H ** -0.5)
+  assert torch.equal(oa, ob)
+  g = torch.randn_like(oa)
+  oa.backward(g)
+  ob.backward(g)
+  assert torch.equal(a.grad, b.grad)

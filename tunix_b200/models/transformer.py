@@ -257,6 +257,15 @@ class Attention(nn.Module):
       k, v = ck, cv
 
     sp_group = getattr(self, "sp_group", None)
+    if (cache is None and sp_group is None and x.is_cuda and not cfg.attn_logits_soft_cap
+        and not (self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size)):
+      # plain causal (or packed-segment) attention straight from the fused q|k|v tensor: one gradient buffer
+      from ..ops import attention as attn_ops, flash as flash_lib
+      seg = isinstance(attn_mask, attn_ops.SegmentMask)
+      if (attn_mask is None or seg) and flash_lib.packed_supported(qkv, N, K):
+        o = flash_lib.flash_attention_packed(qkv, N, K, causal=True, scale=cfg.attn_scale,
+                                             segments=attn_mask.bounds() if seg else None)
+        return self.o_proj(o.reshape(B, T, N * H)), None
     if sp_group is not None:
       if cache is not None or attn_mask is not None:
         raise NotImplementedError("sequence parallelism covers causal training / scoring without a KV cache")

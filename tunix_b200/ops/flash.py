@@ -118,6 +118,40 @@ class _FlashFn(torch.autograd.Function):
     return dq, dk, dv, None, None, None, None
 
 
+class _FlashPackedFn(torch.autograd.Function):
+  """Attention over one packed [B, L, N + 2K, 128] tensor (the layout the fused q|k|v projection produces). The
+  backward writes dq, dk and dv straight into the slices of ONE gradient buffer, which spares autograd the three
+  zero-filled full-size tensors, three slice copies and two adds it needs for separate q/k/v gradients."""
+
+  @staticmethod
+  def forward(ctx, qkv, N, K, causal, scale, seg_lo=None, seg_hi=None):
+    segments = (seg_lo, seg_hi) if seg_lo is not None else None
+    q, k, v = qkv[:, :, :N], qkv[:, :, N:N + K], qkv[:, :, N + K:]
+    o, c = forward(q, k, v, causal=causal, scale=scale, segments=segments)
+    ctx.save_for_backward(qkv, o, c[1])
+    ctx.cfg = (N, K, causal, scale, segments)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    qkv, o, lse = ctx.saved_tensors
+    N, K, causal, scale, segments = ctx.cfg
+    dqkv = torch.empty(qkv.shape, dtype=qkv.dtype, device=qkv.device)
+    backward(do.contiguous(), qkv[:, :, :N], qkv[:, :, N:N + K], qkv[:, :, N + K:], o,
+             ("tx", lse, causal, scale, segments), dqkv[:, :, :N], dqkv[:, :, N:N + K], dqkv[:, :, N + K:])
+    return dqkv, None, None, None, None, None, None
+
+
+def packed_supported(qkv: torch.Tensor, N: int, K: int) -> bool:
+  return (qkv.dim() == 4 and qkv.is_contiguous() and qkv.shape[2] == N + 2 * K and
+          supported(qkv[:, :, :N], qkv[:, :, N:N + K], qkv[:, :, N + K:], None, True))
+
+
+def flash_attention_packed(qkv, N: int, K: int, *, causal: bool, scale: float, segments=None):
+  lo, hi = segments if segments is not None else (None, None)
+  return _FlashPackedFn.apply(qkv, N, K, causal, scale, lo, hi)
+
+
 def flash_attention(q, k, v, *, causal: bool, scale: float, segment_ids=None):
   """`segment_ids` [B, L]: tokens attend only within their own (contiguous) segment."""
   if segment_ids is not None:
