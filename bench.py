@@ -248,6 +248,14 @@ def main():
   ms = e0.elapsed_time(e1)
   launches = _lib.launch_calls - launches0
   clocks = sampler.stop(local_rank) if rank == 0 else None
+  need = None
+  if moe and world > 1:
+    from tunix_b200.dist import moe as dist_moe
+    need = dist_moe.peak_capacity_need()
+    if need is not None and need > args.moe_capacity_factor:
+      raise SystemExit(f"rank {rank}: expert-parallel receive buffer too small: this routing needs a capacity factor of "
+                       f"{need:.2f} (--moe-capacity-factor {args.moe_capacity_factor}); rows beyond it were dropped, "
+                       "so the run is invalid")
   _lib.check_status()
   t = torch.tensor([ms], device=dev)
   if world > 1:
@@ -300,7 +308,8 @@ def main():
                    "optimizer": "AdamW fp32 master/m/v, global-norm clip 1.0"},
         **({"moe": {"full_model_layers": full_layers, "layers_run": cfg.num_layers,
                     "reduced": cfg.num_layers != full_layers, "experts": cfg.num_experts,
-                    "top_k": cfg.num_experts_per_tok, "capacity_factor": args.moe_capacity_factor}} if moe else {}),
+                    "top_k": cfg.num_experts_per_tok, "capacity_factor": args.moe_capacity_factor,
+                    "capacity_needed_rank0": need}} if moe else {}),
         "model_tflops_per_gpu": fl / (ms_total / args.steps / 1e3) / 1e12 / world,
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "train_losses": [float(x) for x in trainer.metrics_logger.get_metric_history("", "loss", "train")[:args.warmup + args.steps]],

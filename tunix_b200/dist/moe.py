@@ -217,6 +217,13 @@ class PeerWorkspace:
 _WORKSPACES = {}
 
 
+def peak_capacity_need() -> Optional[float]:
+  """Largest (padded rows received) / (rows routed) any layer of this rank has seen: the capacity factor that would
+  have sufficed. One device-to-host read; meant for the end of a run."""
+  vals = [float(ws.peak_need) for ws in _WORKSPACES.values() if getattr(ws, "peak_need", None) is not None]
+  return max(vals) if vals else None
+
+
 def peer_workspace(group, device: torch.device, n_rows: int, D: int, ep: int, per: int,
                    capacity_factor: Optional[float]) -> PeerWorkspace:
   """The workspace of (group, D), grown when a larger step arrives. Collective when it (re)allocates, so
@@ -304,6 +311,8 @@ def ep_forward_peer(layer, x2: torch.Tensor, topv: torch.Tensor, topi: torch.Ten
   dist.all_gather_into_tensor(table, counts, group=group)
   ws = peer_workspace(group, x2.device, T * k, D, ep, per, getattr(layer, "ep_capacity_factor", None))
   plan = peer_plan(flat_e, table, layer.ep_rank, ws.capacity)
+  need = plan.layout.offsets[-1:].float() / float(T * k)       # padded rows this rank receives / rows it routes
+  ws.peak_need = need if getattr(ws, "peak_need", None) is None else torch.maximum(ws.peak_need, need)
   x_rows = _PeerDispatch.apply(x2.contiguous(), plan, ws, k)
   y_rows = moe_ops.grouped_mlp_padded(x_rows, plan.layout, layer.gate_up_proj, layer.down_proj, cfg.activation)
   return _PeerCombine.apply(y_rows, topv, plan, ws)
