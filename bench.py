@@ -34,7 +34,7 @@ def parse_args():
   ap.add_argument("--model", default=None, help="default: llama3p1_8b (sft), qwen3_30b_a3b (moe)")
   ap.add_argument("--seq-len", type=int, default=4096)
   ap.add_argument("--global-batch", type=int, default=0, help="default: 64 (sft), 32 (moe)")
-  ap.add_argument("--moe-capacity-factor", type=float, default=1.5,
+  ap.add_argument("--moe-capacity-factor", type=float, default=2.5,
                   help="expert-parallel receive buffer, in multiples of a rank's own routed rows (overflow is an error)")
   ap.add_argument("--micro-batch", type=int, default=0, help="sequences per micro-step per GPU (0 = auto)")
   ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
