@@ -114,6 +114,38 @@ def cases(dev, small=False):
     lg = torch.randn(B, Vq, device=dev, dtype=bf)
     return (lambda: paged.sample(lg, 1.0, False, seed=1, step=2), B * Vq * 2, f"B={B} V={Vq} bf16")
   out["sample"] = sample
+
+  def allgather_gemm():
+    # the all-gather-into-GEMM kernel with 4 "ranks" whose shards all live on this GPU (one launch)
+    from . import kernels
+    M, N, K, world = (2048 if small else 8192), 8192, 4096, 4
+    x = torch.randn(M, K, device=dev, dtype=bf)
+    shards = [torch.randn(N // world, K, device=dev, dtype=bf) * 0.02 for _ in range(world)]
+    stage = torch.empty(N, K, device=dev, dtype=bf)
+    cnt = torch.empty(N // 128, device=dev, dtype=torch.int32)
+    c = torch.empty(M, N, device=dev, dtype=bf)
+    ptrs = [t.data_ptr() for t in shards]
+    return (lambda: kernels.gemm_allgather_b(x, ptrs, 1, N // world, stage, cnt, out=c),
+            (M * K + N * K + M * N) * 2 + (world - 1) * (N // world) * K * 2 * 2,
+            f"M={M} N={N} K={K} world={world} (2*M*N*K = {2 * M * N * K / 1e12:.2f} TFLOP)")
+  out["allgather_gemm"] = allgather_gemm
+
+  def moe_rows():
+    # single-rank dispatch -> combine of routed rows (the kernels the expert-parallel path runs over peer memory)
+    from . import moe as moe_ops
+    T, k, D, E = (2048 if small else 8192), 8, 2048, 128
+    x = torch.randn(T, D, device=dev, dtype=bf)
+    ids = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).reshape(-1)
+    lay = moe_ops.padded_layout(ids, E)
+    dest = lay.dest.int()
+    zero = torch.zeros_like(dest)
+    w = torch.rand(T * k, device=dev)
+
+    def run():
+      buf = moe_ops._dispatch_rows(x, k, None, dest, zero, lay.rows)
+      moe_ops._combine_rows(buf, w, k, T, dest, zero, keep_rows=False)
+    return (run, (lay.rows * D + T * D + 2 * T * k * D + T * D) * 2, f"T={T} k={k} D={D} E={E} rows={lay.rows}")
+  out["moe_dispatch_combine"] = moe_rows
   return out
 
 
