@@ -314,6 +314,8 @@ def main():
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         "train_losses": [float(x) for x in trainer.metrics_logger.get_metric_history("", "loss", "train")[:args.warmup + args.steps]],
         "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30,
+        # the caching allocator does not see symmetric (peer-mapped) buffers: flat parameters, gradients, exchange buffers
+        "device_mem_in_use_gb": (lambda fr_to: (fr_to[1] - fr_to[0]) / 2**30)(torch.cuda.mem_get_info()),
     }
     print(json.dumps(out))
   if world > 1:
