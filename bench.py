@@ -293,6 +293,9 @@ def main():
   if rank == 0:
     fl = flops_lib.train_flops_per_token(cfg, S) * tokens_per_step
     metric = "SFT tokens/s (Llama-3.1-8B full-weight, bf16 + fp32 master AdamW, seq 4096, global batch 64)"
+    if (args.model, S, GB, cfg.num_layers) != ("llama3p1_8b", 4096, 64, 32) and not moe:
+      metric = (f"SFT tokens/s ({args.model}, {cfg.num_layers} layers, full-weight, bf16 + fp32 master AdamW, seq {S}, "
+                f"global batch {GB}) - not the headline configuration")
     if moe:
       metric = (f"SFT tokens/s (Qwen3-30B-A3B MoE full-weight, expert parallel over {world} GPU(s), bf16 + fp32 master "
                 f"AdamW, seq {S}, global batch {GB})")
