@@ -125,11 +125,11 @@ def main():
     reference_arm(args)
     return
   if args.workload == "dpo":
-    from tunix_b200.sft.dpo import dpo_bench
+    from benchmarks import dpo_bench
     dpo_bench.run(args, ClockSampler)
     return
   if args.workload == "grpo":
-    from tunix_b200.rl import grpo_bench
+    from benchmarks import grpo_bench
     grpo_bench.run(args, ClockSampler)
     return
 

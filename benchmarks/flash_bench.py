@@ -1,6 +1,6 @@
 """Times the tcgen05 flash attention forward against the library flash kernel.
 
-  python -m tunix_b200.ops.flash_bench --batch 2 --seq 4096 --heads 32 --kv-heads 8 [--iters 20] [--no-lib]
+  python -m benchmarks.flash_bench --batch 2 --seq 4096 --heads 32 --kv-heads 8 [--iters 20] [--no-lib]
 
 Prints one JSON line per implementation: ms per call and TFLOP/s (causal FLOPs = 2 * B*N*L*L*H).
 """
@@ -12,7 +12,7 @@ import math
 
 import torch
 
-from . import _lib, flash
+from tunix_b200.ops import _lib, flash
 
 
 def _time(fn, iters, warmup):

@@ -1,7 +1,7 @@
 """GEMM micro-benchmark: the tcgen05 kernels of this package against torch.matmul (cuBLAS).
 
-    python -m tunix_b200.ops.gemm_bench                       # Llama-8B training shapes
-    python -m tunix_b200.ops.gemm_bench --shape 8192 6144 4096 --iters 3 --no-cublas
+    python -m benchmarks.gemm_bench                       # Llama-8B training shapes
+    python -m benchmarks.gemm_bench --shape 8192 6144 4096 --iters 3 --no-cublas
 
 Every timed call is preceded by a write larger than L2, timed with CUDA events; the median is
 reported in TFLOP/s. Layouts: tn = forward (x W^T), nn = dgrad, nt = wgrad.
@@ -13,7 +13,7 @@ import json
 
 import torch
 
-from . import _lib, kernels
+from tunix_b200.ops import _lib, kernels
 
 DEFAULT_SHAPES = [(8192, 6144, 4096), (8192, 4096, 4096), (8192, 28672, 4096), (8192, 4096, 14336),
                   (4096, 6144, 4096), (4096, 28672, 4096), (4096, 4096, 14336), (2048, 128256, 4096)]

@@ -1,6 +1,6 @@
 """Times the memory-bound kernels one at a time and prints achieved bandwidth.
 
-  python -m tunix_b200.ops.kernel_bench [--only rmsnorm_fwd,paged_decode] [--iters 10]
+  python -m benchmarks.kernel_bench [--only rmsnorm_fwd,paged_decode] [--iters 10]
 
 Every case works on more bytes than the L2 holds, is warmed up, and is timed
 with CUDA events around `iters` back-to-back launches. "bytes" is the
@@ -17,8 +17,8 @@ import os
 
 import torch
 
-from . import kernels as K
-from . import paged
+from tunix_b200.ops import kernels as K
+from tunix_b200.ops import paged
 
 
 def _time(fn, iters, warmup=3):
@@ -117,7 +117,7 @@ def cases(dev, small=False):
 
   def allgather_gemm():
     # the all-gather-into-GEMM kernel with 4 "ranks" whose shards all live on this GPU (one launch)
-    from . import kernels
+    from tunix_b200.ops import kernels
     M, N, K, world = (2048 if small else 8192), 8192, 4096, 4
     x = torch.randn(M, K, device=dev, dtype=bf)
     shards = [torch.randn(N // world, K, device=dev, dtype=bf) * 0.02 for _ in range(world)]
@@ -132,7 +132,7 @@ def cases(dev, small=False):
 
   def moe_rows():
     # single-rank dispatch -> combine of routed rows (the kernels the expert-parallel path runs over peer memory)
-    from . import moe as moe_ops
+    from tunix_b200.ops import moe as moe_ops
     T, k, D, E = (2048 if small else 8192), 8, 2048, 128
     x = torch.randn(T, D, device=dev, dtype=bf)
     ids = torch.stack([torch.randperm(E, device=dev)[:k] for _ in range(T)]).reshape(-1)

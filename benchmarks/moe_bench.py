@@ -1,7 +1,7 @@
 """Times the grouped expert GEMM (`csrc/gemm_grouped.cu`) on mixture-of-experts shapes.
 
-    python -m tunix_b200.ops.moe_bench                       # Qwen3-30B-A3B: E 128, top-8, D 2048, F 768
-    python -m tunix_b200.ops.moe_bench --tokens 2048 --iters 3 --warmup 1     # small case for a profiler
+    python -m benchmarks.moe_bench                       # Qwen3-30B-A3B: E 128, top-8, D 2048, F 768
+    python -m benchmarks.moe_bench --tokens 2048 --iters 3 --warmup 1     # small case for a profiler
 
 Prints one JSON line per product (forward, dgrad, wgrad of gate|up and of down) with CUDA-event times,
 useful TFLOP/s (padding rows not counted) and, for comparison, the per-expert loop of dense GEMMs.
@@ -13,8 +13,8 @@ import json
 
 import torch
 
-from . import kernels
-from . import moe as moe_ops
+from tunix_b200.ops import kernels
+from tunix_b200.ops import moe as moe_ops
 
 
 def _time(fn, iters, warmup, flush):

@@ -1,6 +1,6 @@
 """Times the peer-memory collectives of the sharded optimizer step against NCCL.
 
-  torchrun --nproc-per-node N --master-addr 127.0.0.1 -m tunix_b200.dist.p2p_bench [--params 2e9]
+  torchrun --nproc-per-node N --master-addr 127.0.0.1 -m benchmarks.p2p_bench [--params 2e9]
 
 For a flat model of `--params` parameters it times, per optimizer step and per rank: the fused
 reduce-scatter (pull the own shard of every peer's fp32 gradient and sum it, with the partial sums

@@ -1,6 +1,6 @@
 """Rollout throughput of the paged engine on random-init weights.
 
-  python -m tunix_b200.rollout.bench --model qwen3_8b --prompts 64 --samples 8 --prompt-len 256 --new-tokens 768
+  python -m benchmarks.rollout_bench --model qwen3_8b --prompts 64 --samples 8 --prompt-len 256 --new-tokens 768
 
 Prints one JSON line: generated tokens/s (device-timed with CUDA events around the whole
 `generate`, prefill included), decode steps and their mean latency.
@@ -13,9 +13,9 @@ import json
 import numpy as np
 import torch
 
-from ..models import automodel, dummy_model_creator
-from ..models.transformer import Transformer
-from . import EngineConfig, PagedEngine
+from tunix_b200.models import automodel, dummy_model_creator
+from tunix_b200.models.transformer import Transformer
+from tunix_b200.rollout import EngineConfig, PagedEngine
 
 
 def main():

@@ -9,6 +9,8 @@
 #include <math.h>
 #include <stdint.h>
 
+#include "tx_host.h"
+
 namespace {
 
 // ------------------------------------------------------------------------------------------------
@@ -331,7 +333,8 @@ extern "C" int tx_kv_page_write(const void* k_new, const void* v_new, long long 
   if (T <= 0) return 0;
   if (row_elems % 8 != 0 || ldk % 8 != 0 || ldv % 8 != 0) return 1;
   const long long total = static_cast<long long>(T) * (row_elems / 8);
-  const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
+  const long long cap = static_cast<long long>(txh::sm_count()) * 16;
+  const int blocks = static_cast<int>(total / 256 + 1 < cap ? total / 256 + 1 : cap);
   kv_page_write_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(k_new),
                                               static_cast<const __nv_bfloat16*>(v_new), ldk, ldv, slots,
                                               static_cast<__nv_bfloat16*>(k_pages),

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tx_host.h"
+
 namespace {
 
 __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
@@ -250,7 +252,7 @@ __global__ void accum_bf16_into_f32_kernel(const __nv_bfloat16* __restrict__ x, 
 
 inline int grid_for(long long work_items, int threads) {
   long long b = (work_items + threads - 1) / threads;
-  const long long cap = 148LL * 16;
+  const long long cap = static_cast<long long>(txh::sm_count()) * 16;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return static_cast<int>(b);
@@ -308,12 +310,12 @@ extern "C" int tx_adamw(float* master, float* m, float* v, float* grad, void* pa
 }
 
 // Scratch: `partials` must hold tx_sumsq_partials() floats.
-extern "C" int tx_sumsq_partials() { return 148 * 8; }
+extern "C" int tx_sumsq_partials() { return txh::sm_count() * 8; }
 
 extern "C" int tx_sumsq(const float* x, long long n, float* partials, float* out, int accumulate,
                         cudaStream_t s) {
   int g = grid_for(n / 4 + 1, 256);
-  if (g > 148 * 8) g = 148 * 8;
+  if (g > tx_sumsq_partials()) g = tx_sumsq_partials();
   sumsq_partial_kernel<<<g, 256, 0, s>>>(x, n, partials);
   fold_partials_kernel<<<1, 256, 0, s>>>(partials, g, out, accumulate);
   return TX_OK();

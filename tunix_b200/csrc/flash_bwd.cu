@@ -628,7 +628,8 @@ extern "C" int tx_flash_bwd_seg(const void* q, const void* k, const void* v, con
   if (!rc) rc = txh::make_map_2d_bf16(&k64, k, rk, ck, ldk, 64, 64);
   if (!rc) rc = txh::make_map_2d_bf16(&v64, v, rk, ck, ldv, 64, 64);
   if (rc) return 300 + rc;
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::kSmemBytes) !=
             cudaSuccess ||

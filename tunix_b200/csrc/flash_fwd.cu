@@ -361,7 +361,8 @@ extern "C" int tx_flash_fwd_seg(const void* q, const void* k, const void* v, voi
   if (rc == 0) rc = txh::make_map_2d_bf16(&mk, k, static_cast<uint64_t>(B) * Lk, static_cast<uint64_t>(Kh) * kHD, ldk, kBN, 64);
   if (rc == 0) rc = txh::make_map_2d_bf16(&mv, v, static_cast<uint64_t>(B) * Lk, static_cast<uint64_t>(Kh) * kHD, ldv, kBN, 64);
   if (rc != 0) return 300 + rc;
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   if (!attr_set) {
     if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
         cudaSuccess)

@@ -287,7 +287,8 @@ static int launch_gather(const void* A, void* const* shards, void* stage, Gather
   if (rc) return 200 + rc;
   rc = txh::make_map_2d_bf16(&mstage, stage, N, K, K, BN, BK);
   if (rc) return 200 + rc;
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   if (!attr_set) {
     if (cudaFuncSetAttribute(gemm_allgather_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              Cfg<BN>::kSmemBytes) != cudaSuccess)

@@ -282,7 +282,8 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 template <bool A_MN, bool B_MN, int MODE>
 int launch(const CUtensorMap& ma, const CUtensorMap& mbm, const CUtensorMap& mc, const GroupedParams& p,
            cudaStream_t stream) {
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   auto kern = gemm_grouped_kernel<A_MN, B_MN, MODE>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)

@@ -248,7 +248,8 @@ int launch(const void* A, const void* B, const GemmParams& p, long long lda, lon
     else      rc = txh::make_map_2d_bf16(&mb2, B2, p.N, p.K2, ldb2, BN, BK);
     if (rc) return 200 + rc;
   }
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess)

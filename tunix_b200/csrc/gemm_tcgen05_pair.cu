@@ -275,7 +275,8 @@ int launch(const void* A, const void* B, const void* A2, const void* B2, const G
     else mc = ma;
   }
   auto kern = gemm_bf16_pair_kernel<A_MN, B_MN>;
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess) return 300;
     attr_set = true;

@@ -14,6 +14,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tx_host.h"
+
 namespace {
 
 constexpr int kMaxPeers = 16;
@@ -126,7 +128,7 @@ extern "C" int tx_moe_dispatch_rows(const void* src, long long ld, const int* to
   PeerTable t;
   for (int i = 0; i < world; ++i) t.p[i] = recv_ptrs[i];
   long long blocks = (n + 7) / 8;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > txh::sm_count() * 8) blocks = txh::sm_count() * 8;
   moe_dispatch_kernel<<<static_cast<int>(blocks), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), ld, tok, k,
                                                                scale, dest_rank, dest_row, t, world, n, D, capacity,
                                                                status);
@@ -142,7 +144,8 @@ extern "C" int tx_moe_combine_rows(void* const* send_ptrs, int world, const int*
   if (T <= 0) return 0;
   PeerTable t;
   for (int i = 0; i < world; ++i) t.p[i] = send_ptrs[i];
-  const int grid = static_cast<int>(T < 148 * 16 ? T : 148 * 16);
+  const long long cap = static_cast<long long>(txh::sm_count()) * 16;
+  const int grid = static_cast<int>(T < cap ? T : cap);
   auto* o = static_cast<__nv_bfloat16*>(out);
   auto* g = static_cast<__nv_bfloat16*>(gathered);
   if (k <= 2)

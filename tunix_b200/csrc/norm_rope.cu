@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tx_host.h"
+
 namespace {
 
 constexpr int kNormThreads = 256;
@@ -190,6 +192,14 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, float*
   dw[j] = accumulate ? dw[j] + s : s;
 }
 
+// A position outside the rotary table is an argument error: it is clamped (no out-of-range read) and
+// reported through status bit 8.
+__device__ __forceinline__ int checked_position(int pos, int table_rows, int* status, int lane) {
+  if (pos >= 0 && pos < table_rows) return pos;
+  if (lane == 0 && status != nullptr) atomicOr(status, 8);
+  return pos < 0 ? 0 : table_rows - 1;
+}
+
 // One warp per (token, head). Heads [0, n_norm_q) use wq, heads [n_norm_q, n_rot) use wk for
 // the optional per-head RMSNorm (wq == nullptr disables it); heads >= n_rot are copied.
 // Rotation is the half-split form: (x1, x2) -> (x1 cos - x2 sin, x2 cos + x1 sin).
@@ -200,7 +210,9 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __re
                        const int* __restrict__ positions, const float* __restrict__ cos_sin,
                        const __nv_bfloat16* __restrict__ wq, const __nv_bfloat16* __restrict__ wk,
                        float* __restrict__ rstd_out, long long T, int n_heads_total, int n_norm_q, int n_rot,
-                       long long in_stride, long long out_stride, float eps, float w_offset, int inverse) {
+                       long long in_stride, long long out_stride, float eps, float w_offset, int inverse,
+                       int table_rows, int* __restrict__ status, const long long* __restrict__ slots,
+                       __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages) {
   constexpr int PER = H / 32;  // elements per lane (2, 4 or 8)
   const int lane = threadIdx.x & 31;
   const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
@@ -228,7 +240,7 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __re
 #pragma unroll
       for (int e = 0; e < PER; ++e) v[e] = __bfloat162float(__float2bfloat16_rn(v[e]));
     }
-    const int pos = positions[t];
+    const int pos = checked_position(positions[t], table_rows, status, lane);
     const float* cs = cos_sin + static_cast<long long>(pos) * H;  // [cos(H/2) | sin(H/2)]
 #pragma unroll
     for (int e = 0; e < PER; ++e) {
@@ -242,6 +254,18 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __re
   }
 #pragma unroll
   for (int e = 0; e < PER; ++e) dst[e] = __float2bfloat16_rn(v[e]);
+  if (slots != nullptr && h >= n_norm_q) {
+    // decode / prefill into a paged cache: the rotated key and the value also go to their page row
+    const long long slot = slots[t];
+    if (slot >= 0) {
+      const int n_k = n_rot - n_norm_q;
+      const bool is_k = h < n_rot;
+      __nv_bfloat16* page = (is_k ? k_pages : v_pages) + slot * (static_cast<long long>(n_k) * H) +
+                            static_cast<long long>(is_k ? h - n_norm_q : h - n_rot) * H + lane * PER;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) page[e] = __float2bfloat16_rn(v[e]);
+    }
+  }
 }
 
 // Backward of qknorm_rope_fwd for the normalised heads: un-rotate dy, then RMSNorm backward
@@ -253,7 +277,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        const float* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ wq,
                        const __nv_bfloat16* __restrict__ wk, float* __restrict__ dwq, float* __restrict__ dwk,
                        long long T, int n_heads_total, int n_norm_q, int n_rot, long long x_stride,
-                       long long dy_stride, long long dx_stride, float eps, float w_offset) {
+                       long long dy_stride, long long dx_stride, float eps, float w_offset, int table_rows,
+                       int* __restrict__ status) {
   constexpr int PER = H / 32;
   __shared__ float sdw[2][H];
   for (int i = threadIdx.x; i < 2 * H; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
@@ -269,7 +294,7 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 #pragma unroll
     for (int e = 0; e < PER; ++e) g[e] = __bfloat162float(dy[t * dy_stride + ho + e]);
     if (h < n_rot) {
-      const int pos = positions[t];
+      const int pos = checked_position(positions[t], table_rows, status, lane);
       const float* cs = cos_sin + static_cast<long long>(pos) * H;
 #pragma unroll
       for (int e = 0; e < PER; ++e) {
@@ -322,7 +347,8 @@ extern "C" int tx_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               float* rstd, int T, int D, float eps, float w_offset, cudaStream_t stream) {
   if (D % 8 != 0 || D > kNormThreads * 8 * kMaxVec) return 1;
   if (T <= 0) return 0;
-  const int grid = T < 148 * 8 ? T : 148 * 8;
+  const int cap = txh::sm_count() * 8;
+  const int grid = T < cap ? T : cap;
   rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(res),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(sum_out),
@@ -332,7 +358,11 @@ extern "C" int tx_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
 
 // Number of partial rows the backward kernel writes; the caller allocates
 // dw_partial as [tx_rmsnorm_bwd_partials(T), D] fp32.
-extern "C" int tx_rmsnorm_bwd_partials(int T) { return T < 148 * 2 ? (T > 0 ? T : 1) : 148 * 2; }
+extern "C" int tx_rmsnorm_bwd_partials(int T) {
+  int cap = txh::sm_count() * 2;
+  if (cap > 296) cap = 296;      // the library-owned scratch of tx_rmsnorm_bwd_static holds 296 rows
+  return T < cap ? (T > 0 ? T : 1) : cap;
+}
 
 extern "C" int tx_rmsnorm_bwd(const void* x, const void* w, const void* dy, const float* rstd, const void* dres,
                               void* dx, float* dw_partial, float* dw, int dw_accumulate, int T, int D, float eps,
@@ -359,14 +389,19 @@ extern "C" int tx_rmsnorm_bwd(const void* x, const void* w, const void* dy, cons
 extern "C" int tx_qknorm_rope_fwd(const void* in, void* out, const int* positions, const float* cos_sin,
                                   const void* wq, const void* wk, float* rstd, long long T, int n_heads_total,
                                   int n_norm_q, int n_rot, int H, long long in_stride, long long out_stride,
-                                  float eps, float w_offset, int inverse, cudaStream_t stream) {
+                                  float eps, float w_offset, int inverse, int table_rows, int* status,
+                                  const long long* slots, void* k_pages, void* v_pages, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (table_rows <= 0) return 1;
+  if (slots != nullptr && (!k_pages || !v_pages || n_heads_total - n_rot != n_rot - n_norm_q)) return 1;
   const long long warps = T * n_heads_total;
   const int blocks = static_cast<int>((warps + 7) / 8);
   TX_DISPATCH_H(H, (qknorm_rope_fwd_kernel<kH><<<blocks, 256, 0, stream>>>(
                        static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), positions,
                        cos_sin, static_cast<const __nv_bfloat16*>(wq), static_cast<const __nv_bfloat16*>(wk),
-                       rstd, T, n_heads_total, n_norm_q, n_rot, in_stride, out_stride, eps, w_offset, inverse)));
+                       rstd, T, n_heads_total, n_norm_q, n_rot, in_stride, out_stride, eps, w_offset, inverse,
+                       table_rows, status, slots, static_cast<__nv_bfloat16*>(k_pages),
+                       static_cast<__nv_bfloat16*>(v_pages))));
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 
@@ -374,15 +409,16 @@ extern "C" int tx_qknorm_rope_bwd(const void* x, const void* dy, void* dx, const
                                   const float* cos_sin, const void* wq, const void* wk, float* dwq, float* dwk,
                                   long long T, int n_heads_total, int n_norm_q, int n_rot, int H,
                                   long long x_stride, long long dy_stride, long long dx_stride, float eps,
-                                  float w_offset, cudaStream_t stream) {
+                                  float w_offset, int table_rows, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (table_rows <= 0) return 1;
   const long long warps = T * n_heads_total;
   const int blocks = static_cast<int>((warps + 7) / 8);
   TX_DISPATCH_H(H, (qknorm_rope_bwd_kernel<kH><<<blocks, 256, 0, stream>>>(
                        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(dy),
                        static_cast<__nv_bfloat16*>(dx), positions, cos_sin, static_cast<const __nv_bfloat16*>(wq),
                        static_cast<const __nv_bfloat16*>(wk), dwq, dwk, T, n_heads_total, n_norm_q, n_rot,
-                       x_stride, dy_stride, dx_stride, eps, w_offset)));
+                       x_stride, dy_stride, dx_stride, eps, w_offset, table_rows, status)));
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 

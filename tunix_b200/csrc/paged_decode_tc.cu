@@ -388,7 +388,8 @@ extern "C" int tx_paged_decode_attn_tc(const void* q, long long ldq, const void*
   int rc = txh::make_map_2d_bf16(&mk, k_pages, rows, cols, cols, page_size, 64);
   if (rc == 0) rc = txh::make_map_2d_bf16(&mv, v_pages, rows, cols, cols, page_size, 64);
   if (rc != 0) return 300 + rc;
-  static bool attr_set = false;
+  static txh::DeviceFlag attr_flag;
+  bool& attr_set = attr_flag.cur();
   if (!attr_set) {
     if (cudaFuncSetAttribute(paged_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
         cudaSuccess)

@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tx_host.h"
+
 namespace {
 
 constexpr int kMaxPeers = 16;
@@ -153,7 +155,7 @@ peer_copy_2d_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long
 
 inline int grid_for(long long items, int threads, int cap_per_sm) {
   long long b = (items + threads - 1) / threads;
-  const long long cap = 148LL * cap_per_sm;
+  const long long cap = static_cast<long long>(txh::sm_count()) * cap_per_sm;
   if (b > cap) b = cap;
   if (b < 1) b = 1;
   return static_cast<int>(b);
@@ -172,7 +174,7 @@ extern "C" int tx_peer_barrier(void* const* flag_rows, int rank, int world, int 
 }
 
 // Number of CTAs (and of floats in `sumsq_partials`) the reduce-scatter kernel uses.
-extern "C" int tx_reduce_scatter_grid() { return 148 * 4; }
+extern "C" int tx_reduce_scatter_grid() { return txh::sm_count() * 4; }
 
 extern "C" int tx_reduce_scatter_sum_f32(void* const* grad_ptrs, float* out_shard, long long shard_off, long long n,
                                          int world, int rank, float* sumsq_partials, cudaStream_t s) {

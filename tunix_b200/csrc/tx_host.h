@@ -92,15 +92,31 @@ inline int make_map_3d_bf16(CUtensorMap* map, const void* base, uint64_t d0, uin
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
-inline int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
+constexpr int kMaxDevices = 64;
+
+inline int current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
 }
+
+// SM count of the current device (cached per device).
+inline int sm_count() {
+  static int n[kMaxDevices] = {};
+  const int dev = current_device();
+  if (!n[dev]) {
+    int v = 0;
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    n[dev] = v > 0 ? v : 148;
+  }
+  return n[dev];
+}
+
+// One boolean per device: function attributes (dynamic shared memory limits) are per device, so a
+// "done once" flag has to be too when a process drives several GPUs.
+struct DeviceFlag {
+  bool done[kMaxDevices] = {};
+  bool& cur() { return done[current_device()]; }
+};
 
 }  // namespace txh

@@ -125,6 +125,69 @@ class FusedRowExit(torch.nn.Module):
     return out.view(*x.shape[:-1], N)
 
 
+class SkinnyExitContext:
+  """Peer-mapped scratch shared by all in-kernel tensor-parallel exits of one model replica.
+
+  `part`: this rank's partial sums, two parities of [max_rows, max_out] fp32 (a call writes parity
+  `epoch & 1`; the peers read it while the next call already fills the other one). `flags`: one int per
+  (rank, 128-column block) that the owner of a block of partial sums sets to the call number. `epoch` and
+  `done` are private device counters that the kernel itself advances, so the calls replay inside CUDA graphs.
+  The exits of a model run one after another on one stream and therefore share one context."""
+
+  def __init__(self, group, device: torch.device, max_rows: int, max_out: int, symm=None):
+    from ..ops import _lib
+    from . import symm as symm_lib
+    lib = _lib.require()
+    self.symm = symm or symm_lib.SymmetricBuffers(group, device)
+    self.n_ranks, self.rank = self.symm.world, self.symm.rank
+    self.max_rows, self.max_out = int(max_rows), int(max_out)
+    self.part_stride = self.max_rows * self.max_out
+    self.flag_blocks = lib.tx_gemm_skinny_flag_blocks()
+    if (self.max_out + 127) // 128 > self.flag_blocks:
+      raise ValueError(f"tensor-parallel exit wider than {128 * self.flag_blocks} columns")
+    part = self.symm.alloc("tp_skinny_part", 2 * self.part_stride, torch.float32)
+    flags = self.symm.alloc("tp_skinny_flags", self.n_ranks * self.flag_blocks, torch.int32)
+    part.zero_()
+    flags.zero_()
+    self.symm.rendezvous()
+    self.part_ptrs = symm_lib._ptr_array(self.symm.peer_ptrs["tp_skinny_part"])
+    self.flag_ptrs = symm_lib._ptr_array(self.symm.peer_ptrs["tp_skinny_flags"])
+    self.epoch = torch.zeros(1, dtype=torch.int32, device=device)
+    self.done = torch.zeros(1, dtype=torch.int32, device=device)
+    self.wait_ms = self.symm.wait_limit_ms
+
+  def fits(self, rows: int, out_dim: int) -> bool:
+    return rows <= min(self.max_rows, 128) and out_dim <= self.max_out and rows * out_dim <= self.part_stride
+
+
+class SkinnyRowExit(torch.nn.Module):
+  """Row-parallel projection of a tensor-parallel group. Decode-shaped inputs (at most 128 rows, no
+  gradient) run `tx_gemm_skinny` with its in-kernel all-reduce over peer memory (`SkinnyExitContext`);
+  anything else is GEMM + library all-reduce, like `_RowExit`."""
+
+  skinny_exit = True
+
+  def __init__(self, inner: torch.nn.Module, group, ctx: SkinnyExitContext):
+    super().__init__()
+    self.inner, self.group, self.tp_exit = inner, group, ctx
+
+  def __getattr__(self, name):
+    try:
+      return super().__getattr__(name)
+    except AttributeError:
+      return getattr(super().__getattr__("inner"), name)
+
+  def forward(self, x):
+    lin = self.inner
+    x2 = x.reshape(-1, x.shape[-1])
+    from ..ops import kernels
+    if (not torch.is_grad_enabled() and self.tp_exit.fits(x2.shape[0], lin.out_dim) and lin.b is None
+        and lin.quant is None and not lin._lora_active() and kernels.gemm_skinny_supported(x2, lin.w)):
+      y = kernels.gemm_skinny(x2 if x2.is_contiguous() else x2.contiguous(), lin.w, tp=self.tp_exit)
+      return y.view(*x.shape[:-1], lin.out_dim)
+    return _ReduceFromRegion.apply(lin(x), self.group)
+
+
 def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
   """Takes rank r's share of every row section (sizes in `sections`) of w."""
   parts, off = [], 0
@@ -136,12 +199,14 @@ def _slice_rows(w: torch.Tensor, sections, tp: int, r: int) -> torch.Tensor:
 
 
 def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_rows: int = 0,
-                   shard_vocab: bool = False) -> torch.nn.Module:
+                   shard_vocab: bool = False, skinny_exit: bool = False) -> torch.nn.Module:
   """Builds this rank's tensor-parallel slice from a full (replicated) model and returns it.
   `shard_vocab` also splits an untied lm_head by vocabulary rows: log-probs then go through
   `ops.vocab_parallel` (three numbers per token cross the ranks), full logits are all-gathered.
   `fused_max_rows > 0` (CUDA ranks on one NVLink domain) makes the two exits of every layer `FusedRowExit`s
-  for up to that many token rows per call (decode and chunked prefill of a rollout engine)."""
+  for up to that many token rows per call (decode and chunked prefill of a rollout engine).
+  `skinny_exit` (CUDA ranks on one NVLink domain) makes them `SkinnyRowExit`s instead: decode steps of up to 128
+  rows sum the ranks' partial products inside the skinny GEMM kernel over peer memory."""
   from ..models.transformer import Transformer
   tp, r = mesh.axis_size(axis), mesh.axis_index(axis)
   if tp == 1:
@@ -175,6 +240,15 @@ def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_row
       else:
         p.copy_(w)
   symm = None
+  if skinny_exit and dev.type == "cuda":
+    ctx = SkinnyExitContext(group, dev, 128, cfg.embed_dim)
+    for layer in out.layers:
+      layer.attn.qkv_proj = _ColumnEntry(layer.attn.qkv_proj, group)
+      layer.mlp.gate_up_proj = _ColumnEntry(layer.mlp.gate_up_proj, group)
+      layer.attn.o_proj = SkinnyRowExit(layer.attn.o_proj, group, ctx)
+      layer.mlp.down_proj = SkinnyRowExit(layer.mlp.down_proj, group, ctx)
+    out.tp_exit = ctx
+    return _finish_tp(out, local, cfg, group, tp, r, shard_vocab)
   if fused_max_rows > 0 and dev.type == "cuda":
     from . import symm as symm_lib
     symm = symm_lib.SymmetricBuffers(group, dev)
@@ -194,6 +268,10 @@ def shard_model_tp(model: torch.nn.Module, mesh, axis: str = "tp", fused_max_row
       layer.mlp.down_proj.buf.zero_()
     torch.cuda.synchronize(dev)
     dist.barrier(group=group)
+  return _finish_tp(out, local, cfg, group, tp, r, shard_vocab)
+
+
+def _finish_tp(out, local, cfg, group, tp: int, r: int, shard_vocab: bool):
   # the fused decoder-layer node bypasses the wrapped projections
   out.config = local.replace(fused_layers=False)
   for layer in out.layers:

@@ -411,6 +411,10 @@ class DecoderLayer(nn.Module):
       from ..ops import fused_layer
       if fused_layer.eligible(self, h, cache, attn_mask):
         return fused_layer.run(self, h, positions, attn_mask), None
+    if cache is not None and not isinstance(cache, dict) and not torch.is_grad_enabled():
+      from ..ops import decode_layer
+      if decode_layer.eligible(self, h, cache):      # paged decode step: eight launches per layer
+        return decode_layer.run(self, h, positions, cache), cache
     x = self.input_layernorm(h)
     a, new_cache = self.attn(x, positions, cache, attn_mask, layer_name)
     if self.post_attn_norm is not None:

@@ -12,6 +12,7 @@ micro-batches costs no extra pass and no bf16 rounding.
 from __future__ import annotations
 
 import math
+import threading
 from typing import Optional, Tuple
 
 import torch
@@ -69,6 +70,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if not x2.is_contiguous():
       x2 = x2.contiguous()
     M, N = x2.shape[0], w.shape[0]
+    if (M <= 128 and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad))
+        and kernels.gemm_skinny_supported(x2, w) and (bias is None or (bias.dtype == bf16 and bias.is_contiguous()))):
+      # decode-shaped product without a backward pass: one launch that streams w once
+      return kernels.gemm_skinny(x2, w, bias=bias).view(*x.shape[:-1], N)
     if kernels.gemm_supported(M, N, K, x2, w) and w.is_contiguous():
       y = _LinearFn.apply(x2, w, w)
       y = y.view(*x.shape[:-1], N)
@@ -150,16 +155,21 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, w: torch.Tensor, eps: 
 
 # ------------------------------------------------------------------------------ qk-norm + rope
 _rope_tables = {}
-_position_bound = 0
+_bound = threading.local()     # per host thread: a rollout thread's bound must not leak into a trainer thread
+
+
+def _position_bound() -> int:
+  return getattr(_bound, "n", 0)
 
 
 def set_position_bound(n: int) -> int:
-  """Declares that every position passed to `qk_norm_rope` is below `n` until further notice
-  (0 = unknown). With a bound the rotary table is sized once and the per-call device-to-host
-  read of `positions.max()` is skipped, which also makes the call capturable in a CUDA graph.
-  Returns the previous bound."""
-  global _position_bound
-  old, _position_bound = _position_bound, int(n)
+  """Declares that every position this thread passes to `qk_norm_rope` is below `n` until further
+  notice (0 = unknown). With a bound the rotary table is sized once and the per-call
+  device-to-host read of `positions.max()` is skipped, which also makes the call capturable in
+  a CUDA graph. A position that breaks the promise is clamped by the kernel and reported through
+  the status word (bit 8). Returns the previous bound."""
+  old = _position_bound()
+  _bound.n = int(n)
   return old
 
 
@@ -209,8 +219,9 @@ def qk_norm_rope(qkv: torch.Tensor, positions: torch.Tensor, n_q: int, n_k: int,
   if _use_kernels(qkv) and head_dim in (64, 128, 256):
     q2 = qkv.reshape(-1, qkv.shape[-1]).contiguous()
     pos = positions.reshape(-1).to(torch.int32)
-    table = rope_table(head_dim, theta, max_pos or _position_bound or 4096, qkv.device, rope_scale)
-    if max_pos == 0 and _position_bound == 0 and table.shape[0] < 1 << 20:
+    bound = _position_bound()
+    table = rope_table(head_dim, theta, max_pos or bound or 4096, qkv.device, rope_scale)
+    if max_pos == 0 and bound == 0 and table.shape[0] < 1 << 20:
       # positions are data; make sure the table covers them (rare: only beyond 4096 tokens)
       need = int(pos.max().item()) + 1 if pos.numel() else 1
       if need > table.shape[0]:

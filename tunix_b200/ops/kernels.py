@@ -6,6 +6,7 @@ on the current stream. Autograd glue and the CPU oracle live in `functional.py`.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -90,16 +91,26 @@ def rmsnorm_bwd(x, w, dy, rstd, eps, w_offset=0.0, dres=None, dw_out: Optional[t
 
 def qknorm_rope_fwd(x: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, n_q: int, n_k: int,
                     head_dim: int, wq: Optional[torch.Tensor] = None, wk: Optional[torch.Tensor] = None,
-                    eps: float = 1e-6, w_offset: float = 0.0, inverse: bool = False) -> torch.Tensor:
+                    eps: float = 1e-6, w_offset: float = 0.0, inverse: bool = False,
+                    slots: Optional[torch.Tensor] = None, k_pages: Optional[torch.Tensor] = None,
+                    v_pages: Optional[torch.Tensor] = None) -> torch.Tensor:
   """x: [T, n_total*H] bf16 (q heads, then k heads, then anything else, e.g. v). The first
-  n_q + n_k heads get (optional per-head RMSNorm and) rotary embedding; the rest is copied."""
+  n_q + n_k heads get (optional per-head RMSNorm and) rotary embedding; the rest is copied.
+
+  With `slots` (int64 [T], -1 = skip) the rotated keys and the values are also stored into row
+  `slots[t]` of the paged cache tensors `k_pages` / `v_pages` ([pages, page, n_k, H]) in the same
+  launch. A position outside the rotary table (`cos_sin.shape[0]` rows) is clamped and sets
+  status bit 8 instead of reading out of range."""
   T, W = x.shape
   n_total = W // head_dim
   out = torch.empty_like(x)
+  if slots is not None:
+    assert slots.dtype == torch.int64 and k_pages.is_contiguous() and v_pages.is_contiguous()
   rc = _lib.require().tx_qknorm_rope_fwd(x.data_ptr(), out.data_ptr(), positions.data_ptr(), cos_sin.data_ptr(),
                                          _p(wq), _p(wk), None, T, n_total, n_q, n_q + n_k, head_dim, x.stride(0),
                                          out.stride(0), float(eps), float(w_offset), int(inverse),
-                                         _lib.stream_ptr())
+                                         cos_sin.shape[0], _lib.status_word(x.device).data_ptr(), _p(slots),
+                                         _p(k_pages), _p(v_pages), _lib.stream_ptr())
   _lib.check_rc(rc, "tx_qknorm_rope_fwd")
   return out
 
@@ -116,7 +127,8 @@ def qknorm_rope_bwd(x, dy, positions, cos_sin, n_q, n_k, head_dim, wq=None, wk=N
   rc = _lib.require().tx_qknorm_rope_bwd(x.data_ptr(), dy.data_ptr(), dx.data_ptr(), positions.data_ptr(),
                                          cos_sin.data_ptr(), _p(wq), _p(wk), _p(dwq), _p(dwk), T, n_total, n_q,
                                          n_q + n_k, head_dim, x.stride(0), dy.stride(0), dx.stride(0), float(eps),
-                                         float(w_offset), _lib.stream_ptr())
+                                         float(w_offset), cos_sin.shape[0], _lib.status_word(x.device).data_ptr(),
+                                         _lib.stream_ptr())
   _lib.check_rc(rc, "tx_qknorm_rope_bwd")
   return dx, dwq, dwk
 
@@ -262,4 +274,66 @@ def gemm_allgather_b(a: torch.Tensor, shard_ptrs, rank: int, shard_rows: int, st
       int(ldb or K), out.stride(0), int(out.dtype == torch.float32), int(accumulate), float(alpha), int(wait_limit_ms),
       _lib.status_word(a.device).data_ptr(), _lib.stream_ptr())
   _lib.check_rc(rc, f"tx_gemm_bf16_allgather_b(M={M},N={N},K={K},world={world})")
+  return out
+
+
+# ------------------------------------------------------------------------------ skinny (decode) GEMM
+_skinny_ws = {}
+_SKINNY = os.environ.get("TUNIX_B200_SKINNY", "1") != "0"     # 0: decode products take the general GEMM (A/B runs)
+
+
+def _skinny_workspace(device: torch.device):
+  """Scratch slots and slab counters of the stream-K skinny GEMM, one set per (device, stream):
+  the kernel leaves them zeroed, and launches that share a set must be ordered on one stream."""
+  key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+  ws = _skinny_ws.get(key)
+  if ws is None:
+    lib = _lib.require()
+    slots = lib.tx_gemm_skinny_slots()
+    ws = (torch.zeros(slots * lib.tx_gemm_skinny_slot_floats(), dtype=torch.float32, device=device),
+          torch.zeros(slots, dtype=torch.int32, device=device))
+    _skinny_ws[key] = ws
+  return ws
+
+
+def gemm_skinny_supported(x2: torch.Tensor, w: torch.Tensor, glu: bool = False) -> bool:
+  """At most 128 activation rows, bf16, 16-byte aligned rows, output width a multiple of 8."""
+  if not _SKINNY or not (x2.is_cuda and x2.dtype == bf16 and w.dtype == bf16 and x2.dim() == 2 and w.dim() == 2):
+    return False
+  M, K = x2.shape
+  N = w.shape[0] // 2 if glu else w.shape[0]
+  return (0 < M <= 128 and w.shape[1] == K and K % 8 == 0 and N % 8 == 0 and x2.stride(1) == 1 and w.stride(1) == 1
+          and x2.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x2.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None, glu: Optional[str] = None,
+                residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, alpha: float = 1.0,
+                max_ctas: int = 0, tp=None) -> torch.Tensor:
+  """y[M, N] = epilogue(alpha * x[M, K] @ w[N, K]^T) for M <= 128 in one launch that streams `w` once
+  (`csrc/gemm_skinny.cu`: swapped operands, stream-K over all SMs, self-cleaning fp32 scratch).
+
+  glu: None | "silu" | "gelu" - `w` is then [gate rows | up rows] ([2N, K]) and y = act(x gate^T) * (x up^T).
+  residual: [M, N] added to the product (may be `out` itself). bias: [N].
+  tp: a `dist.tp.SkinnyExit`-like object with `n_ranks, rank, part_ptrs, flag_ptrs, part_stride, epoch, done,
+  wait_ms`: the partial products of a tensor-parallel group are summed inside the kernel over peer memory.
+  """
+  M, K = x.shape
+  N = w.shape[0] // 2 if glu else w.shape[0]
+  if out is None:
+    out = torch.empty((M, N), dtype=bf16, device=x.device)
+  assert out.shape == (M, N) and out.dtype == bf16 and out.stride(1) == 1
+  ws, counters = _skinny_workspace(x.device)
+  lib = _lib.require()
+  g = {None: 0, "silu": 1, "gelu": 2}[glu]
+  if tp is None:
+    n_ranks, rank, parts, flags, stride, epoch, done, wait_ms = 1, 0, None, None, 0, None, None, 0
+  else:
+    n_ranks, rank, parts, flags = tp.n_ranks, tp.rank, tp.part_ptrs, tp.flag_ptrs
+    stride, epoch, done, wait_ms = tp.part_stride, tp.epoch.data_ptr(), tp.done.data_ptr(), tp.wait_ms
+  rc = lib.tx_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(residual), _p(bias), M, N, K, x.stride(0),
+                          w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, float(alpha),
+                          g, int(_lib.deterministic()), ws.data_ptr(), counters.data_ptr(),
+                          _lib.status_word(x.device).data_ptr(), int(max_ctas), n_ranks, rank, parts, flags, stride,
+                          epoch, done, wait_ms, _lib.stream_ptr())
+  _lib.check_rc(rc, f"tx_gemm_skinny(M={M},N={N},K={K},glu={glu})")
   return out

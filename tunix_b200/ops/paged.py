@@ -139,30 +139,65 @@ def sample_ref(logits: torch.Tensor, temperature: float, greedy: bool, generator
   return tok, lp.gather(-1, tok[:, None]).squeeze(-1)
 
 
+def sample_filtered_ref(logits: torch.Tensor, temperature: float, top_k: Optional[int], top_p: Optional[float],
+                        generator: Optional[torch.Generator] = None,
+                        forbidden: Optional[Sequence[int]] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+  """Top-k then top-p over the sorted candidates, categorical draw among the survivors; the log-prob is
+  that of the drawn token under the full tempered softmax (tunix/generate/sampler.py:105-161)."""
+  z = logits.float() / temperature
+  if forbidden:
+    z = z.clone()
+    z[:, list(forbidden)] = float("-inf")
+  k = z.shape[-1] if not top_k or top_k <= 0 else min(int(top_k), z.shape[-1])
+  zs, idx = torch.topk(z, k, dim=-1)
+  if top_p is not None and top_p < 1.0:
+    ps = torch.softmax(zs, dim=-1)
+    zs = torch.where(torch.cumsum(ps, dim=-1) - ps > top_p, torch.full_like(zs, float("-inf")), zs)
+  pick = torch.multinomial(torch.softmax(zs, -1), 1, generator=generator)
+  tok = idx.gather(-1, pick).squeeze(-1)
+  lp = torch.log_softmax(z, -1).gather(-1, tok[:, None]).squeeze(-1)
+  return tok, lp
+
+
 def sample(logits: torch.Tensor, temperature: float = 1.0, greedy: bool = False, seed: int = 0,
            step: int = 0, step_tensor: Optional[torch.Tensor] = None, forbidden: Optional[torch.Tensor] = None,
-           want_logprobs: bool = True) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+           want_logprobs: bool = True, top_k: Optional[int] = None, top_p: Optional[float] = None,
+           n_forbidden: Optional[int] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
   """logits [B, V] (fp32 or bf16, contiguous rows) -> (tokens int64 [B], logprobs fp32 [B]).
 
   Greedy, or an exact categorical draw from softmax(logits / temperature) (Gumbel-max with a
-  counter-based generator keyed by seed and step). `step_tensor` (int64 scalar on the device)
+  counter-based generator keyed by seed and step), optionally restricted to the top-k / top-p
+  candidates first - all inside one kernel launch. `step_tensor` (int64 scalar on the device)
   is added to `step`, so a captured CUDA graph can advance the stream of draws by bumping it.
-  `forbidden` is an int32 tensor of token ids that are never chosen. The returned log-prob is
-  that of the chosen token under the (forbidden-masked) distribution at that temperature."""
+  `forbidden` is an int32 tensor of token ids that are never chosen (`n_forbidden` of them when the
+  tensor is a larger static buffer). The returned log-prob is that of the chosen token under the
+  full (forbidden-masked) distribution at that temperature."""
   B, V = logits.shape
+  filtered = not greedy and ((top_k is not None and 0 < top_k < V) or (top_p is not None and top_p < 1.0))
+  nf = 0 if forbidden is None else (forbidden.numel() if n_forbidden is None else int(n_forbidden))
   if not (logits.is_cuda and _lib.available() and logits.dtype in (torch.float32, torch.bfloat16)
           and logits.stride(1) == 1):
     g = torch.Generator(device=logits.device)
     extra = int(step_tensor.item()) if step_tensor is not None else 0
     g.manual_seed((seed * 1_000_003 + (step + extra) * 7919 + 12345) % (2 ** 63 - 1))
-    return sample_ref(logits, temperature, greedy, g, forbidden.tolist() if forbidden is not None else None)
+    fl = forbidden[:nf].tolist() if nf else None
+    if filtered:
+      return sample_filtered_ref(logits, temperature, top_k, top_p, g, fl)
+    return sample_ref(logits, temperature, greedy, g, fl)
   tokens = torch.empty(B, dtype=torch.int64, device=logits.device)
   lps = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprobs else None
+  fptr = forbidden.data_ptr() if nf else None
+  sptr = step_tensor.data_ptr() if step_tensor is not None else None
+  if filtered:
+    rc = _lib.require().tx_sample_filtered(
+        logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0), B, V, float(temperature),
+        int(top_k or 0), float(top_p if top_p is not None else 1.0), int(seed) & (2 ** 64 - 1), sptr, int(step), fptr,
+        nf, tokens.data_ptr(), lps.data_ptr() if lps is not None else None, _lib.stream_ptr())
+    _lib.check_rc(rc, "tx_sample_filtered")
+    return tokens, lps
   rc = _lib.require().tx_sample(
       logits.data_ptr(), int(logits.dtype == torch.bfloat16), logits.stride(0), B, V, float(temperature), int(greedy),
-      int(seed) & (2 ** 64 - 1), step_tensor.data_ptr() if step_tensor is not None else None, int(step),
-      forbidden.data_ptr() if forbidden is not None and forbidden.numel() else None,
-      int(forbidden.numel()) if forbidden is not None else 0, tokens.data_ptr(),
+      int(seed) & (2 ** 64 - 1), sptr, int(step), fptr, nf, tokens.data_ptr(),
       lps.data_ptr() if lps is not None else None, _lib.stream_ptr())
   _lib.check_rc(rc, "tx_sample")
   return tokens, lps

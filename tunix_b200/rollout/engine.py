@@ -62,6 +62,9 @@ def supported(cfg) -> bool:
 
 
 class PagedEngine:
+  _max_forbidden = 64       # capacity of the static buffer of never-sampled token ids
+  _max_graphs = 16          # captured decode graphs kept (least recently used is dropped)
+
   def __init__(self, model: torch.nn.Module, config: Optional[EngineConfig] = None):
     self.model = model
     self.cfg = config or EngineConfig()
@@ -78,6 +81,7 @@ class PagedEngine:
     self._graphs: Dict[int, Any] = {}
     self._static: Dict[int, Dict[str, torch.Tensor]] = {}
     self._step_counter = torch.zeros((), dtype=torch.int64, device=self.device)
+    self._forbidden = torch.zeros(self._max_forbidden, dtype=torch.int32, device=self.device)
     self._num_splits = paged.choose_splits(max(c.max_batch // 4, 1), mc.num_kv_heads, c.max_seq_len)
 
   # ---- page bookkeeping ----------------------------------------------------------------------
@@ -132,29 +136,12 @@ class PagedEngine:
     return self._sample(logits, sampling)
 
   def _sample(self, logits: torch.Tensor, sampling: Dict[str, Any]):
-    """Greedy / temperature sampling in one kernel; with top-k or top-p the candidates are cut first
-    (device-side, capturable) and the kernel draws among them. The returned log-prob is that of the token
-    under the full tempered distribution, as the trainer recomputes it."""
-    top_k, top_p = sampling.get("top_k"), sampling.get("top_p")
-    filtered = (top_k is not None and top_k > 0) or (top_p is not None and top_p < 1.0)
-    if sampling["greedy"] or not filtered:
-      return paged.sample(logits, temperature=sampling["temperature"], greedy=sampling["greedy"],
-                          seed=sampling["seed"], step=0, step_tensor=self._step_counter,
-                          forbidden=sampling["forbidden"])
-    T = sampling["temperature"]
-    z = logits.float() / T
-    if sampling["forbidden"] is not None:
-      z = z.index_fill(1, sampling["forbidden"].long(), float("-inf"))
-    k = z.shape[-1] if not top_k or top_k <= 0 else min(int(top_k), z.shape[-1])
-    zs, idx = torch.topk(z, k, dim=-1)
-    if top_p is not None and top_p < 1.0:
-      ps = torch.softmax(zs, dim=-1)
-      zs = torch.where(torch.cumsum(ps, dim=-1) - ps > top_p, torch.full_like(zs, float("-inf")), zs)
-    pick, _ = paged.sample(zs.contiguous(), temperature=1.0, greedy=False, seed=sampling["seed"], step=0,
-                           step_tensor=self._step_counter, want_logprobs=False)
-    tok = idx.gather(-1, pick[:, None]).squeeze(-1)
-    lp = z.gather(-1, tok[:, None]).squeeze(-1) - torch.logsumexp(z, dim=-1)
-    return tok, lp
+    """Greedy / temperature / top-k / top-p sampling in one kernel launch (`ops.paged.sample`). The returned
+    log-prob is that of the token under the full tempered distribution, as the trainer recomputes it."""
+    return paged.sample(logits, temperature=sampling["temperature"], greedy=sampling["greedy"],
+                        seed=sampling["seed"], step=0, step_tensor=self._step_counter,
+                        forbidden=self._forbidden, n_forbidden=sampling["n_forbidden"],
+                        top_k=sampling.get("top_k"), top_p=sampling.get("top_p"))
 
   @torch.no_grad()
   def _decode_step(self, running: List[_Seq], sampling: Dict[str, Any]) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -174,16 +161,19 @@ class PagedEngine:
       lens[i] = s.length + 1
     for name, arr in (("tokens", tok), ("positions", pos), ("slots", slots), ("block_tables", bt), ("seq_lens", lens)):
       st[name].copy_(torch.from_numpy(arr), non_blocking=True)
-    key = (bucket, sampling["greedy"], sampling["temperature"], sampling["seed"], id(sampling["forbidden"]),
+    # everything a captured launch bakes in by value; the forbidden ids live in an engine-owned static buffer
+    key = (bucket, sampling["greedy"], sampling["temperature"], sampling["seed"], sampling["n_forbidden"],
            sampling.get("top_k"), sampling.get("top_p"))
     use_graph = self.cfg.use_cuda_graphs and self.device.type == "cuda"
     if not use_graph:
       out = self._decode_body(st, sampling)
     else:
-      entry = self._graphs.get(key)
+      entry = self._graphs.pop(key, None)
       if entry is None:
         entry = self._capture(st, sampling)
-        self._graphs[key] = entry
+        while len(self._graphs) >= self._max_graphs:      # least recently used first (dicts keep insertion order)
+          self._graphs.pop(next(iter(self._graphs)))
+      self._graphs[key] = entry                            # (re)insert as most recent
       if entry is False:                       # capture failed once: stay eager for this key
         out = self._decode_body(st, sampling)
       else:
@@ -304,9 +294,14 @@ class PagedEngine:
     self.model.eval()
     from ..ops import functional as F
     old_bound = F.set_position_bound(self.cfg.max_seq_len)
+    forbidden = [int(f) for f in forbidden]
+    if len(forbidden) > self._max_forbidden:
+      raise ValueError(f"at most {self._max_forbidden} forbidden token ids are supported, got {len(forbidden)}")
+    if forbidden:     # captured graphs read this buffer: rewrite it in place, never reallocate it
+      self._forbidden[:len(forbidden)].copy_(torch.tensor(forbidden, dtype=torch.int32))
     sampling = {"temperature": float(temperature), "greedy": bool(greedy or temperature == 0.0), "seed": int(seed),
                 "eos": set(int(e) for e in eos_ids), "top_k": top_k, "top_p": top_p,
-                "forbidden": torch.tensor(list(forbidden), dtype=torch.int32, device=self.device) if forbidden else None}
+                "n_forbidden": len(forbidden)}
     self._step_counter.zero_()
     waiting: Deque[_Seq] = deque(_Seq(i, tuple(int(t) for t in p), int(max_new_tokens)) for i, p in enumerate(prompts))
     for s in waiting:
@@ -334,6 +329,9 @@ class PagedEngine:
         self.cache.allocator.free(s.pages)
       self.model.train(was_training)
       F.set_position_bound(old_bound)
+    if self.device.type == "cuda":
+      from ..ops import _lib
+      _lib.check_status(self.device)     # a kernel that gave up a bounded wait or met a bad argument: not a result
     order = [results[i] for i in range(len(prompts))]
     return GenerationResult(tokens=[np.asarray(s.out, dtype=np.int64) for s in order],
                             logprobs=[np.asarray(s.lps, dtype=np.float32) for s in order] if return_logprobs else None,
