@@ -30,7 +30,9 @@ def parse_args():
   ap.add_argument("--gpus", type=int, default=1)
   ap.add_argument("--steps", type=int, default=2)
   ap.add_argument("--warmup", type=int, default=3)
-  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch_baseline"],
+                  help="ours: this framework; reference: the unmodified reference from baseline/_ref; torch_baseline: "
+                       "the same step on stock PyTorch (fully_shard over NCCL, cuBLAS, library attention)")
   ap.add_argument("--model", default=None, help="default: llama3p1_8b (sft), qwen3_30b_a3b (moe)")
   ap.add_argument("--seq-len", type=int, default=4096)
   ap.add_argument("--global-batch", type=int, default=0, help="default: 64 (sft), 32 (moe)")
@@ -123,6 +125,10 @@ def main():
   args = parse_args()
   if args.impl == "reference":
     reference_arm(args)
+    return
+  if args.impl == "torch_baseline":
+    from baseline import torch_baseline
+    torch_baseline.run(args, ClockSampler)
     return
   if args.workload == "dpo":
     from benchmarks import dpo_bench

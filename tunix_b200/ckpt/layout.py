@@ -20,7 +20,7 @@ from typing import Any, Callable, Dict, Iterable, List, Mapping, Optional, Tuple
 
 import torch
 
-from .orbax_layout import Key
+from .orbax_layout import Key, ShardedArray
 
 
 def _generic_key(name: str) -> Key:
@@ -81,9 +81,17 @@ def model_to_tree(model: torch.nn.Module, lora_only: bool = False) -> Dict[Key, 
       Fh = cfg.moe_hidden_dim
       put(L + ("mlp", "router", "kernel"), m.router.w.detach().t())
       gu = m.gate_up_proj.detach()
-      put(L + ("mlp", "gate_proj"), gu[:, :Fh].transpose(1, 2))
-      put(L + ("mlp", "up_proj"), gu[:, Fh:].transpose(1, 2))
-      put(L + ("mlp", "down_proj"), m.down_proj.detach().transpose(1, 2))
+      experts = {"gate_proj": gu[:, :Fh].transpose(1, 2), "up_proj": gu[:, Fh:].transpose(1, 2),
+                 "down_proj": m.down_proj.detach().transpose(1, 2)}
+      ep = getattr(m, "ep_size", 1) if getattr(m, "ep_group", None) is not None else 1
+      for nm, t in experts.items():
+        if ep > 1 and not lora_only:
+          # this rank holds experts [ep_rank * E/ep, (ep_rank + 1) * E/ep): one chunk of the [E, ...] array
+          t = t.contiguous()
+          out[L + ("mlp", nm, "value")] = ShardedArray(t, (cfg.num_experts,) + tuple(t.shape[1:]), tuple(t.shape),
+                                                       (m.ep_rank,) + (0,) * (t.dim() - 1))
+        else:
+          put(L + ("mlp", nm), t)
     else:
       Fh = cfg.hidden_dim
       gu = m.gate_up_proj.w.detach()
@@ -183,6 +191,9 @@ def tree_to_model(model: torch.nn.Module, tree: Mapping[Key, torch.Tensor], lora
       if r is not None:
         assign(m.router.w, r.t())
         g, u, d = get(L + ("mlp", "gate_proj")), get(L + ("mlp", "up_proj")), get(L + ("mlp", "down_proj"))
+        if getattr(m, "ep_group", None) is not None and g.shape[0] != m.gate_up_proj.shape[0]:
+          per = m.gate_up_proj.shape[0]        # expert parallel: keep this rank's experts of the full arrays
+          g, u, d = (t[m.ep_rank * per:(m.ep_rank + 1) * per] for t in (g, u, d))
         m.gate_up_proj[:, :Fh].copy_(g.transpose(1, 2).to(m.gate_up_proj))
         m.gate_up_proj[:, Fh:].copy_(u.transpose(1, 2).to(m.gate_up_proj))
         m.down_proj.copy_(d.transpose(1, 2).to(m.down_proj))

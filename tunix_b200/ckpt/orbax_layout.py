@@ -13,6 +13,7 @@ dict keys (key_type 2), ints are sequence indices (key_type 1).
 from __future__ import annotations
 
 import base64
+import dataclasses
 import ctypes
 import ctypes.util
 import json
@@ -24,6 +25,22 @@ import numpy as np
 import torch
 
 Key = Tuple[Union[str, int], ...]
+
+
+@dataclasses.dataclass
+class ShardedArray:
+  """A leaf that is split over the ranks of a job: this process holds `local`, one chunk of a larger
+  array of shape `global_shape` cut on a regular grid of `chunk_shape` blocks, at grid position
+  `chunk_index`. On disk that is an ordinary zarr array whose chunk files come from different
+  processes - the form Orbax writes for an array sharded over hosts - so nothing is gathered to save it.
+  """
+  local: torch.Tensor
+  global_shape: Tuple[int, ...]
+  chunk_shape: Tuple[int, ...]
+  chunk_index: Tuple[int, ...]
+
+  def detach(self) -> "ShardedArray":
+    return self
 
 _ZARR_DTYPES = {
     "float32": "<f4", "float64": "<f8", "float16": "<f2", "bfloat16": "bfloat16", "int32": "<i4", "int64": "<i8",
@@ -113,9 +130,14 @@ def _write_file(path: str, data: bytes) -> None:
   os.replace(tmp, path)
 
 
-def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: int = 0,
+def write_tree(directory: str, tree: Mapping[Key, Any], process_index: int = 0,
                sharding_desc: Optional[Mapping[Key, Mapping[str, Any]]] = None) -> None:
-  """Writes `{key tuple: tensor}` under `directory` in the Orbax plain-zarr layout."""
+  """Writes `{key tuple: tensor | ShardedArray}` under `directory` in the Orbax plain-zarr layout.
+
+  Called by every process of a job with the same keys. Plain tensors are replicated state: process 0
+  writes them. A `ShardedArray` leaf is written by every process - its own chunk file - while process 0
+  adds the array's `.zarray`. Process 0 also writes `_METADATA` / `_sharding`; each process its
+  `array_metadatas/process_<r>`."""
   os.makedirs(directory, exist_ok=True)
   tree_md: Dict[str, Any] = {}
   arr_md: List[Dict[str, Any]] = []
@@ -124,35 +146,48 @@ def write_tree(directory: str, tree: Mapping[Key, torch.Tensor], process_index: 
   from ..runtime import native
   writer = native.AsyncWriter(threads=8)
   try:
-    _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md)
+    _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index)
     writer.wait()
   finally:
     writer.close()
   _write_tree_metadata(directory, process_index, tree_md, arr_md, shard_md)
 
 
-def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md) -> None:
+def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index=0) -> None:
   for key, t in tree.items():
-    if not isinstance(t, torch.Tensor):
+    sharded = isinstance(t, ShardedArray)
+    if not sharded and not isinstance(t, torch.Tensor):
       t = torch.as_tensor(t)
-    data, zdtype, shape = _tensor_to_bytes(t)
     name = param_name(key)
     pdir = os.path.join(directory, name)
-    os.makedirs(pdir, exist_ok=True)
-    zarray = {
-        "chunks": shape if shape else [], "compressor": None, "dimension_separator": ".", "dtype": zdtype,
-        "fill_value": None, "filters": None, "order": "C", "shape": shape, "zarr_format": 2,
-    }
-    _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
-    chunk_name = ".".join("0" for _ in shape) if shape else "0"
-    writer.submit(os.path.join(pdir, chunk_name), data)
+    if sharded:
+      data, zdtype, _ = _tensor_to_bytes(t.local)
+      shape, chunks = list(t.global_shape), list(t.chunk_shape)
+      if list(t.local.shape) != chunks:
+        raise ValueError(f"{name}: local chunk {list(t.local.shape)} does not match chunk_shape {chunks}")
+      chunk_name = ".".join(str(i) for i in t.chunk_index)
+      sharding_type = "NamedSharding"
+    else:
+      data, zdtype, shape = _tensor_to_bytes(t)
+      chunks = shape
+      chunk_name = ".".join("0" for _ in shape) if shape else "0"
+      sharding_type = "SingleDeviceSharding"
+    if sharded or process_index == 0:
+      os.makedirs(pdir, exist_ok=True)
+      writer.submit(os.path.join(pdir, chunk_name), data)
+    if process_index == 0:
+      zarray = {
+          "chunks": chunks if chunks else [], "compressor": None, "dimension_separator": ".", "dtype": zdtype,
+          "fill_value": None, "filters": None, "order": "C", "shape": shape, "zarr_format": 2,
+      }
+      _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
     tree_md[key_to_str(key)] = {
         "key_metadata": [{"key": str(k), "key_type": 1 if isinstance(k, int) else 2} for k in key],
-        "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, "write_shape": shape},
+        "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, "write_shape": chunks},
     }
-    arr_md.append({"array_metadata": {"param_name": name, "write_shape": shape, "chunk_shape": shape,
+    arr_md.append({"array_metadata": {"param_name": name, "write_shape": chunks, "chunk_shape": chunks,
                                       "ext_metadata": None}})
-    desc = (sharding_desc or {}).get(key) or {"sharding_type": "SingleDeviceSharding", "device_str": "cuda:0"}
+    desc = (sharding_desc or {}).get(key) or {"sharding_type": sharding_type, "device_str": "cuda:0"}
     shard_md[base64.b64encode(name.encode()).decode()] = json.dumps(desc)
 
 
@@ -243,6 +278,38 @@ def read_array(kv, name: str) -> torch.Tensor:
     block = np.frombuffer(buf, dtype=npd).reshape(chunks)
     sl = tuple(slice(i * c, min((i + 1) * c, s)) for i, c, s in zip(idx, chunks, shape))
     out[sl] = block[tuple(slice(0, s.stop - s.start) for s in sl)]
+  t = torch.from_numpy(out)
+  return t.view(torch.bfloat16) if zdtype == "bfloat16" else t
+
+
+def read_array_rows(kv, name: str, lo: int, hi: int) -> torch.Tensor:
+  """Rows [lo, hi) along the first axis of a stored array, touching only the chunk files that hold them
+  (how a rank reads its part of state that another job size wrote). Ranges past the end read as zeros."""
+  zraw = kv.get(f"{name}/.zarray")
+  if zraw is None:
+    raise KeyError(name)
+  zarray = json.loads(zraw)
+  shape, chunks = list(zarray["shape"]), list(zarray["chunks"])
+  zdtype = zarray["dtype"]
+  sep = zarray.get("dimension_separator", ".")
+  npd = np.int16 if zdtype == "bfloat16" else np.dtype(_NP_FROM_ZARR.get(zdtype, zdtype))
+  itemsize = np.dtype(npd).itemsize
+  out = np.zeros([hi - lo] + shape[1:], dtype=npd)
+  c0 = chunks[0]
+  rest_grid = [max(1, -(-s // c)) for s, c in zip(shape[1:], chunks[1:])]
+  for i0 in range(lo // c0, min(-(-hi // c0), max(1, -(-shape[0] // c0)))):
+    for idx in (np.ndindex(*rest_grid) if rest_grid else [()]):
+      raw = kv.get(f"{name}/" + sep.join(str(i) for i in (i0,) + tuple(idx)))
+      if raw is None:
+        continue
+      block = np.frombuffer(_decode_chunk(raw, zarray, int(np.prod(chunks)) * itemsize), dtype=npd).reshape(chunks)
+      a, b = max(lo, i0 * c0), min(hi, (i0 + 1) * c0, shape[0])
+      if b <= a:
+        continue
+      dst = (slice(a - lo, b - lo),) + tuple(slice(i * c, min((i + 1) * c, s))
+                                              for i, c, s in zip(idx, chunks[1:], shape[1:]))
+      src = (slice(a - i0 * c0, b - i0 * c0),) + tuple(slice(0, d.stop - d.start) for d in dst[1:])
+      out[dst] = block[src]
   t = torch.from_numpy(out)
   return t.view(torch.bfloat16) if zdtype == "bfloat16" else t
 

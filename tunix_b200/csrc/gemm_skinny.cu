@@ -8,13 +8,15 @@
 //  * swapped operands: a 128-row slab of W is the M operand of tcgen05.mma (UMMA 128 x BNX x 16,
 //    BNX = 16/32/64/128 >= Mx), the activations are the small N operand. Every byte of W that
 //    arrives feeds a full-height MMA, whatever the batch size.
-//  * stream-K: the (weight slab, k-block) space is cut into one contiguous range per CTA, one CTA
-//    per SM, so all SMs pull the same number of bytes. A slab whose k-blocks are shared by several
-//    CTAs is summed in an fp32 scratch slot with `red.global.add`; the CTA that completes the slab
-//    (a counter tells it) applies the epilogue, writes C and leaves slot and counter zeroed, so the
-//    product is ONE launch - no memset before and no conversion pass after.
-//  * deep TMA ring (4-12 stages of 16-32 KB of W), single-thread MMA issue, TMEM double-buffered
-//    accumulators, four epilogue warps.
+//  * split-K inside a thread-block cluster: decode weights have 32-200 slabs, fewer than the 148
+//    SMs, so the K range of a slab is cut over the S CTAs of a cluster (S = 1..8 chosen per shape
+//    so that slabs x S fills the machine). The partial accumulators never touch global memory:
+//    each CTA owns 128/S of the slab's output columns, the others add their share of those
+//    columns into the owner's shared memory with `red.shared::cluster` (distributed shared
+//    memory), an mbarrier in the owner's shared memory counts the arrivals, and the owner adds
+//    its own accumulator and runs the epilogue. One launch, no workspace, no memset, no fix-up pass.
+//  * deep TMA ring (3-12 stages of 16-32 KB of W), single-thread MMA issue, TMEM double-buffered
+//    accumulators, four epilogue warps; clusters walk slabs persistently.
 //
 // Epilogues: bias, residual add (C = R + X W^T, C may alias R), and gated activations - with
 // `glu` the weight is [gate rows | up rows] (2 x Nw rows), both slabs of a k-block are loaded and
@@ -22,12 +24,15 @@
 //
 // Tensor-parallel exit (n_ranks > 1): every rank holds a K-shard of W, computes its partial
 // product with the schedule above, stores each finished 128-column block of partial sums (fp32)
-// into its own peer-mapped buffer and raises a per-block flag in every peer's flag table; the CTA
-// that finished a block then waits (bounded) for the same block of every peer, adds the partials
-// in rank order with plain peer loads over NVLink, and writes the reduced bf16 result - the
+// into its own peer-mapped buffer and raises a per-block flag in every peer's flag table; the CTAs
+// that finished a block then wait (bounded) for the same block of every peer, add the partials
+// in rank order with plain peer loads over NVLink, and write the reduced bf16 result - the
 // all-reduce overlaps the remaining slabs block by block, inside the GEMM kernel. No multicast
 // object is involved. The call counter (`epoch`) lives in device memory and is advanced by the
 // kernel itself, so a CUDA graph can replay the launch.
+//
+// With S = 1 (deterministic mode) a slab is reduced over K in one accumulator in k-block order, so
+// repeated launches give identical bits. All TMA loads are plain (no cluster multicast).
 #include "tx_host.h"
 #include "tx_ptx.cuh"
 
@@ -41,7 +46,9 @@ constexpr int UMMA_K = 16;
 constexpr int NUM_THREADS = 192;
 constexpr int kMaxRanks = 8;
 constexpr int kMaxFlagBlocks = 256;      // Nw <= 32768 on a tensor-parallel exit
-constexpr int kSlotFloats = 2 * 128 * 128;   // scratch slot: [gate|up][BNX <= 128 rows][128 columns]
+constexpr int kMaxStages = 12;
+constexpr int kMaxMyBlocks = 32;
+constexpr int kSmemLimit = 227 * 1024;
 
 struct SkinnyParams {
   __nv_bfloat16* C;
@@ -52,13 +59,13 @@ struct SkinnyParams {
   int Mx, Nw, K;
   float alpha;
   int glu;                         // 0: none, 1: SiLU(gate) * up, 2: tanh-GELU(gate) * up
-  int whole_slabs;                 // 1: no slab is shared between CTAs (bitwise reproducible)
-  float* ws;                       // gridDim.x slots of kSlotFloats floats, zero between launches
-  int* counters;                   // gridDim.x ints, zero between launches
+  int split;                       // S: CTAs per cluster = K ranges per slab
+  int n_clusters;
+  int stages;                      // TMA ring depth (fits beside the reduction buffers)
   int* status;
   // tensor-parallel exit
   int n_ranks, rank;
-  float* part[kMaxRanks];          // rank r's partial buffer: [2 parities][part_rows * part_ld] fp32
+  float* part[kMaxRanks];          // rank r's partial buffer: [2 parities][part_stride] fp32
   int* flags[kMaxRanks];           // rank r's flag table: [n_ranks][kMaxFlagBlocks]
   long long part_stride;           // floats per parity
   int* epoch;                      // device call counter (same value on every rank)
@@ -73,59 +80,17 @@ struct SCfg {
   static constexpr int kABytes = kWBytes * kAcc;
   static constexpr int kXBytes = BNX * BK * 2;
   static constexpr int kStageBytes = kABytes + kXBytes;
-  static constexpr int kFit = (227 * 1024 - 4096) / kStageBytes;
-  static constexpr int kStages = kFit > 12 ? 12 : kFit;
-  static constexpr int kAccCols = kAcc * BNX;
+  static constexpr int kAccCols = kAcc * BNX;              // fp32 values per output column (TMEM lane)
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 512 /*barriers, flags*/;
 };
 
-// The k-block ranges (slab, [k0, k1)) of one CTA, in order.
-class Segments {
- public:
-  __device__ Segments(int slabs, int kb, int ctas, int cta, bool whole) : slabs_(slabs), kb_(kb), ctas_(ctas), whole_(whole) {
-    if (whole) {
-      slab_ = cta;
-    } else {
-      const long long total = static_cast<long long>(slabs) * kb;
-      pos_ = total * cta / ctas;
-      end_ = total * (cta + 1) / ctas;
-    }
-  }
-  __device__ bool next(int& slab, int& k0, int& k1) {
-    if (whole_) {
-      if (slab_ >= slabs_) return false;
-      slab = slab_; k0 = 0; k1 = kb_;
-      slab_ += ctas_;
-      return true;
-    }
-    if (pos_ >= end_) return false;
-    slab = static_cast<int>(pos_ / kb_);
-    const long long base = static_cast<long long>(slab) * kb_;
-    const long long stop = end_ < base + kb_ ? end_ : base + kb_;
-    k0 = static_cast<int>(pos_ - base);
-    k1 = static_cast<int>(stop - base);
-    pos_ = stop;
-    return true;
-  }
-
- private:
-  int slabs_, kb_, ctas_;
-  bool whole_;
-  int slab_ = 0;
-  long long pos_ = 0, end_ = 0;
-};
-
-// Scratch slot of a shared slab: the CTA whose range holds the slab's first k-block. Two shared
-// slabs never map to one CTA (a CTA's range cannot contain the first block of two slabs without
-// containing the whole of the earlier one).
-__device__ __forceinline__ int slot_of(int slab, int kb, int slabs, int ctas) {
-  const long long total = static_cast<long long>(slabs) * kb, x = static_cast<long long>(slab) * kb;
-  int g = static_cast<int>(x * ctas / total);
-  while (g + 1 < ctas && total * (g + 1) / ctas <= x) ++g;
-  while (g > 0 && total * g / ctas > x) --g;
-  return g;
+// Reduction buffers of one CTA for a cluster of `split`: 2 parities x [kAccCols][rows_max] floats.
+__host__ __device__ inline int rows_max_of(int split) { return (BMW + split - 1) / split; }
+__host__ __device__ inline int red_bytes_of(int split, int acc_cols) {
+  return split > 1 ? ((2 * acc_cols * rows_max_of(split) * 4 + 15) & ~15) : 0;
 }
+// First slab column owned by CTA `o` of the cluster; columns [col_lo(o), col_lo(o + 1)) are its.
+__host__ __device__ inline int col_lo(int o, int split) { return (o * BMW + split - 1) / split; }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh_f(float x) {
@@ -148,16 +113,9 @@ __device__ __forceinline__ bool bar_epilogue_all(bool pred) {
       : "memory");
   return r != 0;
 }
-// L2 reads of data other CTAs produced with reductions (never cached in L1).
-__device__ __forceinline__ float4 ld_cg_f32x4(const float* p) {
-  float4 v;
-  asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-  return v;
-}
-// System-scope reads of a peer's buffer.
-__device__ __forceinline__ float4 ld_sys_f32x4(const float* p) {
-  float4 v;
-  asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+__device__ __forceinline__ float ld_sys_f32(const float* p) {
+  float v;
+  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
   return v;
 }
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -167,6 +125,36 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
+}
+// Adds into the shared memory of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void red_add_dsmem(uint32_t cluster_addr, float v) {
+  asm volatile("red.shared::cluster.add.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait that makes the other CTAs' shared-memory writes visible (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > TX_WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
 }
 
 // Final value of one output element from its accumulated product(s).
@@ -191,30 +179,6 @@ __device__ __forceinline__ void emit(const SkinnyParams& p, float* part_self, in
   p.C[static_cast<long long>(j) * p.ldc + n] = __float2bfloat16_rn(v);
 }
 
-// Four finished values of row j, columns n .. n + 3 (n a multiple of 4, n + 3 < Nw).
-__device__ __forceinline__ void emit4(const SkinnyParams& p, float* part_self, int j, int n, float4 v) {
-  if (p.n_ranks > 1) {
-    *reinterpret_cast<float4*>(part_self + static_cast<long long>(j) * p.Nw + n) = v;
-    return;
-  }
-  if (p.bias) {
-    const uint2 b = *reinterpret_cast<const uint2*>(p.bias + n);
-    const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
-    const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
-    v.x += b0.x; v.y += b0.y; v.z += b1.x; v.w += b1.y;
-  }
-  if (p.residual) {
-    const uint2 r = *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(j) * p.ldr + n);
-    const float2 r0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
-    const float2 r1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
-    v.x += r0.x; v.y += r0.y; v.z += r1.x; v.w += r1.y;
-  }
-  uint2 o;
-  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
-  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
-  *reinterpret_cast<uint2*>(p.C + static_cast<long long>(j) * p.ldc + n) = o;
-}
-
 template <int BNX, bool GLU>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
@@ -223,39 +187,51 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + C::kStages * C::kStageBytes);
+  const int S = p.split, stages = p.stages;
+  const int rows_max = rows_max_of(S);
+  // layout: [stages x stage][reduction buffers, 2 parities][barriers and flags]
+  float* redbuf = reinterpret_cast<float*>(smem_gen + stages * C::kStageBytes);
+  const int red_bytes = red_bytes_of(S, C::kAccCols);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + stages * C::kStageBytes + red_bytes);
   const uint32_t bar_full = smem_u32(bars);
-  const uint32_t bar_empty = bar_full + 8 * C::kStages;
-  const uint32_t bar_tfull = bar_empty + 8 * C::kStages;
+  const uint32_t bar_empty = bar_full + 8 * kMaxStages;
+  const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;
   const uint32_t bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 4);
+  const uint32_t bar_red = bar_tempty + 16;       // [2]: contributions to my columns have arrived (per parity)
+  const uint32_t bar_emit = bar_red + 16;         // tensor-parallel: every CTA of the cluster stored its part of a block
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 7);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);
-  int* my_blocks = reinterpret_cast<int*>(tmem_slot + 4);      // blocks this CTA has to reduce (<= 24)
-  volatile int* n_my_blocks = reinterpret_cast<volatile int*>(tmem_slot + 3);
-  constexpr int kMaxMyBlocks = 24;
+  volatile int* n_my_blocks = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  int* my_blocks = reinterpret_cast<int*>(tmem_slot + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int slabs = (p.Nw + BMW - 1) / BMW;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int ctas = gridDim.x, cta = blockIdx.x;
-  const bool whole = p.whole_slabs != 0;
+  const int crank = S > 1 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int cluster_id = blockIdx.x / S;
+  const int kb_lo = static_cast<int>(static_cast<long long>(num_kb) * crank / S);
+  const int kb_hi = static_cast<int>(static_cast<long long>(num_kb) * (crank + 1) / S);
+  const int my_lo = col_lo(crank, S), my_hi = col_lo(crank + 1, S);
   const int epoch = p.n_ranks > 1 ? (*reinterpret_cast<volatile int*>(p.epoch) + 1) : 0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    *last_flag = 0;
     *n_my_blocks = 0;
-    for (int s = 0; s < C::kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 128);
+      mbar_init(bar_red + 8 * a, S > 1 ? (S - 1) * (my_hi - my_lo) : 1);
     }
+    mbar_init(bar_emit, S);
     mbar_fence_init();
+  }
+  if (S > 1) {
+    for (int i = threadIdx.x; i < red_bytes / 4; i += NUM_THREADS) redbuf[i] = 0.f;
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -263,6 +239,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
+  if (S > 1) cluster_sync_all();      // everybody's barriers and zeroed buffers exist before anyone adds into them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -272,12 +249,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       tma_prefetch_desc(&map_w);
       tma_prefetch_desc(&map_x);
       if (GLU) tma_prefetch_desc(&map_w2);
-      Segments seg(slabs, num_kb, ctas, cta, whole);
-      int slab, k0, k1, stage = 0;
+      int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      while (ok && seg.next(slab, k0, k1)) {
-        for (int kb = k0; kb < k1; ++kb) {
+      for (int slab = cluster_id; slab < slabs && ok; slab += p.n_clusters) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             atomicOr(p.status, kStatusWaitTimeoutProducer);
             ok = false;
@@ -289,7 +265,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tma_load_2d(sa, &map_w, kb * BK, slab * BMW, full);
           if (GLU) tma_load_2d(sa + C::kWBytes, &map_w2, kb * BK, slab * BMW, full);
           tma_load_2d(sa + C::kABytes, &map_x, kb * BK, 0, full);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -297,18 +273,17 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // ------------------------------------------------------------ MMA issuer
     if (elect_one()) {
       constexpr uint32_t idesc = make_idesc_bf16(BMW, BNX, false, false);
-      Segments seg(slabs, num_kb, ctas, cta, whole);
-      int slab, k0, k1, stage = 0, acc = 0;
+      int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      while (ok && seg.next(slab, k0, k1)) {
+      for (int slab = cluster_id; slab < slabs && ok; slab += p.n_clusters) {
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag)) {
           atomicOr(p.status, kStatusWaitTimeoutMma);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * C::kAccCols;
-        for (int kb = k0; kb < k1; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb) {
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag)) {
             atomicOr(p.status, kStatusWaitTimeoutMma);
             ok = false;
@@ -320,12 +295,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             const uint64_t dx = make_smem_desc_sw128(sx + k * 32, 16, 1024);
-            const uint32_t accum = (kb > k0 || k > 0) ? 1u : 0u;
+            const uint32_t accum = (kb > kb_lo || k > 0) ? 1u : 0u;
             umma_bf16(tmem_d, make_smem_desc_sw128(sa + k * 32, 16, 1024), dx, idesc, accum);
             if (GLU) umma_bf16(tmem_d + BNX, make_smem_desc_sw128(sa + C::kWBytes + k * 32, 16, 1024), dx, idesc, accum);
           }
           umma_commit(bar_empty + 8 * stage);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == stages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         umma_commit(bar_tfull + 8 * acc);
@@ -335,49 +310,58 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;              // TMEM lane quarter this warp may access
-    const int col = quarter * 32 + lane;       // column of the slab this thread owns
+    const int col = quarter * 32 + lane;       // slab column (TMEM lane) of this thread
     const bool leader = (warp == 2 && lane == 0);
+    const int owner = (col * S) >> 7;          // CTA of the cluster that finishes this column
+    const bool mine = owner == crank;
+    const int own_lo = col_lo(owner, S);
     float* part_self = p.n_ranks > 1 ? p.part[p.rank] + (epoch & 1) * p.part_stride : nullptr;
-    Segments seg(slabs, num_kb, ctas, cta, whole);
-    int slab, k0, k1, acc = 0;
+    int acc = 0, round = 0;
     uint32_t acc_phase = 0;
-    while (seg.next(slab, k0, k1)) {
+    for (int slab = cluster_id; slab < slabs; slab += p.n_clusters, ++round) {
       bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag);
       if (!ok) atomicOr(p.status, kStatusWaitTimeoutEpilogue);
       if (!bar_epilogue_all(ok)) break;          // all four warps leave together
       tc_fence_after();
       const int n = slab * BMW + col;
-      const bool complete = (k0 == 0 && k1 == num_kb);
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
-      float* slot = nullptr;
-      int slot_idx = 0;
-      if (!complete) {
-        slot_idx = slot_of(slab, num_kb, slabs, ctas);
-        slot = p.ws + static_cast<long long>(slot_idx) * kSlotFloats;
-      }
+      const int par = round & 1;
+      if (!mine) {
+        // my accumulator row belongs to another CTA's columns: add it into that CTA's buffer
+        const uint32_t dst = map_to_cta(smem_u32(redbuf + par * C::kAccCols * rows_max + (col - own_lo)), owner);
 #pragma unroll 1
-      for (int c = 0; c < BNX; c += 16) {
-        uint32_t rg[16], ru[16];
-        tmem_ld_32x32b_x16(taddr + c, rg);
-        if (GLU) tmem_ld_32x32b_x16(taddr + BNX + c, ru);
-        tmem_ld_wait();
-        if (complete) {
-          if (n < p.Nw) {
+        for (int c = 0; c < C::kAccCols; c += 16) {
+          if ((c & (BNX - 1)) >= p.Mx) continue;     // rows of X beyond Mx are zero-filled: nothing to add
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int j = c + e;
-              if (j < p.Mx)
-                emit(p, part_self, j, n, activate<GLU>(p, __uint_as_float(rg[e]), GLU ? __uint_as_float(ru[e]) : 0.f));
-            }
-          }
-        } else {
+          for (int e = 0; e < 16; ++e) red_add_dsmem(dst + (c + e) * rows_max * 4, __uint_as_float(r[e]));
+        }
+        mbar_arrive_cluster(map_to_cta(bar_red + 8 * par, owner));     // release: the adds above are visible to the owner
+      } else {
+        if (S > 1 && !mbar_wait_cluster(bar_red + 8 * par, (round >> 1) & 1, abort_flag))
+          atomicOr(p.status, kStatusWaitTimeoutEpilogue);
+        float* mybuf = redbuf + par * C::kAccCols * rows_max + (col - own_lo);
+#pragma unroll 1
+        for (int c = 0; c < BNX && c < p.Mx; c += 16) {
+          uint32_t rg[16], ru[16];
+          tmem_ld_32x32b_x16(taddr + c, rg);
+          if (GLU) tmem_ld_32x32b_x16(taddr + BNX + c, ru);
+          tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const int j = c + e;
-            if (j < p.Mx) {
-              atomicAdd(slot + j * BMW + col, __uint_as_float(rg[e]));
-              if (GLU) atomicAdd(slot + (BNX + j) * BMW + col, __uint_as_float(ru[e]));
+            float a = __uint_as_float(rg[e]), u = GLU ? __uint_as_float(ru[e]) : 0.f;
+            if (S > 1) {
+              a += mybuf[j * rows_max];
+              mybuf[j * rows_max] = 0.f;       // clean for the round after next, which reuses this parity
+              if (GLU) {
+                u += mybuf[(BNX + j) * rows_max];
+                mybuf[(BNX + j) * rows_max] = 0.f;
+              }
             }
+            if (j < p.Mx && n < p.Nw) emit(p, part_self, j, n, activate<GLU>(p, a, u));
           }
         }
       }
@@ -385,64 +369,22 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       mbar_arrive(bar_tempty + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
 
-      bool finished_block = complete;
-      if (!complete) {
-        // publish this CTA's share; whoever brings the slab's k-block count to num_kb finishes it
-        __threadfence();
-        bar_epilogue();
-        if (leader) {
-          __threadfence();
-          const int old = atomicAdd(p.counters + slot_idx, k1 - k0);
-          *last_flag = (old + (k1 - k0) == num_kb) ? 1 : 0;
-          if (*last_flag) __threadfence();
-        }
-        bar_epilogue();
-        if (*last_flag) {
-          finished_block = true;
-          // thread -> 4 columns x every 4th row; 8 rows of loads in flight at a time
-          const int c4 = (col & 31) * 4, r0 = col >> 5;
-          const int n4 = slab * BMW + c4;
-          for (int jb = r0; jb < p.Mx; jb += 32) {
-            float4 a[8], u[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int j = jb + 4 * e;
-              if (j < p.Mx) {
-                a[e] = ld_cg_f32x4(slot + j * BMW + c4);
-                if (GLU) u[e] = ld_cg_f32x4(slot + (BNX + j) * BMW + c4);
-              }
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int j = jb + 4 * e;
-              if (j < p.Mx) {
-                *reinterpret_cast<float4*>(slot + j * BMW + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (GLU) *reinterpret_cast<float4*>(slot + (BNX + j) * BMW + c4) = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (n4 < p.Nw) {
-                  float4 v;
-                  v.x = activate<GLU>(p, a[e].x, GLU ? u[e].x : 0.f);
-                  v.y = activate<GLU>(p, a[e].y, GLU ? u[e].y : 0.f);
-                  v.z = activate<GLU>(p, a[e].z, GLU ? u[e].z : 0.f);
-                  v.w = activate<GLU>(p, a[e].w, GLU ? u[e].w : 0.f);
-                  emit4(p, part_self, j, n4, v);
-                }
-              }
-            }
-          }
-          if (leader) p.counters[slot_idx] = 0;
-        }
-        bar_epilogue();       // last_flag is rewritten by the next shared slab
-      }
-      if (finished_block && p.n_ranks > 1) {
-        // the block of partial sums is in this rank's buffer: tell every rank, remember to reduce it
+      if (p.n_ranks > 1) {
+        // this CTA's columns of the block are in the rank's partial buffer; once all CTAs of the cluster say
+        // so, its first CTA raises the block's flag on every rank. Everybody remembers the block for the reduction.
         __threadfence_system();
         bar_epilogue();
-        if (lane < p.n_ranks && warp == 2)
-          st_release_sys(p.flags[lane] + p.rank * kMaxFlagBlocks + slab, epoch);
         if (leader) {
+          if (S > 1) mbar_arrive_cluster(map_to_cta(bar_emit, 0));
           const int i = *n_my_blocks;
           if (i < kMaxMyBlocks) { my_blocks[i] = slab; *n_my_blocks = i + 1; }
           else atomicOr(p.status, kStatusBadArgument);
+        }
+        if (crank == 0 && warp == 2) {
+          bool ready = true;
+          if (S > 1) ready = mbar_wait_cluster(bar_emit, round & 1, abort_flag);
+          __threadfence_system();
+          if (ready && lane < p.n_ranks) st_release_sys(p.flags[lane] + p.rank * kMaxFlagBlocks + slab, epoch);
         }
       }
     }
@@ -466,44 +408,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           }
         }
         if (!bar_epilogue_all(*abort_flag == 0)) break;
-        const int c4 = (col & 31) * 4, r0 = col >> 5;
-        const int n4 = blk * BMW + c4;
-        if (n4 < p.Nw) {
-          const long long off = (epoch & 1) * p.part_stride + n4;
-          float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.bias) {
-            const uint2 b = *reinterpret_cast<const uint2*>(p.bias + n4);
-            const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.x));
-            const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b.y));
-            bias = make_float4(b0.x, b0.y, b1.x, b1.y);
-          }
-          for (int jb = r0; jb < p.Mx; jb += 16) {
-            float4 v[4][kMaxRanks];
+        const int n = blk * BMW + col;
+        if (mine && n < p.Nw) {
+          const long long off = (epoch & 1) * p.part_stride + n;
+          const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
+          for (int j0 = 0; j0 < p.Mx; j0 += 8) {
+            float v[8][kMaxRanks];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = jb + 4 * e;
+            for (int e = 0; e < 8; ++e) {
 #pragma unroll
               for (int r = 0; r < kMaxRanks; ++r)
-                if (r < p.n_ranks && j < p.Mx) v[e][r] = ld_sys_f32x4(p.part[r] + off + static_cast<long long>(j) * p.Nw);
+                if (r < p.n_ranks && j0 + e < p.Mx)
+                  v[e][r] = ld_sys_f32(p.part[r] + off + static_cast<long long>(j0 + e) * p.Nw);
             }
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int j = jb + 4 * e;
+            for (int e = 0; e < 8; ++e) {
+              const int j = j0 + e;
               if (j >= p.Mx) continue;
-              float4 s = bias;
+              float s = bias;
 #pragma unroll
               for (int r = 0; r < kMaxRanks; ++r)       // rank order: every rank computes the same bits
-                if (r < p.n_ranks) { s.x += v[e][r].x; s.y += v[e][r].y; s.z += v[e][r].z; s.w += v[e][r].w; }
-              if (p.residual) {
-                const uint2 q = *reinterpret_cast<const uint2*>(p.residual + static_cast<long long>(j) * p.ldr + n4);
-                const float2 q0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
-                const float2 q1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
-                s.x += q0.x; s.y += q0.y; s.z += q1.x; s.w += q1.y;
-              }
-              uint2 o;
-              *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(s.x, s.y);
-              *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(s.z, s.w);
-              *reinterpret_cast<uint2*>(p.C + static_cast<long long>(j) * p.ldc + n4) = o;
+                if (r < p.n_ranks) s += v[e][r];
+              if (p.residual) s += __bfloat162float(p.residual[static_cast<long long>(j) * p.ldr + n]);
+              p.C[static_cast<long long>(j) * p.ldc + n] = __float2bfloat16_rn(s);
             }
           }
         }
@@ -514,6 +441,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (*abort_flag) __nanosleep(200000);
   tc_fence_before();
   __syncthreads();
+  if (S > 1) cluster_sync_all();        // nobody leaves while a peer may still add into its shared memory
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
@@ -522,7 +450,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     // the last CTA to leave advances the call counter for the next launch (or graph replay)
     __threadfence();
     const int old = atomicAdd(p.done, 1);
-    if (old == ctas - 1) {
+    if (old == static_cast<int>(gridDim.x) - 1) {
       *p.done = 0;
       *p.epoch = epoch;
       __threadfence();
@@ -530,10 +458,77 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
+// Per (kernel, device, split) cache of how many clusters can be resident at once.
+struct ClusterFit {
+  int stages[9] = {};
+  int max_clusters[9] = {};
+  bool known[9] = {};
+};
+
 template <int BNX, bool GLU>
-int launch_skinny(const void* X, const void* W, const SkinnyParams& p, long long ldx, long long ldw, int grid,
-                  cudaStream_t stream) {
+int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, long long ldw, int deterministic,
+                  int max_ctas, cudaStream_t stream) {
   using C = SCfg<BNX, GLU>;
+  auto kern = gemm_skinny_kernel<BNX, GLU>;
+  static txh::DeviceFlag attr_flag;
+  static ClusterFit fits[txh::kMaxDevices];
+  bool& attr_set = attr_flag.cur();
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) return 300;
+    attr_set = true;
+  }
+  ClusterFit& fit = fits[txh::current_device()];
+  const int slabs = (p.Nw + BMW - 1) / BMW, num_kb = (p.K + BK - 1) / BK;
+  int sms = txh::sm_count();
+  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
+
+  auto smem_for = [&](int split, int stages) { return stages * C::kStageBytes + red_bytes_of(split, C::kAccCols) + 1024 + 512; };
+  auto probe = [&](int split) {
+    if (fit.known[split]) return;
+    fit.known[split] = true;
+    int stages = (kSmemLimit - red_bytes_of(split, C::kAccCols) - 1024 - 512) / C::kStageBytes;
+    if (stages > kMaxStages) stages = kMaxStages;
+    if (stages < 3) return;                          // not worth it: max_clusters stays 0
+    fit.stages[split] = stages;
+    if (split == 1) { fit.max_clusters[1] = txh::sm_count(); return; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(split * txh::sm_count(), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem_for(split, stages);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+    fit.max_clusters[split] = n;
+  };
+
+  // Pick the split whose schedule streams the weight in the fewest k-block steps: rounds x k-blocks per CTA,
+  // plus a small charge per round for the exchange of partial sums.
+  int best_s = 1, best_nc = 1;
+  long long best_cost = -1;
+  const int max_split = deterministic ? 1 : 8;
+  for (int s = 1; s <= max_split; ++s) {
+    if (s > 1 && num_kb / s < 4) break;              // every CTA keeps at least 4 k-blocks
+    probe(s);
+    int nc = fit.max_clusters[s];
+    if (nc > sms / s) nc = sms / s;
+    if (nc < 1) continue;
+    if (nc > slabs) nc = slabs;
+    const int rounds = (slabs + nc - 1) / nc;
+    const long long cost = static_cast<long long>(rounds) * ((num_kb + s - 1) / s + (s > 1 ? 3 : 0));
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; best_nc = nc; }
+  }
+  if (best_cost < 0) return 301;
+  p.split = best_s;
+  p.n_clusters = best_nc;
+  p.stages = fit.stages[best_s];
+  if (p.n_ranks > 1 && (slabs + best_nc - 1) / best_nc > kMaxMyBlocks) return 4;
+
   CUtensorMap mw, mw2, mx;
   int rc = txh::make_map_2d_bf16(&mw, W, p.Nw, p.K, ldw, BMW, BK);
   if (rc) return 100 + rc;
@@ -545,51 +540,52 @@ int launch_skinny(const void* X, const void* W, const SkinnyParams& p, long long
   }
   rc = txh::make_map_2d_bf16(&mx, X, p.Mx, p.K, ldx, BNX, BK);
   if (rc) return 200 + rc;
-  auto kern = gemm_skinny_kernel<BNX, GLU>;
-  static txh::DeviceFlag attr_flag;
-  bool& attr_set = attr_flag.cur();
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) != cudaSuccess) return 300;
-    attr_set = true;
-  }
-  kern<<<grid, NUM_THREADS, C::kSmemBytes, stream>>>(mw, mw2, mx, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(best_nc * best_s, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem_for(best_s, p.stages);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = best_s;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, mw, mw2, mx, p) != cudaSuccess) { (void)cudaGetLastError(); return 400; }
+  return 0;
 }
 
 template <bool GLU>
-int dispatch_bnx(int Mx, const void* X, const void* W, const SkinnyParams& p, long long ldx, long long ldw, int grid,
-                 cudaStream_t stream) {
-  if (Mx <= 16) return launch_skinny<16, GLU>(X, W, p, ldx, ldw, grid, stream);
-  if (Mx <= 32) return launch_skinny<32, GLU>(X, W, p, ldx, ldw, grid, stream);
-  if (Mx <= 64) return launch_skinny<64, GLU>(X, W, p, ldx, ldw, grid, stream);
-  return launch_skinny<128, GLU>(X, W, p, ldx, ldw, grid, stream);
+int dispatch_bnx(int Mx, const void* X, const void* W, const SkinnyParams& p, long long ldx, long long ldw,
+                 int deterministic, int max_ctas, cudaStream_t stream) {
+  if (Mx <= 16) return launch_skinny<16, GLU>(X, W, p, ldx, ldw, deterministic, max_ctas, stream);
+  if (Mx <= 32) return launch_skinny<32, GLU>(X, W, p, ldx, ldw, deterministic, max_ctas, stream);
+  if (Mx <= 64) return launch_skinny<64, GLU>(X, W, p, ldx, ldw, deterministic, max_ctas, stream);
+  return launch_skinny<128, GLU>(X, W, p, ldx, ldw, deterministic, max_ctas, stream);
 }
 
 }  // namespace
 
-// Number of scratch slots (= the largest grid) and floats per slot that `tx_gemm_skinny` may use.
-extern "C" int tx_gemm_skinny_slots() { return txh::sm_count(); }
-extern "C" int tx_gemm_skinny_slot_floats() { return kSlotFloats; }
 extern "C" int tx_gemm_skinny_flag_blocks() { return kMaxFlagBlocks; }
 
 // C[Mx, Nw] = epilogue(alpha * X W^T); see the top of this file.
 //   X [Mx, K] bf16 (row stride ldx), W [Nw, K] bf16 - with glu != 0, [2 Nw, K]: gate rows then up rows - (row
 //   stride ldw), C [Mx, Nw] bf16 (row stride ldc). Bases 16-byte aligned, ldx / ldw multiples of 8, Mx <= 128.
-//   ws: tx_gemm_skinny_slots() * tx_gemm_skinny_slot_floats() floats, counters: tx_gemm_skinny_slots() ints; both
-//   zero before the first call and left zero by every call; launches sharing them must be ordered on one stream.
-//   deterministic != 0: no slab is shared between CTAs, so repeated launches give identical bits.
-//   max_ctas > 0 caps the grid.
+//   deterministic != 0: a slab is never split over CTAs, so repeated launches give identical bits.
+//   max_ctas > 0 caps the number of CTAs.
 // Tensor-parallel exit when n_ranks > 1 (no glu): part[r] / flags[r] are rank r's peer-mapped partial buffer
 // (2 * part_stride floats, part_stride >= Mx * Nw) and flag table (n_ranks * tx_gemm_skinny_flag_blocks() ints,
 // zero-initialised); epoch / done are two zero-initialised device ints private to this rank. Every rank of the
 // group must issue the same sequence of calls, and the kernel must be able to have all its CTAs resident.
 extern "C" int tx_gemm_skinny(const void* X, const void* W, void* C, const void* residual, const void* bias, int Mx,
                               int Nw, int K, long long ldx, long long ldw, long long ldc, long long ldr, float alpha,
-                              int glu, int deterministic, float* ws, int* counters, int* status, int max_ctas,
-                              int n_ranks, int rank, void* const* part, void* const* flags, long long part_stride,
-                              int* epoch, int* done, long long wait_ms, cudaStream_t stream) {
+                              int glu, int deterministic, int* status, int max_ctas, int n_ranks, int rank,
+                              void* const* part, void* const* flags, long long part_stride, int* epoch, int* done,
+                              long long wait_ms, cudaStream_t stream) {
   if (Mx <= 0 || Mx > 128 || Nw <= 0 || K <= 0 || glu < 0 || glu > 2) return 1;
-  if ((ldx & 7) || (ldw & 7) || (ldc & 7) || (Nw & 7) || (residual && (ldr & 7)) || !ws || !counters || !status) return 2;
+  if ((ldx & 7) || (ldw & 7) || !status) return 2;
   if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return 3;
   if (glu && ((static_cast<long long>(Nw) * ldw * 2) & 15)) return 3;
   if (n_ranks > 1) {
@@ -605,8 +601,6 @@ extern "C" int tx_gemm_skinny(const void* X, const void* W, void* C, const void*
   p.Mx = Mx; p.Nw = Nw; p.K = K;
   p.alpha = alpha;
   p.glu = glu;
-  p.ws = ws;
-  p.counters = counters;
   p.status = status;
   p.n_ranks = n_ranks > 1 ? n_ranks : 1;
   p.rank = rank;
@@ -621,23 +615,6 @@ extern "C" int tx_gemm_skinny(const void* X, const void* W, void* C, const void*
     p.done = done;
     p.wait_ns = static_cast<unsigned long long>(wait_ms > 0 ? wait_ms : 2000) * 1000000ull;
   }
-  const int slabs = (Nw + BMW - 1) / BMW, num_kb = (K + BK - 1) / BK;
-  int sms = txh::sm_count();
-  if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
-  int grid;
-  if (deterministic) {
-    p.whole_slabs = 1;
-    grid = slabs < sms ? slabs : sms;
-  } else {
-    // every CTA gets at least 4 k-blocks; with fewer the fix-up costs more than the balance gains
-    const long long total = static_cast<long long>(slabs) * num_kb;
-    long long g = total / 4;
-    if (g < 1) g = 1;
-    grid = static_cast<int>(g < sms ? g : sms);
-    // a tensor-parallel CTA remembers at most 24 finished blocks
-    p.whole_slabs = 0;
-  }
-  if (n_ranks > 1 && (slabs + grid - 1) / grid + 2 > 24) return 4;
-  return glu ? dispatch_bnx<true>(Mx, X, W, p, ldx, ldw, grid, stream)
-             : dispatch_bnx<false>(Mx, X, W, p, ldx, ldw, grid, stream);
+  return glu ? dispatch_bnx<true>(Mx, X, W, p, ldx, ldw, deterministic, max_ctas, stream)
+             : dispatch_bnx<false>(Mx, X, W, p, ldx, ldw, deterministic, max_ctas, stream);
 }

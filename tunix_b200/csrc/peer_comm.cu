@@ -153,6 +153,50 @@ peer_copy_2d_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long
   }
 }
 
+// One 2-D block of a re-sharding plan: dst[r, 0:cols] = src[r, 0:cols] for r < rows, 2-byte elements.
+// `src` / `dst` are absolute device addresses (either may be a peer mapping); leading dimensions in elements.
+// `first_chunk` is the running count of 16-byte chunks (or of elements, for unaligned segments) before this one.
+struct ReshardSeg {
+  unsigned long long src, dst;
+  long long rows, cols, src_ld, dst_ld;
+  long long first_unit;      // prefix sum of work units
+  int vec;                   // 1: every row start and `cols` are multiples of 8 elements -> 16-byte moves
+  int pad;
+};
+
+// Walks a whole plan in one launch: work unit u belongs to the segment found by binary search in the
+// prefix sums; a unit is a 16-byte chunk of a row (vec) or a single element.
+__global__ void __launch_bounds__(256)
+reshard_copy_kernel(const ReshardSeg* __restrict__ segs, int n_segs, long long total_units) {
+  for (long long u = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; u < total_units;
+       u += static_cast<long long>(gridDim.x) * blockDim.x) {
+    int lo = 0, hi = n_segs - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (segs[mid].first_unit <= u) lo = mid; else hi = mid - 1;
+    }
+    const ReshardSeg sg = segs[lo];
+    const long long k = u - sg.first_unit;
+    if (sg.vec) {
+      const long long per_row = sg.cols >> 3;
+      const long long r = k / per_row, c = k - r * per_row;
+      const uint4* s = reinterpret_cast<const uint4*>(sg.src) + ((r * sg.src_ld) >> 3) + c;
+      uint4* d = reinterpret_cast<uint4*>(sg.dst) + ((r * sg.dst_ld) >> 3) + c;
+      *d = *s;
+    } else {
+      const long long r = k / sg.cols, c = k - r * sg.cols;
+      reinterpret_cast<unsigned short*>(sg.dst)[r * sg.dst_ld + c] =
+          reinterpret_cast<const unsigned short*>(sg.src)[r * sg.src_ld + c];
+    }
+  }
+}
+
+// Publishes a finished copy: version word = value, after everything the stream did before.
+__global__ void publish_version_kernel(int* version, int value) {
+  __threadfence_system();
+  *reinterpret_cast<volatile int*>(version) = value;
+}
+
 inline int grid_for(long long items, int threads, int cap_per_sm) {
   long long b = (items + threads - 1) / threads;
   const long long cap = static_cast<long long>(txh::sm_count()) * cap_per_sm;
@@ -209,3 +253,21 @@ extern "C" int tx_peer_copy_2d(const void* src, void* dst, long long rows, long 
       static_cast<const uint4*>(src), static_cast<uint4*>(dst), rows, cols / 8, src_ld / 8, dst_ld / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
+
+// Executes a re-sharding plan (`n_segs` ReshardSeg records in device memory, `total_units` = the last prefix sum +
+// the last segment's units) in one launch, then - when `version` is given - stores `version_value` there, ordered
+// after the copies, so a reader that polls the word knows the whole replica is in place. Sources may be peer
+// mappings (trainer rank -> rollout rank over NVLink); plain loads and stores only.
+extern "C" int tx_reshard_copy(const void* segs, int n_segs, long long total_units, int* version, int version_value,
+                               cudaStream_t s) {
+  if (n_segs < 0 || total_units < 0) return 1;
+  if (n_segs > 0 && total_units > 0) {
+    reshard_copy_kernel<<<grid_for(total_units, 256, 8), 256, 0, s>>>(static_cast<const ReshardSeg*>(segs), n_segs,
+                                                                     total_units);
+    if (cudaGetLastError() != cudaSuccess) return 400;
+  }
+  if (version) publish_version_kernel<<<1, 1, 0, s>>>(version, version_value);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+extern "C" int tx_reshard_seg_bytes() { return static_cast<int>(sizeof(ReshardSeg)); }

@@ -227,7 +227,51 @@ class FlatParamStore:
                        eps=inner.eps, weight_decay=inner.weight_decay, step=count, grad_scale=scale, zero_grad=True)
 
   # ---- checkpoint support ---------------------------------------------------------------------
+  def state_shards(self, state: Mapping[str, Any]) -> Dict[Tuple, Any]:
+    """This rank's part of the optimizer state as a checkpoint tree whose sharded leaves are chunks of
+    flat arrays: `mu/nu/master.flat` of shape [numel] cut into `world` chunks of [shard_numel] (rank r
+    holds chunk r) and, with expert parallelism, `*.local` of shape [world * local_numel]. Every rank
+    writes its own chunk files; nothing crosses the ranks."""
+    from ..ckpt.orbax_layout import ShardedArray
+    out: Dict[Tuple, Any] = {("count", "value"): torch.as_tensor(state["count"])}
+    for k in ("mu", "nu", "master"):
+      out[(k, "flat", "value")] = ShardedArray(state[k]["flat"], (self.numel,), (self.shard_numel,), (self.rank,))
+      if "local" in state[k]:
+        out[(k, "local", "value")] = ShardedArray(state[k]["local"], (self.world * self.local_numel,),
+                                                  (self.local_numel,), (self.rank,))
+    for n, v in (state.get("hyperparams") or {}).items():
+      out[("hyperparams", n, "value")] = torch.as_tensor(v)
+    return out
+
+  def flat_index(self) -> Dict[str, Any]:
+    """Where each parameter sits in the flat arrays of `state_shards` (JSON-serialisable)."""
+    return {"format": "tunix_b200.flat_state.v1", "numel": self.numel, "used": self.used, "world": self.world,
+            "shard_numel": self.shard_numel, "names": list(self.names),
+            "offsets": [self.offsets[n] for n in self.names], "shapes": [list(self.shapes[n]) for n in self.names],
+            "local_numel": self.local_numel, "local_names": list(self.local_names),
+            "local_offsets": [self.local_offsets[n] for n in self.local_names],
+            "local_shapes": [list(self.local_shapes[n]) for n in self.local_names]}
+
+  @torch.no_grad()
+  def load_state_shards(self, state: Dict[str, Any], index: Mapping[str, Any], read_rows) -> None:
+    """Restores this rank's shard from flat arrays written by `state_shards`, possibly by a job of another
+    size: `read_rows(name, lo, hi)` returns elements [lo, hi) of the stored 1-D array `name`. Parameter
+    offsets do not depend on the number of ranks, so a rank's flat range is the same range of the file."""
+    if list(index["names"]) != list(self.names) or list(index["offsets"]) != [self.offsets[n] for n in self.names]:
+      raise ValueError("checkpointed optimizer state was written for a different parameter layout")
+    lo, hi = self.shard.start, self.shard.stop
+    for k in ("mu", "nu", "master"):
+      part = read_rows(f"{k}.flat", lo, hi)
+      state[k]["flat"].copy_(part.to(self.device, torch.float32))
+      if "local" in state[k]:
+        if index.get("world") != self.world or index.get("local_numel") != self.local_numel:
+          raise ValueError("expert-parallel optimizer state can only be restored at the expert-parallel size "
+                           f"it was saved with ({index.get('world')} ranks)")
+        a = self.rank * self.local_numel
+        state[k]["local"].copy_(read_rows(f"{k}.local", a, a + self.local_numel).to(self.device, torch.float32))
+
   def full_state_tensor(self, shard_tensor: torch.Tensor) -> torch.Tensor:
+    """All-gathers a sharded state tensor (per-parameter views for export; checkpoints do not use this)."""
     if self.world == 1:
       return shard_tensor
     full = torch.empty(self.numel, dtype=shard_tensor.dtype, device=shard_tensor.device)

@@ -479,7 +479,14 @@ class Transformer(nn.Module):
     `as_float=False` returns the GEMM's own dtype when no soft-cap applies: the sampler kernel
     reads bf16 rows directly, which saves a pass over [B, V] per decode step."""
     w = self.head_weight()
-    logits = F.linear(hidden, w)
+    if getattr(self, "tp_size", 1) > 1 and getattr(w, "vocab_parallel", None) is None:
+      # a replicated head on tensor-parallel ranks: every rank must get the same bits, or the ranks of a
+      # group would sample different tokens - no reduction whose order varies from run to run
+      from ..ops import kernels
+      with kernels.fixed_reduction_order():
+        logits = F.linear(hidden, w)
+    else:
+      logits = F.linear(hidden, w)
     vp = getattr(w, "vocab_parallel", None)
     if vp is not None:       # vocabulary-parallel head: every rank computed its slice of the logits
       import torch.distributed as dist

@@ -73,10 +73,8 @@ def _declare(lib):
       "tx_peer_copy_2d": [P, P, L, L, L, L, P],
       "tx_sample": [P, I, L, I, I, F, I, ctypes.c_ulonglong, P, L, P, I, P, P, P],
       "tx_sample_filtered": [P, I, L, I, I, F, I, F, ctypes.c_ulonglong, P, L, P, I, P, P, P],
-      "tx_gemm_skinny_slots": [],
-      "tx_gemm_skinny_slot_floats": [],
       "tx_gemm_skinny_flag_blocks": [],
-      "tx_gemm_skinny": [P, P, P, P, P, I, I, I, L, L, L, L, F, I, I, P, P, P, I, I, I, ctypes.POINTER(P),
+      "tx_gemm_skinny": [P, P, P, P, P, I, I, I, L, L, L, L, F, I, I, P, I, I, I, ctypes.POINTER(P),
                          ctypes.POINTER(P), L, P, P, L, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
       "tx_logprob_bwd": [P, I, L, P, P, P, P, P, P, L, I, I, I, F, F, P],

@@ -5,8 +5,10 @@ on the current stream. Autograd glue and the CPU oracle live in `functional.py`.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import os
+import threading
 from typing import Optional, Tuple
 
 import torch
@@ -278,22 +280,23 @@ def gemm_allgather_b(a: torch.Tensor, shard_ptrs, rank: int, shard_rows: int, st
 
 
 # ------------------------------------------------------------------------------ skinny (decode) GEMM
-_skinny_ws = {}
 _SKINNY = os.environ.get("TUNIX_B200_SKINNY", "1") != "0"     # 0: decode products take the general GEMM (A/B runs)
 
 
-def _skinny_workspace(device: torch.device):
-  """Scratch slots and slab counters of the stream-K skinny GEMM, one set per (device, stream):
-  the kernel leaves them zeroed, and launches that share a set must be ordered on one stream."""
-  key = (device.index, torch.cuda.current_stream(device).cuda_stream)
-  ws = _skinny_ws.get(key)
-  if ws is None:
-    lib = _lib.require()
-    slots = lib.tx_gemm_skinny_slots()
-    ws = (torch.zeros(slots * lib.tx_gemm_skinny_slot_floats(), dtype=torch.float32, device=device),
-          torch.zeros(slots, dtype=torch.int32, device=device))
-    _skinny_ws[key] = ws
-  return ws
+_fixed_order = threading.local()
+
+
+@contextlib.contextmanager
+def fixed_reduction_order():
+  """Within the block, skinny GEMMs of this thread reduce every output in one fixed order (no split of K over
+  CTAs), as in the package-wide deterministic mode: computations that are replicated on several ranks and must
+  agree bit for bit (the lm_head of a tensor-parallel rollout group) use it."""
+  old = getattr(_fixed_order, "on", False)
+  _fixed_order.on = True
+  try:
+    yield
+  finally:
+    _fixed_order.on = old
 
 
 def gemm_skinny_supported(x2: torch.Tensor, w: torch.Tensor, glu: bool = False) -> bool:
@@ -310,7 +313,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor]
                 residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, alpha: float = 1.0,
                 max_ctas: int = 0, tp=None) -> torch.Tensor:
   """y[M, N] = epilogue(alpha * x[M, K] @ w[N, K]^T) for M <= 128 in one launch that streams `w` once
-  (`csrc/gemm_skinny.cu`: swapped operands, stream-K over all SMs, self-cleaning fp32 scratch).
+  (`csrc/gemm_skinny.cu`: swapped operands, split-K over thread-block clusters with the partial sums
+  exchanged through distributed shared memory; no workspace).
 
   glu: None | "silu" | "gelu" - `w` is then [gate rows | up rows] ([2N, K]) and y = act(x gate^T) * (x up^T).
   residual: [M, N] added to the product (may be `out` itself). bias: [N].
@@ -322,7 +326,6 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor]
   if out is None:
     out = torch.empty((M, N), dtype=bf16, device=x.device)
   assert out.shape == (M, N) and out.dtype == bf16 and out.stride(1) == 1
-  ws, counters = _skinny_workspace(x.device)
   lib = _lib.require()
   g = {None: 0, "silu": 1, "gelu": 2}[glu]
   if tp is None:
@@ -332,8 +335,7 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor]
     stride, epoch, done, wait_ms = tp.part_stride, tp.epoch.data_ptr(), tp.done.data_ptr(), tp.wait_ms
   rc = lib.tx_gemm_skinny(x.data_ptr(), w.data_ptr(), out.data_ptr(), _p(residual), _p(bias), M, N, K, x.stride(0),
                           w.stride(0), out.stride(0), residual.stride(0) if residual is not None else 0, float(alpha),
-                          g, int(_lib.deterministic()), ws.data_ptr(), counters.data_ptr(),
-                          _lib.status_word(x.device).data_ptr(), int(max_ctas), n_ranks, rank, parts, flags, stride,
+                          g, int(_lib.deterministic() or getattr(_fixed_order, "on", False)), _lib.status_word(x.device).data_ptr(), int(max_ctas), n_ranks, rank, parts, flags, stride,
                           epoch, done, wait_ms, _lib.stream_ptr())
   _lib.check_rc(rc, f"tx_gemm_skinny(M={M},N={N},K={K},glu={glu})")
   return out

@@ -156,6 +156,29 @@ class ModelOptimizer:
     return None
 
   # checkpoint hooks used by CheckpointManager
+  def checkpoint_group(self):
+    """Process group whose ranks save and restore together (None: a single process)."""
+    return self.flat.group if self.flat is not None and self.flat.world > 1 else None
+
+  def checkpoint_shards(self):
+    """(tree, extras) when the state is sharded over ranks: every rank contributes its own chunks and no
+    state is gathered. None for single-rank state, which is saved per parameter."""
+    if self.flat is None or self.flat.world == 1:
+      return None
+    import json
+    return self.flat.state_shards(self.opt_state), {"_flat_index.json": json.dumps(self.flat.flat_index()).encode()}
+
+  def restore_shards(self, index, read_rows, small: Mapping[Any, torch.Tensor]) -> None:
+    """Inverse of `checkpoint_shards`: `read_rows(name, lo, hi)` reads a range of a flat array, `small`
+    holds the replicated leaves (step count, hyper-parameters)."""
+    self.flat.load_state_shards(self.opt_state, index, read_rows)
+    if ("count", "value") in small:
+      self.opt_state["count"] = small[("count", "value")].to(torch.int32).reshape(())
+    for key, v in small.items():
+      if key[0] == "hyperparams" and "hyperparams" in self.opt_state:
+        self.opt_state["hyperparams"][key[1]] = v.to(torch.float32).reshape(())
+    self._master_restored = True
+
   def gather_for_checkpoint(self):
     from ..ckpt import layout
     st = self.flat.opt_state_tree(self.opt_state) if self.flat is not None else self.opt_state
@@ -451,6 +474,17 @@ class PeftTrainer:
     self._log_metrics(loss=self._global_loss(metrics_buffer), step=metrics_buffer.step,
                       additional_metrics={k: apply_op(v, op) for k, (v, op) in
                                           metrics_buffer.additional_metrics.items()})
+    self._check_kernel_status()
+
+  def _check_kernel_status(self) -> None:
+    """Raises when a kernel of the steps written so far reported an error (a bounded wait on a peer or a
+    pipeline barrier that ran out, a bad argument, rows dropped by an expert-parallel receive buffer).
+    Called where the loss has just been read back, so the check adds no synchronisation of its own; a
+    step whose kernels failed is therefore reported at most one optimizer step late, before its
+    parameters reach a checkpoint."""
+    if self._device is not None and self._device.type == "cuda":
+      from ..ops import _lib
+      _lib.check_status(self._device)
 
   def _global_loss(self, metrics_buffer: MetricsBuffer) -> float:
     """Loss of the step over all data-parallel ranks (each rank buffered its own share)."""
