@@ -292,7 +292,7 @@ def test_round_tracker_rejects_stale_and_stray_phases():
 
 
 def test_manifest_validation():
-  with pytest.raises(ValueError, match="two tensor dimensions"):
+  with pytest.raises(ValueError, match="one mesh axis for two tensor"):
     weight_sync.TensorMetadata(name="w", shape=(2, 2), mesh_shape=(1, 1), layout=(1, 0), item_size=2, sharding_spec=("x", "x"))
   with pytest.raises(ValueError, match="rank"):
     weight_sync.TensorMetadata(name="w", shape=(2, 2), mesh_shape=(1,), layout=(1, 0), item_size=2)

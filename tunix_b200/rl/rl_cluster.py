@@ -272,45 +272,37 @@ class RLEngine:
     self._external_metrics_logger = external_metrics_logger
     return self
 
-  def buffer_metrics(self, metrics: MetricsT, mode: Mode = Mode.TRAIN) -> None:
-    """Buffers RL metrics; they are written when the global step advances."""
-    buffered = self._buffered_train_metrics if mode == Mode.TRAIN else self._buffered_eval_metrics
-    if not buffered:
-      buffered.append(MetricsBuffer(self.global_steps, mode=str(mode)))
-    if self._buffered_train_metrics and self._buffered_train_metrics[0].global_steps != self.global_steps:
-      self._buffered_train_metrics.append(MetricsBuffer(self.global_steps, mode=str(Mode.TRAIN)))
-      flush = [self._buffered_train_metrics.pop(0)]
-      if self._buffered_eval_metrics and self._buffered_eval_metrics[0].global_steps != self.global_steps:
-        flush.append(self._buffered_eval_metrics.pop(0))
-        if mode != Mode.TRAIN:
-          self._buffered_eval_metrics.append(MetricsBuffer(self.global_steps, mode=str(mode)))
-      for m in flush:
-        self._log_metrics(m)
-      buffered = self._buffered_train_metrics if mode == Mode.TRAIN else self._buffered_eval_metrics
-      if not buffered:
-        buffered.append(MetricsBuffer(self.global_steps, mode=str(mode)))
-    cur = buffered[-1]
+  # RL metrics are kept in a ledger keyed by (mode, global step) and written once the run has moved past
+  # their step, so everything that belongs to one step - rollout statistics recorded by the producer thread,
+  # rewards, trainer-side values - lands in one logger call, in step order.
+  def _ledger(self, mode: Mode) -> List[MetricsBuffer]:
+    return self._buffered_train_metrics if mode == Mode.TRAIN else self._buffered_eval_metrics
+
+  def _record(self, metrics: MetricsT, mode: Mode, step: int) -> None:
+    ledger = self._ledger(mode)
+    page = next((m for m in reversed(ledger) if m.global_steps == step), None)
+    if page is None:
+      page = MetricsBuffer(step, mode=str(mode))
+      ledger.append(page)
+      ledger.sort(key=lambda m: m.global_steps)
     for name, (value, op) in metrics.items():
-      if name not in cur.metrics:
-        cur.metrics[name] = ([value], op)
-      else:
-        cur.metrics[name][0].append(value)
+      page.metrics.setdefault(name, ([], op))[0].append(value)
+
+  def _write_finished_steps(self) -> None:
+    for ledger in (self._buffered_train_metrics, self._buffered_eval_metrics):
+      while ledger and ledger[0].global_steps < self.global_steps:
+        self._log_metrics(ledger.pop(0))
+
+  def buffer_metrics(self, metrics: MetricsT, mode: Mode = Mode.TRAIN) -> None:
+    """Records metrics of the current global step; steps the run has left behind are written out."""
+    self._write_finished_steps()
+    self._record(metrics, mode, self.global_steps)
 
   def buffer_metrics_async(self, metrics: MetricsT, mode: Mode = Mode.TRAIN, step: int = 0) -> None:
-    buffered = self._buffered_train_metrics if mode == Mode.TRAIN else self._buffered_eval_metrics
-    if not buffered:
-      buffered.append(MetricsBuffer(self.global_steps, mode=str(mode)))
-    elif step != buffered[-1].global_steps:
-      buffered.append(MetricsBuffer(step, mode=str(mode)))
-    cur = buffered[-1]
-    for name, (value, op) in metrics.items():
-      if name not in cur.metrics:
-        cur.metrics[name] = ([value], op)
-      else:
-        cur.metrics[name][0].append(value)
-    for lst in (self._buffered_train_metrics, self._buffered_eval_metrics):
-      if lst and lst[0].global_steps < self.global_steps:
-        self._log_metrics(lst.pop(0))
+    """Like `buffer_metrics` for a producer that runs ahead of (or behind) the trainer: the caller names the
+    step the values belong to."""
+    self._record(metrics, mode, step)
+    self._write_finished_steps()
 
   # ---- training ----------------------------------------------------------------------------------------
   def train(self, role: Role, train_ds: Any, eval_ds: Any, skip_jit: bool = False) -> None:
@@ -347,40 +339,50 @@ class RLEngine:
     rc = self.cluster_config.rollout_config
     return rc[mode] if isinstance(rc, dict) else rc
 
+  def _render_prompts(self, prompts, apply_chat_template: bool) -> List[str]:
+    if not apply_chat_template:
+      return list(prompts)
+    if self.tokenizer is None:
+      raise ValueError("Tokenizer must be initialized to use chat templates.")
+    return [self.tokenizer.apply_chat_template(chat, add_generation_prompt=True, tokenize=False, enable_thinking=False)
+            for chat in prompts]
+
+  @staticmethod
+  def _join_rollouts(parts: List[base_rollout.RolloutOutput]) -> base_rollout.RolloutOutput:
+    """One `RolloutOutput` from the outputs of consecutive micro-batches (optional fields stay optional)."""
+    def flat(field: str, present: bool):
+      return [x for part in parts for x in getattr(part, field)] if present else None
+    head = parts[0]
+    return base_rollout.RolloutOutput(
+        text=flat("text", True), tokens=flat("tokens", True),
+        logits=flat("logits", head.logits is not None and len(head.logits) > 0),
+        logprobs=flat("logprobs", head.logprobs is not None),
+        left_padded_prompt_tokens=np.concatenate([part.left_padded_prompt_tokens for part in parts], axis=0))
+
   def generate(self, prompts, apply_chat_template: bool = False, mode: Mode = Mode.TRAIN,
                micro_batch_size: Optional[int] = None, trace_tags: Optional[Mapping[str, Any]] = None,
                max_generation_steps: Optional[int] = None) -> base_rollout.RolloutOutput:
-    """Generates completions, micro-batched, through the rollout engine."""
-    if apply_chat_template:
-      if self.tokenizer is None:
-        raise ValueError("Tokenizer must be initialized to use chat templates.")
-      string_prompts = [self.tokenizer.apply_chat_template(p, add_generation_prompt=True, tokenize=False,
-                                                           enable_thinking=False) for p in prompts]
-    else:
-      string_prompts = list(prompts)
-    if len(string_prompts) == 0:
+    """Completions for `prompts` (strings, or chats when `apply_chat_template`) from the rollout engine, generated
+    `micro_batch_size` prompts at a time under the rollout configuration of `mode`."""
+    texts = self._render_prompts(prompts, apply_chat_template)
+    if not texts:
       raise ValueError("Cannot generate from an empty list of prompts.")
-    micro_batch_size = micro_batch_size or len(string_prompts)
-    model = self.rollout.model()
-    self._maybe_load_model_from_cpu(model, Role.ROLLOUT)
     rc = self.get_rollout_config(mode)
     if max_generation_steps is not None:
       rc = dataclasses.replace(rc, max_tokens_to_generate=max_generation_steps)
-    tags = {"role": Role.ROLLOUT.value}
-    tags.update(trace_tags or {})
-    with self._perf.span("rollout") as span, self._perf_v2.span("rollout", tags=tags) as span_v2:
-      outputs = [self.rollout.generate(string_prompts[s], rc)
-                 for s in rl_utils.chunk_slices_by_size(len(string_prompts), micro_batch_size)]
-      span.device_end([o.tokens for o in outputs])
-      span_v2.async_end([o.tokens for o in outputs])
-    self._maybe_offload_model_to_cpu(model, Role.ROLLOUT)
-    chain = itertools.chain.from_iterable
-    logprobs = list(chain(o.logprobs for o in outputs)) if outputs[0].logprobs is not None else None
-    logits = list(chain(o.logits for o in outputs)) if outputs[0].logits is not None and len(outputs[0].logits) else None
-    return base_rollout.RolloutOutput(
-        text=list(chain(o.text for o in outputs)), logits=logits, tokens=list(chain(o.tokens for o in outputs)),
-        left_padded_prompt_tokens=np.concatenate([o.left_padded_prompt_tokens for o in outputs], axis=0),
-        logprobs=logprobs)
+    engine_model = self.rollout.model()
+    self._maybe_load_model_from_cpu(engine_model, Role.ROLLOUT)
+    try:
+      with self._perf.span("rollout") as span, \
+           self._perf_v2.span("rollout", tags={"role": Role.ROLLOUT.value, **(trace_tags or {})}) as span_v2:
+        parts = [self.rollout.generate(texts[sl], rc)
+                 for sl in rl_utils.chunk_slices_by_size(len(texts), micro_batch_size or len(texts))]
+        produced = [part.tokens for part in parts]
+        span.device_end(produced)
+        span_v2.async_end(produced)
+    finally:
+      self._maybe_offload_model_to_cpu(engine_model, Role.ROLLOUT)
+    return self._join_rollouts(parts)
 
   def per_token_logps(self, role: Role, prompt_tokens, completion_tokens, pad_id: int, eos_id: int,
                       micro_batch_size: Optional[int] = None, segment_ids=None, **kwargs):

@@ -125,100 +125,116 @@ class RLLearner(abc.ABC):
       self.rl_engine.buffer_metrics(info["log_metrics"], mode=mode)
     return info["rewards"]
 
+  # ---- the producer: dataloader micro-batches -> generated, scored, advantage-annotated examples ----
+  #
+  # Three small stages, each a generator over the previous one, run on the producer thread:
+  #   _tagged_micro_batches : pulls dataloader items (skipping what a restored run already consumed),
+  #                           repeats every prompt G times and stamps trajectory ids;
+  #   _service_batches      : groups them until a rollout/log-prob service batch is full, runs
+  #                           `_generate_and_compute_advantage` once per group and splits the result
+  #                           back into the original micro-batches;
+  #   _prepare_data         : decides WHEN results reach the trainer's queue (as they appear when rollout
+  #                           and trainer run on different devices, else after the whole mini-batch) and
+  #                           how often (`batch_repeat` passes, each freshly shuffled).
+  def _tagged_micro_batches(self, iterator: Iterator[TrainingInputT], sample_repeat: int, mode: Mode, limit: int,
+                            exhausted: List[bool]):
+    train = mode == Mode.TRAIN
+    if train and self._iter_steps < self._last_iter_step:
+      behind = self._last_iter_step - self._iter_steps
+      for _ in range(behind):            # a resumed run: these were trained on before the restart
+        next(iterator, None)
+      self._iter_steps = self._last_iter_step
+      log.info("resumed: skipped %d already-consumed micro-batches", behind)
+    taken = 0
+    while limit <= 0 or taken < limit:
+      with self.rl_engine.perf.span("data_loading"):
+        raw = next(iterator, None)
+      if raw is None:
+        exhausted[0] = True
+        return
+      n_prompts = len(raw["prompts"])
+      example = _repeat_tree(raw, sample_repeat)
+      if "trajectory_ids" in example:
+        raise ValueError("dataloader items must not carry 'trajectory_ids': the learner assigns them")
+      example["trajectory_ids"] = self._compute_trajectory_ids(
+          example, self._iter_steps if train else self._eval_iter_steps)
+      for tid in example["trajectory_ids"]:
+        self.rl_engine.buffer_metrics({"trajectory_ids": (tid, None)}, mode=mode)
+      yield example, n_prompts, n_prompts * sample_repeat
+      if train:
+        self._iter_steps += 1
+      else:
+        self._eval_iter_steps += 1
+      taken += 1
+
+  def _service_batches(self, tagged, target_prompts: int, mode: Mode, drop_tail=lambda: False):
+    group: List[TrainingInputT] = []
+    sizes: List[int] = []
+    prompts_in_group = 0
+
+    def flush():
+      if not group:
+        return []
+      whole = self._generate_and_compute_advantage(rl_utils.merge_micro_batches(group), mode)
+      bounds = np.cumsum([0] + sizes)
+      parts = [rl_utils.get_batch_slice(whole, slice(int(lo), int(hi))) for lo, hi in zip(bounds[:-1], bounds[1:])]
+      group.clear()
+      sizes.clear()
+      return parts
+
+    for example, n_prompts, n_rows in tagged:
+      group.append(example)
+      sizes.append(n_rows)
+      prompts_in_group += n_prompts
+      if prompts_in_group >= target_prompts:
+        prompts_in_group = 0
+        yield flush()
+    if drop_tail():            # the dataloader ran dry inside a counted request: the caller discards it anyway
+      return
+    rest = flush()             # a last, smaller service batch
+    if rest:
+      yield rest
+
   def _process_accumulated_batches(self, micro_batches: List[TrainingInputT], micro_batch_sizes: List[int],
                                    mode: Mode) -> List[Any]:
+    """One generate / advantage pass over several merged micro-batches, split back afterwards."""
     if not micro_batches:
       return []
-    merged = rl_utils.merge_micro_batches(micro_batches)
-    combined = self._generate_and_compute_advantage(merged, mode)
-    produced, off = [], 0
-    for n in micro_batch_sizes:
-      produced.append(rl_utils.get_batch_slice(combined, slice(off, off + n)))
-      off += n
-    return produced
+    whole = self._generate_and_compute_advantage(rl_utils.merge_micro_batches(micro_batches), mode)
+    bounds = np.cumsum([0] + list(micro_batch_sizes))
+    return [rl_utils.get_batch_slice(whole, slice(int(lo), int(hi))) for lo, hi in zip(bounds[:-1], bounds[1:])]
 
   def _prepare_data(self, iterator: Iterator[TrainingInputT], proceed_num_steps: int, sample_repeat: int,
                     batch_repeat: int, service_target_batch_size: int, data_queue, async_loading: bool = False,
                     mode: Mode = Mode.TRAIN) -> None:
-    """Merge -> repeat xG -> one large generate/advantage pass -> split -> enqueue (see module doc).
-    Always terminates the queue with `None`, also on errors."""
-    micro_batches: List[TrainingInputT] = []
-    micro_batch_sizes: List[int] = []
-    accumulated = consumed = 0
-    pending: List[Any] = []
+    """Fills `data_queue` with the examples of `proceed_num_steps` dataloader items (all of them when <= 0),
+    each as a one-element list, and always ends it with `None` - also when the producer fails, so the
+    consumer never waits forever. With a positive step count, a dataloader that runs dry first raises
+    StopIteration (the epoch is over; what was collected is dropped)."""
+    passes = 1 if mode == Mode.EVAL else batch_repeat
+    stream_out = async_loading and mode == Mode.TRAIN      # hand results over while later ones are generated
 
-    def enqueue(examples, repeats):
-      if repeats <= 0 or not examples:
-        return
-      for _ in range(repeats):
-        order = range(len(examples))
-        if self._data_shuffle_rng is not None:
-          order = self._data_shuffle_rng.permutation(len(examples))
-        for i in order:
-          data_queue.put([examples[i]])
+    def deliver(examples: List[Any]) -> None:
+      order: Iterable[int] = range(len(examples))
+      if self._data_shuffle_rng is not None:
+        order = self._data_shuffle_rng.permutation(len(examples))
+      for i in order:
+        data_queue.put([examples[i]])
 
-    def enqueue_or_buffer(produced):
-      if not produced:
-        return
-      if async_loading:
-        enqueue(produced, 1)
-      if not async_loading or batch_repeat > 1:
-        pending.extend(produced)
-
-    def tail():
-      t = self._process_accumulated_batches(micro_batches, micro_batch_sizes, mode)
-      micro_batches.clear()
-      micro_batch_sizes.clear()
-      repeats = 1 if mode == Mode.EVAL else batch_repeat
-      if mode == Mode.EVAL or not async_loading:
-        pending.extend(t)
-        enqueue(pending, repeats)
-        pending.clear()
-        return
-      enqueue_or_buffer(t)
-      if pending:
-        enqueue(pending, repeats - 1)
-        pending.clear()
-
+    exhausted = [False]
     try:
-      while True:
-        while mode == Mode.TRAIN and self._iter_steps < self._last_iter_step:
-          next(iterator)          # resume: skip what a restored run already consumed
-          self._iter_steps += 1
-          if self._iter_steps == self._last_iter_step:
-            log.info("Fast forwarded %d micro-batches.", self._iter_steps)
-        with self.rl_engine.perf.span("data_loading"):
-          example = next(iterator)
-          cur = len(example["prompts"])
-        micro_batch_sizes.append(cur * sample_repeat)
-        accumulated += cur
-        consumed += 1
-        example = _repeat_tree(example, sample_repeat)
-        micro_batches.append(example)
-        tids = self._compute_trajectory_ids(example, self._iter_steps if mode == Mode.TRAIN else self._eval_iter_steps)
-        assert "trajectory_ids" not in example
-        example["trajectory_ids"] = tids
-        for t in tids:
-          self.rl_engine.buffer_metrics({"trajectory_ids": (t, None)}, mode=mode)
-        produced = []
-        if accumulated >= service_target_batch_size:
-          produced = self._process_accumulated_batches(micro_batches, micro_batch_sizes, mode)
-          micro_batches.clear()
-          micro_batch_sizes.clear()
-          accumulated = 0
-        enqueue_or_buffer(produced)
-        if mode == Mode.TRAIN:
-          self._iter_steps += 1
-        else:
-          self._eval_iter_steps += 1
-        if proceed_num_steps > 0 and consumed == proceed_num_steps:
-          tail()
-          return
-    except StopIteration:
-      if proceed_num_steps > 0:
-        raise
-      tail()
-      return
+      kept: List[Any] = []
+      tagged = self._tagged_micro_batches(iterator, sample_repeat, mode, proceed_num_steps, exhausted)
+      for produced in self._service_batches(tagged, service_target_batch_size, mode,
+                                            drop_tail=lambda: exhausted[0] and proceed_num_steps > 0):
+        if stream_out:
+          deliver(produced)
+        if not stream_out or passes > 1:
+          kept.extend(produced)
+      if exhausted[0] and proceed_num_steps > 0:
+        raise StopIteration
+      for _ in range(passes - 1 if stream_out else passes):
+        deliver(kept)
     finally:
       data_queue.put(None)
 
