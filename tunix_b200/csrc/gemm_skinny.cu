@@ -326,8 +326,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       const int n = slab * BMW + col;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
       const int par = round & 1;
-      if (!mine) {
-        // my accumulator row belongs to another CTA's columns: add it into that CTA's buffer
+      // tcgen05.ld is a warp-wide (.aligned) instruction: every branch that contains one is taken by whole warps.
+      // A warp whose 32 columns belong to two owners (cluster sizes that do not divide 32 columns evenly) therefore
+      // runs both phases, each lane acting only in the phase that matches its column.
+      const bool warp_sends = !__all_sync(0xffffffffu, mine);
+      const bool warp_finishes = __any_sync(0xffffffffu, mine);
+      if (warp_sends) {
+        // accumulator rows of columns that another CTA finishes: add them into that CTA's buffer
         const uint32_t dst = map_to_cta(smem_u32(redbuf + par * C::kAccCols * rows_max + (col - own_lo)), owner);
 #pragma unroll 1
         for (int c = 0; c < C::kAccCols; c += 16) {
@@ -335,11 +340,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           uint32_t r[16];
           tmem_ld_32x32b_x16(taddr + c, r);
           tmem_ld_wait();
+          if (!mine) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) red_add_dsmem(dst + (c + e) * rows_max * 4, __uint_as_float(r[e]));
+            for (int e = 0; e < 16; ++e) red_add_dsmem(dst + (c + e) * rows_max * 4, __uint_as_float(r[e]));
+          }
         }
-        mbar_arrive_cluster(map_to_cta(bar_red + 8 * par, owner));     // release: the adds above are visible to the owner
-      } else {
+        if (!mine) mbar_arrive_cluster(map_to_cta(bar_red + 8 * par, owner));   // release: the adds are visible to the owner
+      }
+      if (warp_finishes) {
         if (S > 1 && !mbar_wait_cluster(bar_red + 8 * par, (round >> 1) & 1, abort_flag))
           atomicOr(p.status, kStatusWaitTimeoutEpilogue);
         float* mybuf = redbuf + par * C::kAccCols * rows_max + (col - own_lo);
@@ -349,19 +357,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           tmem_ld_32x32b_x16(taddr + c, rg);
           if (GLU) tmem_ld_32x32b_x16(taddr + BNX + c, ru);
           tmem_ld_wait();
+          if (mine) {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int j = c + e;
-            float a = __uint_as_float(rg[e]), u = GLU ? __uint_as_float(ru[e]) : 0.f;
-            if (S > 1) {
-              a += mybuf[j * rows_max];
-              mybuf[j * rows_max] = 0.f;       // clean for the round after next, which reuses this parity
-              if (GLU) {
-                u += mybuf[(BNX + j) * rows_max];
-                mybuf[(BNX + j) * rows_max] = 0.f;
+            for (int e = 0; e < 16; ++e) {
+              const int j = c + e;
+              float a = __uint_as_float(rg[e]), u = GLU ? __uint_as_float(ru[e]) : 0.f;
+              if (S > 1) {
+                a += mybuf[j * rows_max];
+                mybuf[j * rows_max] = 0.f;       // clean for the round after next, which reuses this parity
+                if (GLU) {
+                  u += mybuf[(BNX + j) * rows_max];
+                  mybuf[(BNX + j) * rows_max] = 0.f;
+                }
               }
+              if (j < p.Mx && n < p.Nw) emit(p, part_self, j, n, activate<GLU>(p, a, u));
             }
-            if (j < p.Mx && n < p.Nw) emit(p, part_self, j, n, activate<GLU>(p, a, u));
           }
         }
       }
