@@ -55,6 +55,9 @@ def parse_args():
   ap.add_argument("--grpo-new-tokens", type=int, default=768)
   ap.add_argument("--grpo-train-micro", type=int, default=1, help="prompts (x generations) per training micro-step")
   ap.add_argument("--grpo-rollout-batch", type=int, default=512, help="sequences decoded together per rank")
+  ap.add_argument("--rollout-tp", type=int, default=1,
+                  help="grpo: tensor-parallel degree of the rollout engine (rollout data parallelism = GPUs / this); the "
+                       "trainer's weights are re-sharded into the rollout layout every step")
   return ap.parse_args()
 
 

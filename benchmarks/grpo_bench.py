@@ -88,8 +88,13 @@ def run(args, ClockSampler) -> None:
                         eval_every_n_steps=10**9, max_steps=steps_total, pbar_description=None, max_grad_norm=1.0,
                         mini_batch_size=per_rank, train_micro_batch_size=args.grpo_train_micro,
                         rollout_micro_batch_size=per_rank, compute_logps_micro_batch_size=args.grpo_train_micro)
+  tp = max(1, int(getattr(args, "rollout_tp", 1)))
+  if world % tp:
+    raise SystemExit(f"--rollout-tp {tp} does not divide {world} GPUs")
+  # the ranks of a tensor-parallel rollout group decode one batch together: they must draw with one seed
   rc = RolloutConfig(max_tokens_to_generate=NEW, max_prompt_length=PL, kv_cache_size=PL + NEW + 16,
-                     temperature=1.0, top_p=1.0, seed=1000 + rank, return_logprobs=True)
+                     temperature=1.0, top_p=1.0, seed=1000 + rank // tp, return_logprobs=True,
+                     tensor_parallel_size=tp if tp > 1 else -1, data_parallel_size=world // tp if tp > 1 else -1)
   cc = ClusterConfig(role_to_mesh={Role.ACTOR: mesh, Role.REFERENCE: mesh, Role.ROLLOUT: mesh},
                      rollout_engine="native", training_config=tc, rollout_config=rc)
   native_rollout.DEFAULT_MAX_BATCH = args.grpo_rollout_batch
@@ -172,9 +177,13 @@ def run(args, ClockSampler) -> None:
         "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights, reward = share of ids = 0 mod 7",
         "impl": "ours",
         "config": {"model": model_name, "layers": cfg.num_layers, "prompts": P, "generations": G, "prompt_len": PL,
-                   "max_new_tokens": NEW, "parallelism": f"rollout dp{world} on the trainer's replica, trainer fsdp{world}",
+                   "max_new_tokens": NEW,
+                   "parallelism": (f"rollout tp{tp} x dp{world // tp} (in-kernel all-reduce exits), trainer fsdp{world}"
+                                   if tp > 1 else f"rollout dp{world} on the trainer's replica, trainer fsdp{world}"),
                    "train_micro_prompts": args.grpo_train_micro, "rollout_batch": args.grpo_rollout_batch,
-                   "weight_sync": "none needed: rollout reads the trainer's bf16 replica in place",
+                   "weight_sync": ("every step: re-sharding copy kernel, flat trainer store -> tensor-parallel slice"
+                                   if tp > 1 else "none needed: rollout reads the trainer's bf16 replica in place"),
+                   "weight_sync_ms": cluster.weight_sync_ms(),
                    "l2": "inputs larger than L2: every decode step streams the 16 GB weights and the KV cache"},
         "generated_tokens_per_step": gen / args.steps,
         "phases_rank0": {"rollout_s_per_step": (gen_counter["rollout_s"] - marks["rollout0"]) / args.steps,

@@ -29,6 +29,8 @@ def main(argv=None):
   ap.add_argument("--copy-gbs", type=float, default=6549.4)
   ap.add_argument("--graph", action="store_true")
   ap.add_argument("--only", default="")
+  ap.add_argument("--trace", action="store_true",
+                  help="print the kernel's own phase timeline (median over CTAs, microseconds since the first CTA start)")
   a = ap.parse_args(argv)
   flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
 
@@ -85,6 +87,28 @@ def main(argv=None):
       row = {"rows": M, "shape": name, "N": N, "K": K, "weight_mb": round(wbytes / 2 ** 20, 1)}
       t = timeit(lambda: kernels.gemm_skinny(x, w(), glu="silu" if glu else None))
       row["skinny_us"] = round(t, 1)
+      if a.trace:
+        import ctypes
+        lib = _lib.require()
+        lib.tx_gemm_skinny_trace.argtypes = [ctypes.c_void_p]
+        lib.tx_gemm_skinny_trace.restype = None
+        buf = torch.zeros(8 * 160 * 16, dtype=torch.int64, device="cuda")
+        flush.zero_()
+        lib.tx_gemm_skinny_trace(buf.data_ptr())
+        kernels.gemm_skinny(x, w(), glu="silu" if glu else None)
+        torch.cuda.synchronize()
+        lib.tx_gemm_skinny_trace(None)
+        tr = buf.view(-1, 16).cpu()
+        tr = tr[tr[:, 0] > 0]
+        t0 = int(tr[:, 0].min())
+        names = ["start", "setup_done", "first_load", "ring_filled", "loads_issued", "first_tile", "mma_first_slab",
+                 "mma_last_slab", "acc_ready", "slab_written", "roles_done", "exit"]
+        med = {n: round(float((tr[:, i][tr[:, i] > 0] - t0).float().median()) / 1e3, 2) for i, n in enumerate(names)
+               if (tr[:, i] > 0).any()}
+        mx = {n: round(float((tr[:, i][tr[:, i] > 0] - t0).float().max()) / 1e3, 2) for i, n in enumerate(names)
+              if (tr[:, i] > 0).any()}
+        row["trace"] = {"ctas": int(tr.shape[0]), "cluster": int(tr[0, 12]), "stages": int(tr[0, 13]), "median_us": med,
+                        "max_us": mx}
       row["skinny_frac_of_copy"] = round(wbytes / (t * 1e-6) / 1e9 / a.copy_gbs, 3)
       if M % 8 == 0:
         if glu:

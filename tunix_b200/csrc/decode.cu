@@ -237,7 +237,7 @@ __device__ __forceinline__ float load_logit<__nv_bfloat16>(const __nv_bfloat16* 
   return __bfloat162float(p[i]);
 }
 
-constexpr int kSampleThreads = 256;
+constexpr int kSampleThreads = 1024;   // one CTA per row: the row (up to ~150k logits) is scanned once, 4 logits per thread and step
 
 template <typename T>
 __global__ void __launch_bounds__(kSampleThreads)

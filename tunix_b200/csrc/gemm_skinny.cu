@@ -11,10 +11,11 @@
 //  * split-K inside a thread-block cluster: decode weights have 32-200 slabs, fewer than the 148
 //    SMs, so the K range of a slab is cut over the S CTAs of a cluster (S = 1..8 chosen per shape
 //    so that slabs x S fills the machine). The partial accumulators never touch global memory:
-//    each CTA owns 128/S of the slab's output columns, the others add their share of those
-//    columns into the owner's shared memory with `red.shared::cluster` (distributed shared
-//    memory), an mbarrier in the owner's shared memory counts the arrivals, and the owner adds
-//    its own accumulator and runs the epilogue. One launch, no workspace, no memset, no fix-up pass.
+//    each CTA owns 128/S of the slab's output columns, the others store their share of those
+//    columns into a slot of the owner's shared memory (16-byte `st.shared::cluster` stores through
+//    distributed shared memory), an mbarrier in the owner's shared memory counts the arrivals, and
+//    the owner adds the S - 1 slots to its own accumulator in a fixed order and runs the epilogue.
+//    One launch, no workspace, no atomics, no memset, no fix-up pass.
 //  * deep TMA ring (3-12 stages of 16-32 KB of W), single-thread MMA issue, TMEM double-buffered
 //    accumulators, four epilogue warps; clusters walk slabs persistently.
 //
@@ -71,6 +72,8 @@ struct SkinnyParams {
   int* epoch;                      // device call counter (same value on every rank)
   int* done;                       // CTAs of this launch that have finished
   unsigned long long wait_ns;
+  // optional timeline: 16 globaltimer stamps per CTA (null = off); see tx_gemm_skinny_trace
+  unsigned long long* trace;
 };
 
 template <int BNX, bool GLU>
@@ -84,13 +87,16 @@ struct SCfg {
   static constexpr int kTmemCols = 2 * kAccCols < 32 ? 32 : 2 * kAccCols;
 };
 
-// Reduction buffers of one CTA for a cluster of `split`: 2 parities x [kAccCols][rows_max] floats.
-__host__ __device__ inline int rows_max_of(int split) { return (BMW + split - 1) / split; }
+// Exchange buffers of one CTA for a cluster of `split`: 2 parities x (split - 1) source slots x
+// [rows_max][acc_cols + 4] floats (rows padded by 16 bytes so that a warp's 16-byte stores spread over the banks).
+// A slab's 128 columns are owned in chunks of 8 (16 bytes of bf16 output): 16 chunks dealt out over the cluster.
+__host__ __device__ inline int col_lo(int o, int split) { return 8 * ((16 * o + split - 1) / split); }
+__host__ __device__ inline int rows_max_of(int split) { return 8 * ((16 + split - 1) / split); }
+__host__ __device__ inline int slot_floats_of(int split, int acc_cols) { return rows_max_of(split) * (acc_cols + 4); }
 __host__ __device__ inline int red_bytes_of(int split, int acc_cols) {
-  return split > 1 ? ((2 * acc_cols * rows_max_of(split) * 4 + 15) & ~15) : 0;
+  return split > 1 ? 2 * (split - 1) * slot_floats_of(split, acc_cols) * 4 : 0;
 }
-// First slab column owned by CTA `o` of the cluster; columns [col_lo(o), col_lo(o + 1)) are its.
-__host__ __device__ inline int col_lo(int o, int split) { return (o * BMW + split - 1) / split; }
+// Columns [col_lo(o), col_lo(o + 1)) of a slab are finished by CTA `o` of the cluster.
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh_f(float x) {
@@ -113,9 +119,11 @@ __device__ __forceinline__ bool bar_epilogue_all(bool pred) {
       : "memory");
   return r != 0;
 }
-__device__ __forceinline__ float ld_sys_f32(const float* p) {
-  float v;
-  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+// System-scope 16-byte read of a peer's partial sums.
+__device__ __forceinline__ float4 ld_sys_f32x4(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p)
+               : "memory");
   return v;
 }
 __device__ __forceinline__ void st_release_sys(int* addr, int v) {
@@ -126,9 +134,10 @@ __device__ __forceinline__ int ld_acquire_sys(const int* addr) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
   return v;
 }
-// Adds into the shared memory of another CTA of the cluster (address from map_to_cta).
-__device__ __forceinline__ void red_add_dsmem(uint32_t cluster_addr, float v) {
-  asm volatile("red.shared::cluster.add.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+// 16-byte store into the shared memory of another CTA of the cluster (address from map_to_cta).
+__device__ __forceinline__ void st_dsmem_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -157,6 +166,11 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   }
 }
 
+// Records a phase boundary of this CTA when a trace buffer is attached.
+__device__ __forceinline__ void stamp(const SkinnyParams& p, int slot) {
+  if (p.trace) p.trace[blockIdx.x * 16 + slot] = globaltimer_ns();
+}
+
 // Final value of one output element from its accumulated product(s).
 template <bool GLU>
 __device__ __forceinline__ float activate(const SkinnyParams& p, float a, float u) {
@@ -166,17 +180,6 @@ __device__ __forceinline__ float activate(const SkinnyParams& p, float a, float 
     a = (p.glu == 2 ? gelu_tanh_f(a) : silu_f(a)) * u;
   }
   return a;
-}
-
-// Writes one finished value: into this rank's partial buffer on a tensor-parallel exit, else to C.
-__device__ __forceinline__ void emit(const SkinnyParams& p, float* part_self, int j, int n, float v) {
-  if (p.n_ranks > 1) {
-    part_self[static_cast<long long>(j) * p.Nw + n] = v;
-    return;
-  }
-  if (p.bias) v += __bfloat162float(p.bias[n]);
-  if (p.residual) v += __bfloat162float(p.residual[static_cast<long long>(j) * p.ldr + n]);
-  p.C[static_cast<long long>(j) * p.ldc + n] = __float2bfloat16_rn(v);
 }
 
 template <int BNX, bool GLU>
@@ -192,7 +195,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   // layout: [stages x stage][reduction buffers, 2 parities][barriers and flags]
   float* redbuf = reinterpret_cast<float*>(smem_gen + stages * C::kStageBytes);
   const int red_bytes = red_bytes_of(S, C::kAccCols);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + stages * C::kStageBytes + red_bytes);
+  // output staging: [BNX rows][128 columns] fp32, so that C is written in whole 16-byte pieces of a row
+  float* stg = reinterpret_cast<float*>(smem_gen + stages * C::kStageBytes + red_bytes);
+  constexpr int kStgBytes = BNX * BMW * 4;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + stages * C::kStageBytes + red_bytes + kStgBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * kMaxStages;
   const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;
@@ -216,6 +222,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int epoch = p.n_ranks > 1 ? (*reinterpret_cast<volatile int*>(p.epoch) + 1) : 0;
 
   if (threadIdx.x == 0) {
+    stamp(p, 0);                      // CTA started
     *abort_flag = 0;
     *n_my_blocks = 0;
     for (int s = 0; s < stages; ++s) {
@@ -230,18 +237,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     mbar_init(bar_emit, S);
     mbar_fence_init();
   }
-  if (S > 1) {
-    for (int i = threadIdx.x; i < red_bytes / 4; i += NUM_THREADS) redbuf[i] = 0.f;
-  }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
-  if (S > 1) cluster_sync_all();      // everybody's barriers and zeroed buffers exist before anyone adds into them
+  if (S > 1) cluster_sync_all();      // everybody's barriers exist before anyone arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) stamp(p, 1);    // set-up done (barriers, TMEM, cluster rendezvous)
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -266,8 +271,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (GLU) tma_load_2d(sa + C::kWBytes, &map_w2, kb * BK, slab * BMW, full);
           tma_load_2d(sa + C::kABytes, &map_x, kb * BK, 0, full);
           if (++stage == stages) { stage = 0; phase ^= 1; }
+          if (slab == cluster_id && kb == kb_lo) stamp(p, 2);                       // first load issued
+          if (slab == cluster_id && kb == kb_lo + stages - 1) stamp(p, 3);          // ring filled once
         }
       }
+      stamp(p, 4);                                                                  // all loads issued
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
@@ -290,6 +298,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             break;
           }
           tc_fence_after();
+          if (slab == cluster_id && kb == kb_lo) stamp(p, 5);                       // first tile arrived
           const uint32_t sa = smem_base + stage * C::kStageBytes;
           const uint32_t sx = sa + C::kABytes;
 #pragma unroll
@@ -305,14 +314,16 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (!ok) break;
         umma_commit(bar_tfull + 8 * acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        if (slab == cluster_id) stamp(p, 6);                                        // first slab: all MMAs issued
       }
+      stamp(p, 7);                                                                  // last slab: all MMAs issued
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;              // TMEM lane quarter this warp may access
     const int col = quarter * 32 + lane;       // slab column (TMEM lane) of this thread
     const bool leader = (warp == 2 && lane == 0);
-    const int owner = (col * S) >> 7;          // CTA of the cluster that finishes this column
+    const int owner = ((col >> 3) * S) >> 4;   // CTA of the cluster that finishes this column (8-column chunks)
     const bool mine = owner == crank;
     const int own_lo = col_lo(owner, S);
     float* part_self = p.n_ranks > 1 ? p.part[p.rank] + (epoch & 1) * p.part_stride : nullptr;
@@ -323,7 +334,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       if (!ok) atomicOr(p.status, kStatusWaitTimeoutEpilogue);
       if (!bar_epilogue_all(ok)) break;          // all four warps leave together
       tc_fence_after();
-      const int n = slab * BMW + col;
+      if (leader && round == 0) stamp(p, 8);     // first accumulator complete
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * C::kAccCols;
       const int par = round & 1;
       // tcgen05.ld is a warp-wide (.aligned) instruction: every branch that contains one is taken by whole warps.
@@ -331,26 +342,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       // runs both phases, each lane acting only in the phase that matches its column.
       const bool warp_sends = !__all_sync(0xffffffffu, mine);
       const bool warp_finishes = __any_sync(0xffffffffu, mine);
+      constexpr int kRow = C::kAccCols + 4;                       // floats per exchanged row
+      const int slot_floats = rows_max * kRow;
       if (warp_sends) {
-        // accumulator rows of columns that another CTA finishes: add them into that CTA's buffer
-        const uint32_t dst = map_to_cta(smem_u32(redbuf + par * C::kAccCols * rows_max + (col - own_lo)), owner);
+        // accumulator rows of columns that another CTA finishes: store them into my slot of that CTA's buffer
+        const int my_slot = crank < owner ? crank : crank - 1;
+        const uint32_t dst = map_to_cta(
+            smem_u32(redbuf + (par * (S - 1) + my_slot) * slot_floats + (col - own_lo) * kRow), owner);
 #pragma unroll 1
         for (int c = 0; c < C::kAccCols; c += 16) {
-          if ((c & (BNX - 1)) >= p.Mx) continue;     // rows of X beyond Mx are zero-filled: nothing to add
+          if ((c & (BNX - 1)) >= p.Mx) continue;     // rows of X beyond Mx are zero-filled: nothing to send
           uint32_t r[16];
           tmem_ld_32x32b_x16(taddr + c, r);
           tmem_ld_wait();
           if (!mine) {
 #pragma unroll
-            for (int e = 0; e < 16; ++e) red_add_dsmem(dst + (c + e) * rows_max * 4, __uint_as_float(r[e]));
+            for (int e = 0; e < 16; e += 4) st_dsmem_v4(dst + (c + e) * 4, r[e], r[e + 1], r[e + 2], r[e + 3]);
           }
         }
-        if (!mine) mbar_arrive_cluster(map_to_cta(bar_red + 8 * par, owner));   // release: the adds are visible to the owner
+        if (!mine) mbar_arrive_cluster(map_to_cta(bar_red + 8 * par, owner));   // release: the stores are visible to the owner
       }
       if (warp_finishes) {
-        if (S > 1 && !mbar_wait_cluster(bar_red + 8 * par, (round >> 1) & 1, abort_flag))
-          atomicOr(p.status, kStatusWaitTimeoutEpilogue);
-        float* mybuf = redbuf + par * C::kAccCols * rows_max + (col - own_lo);
+        if (S > 1) {
+          // one lane polls (an acquire at cluster scope per poll is not cheap), the warp follows
+          if (lane == 0 && !mbar_wait_cluster(bar_red + 8 * par, (round >> 1) & 1, abort_flag))
+            atomicOr(p.status, kStatusWaitTimeoutEpilogue);
+          __syncwarp();
+          asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        }
+        const float* mybuf = redbuf + par * (S - 1) * slot_floats + (col - own_lo) * kRow;
 #pragma unroll 1
         for (int c = 0; c < BNX && c < p.Mx; c += 16) {
           uint32_t rg[16], ru[16];
@@ -358,26 +378,69 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (GLU) tmem_ld_32x32b_x16(taddr + BNX + c, ru);
           tmem_ld_wait();
           if (mine) {
+            float a[16], u[16];
 #pragma unroll
-            for (int e = 0; e < 16; ++e) {
-              const int j = c + e;
-              float a = __uint_as_float(rg[e]), u = GLU ? __uint_as_float(ru[e]) : 0.f;
-              if (S > 1) {
-                a += mybuf[j * rows_max];
-                mybuf[j * rows_max] = 0.f;       // clean for the round after next, which reuses this parity
+            for (int e = 0; e < 16; ++e) { a[e] = __uint_as_float(rg[e]); u[e] = GLU ? __uint_as_float(ru[e]) : 0.f; }
+            for (int sl = 0; sl < S - 1; ++sl) {               // slot order = rank order: a fixed summation order
+              const float4* ga = reinterpret_cast<const float4*>(mybuf + sl * slot_floats + c);
+              const float4* gu = reinterpret_cast<const float4*>(mybuf + sl * slot_floats + BNX + c);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 v = ga[q];
+                a[4 * q] += v.x; a[4 * q + 1] += v.y; a[4 * q + 2] += v.z; a[4 * q + 3] += v.w;
                 if (GLU) {
-                  u += mybuf[(BNX + j) * rows_max];
-                  mybuf[(BNX + j) * rows_max] = 0.f;
+                  const float4 w = gu[q];
+                  u[4 * q] += w.x; u[4 * q + 1] += w.y; u[4 * q + 2] += w.z; u[4 * q + 3] += w.w;
                 }
               }
-              if (j < p.Mx && n < p.Nw) emit(p, part_self, j, n, activate<GLU>(p, a, u));
             }
+#pragma unroll
+            for (int e = 0; e < 16; ++e) stg[(c + e) * BMW + col] = activate<GLU>(p, a[e], u[e]);
           }
         }
       }
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      // ---- copy-out: all four warps move this CTA's columns of the staged tile, 8 outputs (16 bytes) at a time
+      bar_epilogue();
+      {
+        const int nch = (my_hi - my_lo) >> 3;            // 8-column chunks this CTA finishes
+        const int tid = (warp - 2) * 32 + lane;
+        for (int idx = tid; idx < p.Mx * nch; idx += 128) {
+          const int j = idx / nch, ch = idx - j * nch;
+          const int cl = my_lo + ch * 8;                 // column within the slab
+          const int n8 = slab * BMW + cl;
+          if (n8 >= p.Nw) continue;                      // Nw is a multiple of 8: a chunk is inside or outside
+          const float4 v0 = *reinterpret_cast<const float4*>(stg + j * BMW + cl);
+          const float4 v1 = *reinterpret_cast<const float4*>(stg + j * BMW + cl + 4);
+          float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+          if (p.n_ranks > 1) {
+            float* dst = part_self + static_cast<long long>(j) * p.Nw + n8;
+            *reinterpret_cast<float4*>(dst) = v0;
+            *reinterpret_cast<float4*>(dst + 4) = v1;
+            continue;
+          }
+          if (p.bias) {
+            const uint4 b = *reinterpret_cast<const uint4*>(p.bias + n8);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float2 t = __bfloat1622float2(b2[q]); f[2 * q] += t.x; f[2 * q + 1] += t.y; }
+          }
+          if (p.residual) {
+            const uint4 r = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(j) * p.ldr + n8);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float2 t = __bfloat1622float2(r2[q]); f[2 * q] += t.x; f[2 * q + 1] += t.y; }
+          }
+          uint4 o;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+          *reinterpret_cast<uint4*>(p.C + static_cast<long long>(j) * p.ldc + n8) = o;
+        }
+      }
+      if (leader && round == 0) stamp(p, 9);     // first slab written
 
       if (p.n_ranks > 1) {
         // this CTA's columns of the block are in the rank's partial buffer; once all CTAs of the cluster say
@@ -418,31 +481,48 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           }
         }
         if (!bar_epilogue_all(*abort_flag == 0)) break;
-        const int n = blk * BMW + col;
-        if (mine && n < p.Nw) {
-          const long long off = (epoch & 1) * p.part_stride + n;
-          const float bias = p.bias ? __bfloat162float(p.bias[n]) : 0.f;
-          for (int j0 = 0; j0 < p.Mx; j0 += 8) {
-            float v[8][kMaxRanks];
+        // this CTA's columns of the block, 8 outputs at a time: sum the ranks' partials in rank order (every rank
+        // computes the same bits), add bias and residual, round once
+        const int nch = (my_hi - my_lo) >> 3;
+        const int tid = (warp - 2) * 32 + lane;
+        for (int idx = tid; idx < p.Mx * nch; idx += 128) {
+          const int j = idx / nch, ch = idx - j * nch;
+          const int n8 = blk * BMW + my_lo + ch * 8;
+          if (n8 >= p.Nw) continue;
+          const long long off = (epoch & 1) * p.part_stride + static_cast<long long>(j) * p.Nw + n8;
+          float4 v[kMaxRanks][2];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-#pragma unroll
-              for (int r = 0; r < kMaxRanks; ++r)
-                if (r < p.n_ranks && j0 + e < p.Mx)
-                  v[e][r] = ld_sys_f32(p.part[r] + off + static_cast<long long>(j0 + e) * p.Nw);
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int j = j0 + e;
-              if (j >= p.Mx) continue;
-              float s = bias;
-#pragma unroll
-              for (int r = 0; r < kMaxRanks; ++r)       // rank order: every rank computes the same bits
-                if (r < p.n_ranks) s += v[e][r];
-              if (p.residual) s += __bfloat162float(p.residual[static_cast<long long>(j) * p.ldr + n]);
-              p.C[static_cast<long long>(j) * p.ldc + n] = __float2bfloat16_rn(s);
+          for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.n_ranks) {
+              v[r][0] = ld_sys_f32x4(p.part[r] + off);
+              v[r][1] = ld_sys_f32x4(p.part[r] + off + 4);
             }
           }
+          float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int r = 0; r < kMaxRanks; ++r) {
+            if (r < p.n_ranks) {
+              f[0] += v[r][0].x; f[1] += v[r][0].y; f[2] += v[r][0].z; f[3] += v[r][0].w;
+              f[4] += v[r][1].x; f[5] += v[r][1].y; f[6] += v[r][1].z; f[7] += v[r][1].w;
+            }
+          }
+          if (p.bias) {
+            const uint4 bb = *reinterpret_cast<const uint4*>(p.bias + n8);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bb);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float2 t = __bfloat1622float2(b2[q]); f[2 * q] += t.x; f[2 * q + 1] += t.y; }
+          }
+          if (p.residual) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(j) * p.ldr + n8);
+            const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rr);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { const float2 t = __bfloat1622float2(r2[q]); f[2 * q] += t.x; f[2 * q + 1] += t.y; }
+          }
+          uint4 o;
+          __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+          *reinterpret_cast<uint4*>(p.C + static_cast<long long>(j) * p.ldc + n8) = o;
         }
       }
     }
@@ -451,7 +531,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (*abort_flag) __nanosleep(200000);
   tc_fence_before();
   __syncthreads();
-  if (S > 1) cluster_sync_all();        // nobody leaves while a peer may still add into its shared memory
+  if (threadIdx.x == 0) stamp(p, 10);   // all roles done
+  // No rendezvous at exit: peers store into this CTA's shared memory only before they arrive on its exchange
+  // barrier, and this CTA has waited for every such arrival before it got here.
+  if (threadIdx.x == 0) { stamp(p, 11); if (p.trace) { p.trace[blockIdx.x * 16 + 12] = S; p.trace[blockIdx.x * 16 + 13] = stages; } }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
@@ -492,11 +575,12 @@ int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, l
   int sms = txh::sm_count();
   if (max_ctas > 0 && max_ctas < sms) sms = max_ctas;
 
-  auto smem_for = [&](int split, int stages) { return stages * C::kStageBytes + red_bytes_of(split, C::kAccCols) + 1024 + 512; };
+  constexpr int kStg = BNX * BMW * 4;       // output staging tile
+  auto smem_for = [&](int split, int stages) { return stages * C::kStageBytes + red_bytes_of(split, C::kAccCols) + kStg + 1024 + 512; };
   auto probe = [&](int split) {
     if (fit.known[split]) return;
     fit.known[split] = true;
-    int stages = (kSmemLimit - red_bytes_of(split, C::kAccCols) - 1024 - 512) / C::kStageBytes;
+    int stages = (kSmemLimit - red_bytes_of(split, C::kAccCols) - kStg - 1024 - 512) / C::kStageBytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 3) return;                          // not worth it: max_clusters stays 0
     fit.stages[split] = stages;
@@ -518,7 +602,8 @@ int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, l
   };
 
   // Pick the split whose schedule streams the weight in the fewest k-block steps: rounds x k-blocks per CTA,
-  // plus a small charge per round for the exchange of partial sums.
+  // plus a charge per round for pipeline start-up and, when K is split, the exchange of partial sums (measured:
+  // about 1.3 us resp. 3.4 us, i.e. 4 resp. 10 k-block times).
   int best_s = 1, best_nc = 1;
   long long best_cost = -1;
   const int max_split = deterministic ? 1 : 8;
@@ -530,7 +615,7 @@ int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, l
     if (nc < 1) continue;
     if (nc > slabs) nc = slabs;
     const int rounds = (slabs + nc - 1) / nc;
-    const long long cost = static_cast<long long>(rounds) * ((num_kb + s - 1) / s + (s > 1 ? 3 : 0));
+    const long long cost = static_cast<long long>(rounds) * ((num_kb + s - 1) / s + (s > 1 ? 10 : 4));
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; best_nc = nc; }
   }
   if (best_cost < 0) return 301;
@@ -580,6 +665,13 @@ int dispatch_bnx(int Mx, const void* X, const void* W, const SkinnyParams& p, lo
 
 extern "C" int tx_gemm_skinny_flag_blocks() { return kMaxFlagBlocks; }
 
+// Debug aid: attaches (or, with null, detaches) a device buffer of 16 x 64-bit words per CTA (room for 8 * SM count
+// CTAs) that later launches fill with %globaltimer stamps of their phase boundaries: 0 start, 1 set-up done, 2 first
+// load issued, 3 ring filled, 4 all loads issued, 5 first tile arrived, 6 / 7 MMAs of the first / last slab issued,
+// 8 first accumulator complete, 9 first slab written, 10 roles done, 11 exit; 12 cluster size, 13 ring depth.
+static unsigned long long* g_trace = nullptr;
+extern "C" void tx_gemm_skinny_trace(unsigned long long* buf) { g_trace = buf; }
+
 // C[Mx, Nw] = epilogue(alpha * X W^T); see the top of this file.
 //   X [Mx, K] bf16 (row stride ldx), W [Nw, K] bf16 - with glu != 0, [2 Nw, K]: gate rows then up rows - (row
 //   stride ldw), C [Mx, Nw] bf16 (row stride ldc). Bases 16-byte aligned, ldx / ldw multiples of 8, Mx <= 128.
@@ -595,8 +687,11 @@ extern "C" int tx_gemm_skinny(const void* X, const void* W, void* C, const void*
                               void* const* part, void* const* flags, long long part_stride, int* epoch, int* done,
                               long long wait_ms, cudaStream_t stream) {
   if (Mx <= 0 || Mx > 128 || Nw <= 0 || K <= 0 || glu < 0 || glu > 2) return 1;
-  if ((ldx & 7) || (ldw & 7) || !status) return 2;
-  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return 3;
+  if ((ldx & 7) || (ldw & 7) || (ldc & 7) || (Nw & 7) || (residual && (ldr & 7)) || !status) return 2;
+  if ((reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(residual) & 15) ||
+      (reinterpret_cast<uintptr_t>(bias) & 15))
+    return 3;
   if (glu && ((static_cast<long long>(Nw) * ldw * 2) & 15)) return 3;
   if (n_ranks > 1) {
     if (glu || n_ranks > kMaxRanks || rank < 0 || rank >= n_ranks || !part || !flags || !epoch || !done) return 4;
@@ -612,6 +707,7 @@ extern "C" int tx_gemm_skinny(const void* X, const void* W, void* C, const void*
   p.alpha = alpha;
   p.glu = glu;
   p.status = status;
+  p.trace = g_trace;
   p.n_ranks = n_ranks > 1 ? n_ranks : 1;
   p.rank = rank;
   if (n_ranks > 1) {

@@ -96,6 +96,9 @@ class GRPOLearner(rl_learner.RLLearner):
                             pad_id=self.rl_engine.rollout.pad_id(), eos_id=self.rl_engine.rollout.eos_id(),
                             compute_logps_chunk_size=tc.compute_logps_chunk_size)
 
+    if self.algo_config.use_rollout_logps and self.algo_config.sampler_is != "token":
+      # the old-policy log-probs come from the sampler: nothing reads the start-of-step snapshot of the weights
+      self.rl_engine.snapshot_anchor_on_sync = False
     tr = self.rl_engine.actor_trainer
     tr.with_loss_fn(loss_fn, has_aux=True)
     tr.with_gen_model_input_fn(lambda x: {"train_example": x, "algo_config": self.algo_config})

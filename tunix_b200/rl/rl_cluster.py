@@ -62,6 +62,9 @@ class RLEngine:
     self.perf_config = perf_config
     self.r2m = cluster_config.role_to_mesh
     self._anchor_policy_state: Optional[Dict[str, torch.Tensor]] = None
+    # `sync_weights` also copies the start-of-step weights to pinned host memory for learners that score with the
+    # old policy (`get_actor_per_token_logps`); a learner that never does may switch the copy off
+    self.snapshot_anchor_on_sync = True
     if cluster_config.rollout_config is None:
       raise ValueError("`cluster_config.rollout_config` cannot be None.")
     if isinstance(cluster_config.rollout_config, dict) and not cluster_config.rollout_config.get(Mode.TRAIN):
@@ -113,9 +116,26 @@ class RLEngine:
       model.to(data_type)
     return model
 
+  def _shard_actor(self):
+    """An actor mesh of several ranks trains data-parallel with sharded optimizer state: parameters move into a
+    flat store whose bf16 replica stays resident on every rank. A rollout engine that shares the module reads each
+    update in place (`sync_weights` has nothing to copy); a tensor-parallel rollout re-shards from the store."""
+    actor_mesh = self.r2m.get(Role.ACTOR)
+    if actor_mesh is None or getattr(actor_mesh, "size", 1) <= 1 or not getattr(actor_mesh, "contains_me", True):
+      return None
+    import torch.distributed as torch_dist
+    if not (torch_dist.is_available() and torch_dist.is_initialized()):
+      return None
+    from ..dist import fsdp
+    axis = "fsdp" if "fsdp" in actor_mesh.axis_names else actor_mesh.axis_names[0]
+    if not hasattr(self.train_actor, "flat_store"):
+      fsdp.shard_model(self.train_actor, actor_mesh, axis)
+    return fsdp.GradSync(self.train_actor, actor_mesh, axis)
+
   def _init_engine(self):
     cfg = self.cluster_config
     rc = self.get_rollout_config(Mode.TRAIN)
+    actor_sync = self._shard_actor()          # before the rollout engine: it may slice the flat store
     mcfg = getattr(self.rollout_actor, "config", None)
     engine = cfg.rollout_engine
     if isinstance(engine, type) and issubclass(engine, base_rollout.BaseRollout):
@@ -164,19 +184,6 @@ class RLEngine:
     actor_cfg = copy.copy(tc)
     if root:
       actor_cfg.checkpoint_root_directory = f"{root}/actor"
-    # An actor mesh of several ranks trains data-parallel with sharded optimizer state: parameters move into
-    # a flat store whose bf16 replica stays resident on every rank, so a rollout engine that shares the module
-    # reads each update in place and `sync_weights` has nothing to copy.
-    actor_mesh = self.r2m.get(Role.ACTOR)
-    actor_sync = None
-    if actor_mesh is not None and getattr(actor_mesh, "size", 1) > 1 and getattr(actor_mesh, "contains_me", True):
-      import torch.distributed as torch_dist
-      if torch_dist.is_available() and torch_dist.is_initialized():
-        from ..dist import fsdp
-        axis = "fsdp" if "fsdp" in actor_mesh.axis_names else actor_mesh.axis_names[0]
-        if not hasattr(self.train_actor, "flat_store"):
-          fsdp.shard_model(self.train_actor, actor_mesh, axis)
-        actor_sync = fsdp.GradSync(self.train_actor, actor_mesh, axis)
     self._actor_trainer = rl_trainer.Trainer(
         model=self.train_actor, optimizer=tc.actor_optimizer, training_config=_as_training_config(actor_cfg),
         custom_checkpoint_metadata_fn=lambda: {
@@ -471,9 +478,15 @@ class RLEngine:
     lora = sft_utils.is_lora_enabled(model)
     params = {n: p for n, p in model.named_parameters() if (getattr(p, "is_lora", False) or not lora)}
     self.rollout.update_params(params, ("lora",) if lora else None)
-    self._snapshot_anchor(params)
+    if self.snapshot_anchor_on_sync:
+      self._snapshot_anchor(params)
     gc.collect()
     self.global_steps += 1
+
+  def weight_sync_ms(self) -> Optional[float]:
+    """Device time of the last trainer -> rollout transfer, when the rollout engine measures it."""
+    fn = getattr(self.rollout, "weight_sync_ms", None)
+    return fn() if fn is not None else None
 
   def _snapshot_anchor(self, params: Mapping[str, torch.Tensor]) -> None:
     """Copies the start-of-step weights to pinned host buffers that are allocated once and reused.
