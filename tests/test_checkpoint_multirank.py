@@ -28,7 +28,7 @@ def test_ranks_agree_on_saves_and_every_rank_gets_its_own_state_back(tmp_path):
   for r in (r0, r1):
     assert r["restored_step"] == 6 and r["count"] == r["count_saved"] == 6
     assert r["param_err"] == 0.0 and r["mu_err"] == 0.0 and r["master_err"] == 0.0 and r["local_err"] == 0.0
-    assert r["mu_norm"] > 0
+  assert max(r0["mu_norm"], r1["mu_norm"]) > 0       # (a rank's slices of this tiny model may be all padding)
   assert r0["expert_sig"] != r1["expert_sig"]       # each rank restored its own experts, not rank 0's
   # on disk: one chunk file per rank for the flat state and for the expert arrays, no temporary directory left
   step_dir = os.path.join(root, "6")

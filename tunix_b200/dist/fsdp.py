@@ -19,6 +19,13 @@ Optimizer step, once all micro-batches have accumulated into the local flat grad
   3. AdamW on shard r with scale = clip / sum(denominators), refreshing shard r of the bf16 copy,
   4. all-gather of the bf16 shards.
 
+Ownership is interleaved by bucket. The flat index space is cut into buckets of a few decoder layers
+each (embedding first, head last, in parameter order); rank r owns the r-th slice of EVERY bucket, so the
+reduce-scatter of a bucket can start as soon as the last micro-batch's backward has passed its layers -
+it then runs on a side stream, hidden behind the rest of the backward pass - and all ranks' links carry
+an equal share of every transfer. Only the bucket that finishes last (the embedding) is reduced after
+the backward pass.
+
 Two transports implement 1 and 3+4: `nccl` (library collectives: the baseline) and `p2p`
 (`tunix_b200.dist.symm`: the gradient and parameter buffers are allocated in peer-mapped
 symmetric memory, one kernel pulls and sums the peers' gradient shards over NVLink, another
@@ -39,6 +46,23 @@ from . import mesh as mesh_lib
 log = logging.getLogger(__name__)
 
 _ALIGN = 2048   # elements; keeps every shard boundary 16-byte aligned for any dtype and vector width
+_BUCKET_ALIGN = _ALIGN * 16   # bucket boundaries: divisible into 16-byte aligned pieces for up to 16 ranks
+
+
+def _layer_index(name: str) -> Optional[int]:
+  parts = name.split(".")
+  for a, b in zip(parts, parts[1:]):
+    if a == "layers" and b.isdigit():
+      return int(b)
+  return None
+
+
+def _bucket_id(name: str, layers_per_bucket: int) -> int:
+  """Bucket order follows parameter order: what precedes the layers, groups of layers, what follows them."""
+  li = _layer_index(name)
+  if li is not None:
+    return 1 + li // layers_per_bucket
+  return 0 if name.startswith("embedder") else 1 << 30
 
 
 class FlatParamStore:
@@ -65,14 +89,34 @@ class FlatParamStore:
     self.names = [n for n, _ in params]
     self.shapes = {n: tuple(p.shape) for n, p in params}
     self.offsets: Dict[str, int] = {}
-    off = 0
-    for n, p in params:
+    # buckets: consecutive parameters grouped by decoder layer; a bucket starts on a boundary that does not
+    # depend on the number of ranks, so a checkpoint's flat offsets are valid for any power-of-two job size
+    per_bucket = int(os.environ.get("TUNIX_FSDP_BUCKET_LAYERS", "4"))
+    pow2 = self.world & (self.world - 1) == 0 and self.world <= 16
+    ids = [_bucket_id(n, per_bucket) for n, _ in params] if (pow2 and per_bucket > 0) else None
+    if ids is not None and any(b < a for a, b in zip(ids, ids[1:])):
+      ids = None                       # parameter order does not follow the layer order: one bucket
+    off, starts, prev = 0, [0], (ids[0] if ids else 0)
+    for i, (n, p) in enumerate(params):
+      if ids is not None and ids[i] != prev:
+        off = (off + _BUCKET_ALIGN - 1) // _BUCKET_ALIGN * _BUCKET_ALIGN
+        starts.append(off)
+        prev = ids[i]
       self.offsets[n] = off
       off += (p.numel() + 7) // 8 * 8     # 16-byte aligned starts (TMA / vector loads)
-    unit = _ALIGN * self.world
-    self.numel = (off + unit - 1) // unit * unit
     self.used = off
-    self.shard_numel = self.numel // self.world
+    unit = _BUCKET_ALIGN if ids is not None else _ALIGN * self.world
+    self.numel = (off + unit - 1) // unit * unit
+    bounds = starts + [self.numel]
+    # this rank's pieces: (flat start, length, offset inside the rank's shard tensors), one per bucket
+    self.buckets: List[Tuple[int, int]] = [(lo, hi - lo) for lo, hi in zip(bounds[:-1], bounds[1:])]
+    self.pieces: List[Tuple[int, int, int]] = []
+    so = 0
+    for lo, n in self.buckets:
+      per = n // self.world
+      self.pieces.append((lo + self.rank * per, per, so))
+      so += per
+    self.shard_numel = so
     self.transport = transport or os.environ.get("TUNIX_FSDP_TRANSPORT", "p2p" if self.world > 1 else "local")
     self.symm = None
     if self.world > 1 and self.transport == "p2p":
@@ -120,9 +164,25 @@ class FlatParamStore:
           p.data = view
           p.main_grad = self.local_grad[o:o + p.numel()].view(p.shape)
       self.params.update(dict(local))
-    lo = self.rank * self.shard_numel
-    self.shard = slice(lo, lo + self.shard_numel)
     self._scratch: Dict[str, torch.Tensor] = {}
+    self._reduced: set = set()             # buckets whose reduce-scatter already ran (overlapped with backward)
+    self._armed = False
+    self._layers_done = 0
+    self._side = None
+    self._bucket_of_layer: Dict[int, int] = {}
+    self._layers_in_bucket: Dict[int, int] = {}
+    if ids is not None:
+      b = -1
+      last = None
+      for i, (n, _) in enumerate(params):
+        if ids[i] != last:
+          b += 1
+          last = ids[i]
+        li = _layer_index(n)
+        if li is not None and li not in self._bucket_of_layer:
+          self._bucket_of_layer[li] = b
+          self._layers_in_bucket[b] = self._layers_in_bucket.get(b, 0) + 1
+      self._install_backward_hooks(model)
     self.grad_shard: Optional[torch.Tensor] = None   # fp32 [shard_numel]: reduced gradient of my shard
     if self.world > 1:
       self.grad_shard = torch.zeros(self.shard_numel, dtype=torch.float32, device=dev)
@@ -130,7 +190,7 @@ class FlatParamStore:
   # ---- optimizer state ------------------------------------------------------------------
   def init_state(self, tx) -> Dict[str, Any]:
     """Flat fp32 master / mu / nu for this rank's shard (names follow the optax tree)."""
-    master = self.flat_param[self.shard].float()
+    master = self._my_part(self.flat_param).float()
     st: Dict[str, Any] = {
         "count": torch.zeros((), dtype=torch.int32),
         "master": {"flat": master},
@@ -152,6 +212,62 @@ class FlatParamStore:
       self._scratch[name] = t
     return t
 
+  def _my_part(self, flat: torch.Tensor) -> torch.Tensor:
+    """This rank's pieces of a flat [numel] tensor, concatenated in bucket order ([shard_numel])."""
+    if len(self.pieces) == 1:
+      lo, n, _ = self.pieces[0]
+      return flat[lo:lo + n]
+    return torch.cat([flat[lo:lo + n] for lo, n, _ in self.pieces])
+
+  def _put_my_part(self, flat: torch.Tensor, part: torch.Tensor) -> None:
+    for lo, n, so in self.pieces:
+      flat[lo:lo + n].copy_(part[so:so + n])
+
+  # ---- overlap of the gradient reduce-scatter with the last backward pass ----------------------------
+  def _install_backward_hooks(self, model: torch.nn.Module) -> None:
+    """The fused decoder-layer node calls `grad_ready_hook` of its first norm weight when the layer's backward
+    (all its weight gradients included) has been issued."""
+    layers = getattr(model, "layers", None)
+    if layers is None or self.symm is None:
+      return
+    import functools
+    for i, layer in enumerate(layers):
+      w = getattr(getattr(layer, "input_layernorm", None), "w", None)
+      if w is not None and i in self._bucket_of_layer:
+        w.grad_ready_hook = functools.partial(self._layer_backward_done, i)
+
+  def arm_overlap(self) -> None:
+    """Called by the trainer before the backward pass of the LAST micro-batch of an optimizer step: from now on
+    a bucket whose layers have all run backward holds final gradients and may be reduced."""
+    if self.symm is not None and self._bucket_of_layer:
+      self._armed = True
+      self._done_in_bucket: Dict[int, int] = {}
+
+  def _layer_backward_done(self, layer: int) -> None:
+    if not self._armed:
+      return
+    b = self._bucket_of_layer[layer]
+    self._done_in_bucket[b] = self._done_in_bucket.get(b, 0) + 1
+    if self._done_in_bucket[b] < self._layers_in_bucket[b]:
+      return
+    # every bucket after b in flat order (later layers, head) ran backward earlier: reduce all that are due
+    due = [x for x in range(b, len(self.buckets)) if x not in self._reduced and
+           all(self._done_in_bucket.get(y, 0) >= n for y, n in self._layers_in_bucket.items() if y >= x)]
+    if not due:
+      return
+    from ..ops import _lib
+    _lib.bind_thread()
+    if self._side is None:
+      self._side = torch.cuda.Stream(device=self.device)
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream(self.device))
+    self._side.wait_event(ev)
+    self.symm.barrier(channel=1, stream=self._side)        # every rank's gradients of these buckets are final
+    for x in sorted(due):
+      lo, n, so = self.pieces[x]
+      self.symm.reduce_scatter_piece(self.flat_grad, self.grad_shard[so:so + n], lo, stream=self._side)
+      self._reduced.add(x)
+
   # ---- the optimizer step ------------------------------------------------------------------
   @torch.no_grad()
   def step(self, tx, state: Dict[str, Any], denom: torch.Tensor, max_grad_norm: Optional[float]) -> torch.Tensor:
@@ -162,18 +278,29 @@ class FlatParamStore:
     d = self._buf("denom")
     d.copy_(denom.reshape(1))
     ss = self._buf("sumsq")
+    self._armed = False
     if self.world == 1:
       g = self.flat_grad
     elif self.symm is not None:
-      self.symm.reduce_scatter_sum(self.flat_grad, self.grad_shard, self.rank)
+      rest = [x for x in range(len(self.buckets)) if x not in self._reduced]
+      if rest:
+        self.symm.barrier()      # every rank's gradients are final before anybody reads them
+        for x in rest:
+          lo, n, so = self.pieces[x]
+          self.symm.reduce_scatter_piece(self.flat_grad, self.grad_shard[so:so + n], lo)
+      if self._side is not None and self._reduced:
+        torch.cuda.current_stream(self.device).wait_stream(self._side)
+      self._reduced = set()
       g = self.grad_shard
     elif self.device.type == "cuda":
-      dist.reduce_scatter_tensor(self.grad_shard, self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
+      for (blo, bn), (_, n, so) in zip(self.buckets, self.pieces):
+        dist.reduce_scatter_tensor(self.grad_shard[so:so + n], self.flat_grad[blo:blo + bn], op=dist.ReduceOp.SUM,
+                                   group=self.group)
       g = self.grad_shard
     else:
-      # gloo (CPU ranks in tests) has no reduce-scatter: all-reduce and keep this rank's slice
+      # gloo (CPU ranks in tests) has no reduce-scatter: all-reduce and keep this rank's pieces
       dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
-      self.grad_shard.copy_(self.flat_grad[self.shard])
+      self.grad_shard.copy_(self._my_part(self.flat_grad))
       g = self.grad_shard
     if self.device.type == "cuda":
       kernels.sumsq(g, ss, accumulate=False)
@@ -207,12 +334,18 @@ class FlatParamStore:
     if self.local_grad is not None:
       self._local_update(inner, state, scale)
     if self.world > 1 and self.symm is not None:
-      self.symm.adamw_allgather(inner, state, g, self.flat_param, self.shard, scale)
+      self.symm.adamw_allgather(inner, state, g, self.flat_param, self.pieces, scale)
     else:
-      inner.fused_flat_step(state["master"]["flat"], state["mu"]["flat"], state["nu"]["flat"], g,
-                            self.flat_param[self.shard], state, scale, zero_grad=False)
-      if self.world > 1:
-        dist.all_gather_into_tensor(self.flat_param, self.flat_param[self.shard], group=self.group)
+      if self.world == 1:
+        inner.fused_flat_step(state["master"]["flat"], state["mu"]["flat"], state["nu"]["flat"], g,
+                              self.flat_param[:self.shard_numel], state, scale, zero_grad=False)
+      else:
+        mine = self._my_part(self.flat_param).contiguous()
+        inner.fused_flat_step(state["master"]["flat"], state["mu"]["flat"], state["nu"]["flat"], g, mine, state, scale,
+                              zero_grad=False)
+        self._put_my_part(self.flat_param, mine)
+        for (blo, bn), (lo, n, _) in zip(self.buckets, self.pieces):
+          dist.all_gather_into_tensor(self.flat_param[blo:blo + bn], self.flat_param[lo:lo + n].clone(), group=self.group)
     self.flat_grad.zero_()
     return norm[0].clone()
 
@@ -229,13 +362,14 @@ class FlatParamStore:
   # ---- checkpoint support ---------------------------------------------------------------------
   def state_shards(self, state: Mapping[str, Any]) -> Dict[Tuple, Any]:
     """This rank's part of the optimizer state as a checkpoint tree whose sharded leaves are chunks of
-    flat arrays: `mu/nu/master.flat` of shape [numel] cut into `world` chunks of [shard_numel] (rank r
-    holds chunk r) and, with expert parallelism, `*.local` of shape [world * local_numel]. Every rank
-    writes its own chunk files; nothing crosses the ranks."""
+    rank-major arrays: `mu/nu/master.flat` of shape [world * shard_numel], chunk r = rank r's pieces of all
+    buckets in bucket order (the piece table is in `flat_index`), and, with expert parallelism, `*.local`
+    of shape [world * local_numel]. Every rank writes its own chunk files; nothing crosses the ranks."""
     from ..ckpt.orbax_layout import ShardedArray
     out: Dict[Tuple, Any] = {("count", "value"): torch.as_tensor(state["count"])}
     for k in ("mu", "nu", "master"):
-      out[(k, "flat", "value")] = ShardedArray(state[k]["flat"], (self.numel,), (self.shard_numel,), (self.rank,))
+      out[(k, "flat", "value")] = ShardedArray(state[k]["flat"], (self.world * self.shard_numel,), (self.shard_numel,),
+                                               (self.rank,))
       if "local" in state[k]:
         out[(k, "local", "value")] = ShardedArray(state[k]["local"], (self.world * self.local_numel,),
                                                   (self.local_numel,), (self.rank,))
@@ -244,9 +378,18 @@ class FlatParamStore:
     return out
 
   def flat_index(self) -> Dict[str, Any]:
-    """Where each parameter sits in the flat arrays of `state_shards` (JSON-serialisable)."""
-    return {"format": "tunix_b200.flat_state.v1", "numel": self.numel, "used": self.used, "world": self.world,
-            "shard_numel": self.shard_numel, "names": list(self.names),
+    """Where each parameter sits in the flat index space and which flat ranges each rank's chunk of the
+    `state_shards` arrays holds (JSON-serialisable)."""
+    per_rank = []
+    for r in range(self.world):
+      so, rows = 0, []
+      for lo, n in self.buckets:
+        per = n // self.world
+        rows.append([lo + r * per, per, r * self.shard_numel + so])     # flat start, length, position in the array
+        so += per
+      per_rank.append(rows)
+    return {"format": "tunix_b200.flat_state.v2", "numel": self.numel, "used": self.used, "world": self.world,
+            "shard_numel": self.shard_numel, "pieces": per_rank, "names": list(self.names),
             "offsets": [self.offsets[n] for n in self.names], "shapes": [list(self.shapes[n]) for n in self.names],
             "local_numel": self.local_numel, "local_names": list(self.local_names),
             "local_offsets": [self.local_offsets[n] for n in self.local_names],
@@ -254,15 +397,21 @@ class FlatParamStore:
 
   @torch.no_grad()
   def load_state_shards(self, state: Dict[str, Any], index: Mapping[str, Any], read_rows) -> None:
-    """Restores this rank's shard from flat arrays written by `state_shards`, possibly by a job of another
-    size: `read_rows(name, lo, hi)` returns elements [lo, hi) of the stored 1-D array `name`. Parameter
-    offsets do not depend on the number of ranks, so a rank's flat range is the same range of the file."""
+    """Restores this rank's shard from arrays written by `state_shards`, possibly by a job of another
+    size: `read_rows(name, lo, hi)` returns elements [lo, hi) of the stored 1-D array `name`. Every piece
+    this rank owns is assembled from the saved pieces that overlap it in the flat index space (parameter
+    offsets do not depend on the number of ranks)."""
     if list(index["names"]) != list(self.names) or list(index["offsets"]) != [self.offsets[n] for n in self.names]:
       raise ValueError("checkpointed optimizer state was written for a different parameter layout")
-    lo, hi = self.shard.start, self.shard.stop
+    saved = [tuple(p) for rows in index["pieces"] for p in rows]       # (flat start, length, array position)
     for k in ("mu", "nu", "master"):
-      part = read_rows(f"{k}.flat", lo, hi)
-      state[k]["flat"].copy_(part.to(self.device, torch.float32))
+      dst = state[k]["flat"]
+      for lo, n, so in self.pieces:
+        for flo, fn, pos in saved:
+          a, b = max(lo, flo), min(lo + n, flo + fn)
+          if a < b:
+            part = read_rows(f"{k}.flat", pos + (a - flo), pos + (b - flo))
+            dst[so + (a - lo): so + (b - lo)].copy_(part.to(self.device, torch.float32))
       if "local" in state[k]:
         if index.get("world") != self.world or index.get("local_numel") != self.local_numel:
           raise ValueError("expert-parallel optimizer state can only be restored at the expert-parallel size "
@@ -274,8 +423,15 @@ class FlatParamStore:
     """All-gathers a sharded state tensor (per-parameter views for export; checkpoints do not use this)."""
     if self.world == 1:
       return shard_tensor
-    full = torch.empty(self.numel, dtype=shard_tensor.dtype, device=shard_tensor.device)
-    dist.all_gather_into_tensor(full, shard_tensor.contiguous(), group=self.group)
+    parts = torch.empty(self.world * self.shard_numel, dtype=shard_tensor.dtype, device=shard_tensor.device)
+    dist.all_gather_into_tensor(parts, shard_tensor.contiguous(), group=self.group)
+    full = torch.zeros(self.numel, dtype=shard_tensor.dtype, device=shard_tensor.device)
+    for r in range(self.world):                    # rank-major pieces back into flat order
+      so = 0
+      for lo, n in self.buckets:
+        per = n // self.world
+        full[lo + r * per: lo + (r + 1) * per].copy_(parts[r * self.shard_numel + so: r * self.shard_numel + so + per])
+        so += per
     return full
 
   def unflatten(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
@@ -309,7 +465,7 @@ class FlatParamStore:
         if n in self.offsets:
           o = self.offsets[n]
           full[o:o + t.numel()].copy_(t.reshape(-1).to(self.device, torch.float32))
-      state[k]["flat"].copy_(full[self.shard])
+      state[k]["flat"].copy_(self._my_part(full))
       if "local" in state[k]:
         for n, t in tree[k].items():
           if n in self.local_offsets:
@@ -321,7 +477,7 @@ class FlatParamStore:
   @torch.no_grad()
   def refresh_master_from_params(self, state: Dict[str, Any]) -> None:
     """After parameters were loaded into the bf16 buffer (checkpoint restore, weight import)."""
-    state["master"]["flat"].copy_(self.flat_param[self.shard].float())
+    state["master"]["flat"].copy_(self._my_part(self.flat_param).float())
     if "local" in state["master"]:
       state["master"]["local"].copy_(self.local_param.float())
 

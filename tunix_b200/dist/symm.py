@@ -71,6 +71,8 @@ class SymmetricBuffers:
     self.lib = _declare()
     # one int32 row of flags per rank (kMaxPeers = 16 entries)
     self.alloc("_flags", 16, torch.int32)
+    self.alloc("_flags1", 16, torch.int32)      # second barrier channel: a side stream's barriers use their own flags
+    self._epoch1 = 0
 
   def alloc(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
     t = self._sm.empty(numel, dtype=dtype, device=self.device)
@@ -82,7 +84,7 @@ class SymmetricBuffers:
     for name, t in self.tensors.items():
       if name in self.handles:
         continue
-      if name == "_flags":
+      if name in ("_flags", "_flags1"):
         t.zero_()
       h = self._sm.rendezvous(t, self.group)
       self.handles[name] = h
@@ -101,35 +103,51 @@ class SymmetricBuffers:
     raise ValueError("tensor is not part of a symmetric buffer")
 
   # ---- collectives ---------------------------------------------------------------------
-  def barrier(self) -> None:
-    """Device-side barrier on the current stream (bounded wait)."""
-    self._epoch += 1
-    rc = self.lib.tx_peer_barrier(_ptr_array(self.peer_ptrs["_flags"]), self.rank, self.world, self._epoch,
-                                  self.wait_limit_ms, _lib.status_word(self.device).data_ptr(), _lib.stream_ptr())
+  def barrier(self, channel: int = 0, stream=None) -> None:
+    """Device-side barrier (bounded wait) on the current stream, or on `stream`. Barriers issued from two
+    streams must use different channels: a channel is one flag row per rank plus its own epoch counter."""
+    if channel == 0:
+      self._epoch += 1
+      epoch, name = self._epoch, "_flags"
+    else:
+      self._epoch1 += 1
+      epoch, name = self._epoch1, "_flags1"
+    sp = _lib.stream_ptr() if stream is None else stream.cuda_stream
+    rc = self.lib.tx_peer_barrier(_ptr_array(self.peer_ptrs[name]), self.rank, self.world, epoch,
+                                  self.wait_limit_ms, _lib.status_word(self.device).data_ptr(), sp)
     _lib.check_rc(rc, "tx_peer_barrier")
+
+  def reduce_scatter_piece(self, full_fp32: torch.Tensor, out_piece: torch.Tensor, flat_start: int, stream=None) -> None:
+    """out_piece = sum over ranks of full_fp32[flat_start : flat_start + n], read over NVLink. The caller has
+    made sure (a barrier) that every rank's values in that range are final."""
+    sp = _lib.stream_ptr() if stream is None else stream.cuda_stream
+    rc = self.lib.tx_reduce_scatter_sum_f32(_ptr_array(self.ptrs_for(full_fp32)), out_piece.data_ptr(), flat_start,
+                                            out_piece.numel(), self.world, self.rank, None, sp)
+    _lib.check_rc(rc, "tx_reduce_scatter_sum_f32")
 
   def reduce_scatter_sum(self, full_fp32: torch.Tensor, out_shard: torch.Tensor, rank: int) -> None:
     """out_shard = sum over ranks of full_fp32[rank * n : (rank + 1) * n], read over NVLink."""
-    n = out_shard.numel()
     self.barrier()      # every rank's gradients are final before anybody reads them
-    rc = self.lib.tx_reduce_scatter_sum_f32(_ptr_array(self.ptrs_for(full_fp32)), out_shard.data_ptr(), rank * n, n,
-                                            self.world, rank, None, _lib.stream_ptr())
-    _lib.check_rc(rc, "tx_reduce_scatter_sum_f32")
+    self.reduce_scatter_piece(full_fp32, out_shard, rank * out_shard.numel())
 
-  def adamw_allgather(self, tx, state, grad_shard: torch.Tensor, flat_param: torch.Tensor, shard: slice,
+  def adamw_allgather(self, tx, state, grad_shard: torch.Tensor, flat_param: torch.Tensor, pieces,
                       grad_scale: torch.Tensor) -> None:
-    """Fused AdamW on this rank's shard + store of the new bf16 values into every rank's
-    `flat_param`; closes with a barrier so no rank starts its next forward early."""
+    """Fused AdamW on this rank's shard + store of the new bf16 values into every rank's `flat_param`, one launch
+    per piece `(flat start, length, offset in the shard tensors)`; closes with a barrier so no rank starts its
+    next forward early."""
     from .. import optim
     count = int(state["count"]) + 1
     lr = optim._lr_at(tx._lr, count - 1)
-    n = grad_shard.numel()
-    rc = self.lib.tx_adamw_allgather(
-        state["master"]["flat"].data_ptr(), state["mu"]["flat"].data_ptr(), state["nu"]["flat"].data_ptr(),
-        grad_shard.data_ptr(), _ptr_array(self.ptrs_for(flat_param)), shard.start, n, lr, tx.b1, tx.b2, tx.eps,
-        tx.weight_decay, 1.0 - tx.b1 ** count, 1.0 - tx.b2 ** count, grad_scale.data_ptr(), self.world, self.rank,
-        _lib.stream_ptr())
-    _lib.check_rc(rc, "tx_adamw_allgather")
+    if isinstance(pieces, slice):
+      pieces = [(pieces.start, grad_shard.numel(), 0)]
+    ptrs = _ptr_array(self.ptrs_for(flat_param))
+    ma, mu, nu = state["master"]["flat"], state["mu"]["flat"], state["nu"]["flat"]
+    for lo, n, so in pieces:
+      rc = self.lib.tx_adamw_allgather(
+          ma.data_ptr() + 4 * so, mu.data_ptr() + 4 * so, nu.data_ptr() + 4 * so, grad_shard.data_ptr() + 4 * so, ptrs,
+          lo, n, lr, tx.b1, tx.b2, tx.eps, tx.weight_decay, 1.0 - tx.b1 ** count, 1.0 - tx.b2 ** count,
+          grad_scale.data_ptr(), self.world, self.rank, _lib.stream_ptr())
+      _lib.check_rc(rc, "tx_adamw_allgather")
     self.barrier()      # all pushes have landed everywhere; also orders the next zeroing of gradients
     state["count"] = torch.tensor(count, dtype=torch.int32)
     if "hyperparams" in state:

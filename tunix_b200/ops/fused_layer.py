@@ -137,6 +137,9 @@ class DecoderLayerFn(torch.autograd.Function):
     dh, dw_in = kernels.rmsnorm_bwd(h2d, w_in, dx1, rstd1, eps, off, dres=dh_mid, dw_out=mg,
                                     dw_accumulate=mg is not None)
     g_win = None if mg is not None else dw_in.to(w_in.dtype)
+    ready = getattr(w_in, "grad_ready_hook", None)
+    if ready is not None:
+      ready()        # every weight gradient of this layer has been issued (a sharded store may start reducing them)
     return (dh.view(B, T, D), None, None, g_win, g_wqkv, g_wo, g_wpost, g_wgu, g_wd, g_wq, g_wk, None, None)
 
 

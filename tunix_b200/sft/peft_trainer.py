@@ -328,6 +328,8 @@ class PeftTrainer:
     self.model.train()
     out = self.loss_fn(self.model, **model_inputs)
     loss_t, aux, denom = self._split_loss(out)
+    if is_update_step and self.optimizer.flat is not None:
+      self.optimizer.flat.arm_overlap()      # gradients of this backward pass are final: reduce buckets as they finish
     loss_t.backward()
     loss_val = aux.primary_loss.compute().detach() if isinstance(aux, LossOutput) else loss_t.detach()
     acc = self.grad_accumulator
