@@ -30,32 +30,38 @@ class DAPOConfig(grpo_lib.GRPOConfig):
       raise ValueError("DAPO does not support KL penalty, so beta must be None.")
     if self.epsilon_high < self.epsilon:
       raise ValueError("epsilon_high must be greater than or equal to epsilon.")
-    if self.overlong_buffer is not None and self.overlong_buffer.get("enable"):
-      b = self.overlong_buffer
-      missing = [k for k in ("overlong_buffer_length", "overlong_buffer_penalty", "max_response_length")
-                 if b.get(k) is None]
-      if missing:
-        raise ValueError(f"overlong_buffer is enabled but missing: {missing}")
-      if b["overlong_buffer_penalty"] < 0:
-        raise ValueError("overlong_buffer_penalty must be non-negative.")
-      if b["overlong_buffer_length"] <= 0:
-        raise ValueError("overlong_buffer_length must be positive.")
-      if b["max_response_length"] <= 0:
-        raise ValueError("max_response_length must be positive.")
+    _check_overlong_buffer(self.overlong_buffer)
     super().__post_init__()
+
+
+_OVERLONG_KEYS = ("overlong_buffer_length", "overlong_buffer_penalty", "max_response_length")
+
+
+def _check_overlong_buffer(buf: Optional[Dict[str, Any]]) -> None:
+  """An enabled buffer must give a positive window, a non-negative penalty and a positive response budget."""
+  if not buf or not buf.get("enable"):
+    return
+  missing = [k for k in _OVERLONG_KEYS if buf.get(k) is None]
+  if missing:
+    raise ValueError(f"overlong_buffer is enabled but missing: {missing}")
+  for key, ok, rule in (("overlong_buffer_penalty", buf["overlong_buffer_penalty"] >= 0, "non-negative"),
+                        ("overlong_buffer_length", buf["overlong_buffer_length"] > 0, "positive"),
+                        ("max_response_length", buf["max_response_length"] > 0, "positive")):
+    if not ok:
+      raise ValueError(f"{key} must be {rule}.")
 
 
 def reward_shaping(prompts: List[str], completions: List[str], mode: Any = None,
                    overlong_buffer: Optional[Dict[str, Any]] = None, **kwargs) -> List[float]:
-  """Soft penalty for responses that run into the last `overlong_buffer_length` of the budget:
-  `min(-(len - (max_len - buffer)) / buffer * penalty, 0)`."""
+  """Length penalty of DAPO: a response may use `max_response_length - window` units for free; every unit
+  inside the last `window` costs `penalty / window`, so the penalty reaches `-penalty` at the budget (and keeps
+  growing beyond it); shorter responses get 0."""
   del prompts, mode, kwargs
   if overlong_buffer is None:
     raise ValueError("reward_shaping is called but with empty overlong_buffer.")
-  buf_len = overlong_buffer["overlong_buffer_length"]
-  penalty = overlong_buffer["overlong_buffer_penalty"]
-  expected = overlong_buffer["max_response_length"] - buf_len
-  return [min(-(len(c) - expected) / buf_len * penalty, 0) for c in completions]
+  window, penalty = overlong_buffer["overlong_buffer_length"], overlong_buffer["overlong_buffer_penalty"]
+  free = overlong_buffer["max_response_length"] - window
+  return [min(0, (free - len(text)) * penalty / window) for text in completions]
 
 
 class DAPOLearner(grpo_lib.GRPOLearner):
