@@ -315,7 +315,11 @@ def main():
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "ours",
         "config": {"model": args.model, "layers": cfg.num_layers, "global_batch": GB, "seq_len": S,
-                   "parallelism": f"ep{world}+fsdp{world}" if moe else f"fsdp{world}", "micro_batch_per_gpu": micro, "grad_accum": ga, "remat": remat,
+                   "parallelism": f"ep{world}+fsdp{world}" if moe else f"fsdp{world}",
+                   "sharding": ("fp32 master / Adam moments and the reduced gradient are sharded over the ranks (interleaved by "
+                                "bucket); every rank keeps a resident bf16 parameter replica and its own fp32 gradient "
+                                "accumulator" if world > 1 else "single GPU"),
+                   "micro_batch_per_gpu": micro, "grad_accum": ga, "remat": remat,
                    "l2": "inputs larger than L2: each step streams >100 GB of weights, gradients and optimizer state",
                    "optimizer": "AdamW fp32 master/m/v, global-norm clip 1.0"},
         **({"moe": {"full_model_layers": full_layers, "layers_run": cfg.num_layers,

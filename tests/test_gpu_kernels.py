@@ -377,3 +377,36 @@ def test_deterministic_mode_makes_skinny_gemms_bitwise_reproducible(kernel_lib):
   assert all(torch.equal(outs[0], o) for o in outs[1:])
   assert torch.allclose(outs[0].float(), ref, atol=5e-2, rtol=3e-2)
   assert torch.allclose(kernels.gemm(a, w).float(), ref, atol=5e-2, rtol=3e-2)       # split-K path back on
+
+
+def test_debug_build_reports_indices_the_release_build_clamps(kernel_lib):
+  """The -DTX_DEBUG library records an out-of-range token id (the release kernel clamps it silently)."""
+  import os
+  import subprocess
+  import sys
+  from tunix_b200 import build_kernels
+  build_kernels.build(debug=True)
+  code = r"""
+import torch
+from tunix_b200.ops import _lib, kernels
+table = torch.randn(16, 64, device="cuda").bfloat16()
+ok = kernels.embedding_fwd(torch.tensor([0, 15, 3], device="cuda", dtype=torch.int32), table)
+_lib.status_word("cuda"); _lib.check_status()
+bad = kernels.embedding_fwd(torch.tensor([0, 99, 3], device="cuda", dtype=torch.int32), table)
+assert torch.equal(bad[1], table[15])            # still clamped: no fault
+try:
+  _lib.check_status()
+  print("NO_REPORT")
+except RuntimeError as e:
+  print("REPORT", e)
+_lib.check_status()                               # the record was cleared
+print("DONE")
+"""
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  for debug, want in (("1", "REPORT"), ("0", "NO_REPORT")):
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, TUNIX_B200_DEBUG_KERNELS=debug, PYTHONPATH=root),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert want in r.stdout and "DONE" in r.stdout, r.stdout
+    if debug == "1":
+      assert "token id outside the vocabulary" in r.stdout and "value 99, limit 16" in r.stdout

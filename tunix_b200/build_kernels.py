@@ -4,7 +4,11 @@ Every ``.cu`` under ``tunix_b200/csrc`` is compiled to an object file and linked
 ``tunix_b200/lib/libtunix_b200.so``; the Python side loads it with ctypes. The C++-only
 runtime pieces (``.cc``) are linked into the same library.
 
-Usage: ``python -m tunix_b200.build_kernels [--force] [--verbose]``
+Usage: ``python -m tunix_b200.build_kernels [--force] [--verbose] [--debug]``
+
+``--debug`` builds ``libtunix_b200_debug.so`` from the same sources with ``-DTX_DEBUG``: kernels then record
+index errors that the release build resolves silently (``csrc/tx_debug.cuh``). Load it with
+``TUNIX_B200_DEBUG_KERNELS=1``.
 """
 from __future__ import annotations
 
@@ -56,10 +60,15 @@ def headers():
   return sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
 
 
-def _compile_one(nvcc: str, src: Path, verbose: bool, ptxas_info: bool) -> Path:
-  obj = BUILD_DIR / (src.stem + ".o")
-  stamp = BUILD_DIR / (src.stem + ".sha")
-  want = _digest([src] + headers())
+DEBUG_LIB_PATH = LIB_DIR / "libtunix_b200_debug.so"
+DEBUG_BUILD_DIR = PKG / "lib" / "obj_debug"
+
+
+def _compile_one(nvcc: str, src: Path, verbose: bool, ptxas_info: bool, debug: bool = False) -> Path:
+  bdir = DEBUG_BUILD_DIR if debug else BUILD_DIR
+  obj = bdir / (src.stem + ".o")
+  stamp = bdir / (src.stem + ".sha")
+  want = _digest([src] + headers()) + ("-debug" if debug else "")
   if obj.exists() and stamp.exists() and stamp.read_text() == want:
     return obj
   cmd = [nvcc] + NVCC_FLAGS + ["-I", str(CSRC), "-c", str(src), "-o", str(obj)]
@@ -67,6 +76,8 @@ def _compile_one(nvcc: str, src: Path, verbose: bool, ptxas_info: bool) -> Path:
     cmd = [nvcc] + NVCC_FLAGS + ["-x", "cu", "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
   if ptxas_info:
     cmd += ["-Xptxas", "-v"]
+  if debug:
+    cmd += ["-DTX_DEBUG"]
   if verbose:
     print(" ".join(cmd), flush=True)
   r = subprocess.run(cmd, capture_output=True, text=True)
@@ -78,29 +89,30 @@ def _compile_one(nvcc: str, src: Path, verbose: bool, ptxas_info: bool) -> Path:
   return obj
 
 
-def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
-  """Compiles (if stale) and links the library; returns its path."""
+def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False, debug: bool = False) -> Path:
+  """Compiles (if stale) and links the library (the `-DTX_DEBUG` one with `debug`); returns its path."""
   nvcc = find_nvcc()
+  bdir, lib = (DEBUG_BUILD_DIR, DEBUG_LIB_PATH) if debug else (BUILD_DIR, LIB_PATH)
   LIB_DIR.mkdir(exist_ok=True)
-  BUILD_DIR.mkdir(exist_ok=True)
+  bdir.mkdir(exist_ok=True)
   if force:
-    for f in BUILD_DIR.glob("*.sha"):
+    for f in bdir.glob("*.sha"):
       f.unlink()
   srcs = sources()
-  lib_stamp = BUILD_DIR / "lib.sha"
+  lib_stamp = bdir / "lib.sha"
   want = _digest(srcs + headers())
-  if LIB_PATH.exists() and lib_stamp.exists() and lib_stamp.read_text() == want and not force:
-    return LIB_PATH
+  if lib.exists() and lib_stamp.exists() and lib_stamp.read_text() == want and not force:
+    return lib
   with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(srcs)))) as ex:
-    objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose, ptxas_info), srcs))
-  cmd = [nvcc, "-shared", "-o", str(LIB_PATH)] + [str(o) for o in objs] + ["-lcudart", "-lpthread", "-ldl"]
+    objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose, ptxas_info, debug), srcs))
+  cmd = [nvcc, "-shared", "-o", str(lib)] + [str(o) for o in objs] + ["-lcudart", "-lpthread", "-ldl"]
   if verbose:
     print(" ".join(cmd), flush=True)
   r = subprocess.run(cmd, capture_output=True, text=True)
   if r.returncode != 0:
     raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
   lib_stamp.write_text(want)
-  return LIB_PATH
+  return lib
 
 
 def main(argv=None):
@@ -108,8 +120,9 @@ def main(argv=None):
   ap.add_argument("--force", action="store_true")
   ap.add_argument("--verbose", action="store_true")
   ap.add_argument("--ptxas-info", action="store_true")
+  ap.add_argument("--debug", action="store_true", help="build the index-checking library (-DTX_DEBUG)")
   a = ap.parse_args(argv)
-  p = build(a.force, a.verbose, a.ptxas_info)
+  p = build(a.force, a.verbose, a.ptxas_info, a.debug)
   print(p)
 
 

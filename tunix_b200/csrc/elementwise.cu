@@ -5,7 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tx_debug.cuh"
 #include "tx_host.h"
+
+TX_DEBUG_UNIT(elementwise)
 
 namespace {
 
@@ -98,6 +101,7 @@ __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfl
     const long long t = i / dv;
     const int c = static_cast<int>(i - t * dv) * 8;
     int id = ids[t];
+    TX_DEBUG_CHECK(id >= 0 && id < V, TX_DBG_TOKEN_ID, id, V);
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     float v[8];
     load8(table + static_cast<long long>(id) * D + c, v);

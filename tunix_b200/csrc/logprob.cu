@@ -8,6 +8,10 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "tx_debug.cuh"
+
+TX_DEBUG_UNIT(logprob)
+
 namespace {
 
 constexpr int kThreads = 512;
@@ -144,6 +148,7 @@ logprob_fwd_kernel(const LT* __restrict__ logits, long long ldl, const int* __re
     for (int w = 1; w < kThreads / 32; ++w) r = acc_merge(r, sh[w]);
     const float lse = r.m + logf(r.s);
     const int tgt = targets[row];
+    TX_DEBUG_CHECK(tgt >= 0 && tgt < V, TX_DBG_TARGET_ID, tgt, V);
     float zt = 0.f;
     if (tgt >= 0 && tgt < V) {
       zt = ld<LT>(lr + tgt);

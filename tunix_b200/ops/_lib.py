@@ -15,7 +15,9 @@ import torch
 
 _LIB = None
 _LOCK = threading.Lock()
-_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libtunix_b200.so"
+_DEBUG_KERNELS = os.environ.get("TUNIX_B200_DEBUG_KERNELS", "0") == "1"     # the -DTX_DEBUG build (index checks)
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / (
+    "libtunix_b200_debug.so" if _DEBUG_KERNELS else "libtunix_b200.so")
 
 c_void_p = ctypes.c_void_p
 c_int = ctypes.c_int
@@ -182,10 +184,31 @@ def check_status(device=None) -> None:
   if t is None:
     return
   v = int(t.item())
+  _check_debug_records()
   if v != 0:
     t.zero_()
     raise RuntimeError(f"tunix_b200 kernel reported error status 0x{v:x} "
                        "(1/2/4: producer/MMA/epilogue wait timed out, 8: bad argument, 16: peer wait timed out)")
+
+
+_DEBUG_UNITS = ("elementwise", "logprob")
+_DEBUG_CODES = {1: "token id outside the vocabulary (embedding)", 2: "target id outside the vocabulary (log-prob)",
+                3: "block-table page outside the cache (paged attention)", 4: "slot beyond the cache (KV page write)"}
+
+
+def _check_debug_records() -> None:
+  """Debug build only: raises when a kernel recorded an index that the release build would have resolved silently."""
+  lib = _LIB
+  if lib is None or not _DEBUG_KERNELS:
+    return
+  for unit in _DEBUG_UNITS:
+    fn = getattr(lib, f"tx_debug_read_{unit}", None)
+    if fn is None:
+      continue
+    rec = (ctypes.c_int * 4)()
+    fn.argtypes, fn.restype = [ctypes.POINTER(ctypes.c_int)], ctypes.c_int
+    if fn(rec) > 0:
+      raise RuntimeError(f"debug kernels ({unit}): {_DEBUG_CODES.get(rec[1], rec[1])}: value {rec[2]}, limit {rec[3]}")
 
 
 launch_calls = 0   # number of library launches issued by this process (each is >= 1 kernel)
