@@ -362,3 +362,40 @@ def test_rl_program_end_to_end_with_workers_and_weight_sync():
   for n, p in rollout_model.named_parameters():
     torch.testing.assert_close(p, dict(actor.named_parameters())[n])
   assert all(w.state == S.STOPPED for w in (tw, rw, iw))
+
+
+def test_remote_execution_over_grpc_loopback():
+  """A worker object served by the gRPC `RemoteExecutionServer` on 127.0.0.1 and driven through a
+  `GrpcRemoteActorHandle`: unary calls, remote errors, and the dispatch / long-poll pair."""
+  grpc = pytest.importorskip("grpc")
+
+  class Worker:
+    def __init__(self): self.calls = 0
+    def scale(self, x, k=2): self.calls += 1; return [v * k for v in x]
+    async def slow_add(self, a, b): await asyncio.sleep(0.01); return a + b
+    def fail(self): raise ValueError("nope")
+
+  w = Worker()
+  server = rx.GrpcRemoteExecutionServer(w)
+  server.start_serving(port=0)                      # port 0: the OS picks a free one
+  assert server.port and server.port > 0
+  handle = rx.ActorHandle.from_address(f"grpc://127.0.0.1:{server.port}")
+  try:
+    assert handle.submit("scale", [1, 2, 3], k=3) == [3, 6, 9] and w.calls == 1
+    with pytest.raises(RuntimeError, match=r"RemoteExecutionError \[ValueError\]"):
+      handle.submit("fail")
+
+    async def session():
+      assert await handle.asubmit("slow_add", 2, 5) == 7
+      rid = await handle.dispatch_task("job-1", "scale", [4], k=5)
+      assert rid == "job-1"
+      got = []
+      for _ in range(20):
+        got += await handle.poll_responses(timeout_s=0.5, max_items=4)
+        if got:
+          break
+      assert [r.request_id for r in got] == ["job-1"] and got[0].unwrap() == [20]
+      await handle.close()
+    asyncio.run(session())
+  finally:
+    server.shutdown()
