@@ -52,6 +52,8 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __
                     __nv_bfloat16* __restrict__ out, long long ldo) {
   constexpr int LPK = H / 8;            // lanes per key
   constexpr int KPW = 32 / LPK;         // keys per warp iteration
+  // lets a programmatically launched successor (the output-projection GEMM) prefetch its weights meanwhile
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPK, dl = lane % LPK;
@@ -178,6 +180,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __
 template <int H>
 __global__ void paged_decode_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                             int num_splits, __nv_bfloat16* __restrict__ out, long long ldo, int N) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
   const long long base = (static_cast<long long>(b) * N + head) * num_splits;
   float mn = -INFINITY;

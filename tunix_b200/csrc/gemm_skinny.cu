@@ -219,6 +219,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int kb_lo = static_cast<int>(static_cast<long long>(num_kb) * crank / S);
   const int kb_hi = static_cast<int>(static_cast<long long>(num_kb) * (crank + 1) / S);
   const int my_lo = col_lo(crank, S), my_hi = col_lo(crank + 1, S);
+  if (p.n_ranks > 1) griddep_wait();     // the call counter is written by the previous exit kernel of the chain
   const int epoch = p.n_ranks > 1 ? (*reinterpret_cast<volatile int*>(p.epoch) + 1) : 0;
 
   if (threadIdx.x == 0) {
@@ -247,6 +248,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) stamp(p, 1);    // set-up done (barriers, TMEM, cluster rendezvous)
+  griddep_launch_dependents();          // a successor launched programmatically may take SMs as our CTAs leave
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -257,8 +259,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      // The weights do not depend on the kernel before this one: the first pass over the ring issues its weight
+      // tiles at once, then waits for the predecessor (programmatic dependent launch), then adds the activation
+      // tiles to the same stages. From then on weight and activation tiles are issued together.
+      const int per_slab = kb_hi - kb_lo;
+      int early = 0;
+      for (int slab = cluster_id; slab < slabs && early < stages; slab += p.n_clusters) {
+        for (int kb = kb_lo; kb < kb_hi && early < stages; ++kb, ++early) {
+          const uint32_t full = bar_full + 8 * early;
+          const uint32_t sa = smem_base + early * C::kStageBytes;
+          mbar_expect_tx(full, C::kStageBytes);
+          tma_load_2d(sa, &map_w, kb * BK, slab * BMW, full);
+          if (GLU) tma_load_2d(sa + C::kWBytes, &map_w2, kb * BK, slab * BMW, full);
+          if (early == 0) stamp(p, 2);                                              // first load issued
+        }
+      }
+      griddep_wait();
+      {
+        int q = 0;
+        for (int slab = cluster_id; slab < slabs && q < early; slab += p.n_clusters)
+          for (int kb = kb_lo; kb < kb_hi && q < early; ++kb, ++q)
+            tma_load_2d(smem_base + q * C::kStageBytes + C::kABytes, &map_x, kb * BK, 0, bar_full + 8 * q);
+      }
+      stamp(p, 3);                                                                  // ring filled once
+      stage = early % stages;
+      phase = early == stages ? 1u : 0u;
+      int q = 0;
       for (int slab = cluster_id; slab < slabs && ok; slab += p.n_clusters) {
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
+        for (int kb = kb_lo; kb < kb_hi; ++kb, ++q) {
+          if (q < early) continue;                                                  // issued above
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag)) {
             atomicOr(p.status, kStatusWaitTimeoutProducer);
             ok = false;
@@ -271,10 +300,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
           if (GLU) tma_load_2d(sa + C::kWBytes, &map_w2, kb * BK, slab * BMW, full);
           tma_load_2d(sa + C::kABytes, &map_x, kb * BK, 0, full);
           if (++stage == stages) { stage = 0; phase ^= 1; }
-          if (slab == cluster_id && kb == kb_lo) stamp(p, 2);                       // first load issued
-          if (slab == cluster_id && kb == kb_lo + stages - 1) stamp(p, 3);          // ring filled once
         }
       }
+      (void)per_slab;
       stamp(p, 4);                                                                  // all loads issued
     }
   } else if (warp == 1) {
@@ -327,6 +355,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const bool mine = owner == crank;
     const int own_lo = col_lo(owner, S);
     float* part_self = p.n_ranks > 1 ? p.part[p.rank] + (epoch & 1) * p.part_stride : nullptr;
+    griddep_wait();          // the residual (and C itself) belong to the kernels before this one
     int acc = 0, round = 0;
     uint32_t acc_phase = 0;
     for (int slab = cluster_id; slab < slabs; slab += p.n_clusters, ++round) {
@@ -551,6 +580,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
 }
 
+// 1: launch with programmatic stream serialization, so that set-up and the first weight tiles overlap the tail of
+// the kernel before (which must have been launched on the same stream). Off: an ordinary launch.
+static int g_pdl = [] {
+  const char* e = getenv("TUNIX_B200_PDL");
+  return (e && e[0] == '0') ? 0 : 1;
+}();
+
 // Per (kernel, device, split) cache of how many clusters can be resident at once.
 struct ClusterFit {
   int stages[9] = {};
@@ -641,13 +677,15 @@ int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, l
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem_for(best_s, p.stages);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = best_s;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = g_pdl ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, mw, mw2, mx, p) != cudaSuccess) { (void)cudaGetLastError(); return 400; }
   return 0;
 }
@@ -664,6 +702,11 @@ int dispatch_bnx(int Mx, const void* X, const void* W, const SkinnyParams& p, lo
 }  // namespace
 
 extern "C" int tx_gemm_skinny_flag_blocks() { return kMaxFlagBlocks; }
+extern "C" int tx_gemm_skinny_set_pdl(int on) {
+  const int before = g_pdl;
+  g_pdl = on ? 1 : 0;
+  return before;
+}
 
 // Debug aid: attaches (or, with null, detaches) a device buffer of 16 x 64-bit words per CTA (room for 8 * SM count
 // CTAs) that later launches fill with %globaltimer stamps of their phase boundaries: 0 start, 1 set-up done, 2 first

@@ -59,6 +59,9 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, int T, int D, float eps,
                    float w_offset) {
   __shared__ float sh[32];
+  // A successor launched with programmatic stream serialization (the decode GEMM) may start its set-up and weight
+  // prefetch now; it still waits for this grid to finish before it reads y. No effect on ordinary successors.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int nvec = D / 8;
   for (int row = blockIdx.x; row < T; row += gridDim.x) {
     const __nv_bfloat16* xr = x + static_cast<size_t>(row) * D;

@@ -76,6 +76,7 @@ def _declare(lib):
       "tx_sample": [P, I, L, I, I, F, I, ctypes.c_ulonglong, P, L, P, I, P, P, P],
       "tx_sample_filtered": [P, I, L, I, I, F, I, F, ctypes.c_ulonglong, P, L, P, I, P, P, P],
       "tx_gemm_skinny_flag_blocks": [],
+      "tx_gemm_skinny_set_pdl": [I],
       "tx_gemm_skinny": [P, P, P, P, P, I, I, I, L, L, L, L, F, I, I, P, I, I, I, ctypes.POINTER(P),
                          ctypes.POINTER(P), L, P, P, L, P],
       "tx_logprob_fwd": [P, I, L, P, P, P, P, I, I, F, F, P],
