@@ -229,3 +229,30 @@ def test_frozenlake_environment_and_oracle():
   assert fl.parse_move("first Up, then ```Down```") == "down"
   agent = frozenlake.FrozenLakeAgent()
   assert "frozen lake" in agent.system_prompt
+
+
+def test_function_tool_schema_freeze_and_ordered_parallel_execution():
+  from tunix_b200.rl.agentic.tools import base_tool, tool_manager
+
+  def add(a: int, b: int = 1):
+    """Adds two integers."""
+    return {"sum": a + b}
+
+  tool = base_tool.FunctionTool(add)
+  fn = tool.get_json_schema()["function"]
+  assert fn["name"] == "add" and fn["description"] == "Adds two integers."
+  assert fn["parameters"]["required"] == ["a"] and fn["parameters"]["properties"]["b"]["type"] == "integer"
+  with pytest.raises(AttributeError):
+    tool.name = "other"                      # frozen once the outermost constructor returned
+  mgr = tool_manager.ToolManager({})
+  mgr.register_mcp_tool(tool)
+  calls = []
+  for i in range(5):
+    c = base_tool.ToolCall(name="add", arguments={"a": i})
+    c.id = f"call{i}"
+    calls.append(c)
+  bad = base_tool.ToolCall(name="nope", arguments={})
+  bad.id = "bad"
+  out = mgr.execute_calls(calls + [bad], parallel=True)
+  assert list(out) == [f"call{i}" for i in range(5)] + ["bad"]
+  assert out["call3"] == '{"sum": 4}' and "not registered" in out["bad"]

@@ -106,3 +106,20 @@ def test_tensor_parallel_rollout_with_kernel_weight_sync_two_gpus(kernel_lib, tm
       assert res[f"lp_err_{key}"] < 0.08, res
     assert res["captured_own_graph"] and res["captured_peer_graph"], res
     assert abs(res["update_ratio"] - 1.5) < 0.02, res
+
+
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+def test_sequence_parallel_peer_pull_two_gpus(kernel_lib, tmp_path, layout):
+  """Rows split along the sequence over 2 GPUs; keys / values (and their gradients) move with the peer copy
+  kernel. Logits and reduced parameter gradients equal the unsharded bf16 model's within bf16 error."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  out = str(tmp_path / "sp.pt")
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+  cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+         "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "_sp_worker.py"), "--out", out, "--layout", layout,
+         "--backend", "nccl"]
+  r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+  assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+  for res in torch.load(out, weights_only=False):
+    assert res["fwd"] < 3e-2 and res["grads"] < 6e-2, res

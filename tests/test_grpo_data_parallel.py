@@ -3,6 +3,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
@@ -50,12 +51,14 @@ def test_tensor_parallel_two_ranks_cpu(tmp_path):
     assert res["vp_dhead"] < 1e-4 and res["vp_dembed"] < 1e-4, res
 
 
-def test_sequence_parallel_two_ranks_cpu(tmp_path):
+@pytest.mark.parametrize("layout", ["contiguous", "zigzag"])
+def test_sequence_parallel_two_ranks_cpu(tmp_path, layout):
   """Rows split along the sequence over 2 ranks (all-gathered K/V, causal prefix) give the full model's logits
   and, after the gradient reduction over the axis, its parameter gradients."""
   out = str(tmp_path / "sp.pt")
   cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-         "127.0.0.1", "--master-port", "29671", os.path.join(HERE, "_sp_worker.py"), "--out", out]
+         "127.0.0.1", "--master-port", "29671", os.path.join(HERE, "_sp_worker.py"), "--out", out,
+         "--layout", layout]
   r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2"), capture_output=True, text=True, timeout=600)
   assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
   for res in torch.load(out, weights_only=False):

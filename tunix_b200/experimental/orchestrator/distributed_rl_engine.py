@@ -58,37 +58,6 @@ class DistributedRLEngine(rl_engine_interface.AbstractRLEngine):
       await worker.dispatch_task(r.request_id, "generate", requests=[r])
     return [r.request_id for r in requests]
 
-  async def dispatch_rollouts(self, prompts, *, group_size: int = 1, policy_version: int = 0, generation_args=None,
-                              route_metadata=None, **kwargs) -> List[str]:
-    base_md = {**(route_metadata or {}), **(kwargs.get("metadata") or {})}
-    base_gen = generation_args.as_kwargs() if generation_args else {}
-    version = kwargs.get("policy_version", policy_version)
-    reqs: List[datatypes.RolloutRequest] = []
-    for idx, p in enumerate(prompts):
-      if isinstance(p, datatypes.RolloutRequest):
-        reqs.append(p)
-        continue
-      get = (lambda k, d=None: p.get(k, d)) if isinstance(p, Mapping) else (lambda k, d=None: getattr(p, k, d))
-      pid = get("prompt_id")
-      if not pid:
-        raise ValueError(f"Prompt at index {idx} lacks 'prompt_id'. Every prompt item dispatched to "
-                         "DistributedRLEngine must provide a unique, collision-free 'prompt_id' (as an attribute or "
-                         "dict key).")
-      pid = str(pid)
-      item_md = dict(get("metadata") or {})
-      gid = str(get("group_id") or item_md.get("group_id") or pid)
-      raw = get("prompt", p) if isinstance(p, Mapping) else getattr(p, "prompt", p)
-      for g in range(group_size):
-        md = {**base_md, **item_md, "group_id": gid, "pair_index": g}
-        md.setdefault("prefix_hash", gid)
-        if isinstance(md.get("env_config"), Mapping):
-          md["env_config"] = {"group_id": gid, **md["env_config"], "pair_index": g, "policy_version": version}
-        reqs.append(datatypes.RolloutRequest(
-            request_id=f"req_{pid}_{g}_v{version}", prompt=raw, prompt_id=pid, group_offset_id=str(g),
-            target_policy_version=version, generation_kwargs={**base_gen, **dict(get("generation_kwargs") or {})},
-            max_turns=get("max_turns", 10), metadata=md))
-    return await self.dispatch_rollout_requests(reqs)
-
   async def poll_rollouts(self, timeout_s: float = remote_execution.LONG_POLL_TIMEOUT_S):
     if not self._rollout_workers:
       return []

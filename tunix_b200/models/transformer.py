@@ -269,8 +269,14 @@ class Attention(nn.Module):
     if sp_group is not None:
       if cache is not None or attn_mask is not None:
         raise NotImplementedError("sequence parallelism covers causal training / scoring without a KV cache")
+      if self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size:
+        raise NotImplementedError("sequence parallelism does not cover sliding-window layers")
       from ..dist import sp as sp_lib
-      k, v = sp_lib.causal_prefix(k, v, sp_group, T)    # keys [0, (rank + 1) T); our queries are its last T rows
+      # every held query chunk attends the key prefix that ends with it (queries aligned to the end of the keys)
+      o = sp_lib.attention(q, k, v, sp_group, self.sp_layout,
+                           lambda qc, kc, vc: F.attention(qc, kc, vc, mask=None, causal=True, scale=cfg.attn_scale,
+                                                          softcap=cfg.attn_logits_soft_cap or 0.0))
+      return self.o_proj(o.reshape(B, T, N * H)), None
 
     mask = attn_mask
     causal = mask is None and cache is None

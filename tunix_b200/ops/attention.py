@@ -102,6 +102,11 @@ def attention_cuda(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, mask: O
   qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
   attn_mask = None
   is_causal = causal and mask is None
+  if is_causal and q.shape[1] != k.shape[1]:
+    # the library's causal flag aligns the triangle to the first key; here queries are the LAST rows of the keys
+    T, S = q.shape[1], k.shape[1]
+    mask = torch.ones(T, S, dtype=torch.bool, device=q.device).tril(S - T)[None]
+    is_causal = False
   if mask is not None:
     attn_mask = mask[:, None, :, :]
   o = F.scaled_dot_product_attention(qt, kt, vt, attn_mask=attn_mask, is_causal=is_causal, scale=scale,

@@ -1,5 +1,5 @@
-"""Single-turn environment: the first action ends the episode and is scored by the reward
-function (tunix/rl/agentic/environments/task_environment.py:29-117)."""
+"""Single-turn environment: the first action ends the episode and is scored by the reward function
+(tunix/rl/agentic/environments/task_environment.py:29-117)."""
 from __future__ import annotations
 
 import logging
@@ -8,8 +8,11 @@ from typing import Any, Dict
 from ..agents import agent_types
 from . import base_environment
 
+_PASSED_BY_LEARNER = ("reward_fn", "group_id")
+
 
 class TaskEnvironment(base_environment.BaseTaskEnv):
+
   def __init__(self, single_example: Dict[str, Any] = None, *, reward_fn=None, **kwargs):
     if reward_fn is None:
       logging.warning("No reward_fn provided.")
@@ -19,14 +22,11 @@ class TaskEnvironment(base_environment.BaseTaskEnv):
     return self.task
 
   def _step_impl(self, action: Any) -> base_environment.EnvStepResult:
-    if isinstance(action, agent_types.Action):
-      action = action.action
-    reward = self.reward_fn(task=self.task, action=action) if self.reward_fn is not None else 0.0
-    return base_environment.EnvStepResult(observation={}, reward=reward, done=True, info={"response": action})
+    return self.final(action.action if isinstance(action, agent_types.Action) else action)
 
   @classmethod
   def from_dict(cls, env_args: Dict[str, Any]) -> "TaskEnvironment":
-    env_args = dict(env_args)
-    reward_fn = env_args.pop("reward_fn", None)
-    group_id = env_args.pop("group_id", None)
-    return cls(single_example=env_args, reward_fn=reward_fn, group_id=group_id)
+    """`env_args` is the task record itself, with the learner's extras mixed in under reserved keys."""
+    extras = {k: env_args.get(k) for k in _PASSED_BY_LEARNER}
+    record = {k: v for k, v in env_args.items() if k not in _PASSED_BY_LEARNER}
+    return cls(single_example=record, **extras)

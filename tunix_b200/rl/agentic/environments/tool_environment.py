@@ -1,19 +1,46 @@
-"""Multi-turn tool environment (tunix/rl/agentic/environments/tool_environment.py:36-248): an
-action is a final answer (string, or a `finish` call) that ends the episode and is scored, or a
-list of tool calls whose outputs become the next observation."""
+"""Multi-turn tool environment (tunix/rl/agentic/environments/tool_environment.py:36-248).
+
+An action is normalised into a list of OpenAI-style tool calls or a plain string. A string, or a call to the
+pseudo-tool `finish`, is the final answer: the episode ends and the answer is scored. Anything else is executed
+through the `ToolManager` (calls of one turn run in parallel) and the outputs, keyed by call id, become the next
+observation."""
 from __future__ import annotations
 
 import json
 import logging
 import uuid
-from typing import Any, Dict, List, Optional, Type
+from typing import Any, Dict, List, Optional, Type, Union
 
 from ..agents import agent_types
 from ..tools import base_tool, tool_manager
 from . import base_environment
 
+FINISH = "finish"
+
+
+def _arguments(call: Dict[str, Any]) -> Any:
+  """Arguments of a call as a dict where they parse as JSON, else the raw string."""
+  raw = call["function"].get("arguments", {})
+  if not isinstance(raw, str):
+    return raw
+  try:
+    return json.loads(raw)
+  except json.JSONDecodeError:
+    return raw
+
+
+def _calls_of(action: Any) -> Union[str, List[Dict[str, Any]]]:
+  if isinstance(action, agent_types.Action):
+    action = action.action
+  if action is None:
+    return []
+  if isinstance(action, dict):
+    return [action]
+  return action
+
 
 class ToolEnvironment(base_environment.BaseTaskEnv):
+
   def __init__(self, task: Optional[Dict[str, Any]] = None, *, tool_map: Dict[str, Type[base_tool.BaseTool]],
                reward_fn=None, max_steps: int = 10, **kwargs):
     if reward_fn is None:
@@ -25,55 +52,39 @@ class ToolEnvironment(base_environment.BaseTaskEnv):
     return self.task
 
   @staticmethod
-  def _is_finish(call: Dict[str, Any]) -> bool:
-    return call.get("function", {}).get("name") == "finish"
+  def _finish_call(calls: Any) -> Optional[Dict[str, Any]]:
+    if not isinstance(calls, list):
+      return None
+    return next((c for c in calls if c.get("function", {}).get("name") == FINISH), None)
 
-  def _step_impl(self, action: Any) -> base_environment.EnvStepResult:
-    if isinstance(action, agent_types.Action):
-      action = action.action
-    if action is None:
-      action = []
-    if isinstance(action, dict):
-      action = [action]
-    done = isinstance(action, str) or (isinstance(action, list) and any(self._is_finish(c) for c in action))
-    if done:
-      answer = self._extract_llm_answer(action)
-      reward = self.reward_fn(task=self.task, action=answer) if self.reward_fn is not None else 0.0
-      return base_environment.EnvStepResult(observation={}, reward=reward, done=True, info={"response": action})
-    return base_environment.EnvStepResult(observation={"tool_outputs": self._execute_tool_calls(action)}, reward=0.0,
-                                          done=False, info={"response": action})
-
-  @staticmethod
-  def _extract_llm_answer(action: Any) -> str:
+  @classmethod
+  def _extract_llm_answer(cls, action: Any) -> str:
     if isinstance(action, str):
       return action
-    if isinstance(action, list):
-      for call in action:
-        if ToolEnvironment._is_finish(call):
-          args = call["function"].get("arguments", {})
-          if isinstance(args, str):
-            try:
-              args = json.loads(args)
-            except json.JSONDecodeError:
-              return args
-          return args.get("response", "")
-    return str(action)
+    fin = cls._finish_call(action)
+    if fin is None:
+      return str(action)
+    args = _arguments(fin)
+    return args if isinstance(args, str) else args.get("response", "")
+
+  def _step_impl(self, action: Any) -> base_environment.EnvStepResult:
+    calls = _calls_of(action)
+    if isinstance(calls, str) or self._finish_call(calls) is not None:
+      return self.final(self._extract_llm_answer(calls), response=calls)
+    return self.turn({"tool_outputs": self._execute_tool_calls(calls)}, response=calls)
 
   def _execute_tool_calls(self, tool_calls: List[Dict[str, Any]]) -> Dict[str, str]:
-    objs = []
-    for tc in tool_calls:
-      args = tc["function"]["arguments"]
-      if isinstance(args, str):
-        args = json.loads(args)
-      obj = base_tool.ToolCall(name=tc["function"]["name"], arguments=args)
-      obj.id = tc.get("id") or str(uuid.uuid4())
-      objs.append(obj)
-    return self.tool_manager.execute_calls(objs, parallel=True)
+    batch = []
+    for call in tool_calls:
+      args = call["function"]["arguments"]
+      request = base_tool.ToolCall(name=call["function"]["name"], arguments=json.loads(args) if isinstance(args, str) else args)
+      request.id = call.get("id") or str(uuid.uuid4())
+      batch.append(request)
+    return self.tool_manager.execute_calls(batch, parallel=True)
 
   @classmethod
   def from_dict(cls, env_args: Dict[str, Any]) -> "ToolEnvironment":
-    env_args = dict(env_args)
-    tool_map = env_args.pop("tool_map", None)
-    reward_fn = env_args.pop("reward_fn", None)
-    max_steps = env_args.pop("max_steps", 10)
-    return cls(task=env_args, tool_map=tool_map, reward_fn=reward_fn, max_steps=max_steps)
+    """`env_args` is the task record with `tool_map`, `reward_fn` and `max_steps` mixed in."""
+    record = dict(env_args)
+    return cls(tool_map=record.pop("tool_map", None), reward_fn=record.pop("reward_fn", None),
+               max_steps=record.pop("max_steps", 10), task=record)

@@ -53,6 +53,7 @@ class GroupQueueManager(Generic[T]):
     self.group_size, self.group_fn, self.filter_fn = group_size, group_fn, filter_fn
     self._open_groups: Dict[Hashable, List[T]] = collections.defaultdict(list)
     self._outbox: Deque[T] = collections.deque()
+    self._runs: Deque[int] = collections.deque()      # lengths of the groups that make up the outbox, in order
     self._rejected: List[List[T]] = []
     self._draining = False
     self._poison: Optional[BaseException] = None
@@ -83,6 +84,7 @@ class GroupQueueManager(Generic[T]):
         self._rejected.append(dropped)
       if kept:
         self._outbox.extend(kept)
+        self._runs.append(len(kept))
         self._changed.notify_all()
 
   async def put_exception(self, exc: BaseException) -> None:
@@ -100,9 +102,28 @@ class GroupQueueManager(Generic[T]):
         if self._poison is not None:
           raise self._poison
         while self._outbox and len(out) < batch_size:
-          out.append(self._outbox.popleft())
+          out.append(self._take_one())
         if len(out) >= batch_size or self._draining:
           return out
+        await self._changed.wait()
+
+  def _take_one(self) -> T:
+    self._runs[0] -= 1
+    if self._runs[0] == 0:
+      self._runs.popleft()
+    return self._outbox.popleft()
+
+  async def get_group(self) -> List[T]:
+    """The next whole group in release order (what is left of it, if `get_batch` already took its head); waits
+    for one. Empty only when the queue is being cleared."""
+    async with self._changed:
+      while True:
+        if self._poison is not None:
+          raise self._poison
+        if self._runs:
+          return [self._take_one() for _ in range(self._runs[0])]
+        if self._draining:
+          return []
         await self._changed.wait()
 
   async def get_filtered_groups(self) -> List[List[T]]:
@@ -121,5 +142,6 @@ class GroupQueueManager(Generic[T]):
     async with self._changed:
       self._open_groups.clear()
       self._outbox.clear()
+      self._runs.clear()
       self._rejected = []
       self._poison, self._draining = None, False

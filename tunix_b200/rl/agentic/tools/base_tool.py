@@ -1,11 +1,19 @@
-"""Tool interface (tunix/rl/agentic/tools/base_tool.py:30-216). Tools are stateless and frozen
-after construction, so one instance can serve concurrent episodes."""
+"""Tool interface (tunix/rl/agentic/tools/base_tool.py:30-216).
+
+A tool has a name, a one-line description, an OpenAI function-calling schema and an `apply` (or `apply_async`)
+that returns a `ToolOutput`. Instances are shared between concurrent episodes, so they are frozen once the
+outermost constructor returns: every subclass `__init__` is wrapped by `__init_subclass__`, which counts
+constructor nesting on the instance and locks attribute assignment when the count falls back to zero.
+`FunctionTool` turns a plain Python function into a tool, deriving the parameter schema from its signature.
+"""
 from __future__ import annotations
 
 import abc
 import dataclasses
+import functools
+import inspect
 import json
-from typing import Any, Dict, List, Optional, Union
+from typing import Any, Callable, Dict, List, Optional, Union
 
 
 @dataclasses.dataclass
@@ -21,33 +29,53 @@ class ToolOutput:
   error: Optional[str] = None
   metadata: Optional[Dict[str, Any]] = None
 
-  def __repr__(self) -> str:
+  def render(self) -> str:
+    """What the model reads: the error if there is one, JSON for structured output, else the text."""
     if self.error:
       return f"Error: {self.error}"
     if self.output is None:
       return ""
-    if isinstance(self.output, (dict, list)):
-      return json.dumps(self.output)
-    return str(self.output)
+    return json.dumps(self.output) if isinstance(self.output, (dict, list)) else str(self.output)
 
-  __str__ = __repr__
+  __repr__ = __str__ = render
 
 
-class _FreezeAfterInit(abc.ABCMeta):
-  def __call__(cls, *a, **k):
-    obj = super().__call__(*a, **k)
-    object.__setattr__(obj, "_locked", True)
-    return obj
+def function_schema(name: str, description: str, parameters: Optional[Dict[str, Any]] = None) -> Dict[str, Any]:
+  return {"type": "function", "function": {"name": name, "description": description,
+                                           "parameters": parameters if parameters is not None else {}}}
 
 
-class BaseTool(metaclass=_FreezeAfterInit):
+class BaseTool(abc.ABC):
+  _ctor_depth = 0
+  _frozen = False
+
+  def __init_subclass__(cls, **kwargs):
+    super().__init_subclass__(**kwargs)
+    if "__init__" in cls.__dict__:
+      cls.__init__ = BaseTool._freezing(cls.__dict__["__init__"])
+
+  @staticmethod
+  def _freezing(init: Callable[..., None]) -> Callable[..., None]:
+    @functools.wraps(init)
+    def wrapped(self, *args, **kwargs):
+      object.__setattr__(self, "_ctor_depth", self._ctor_depth + 1)
+      try:
+        init(self, *args, **kwargs)
+      finally:
+        object.__setattr__(self, "_ctor_depth", self._ctor_depth - 1)
+        if self._ctor_depth == 0:
+          object.__setattr__(self, "_frozen", True)
+    return wrapped
+
   def __init__(self, name: str, description: str):
     self.name = name
     self.description = description
+    if type(self).__init__ is BaseTool.__init__:      # no subclass constructor ran: freeze here
+      object.__setattr__(self, "_frozen", True)
 
   def __setattr__(self, name: str, value: Any):
-    if getattr(self, "_locked", False):
-      raise AttributeError(f"Cannot modify immutable {self.__class__.__name__} instance after initialization "
+    if self._frozen:
+      raise AttributeError(f"Cannot modify immutable {type(self).__name__} instance after initialization "
                            f"(attempted to set '{name}')")
     object.__setattr__(self, name, value)
 
@@ -56,11 +84,36 @@ class BaseTool(metaclass=_FreezeAfterInit):
     """OpenAI function-calling schema: {"type": "function", "function": {name, description, parameters}}."""
 
   def to_mcp_json(self) -> Dict[str, Any]:
-    return {"type": "function", "function": {"name": self.name, "description": self.description,
-                                             "parameters": getattr(self, "inputSchema", {})}}
+    return function_schema(self.name, self.description, getattr(self, "inputSchema", {}))
 
   def apply(self, **kwargs) -> ToolOutput:
     raise NotImplementedError("Tool must implement either `apply()` or `apply_async()`")
 
   async def apply_async(self, **kwargs) -> ToolOutput:
     raise NotImplementedError("Tool must implement either `apply()` or `apply_async()`")
+
+
+_JSON_TYPES = {int: "integer", float: "number", bool: "boolean", str: "string", list: "array", dict: "object"}
+
+
+class FunctionTool(BaseTool):
+  """A tool made from a function: parameters and their JSON types come from the signature, the description
+  from the first docstring line (unless given), the output is whatever the function returns."""
+
+  def __init__(self, fn: Callable[..., Any], name: Optional[str] = None, description: Optional[str] = None):
+    super().__init__(name or fn.__name__, description or (inspect.getdoc(fn) or "").split("\n")[0])
+    self.fn = fn
+    props, required = {}, []
+    for pname, p in inspect.signature(fn).parameters.items():
+      if p.kind in (p.VAR_POSITIONAL, p.VAR_KEYWORD):
+        continue
+      props[pname] = {"type": _JSON_TYPES.get(p.annotation, "string")}
+      if p.default is p.empty:
+        required.append(pname)
+    self.inputSchema = {"type": "object", "properties": props, "required": required}
+
+  def get_json_schema(self) -> Dict[str, Any]:
+    return self.to_mcp_json()
+
+  def apply(self, **kwargs) -> ToolOutput:
+    return ToolOutput(name=self.name, output=self.fn(**kwargs))
