@@ -1,21 +1,29 @@
 """Incremental chat-template rendering (tunix/rl/agentic/parser/chat_template_parser/parser.py:30-411).
 
-A multi-turn episode is tokenised message by message, so each parser must render one message
-such that the concatenation of the pieces equals the template applied to the whole
-conversation: `parse(msgs, is_first_msg=True)` emits the conversation prefix (BOS, default
-system prompt), later calls start with the message separator that the previous turn's
-end-of-turn token did not emit. Message content is stripped of the template's own control
-tokens first.
+A multi-turn episode is tokenised message by message, so a parser must render one message such that the
+concatenation of the pieces equals the template applied to the whole conversation: `parse(msgs,
+is_first_msg=True)` emits the conversation preamble (BOS, default system prompt), later calls start with the
+separator that the previous turn's end-of-turn token did not emit. Message content is stripped of the
+template's own control tokens first.
+
+A template is data plus a few hooks. The data is `TokenConfig`; from it `frames()` derives, per role, the text
+that opens and closes a turn. The one renderer (`BaseChatTemplateParser.parse`) is
+`preamble + separator.join(open + content + close for each message) + generation prompt`; model families
+override `frames()`, `preamble()`, `normalise()` (message list rewriting, e.g. Gemma's missing system role) or
+`body()` (content clean-up) where their template deviates.
 """
 from __future__ import annotations
 
 import abc
 import dataclasses
-from typing import Dict, List, Tuple
+from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
 
 from .....utils import token_sanitization
+
+Message = Dict[str, str]
+Frame = Tuple[str, str]            # (text before the content, text after it)
 
 
 @dataclasses.dataclass
@@ -32,68 +40,83 @@ class TokenConfig:
   tool_response_end_token: str = ""
   message_separator: str = ""
 
+  def control_tokens(self) -> set:
+    return {v for k, v in dataclasses.asdict(self).items() if k != "message_separator" and isinstance(v, str) and v}
+
 
 class BaseChatTemplateParser(abc.ABC):
+
   def __init__(self, tokenizer, enable_thinking: bool = True):
     self.tokenizer = tokenizer
     self.enable_thinking = enable_thinking
     self.tokens = self._init_tokens()
     self.generation_prompt = self._init_generation_prompt()
-    self._tokens_to_sanitize = {v for k, v in dataclasses.asdict(self.tokens).items()
-                                if k != "message_separator" and isinstance(v, str) and v}
+    self._tokens_to_sanitize = self.tokens.control_tokens()
+    self._frames = self.frames()
 
+  # ---- what a family defines
   @abc.abstractmethod
   def _init_tokens(self) -> TokenConfig: ...
 
-  @abc.abstractmethod
-  def _init_generation_prompt(self) -> str: ...
+  def _init_generation_prompt(self) -> str:
+    return self.tokens.assistant_token
 
-  def parse(self, messages: List[Dict[str, str]], add_generation_prompt: bool = False,
-            is_first_msg: bool = False) -> str:
-    parts = []
-    if is_first_msg:
-      head = self._handle_first_message(messages)
-      if head:
-        parts.append(head)
-    parts += [self._parse_message(m) for m in messages]
-    if add_generation_prompt:
-      parts.append(self.generation_prompt)
-    sep = self.tokens.message_separator
-    out = sep.join(parts)
-    return sep + out if (not is_first_msg and out) else out
+  def frames(self) -> Dict[str, Frame]:
+    """Opening and closing text of a turn, per role. A tool result is a user turn wrapping the response markers."""
+    t = self.tokens
+    return {"system": (t.system_token, t.eot_token), "user": (t.user_token, t.eot_token),
+            "assistant": (t.assistant_token, t.eot_token),
+            "tool": (t.user_token + t.tool_response_start_token, t.tool_response_end_token + t.eot_token)}
 
-  def _handle_first_message(self, messages: List[Dict[str, str]]) -> str:
+  def preamble(self, messages: Sequence[Message]) -> str:
+    """Text in front of the first message of a conversation."""
     return self.tokens.bos_token
 
-  def _parse_message(self, message: Dict[str, str]) -> str:
-    content = token_sanitization.sanitize_control_tokens(
-        message["content"], extra_tokens=self._tokens_to_sanitize, include_default=not self._tokens_to_sanitize)
-    render = {"system": self._parse_system, "user": self._parse_user, "assistant": self._parse_assistant,
-              "tool": self._parse_tool}.get(message["role"])
-    if render is None:
-      raise NotImplementedError(f"Unsupported message role: {message['role']}")
-    return render(content)
+  def normalise(self, messages: Sequence[Message]) -> Sequence[Message]:
+    return messages
 
-  def _parse_system(self, content: str) -> str:
-    return self.tokens.system_token + content + self.tokens.eot_token
+  def body(self, role: str, content: str) -> str:
+    return content
 
-  def _parse_user(self, content: str) -> str:
-    return self.tokens.user_token + content + self.tokens.eot_token
+  # ---- the renderer
+  def _clean(self, content: str) -> str:
+    return token_sanitization.sanitize_control_tokens(content, extra_tokens=self._tokens_to_sanitize,
+                                                      include_default=not self._tokens_to_sanitize)
 
-  def _parse_assistant(self, content: str) -> str:
-    return self.tokens.assistant_token + content + self.tokens.eot_token
+  def _parse_message(self, message: Message) -> str:
+    role = message["role"]
+    if role not in self._frames:
+      raise NotImplementedError(f"Unsupported message role: {role}")
+    return self.render_turn(role, self.body(role, self._clean(message["content"])))
 
-  def _parse_tool(self, content: str) -> str:
-    t = self.tokens
-    return t.user_token + t.tool_response_start_token + content + t.tool_response_end_token + t.eot_token
+  def render_turn(self, role: str, content: str) -> str:
+    before, after = self._frames[role]
+    return before + content + after
 
+  def parse(self, messages: List[Message], add_generation_prompt: bool = False, is_first_msg: bool = False) -> str:
+    pieces = [self._parse_message(m) for m in self.normalise(messages)]
+    if is_first_msg:
+      head = self.preamble(messages)
+      if head:
+        pieces.insert(0, head)
+    if add_generation_prompt:
+      pieces.append(self.generation_prompt)
+    sep = self.tokens.message_separator
+    text = sep.join(pieces)
+    return text if (is_first_msg or not text) else sep + text
+
+  # ---- what follows an assistant turn
   @property
   def newline_tokens(self) -> List[int]:
     return []
 
   def update_assistant_end_tokens(self, tokens: np.ndarray) -> Tuple[np.ndarray, int]:
-    """Tokens the template puts after an assistant turn that the model itself does not emit."""
-    return tokens, 0
+    """Tokens the template puts after an assistant turn that the model itself does not emit: (tokens with them
+    appended, how many were appended)."""
+    extra = self.newline_tokens
+    if not extra:
+      return tokens, 0
+    return np.concatenate([tokens, np.asarray(extra, dtype=np.int32)], axis=0), len(extra)
 
 
 class DefaultChatTemplateParser(BaseChatTemplateParser):
@@ -102,112 +125,119 @@ class DefaultChatTemplateParser(BaseChatTemplateParser):
   def _init_tokens(self) -> TokenConfig:
     return TokenConfig()
 
-  def _init_generation_prompt(self) -> str:
-    return ""
-
   def parse(self, messages, add_generation_prompt: bool = False, is_first_msg: bool = False) -> str:
     return self.tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=add_generation_prompt)
 
 
 class QwenChatTemplateParser(BaseChatTemplateParser):
+  DEFAULT_SYSTEM = "You are Qwen, created by Alibaba Cloud. You are a helpful assistant."
+  NO_THINKING = "<think>\n\n</think>\n\n"
+
   def _init_tokens(self) -> TokenConfig:
-    assistant = "<|im_start|>assistant\n" + ("" if self.enable_thinking else "<think>\n\n</think>\n\n")
+    special = lambda name: getattr(self.tokenizer, name, "") or ""
     return TokenConfig(
-        bos_token=getattr(self.tokenizer, "bos_token", "") or "", eos_token=getattr(self.tokenizer, "eos_token", "") or "",
-        eot_token="<|im_end|>", system_token="<|im_start|>system\n", user_token="<|im_start|>user\n",
-        assistant_token=assistant, tool_start_token="\n<tool_call>\n", tool_end_token="\n</tool_call>",
+        bos_token=special("bos_token"), eos_token=special("eos_token"), eot_token="<|im_end|>",
+        system_token="<|im_start|>system\n", user_token="<|im_start|>user\n",
+        assistant_token="<|im_start|>assistant\n" + ("" if self.enable_thinking else self.NO_THINKING),
+        tool_start_token="\n<tool_call>\n", tool_end_token="\n</tool_call>",
         tool_response_start_token="<tool_response>\n", tool_response_end_token="\n</tool_response>",
         message_separator="\n")
 
-  def _init_generation_prompt(self) -> str:
-    return self.tokens.assistant_token
-
-  def _handle_first_message(self, messages) -> str:
-    if messages[0]["role"] != "system":
-      return self._parse_system("You are Qwen, created by Alibaba Cloud. You are a helpful assistant.")
-    return ""
+  def preamble(self, messages) -> str:
+    """Qwen's template supplies a system prompt when the conversation has none (and prints no BOS)."""
+    return "" if messages[0]["role"] == "system" else self.render_turn("system", self.DEFAULT_SYSTEM)
 
 
 class LlamaChatTemplateParser(BaseChatTemplateParser):
-  def _init_tokens(self) -> TokenConfig:
-    hdr = lambda role: f"<|start_header_id|>{role}<|end_header_id|>\n\n"
-    return TokenConfig(bos_token="<|begin_of_text|>", eot_token="<|eot_id|>", system_token=hdr("system"),
-                       user_token=hdr("user"), assistant_token=hdr("assistant"), tool_start_token=hdr("tool"),
-                       tool_end_token="<|eot_id|>", tool_response_start_token=hdr("tool_response"),
-                       tool_response_end_token="<|eot_id|>")
 
-  def _init_generation_prompt(self) -> str:
-    return self.tokens.assistant_token
+  @staticmethod
+  def _header(role: str) -> str:
+    return f"<|start_header_id|>{role}<|end_header_id|>\n\n"
+
+  def _init_tokens(self) -> TokenConfig:
+    h = self._header
+    return TokenConfig(bos_token="<|begin_of_text|>", eot_token="<|eot_id|>", system_token=h("system"),
+                       user_token=h("user"), assistant_token=h("assistant"), tool_start_token=h("tool"),
+                       tool_end_token="<|eot_id|>", tool_response_start_token=h("tool_response"),
+                       tool_response_end_token="<|eot_id|>")
 
 
 class GemmaChatTemplateParser(BaseChatTemplateParser):
-  """Gemma has no system role: a leading system message is merged into the first user turn."""
+  """Gemma has no system role: a leading system message is merged into the first user turn. Turns already end
+  with a newline, there is no separator and no preamble, and an assistant turn is left open."""
 
   def _init_tokens(self) -> TokenConfig:
     return TokenConfig(bos_token="<bos>", eot_token="<end_of_turn>\n", user_token="<start_of_turn>user\n",
                        assistant_token="<start_of_turn>model\n")
 
-  def _init_generation_prompt(self) -> str:
-    return self.tokens.assistant_token
+  def frames(self) -> Dict[str, Frame]:
+    out = super().frames()
+    out["assistant"] = (self.tokens.assistant_token, "")
+    return out
 
-  def _parse_assistant(self, content: str) -> str:
-    return self.tokens.assistant_token + content
+  def render_turn(self, role: str, content: str) -> str:
+    if role == "system":
+      raise ValueError("Gemma models do not support system messages directly. The system prompt should be the first "
+                       "message and is handled by merging with the first user message.")
+    return super().render_turn(role, content)
 
-  def _parse_system(self, content: str) -> str:
-    raise ValueError("Gemma models do not support system messages directly. The system prompt should be the first "
-                     "message and is handled by merging with the first user message.")
+  def preprocess_messages(self, messages: List[Message]) -> List[Message]:
+    rest = [dict(m) for m in messages]
+    if not rest or rest[0]["role"] != "system":
+      return rest
+    system = rest.pop(0)["content"]
+    if rest and rest[0]["role"] == "user":
+      rest[0]["content"] = system + "\n" + rest[0]["content"]
+      return rest
+    return [{"role": "user", "content": system}] + rest
 
-  def preprocess_messages(self, messages: List[Dict[str, str]]) -> List[Dict[str, str]]:
-    msgs = [dict(m) for m in messages]
-    if msgs and msgs[0]["role"] == "system":
-      system = msgs.pop(0)
-      if msgs and msgs[0]["role"] == "user":
-        msgs[0]["content"] = system["content"] + "\n" + msgs[0]["content"]
-      else:
-        msgs.insert(0, {"role": "user", "content": system["content"]})
-    return msgs
+  normalise = preprocess_messages
 
   def parse(self, messages, add_generation_prompt: bool = False, is_first_msg: bool = False) -> str:
-    out = "".join(self._parse_message(m) for m in self.preprocess_messages(messages))
-    return out + (self.generation_prompt if add_generation_prompt else "")
+    return super().parse(messages, add_generation_prompt=add_generation_prompt, is_first_msg=False)
+
+  def preamble(self, messages) -> str:
+    return ""
 
 
 class Gemma4ChatTemplateParser(BaseChatTemplateParser):
+  TURN_END = "<turn|>"
+  THINK_SYSTEM = "<|turn>system\n<|think|><turn|>\n"
+
   def __init__(self, tokenizer, enable_thinking: bool = True):
     super().__init__(tokenizer, enable_thinking=enable_thinking)
-    self._tokens_to_sanitize.add("<turn|>")
+    self._tokens_to_sanitize.add(self.TURN_END)
 
   def _init_tokens(self) -> TokenConfig:
+    think = self.enable_thinking
     return TokenConfig(
-        bos_token="<bos>", eot_token="<turn|>\n",
-        system_token="<|turn>system\n" + ("<|think|>" if self.enable_thinking else ""),
-        user_token="<|turn>user\n",
-        assistant_token="<|turn>model\n" + ("" if self.enable_thinking else "<|channel>thought\n<channel|>"),
+        bos_token="<bos>", eot_token=self.TURN_END + "\n",
+        system_token="<|turn>system\n" + ("<|think|>" if think else ""), user_token="<|turn>user\n",
+        assistant_token="<|turn>model\n" + ("" if think else "<|channel>thought\n<channel|>"),
         tool_start_token="<|tool_call>", tool_end_token="<tool_call|>", tool_response_start_token="<|tool_response>",
         tool_response_end_token="<tool_response|>", message_separator="")
 
-  def _init_generation_prompt(self) -> str:
-    return self.tokens.assistant_token
+  def frames(self) -> Dict[str, Frame]:
+    out = super().frames()
+    t = self.tokens
+    out["tool"] = (t.tool_response_start_token, t.tool_response_end_token)     # tool results are bare, not user turns
+    return out
 
-  def _handle_first_message(self, messages) -> str:
-    head = self.tokens.bos_token
-    if messages and messages[0]["role"] not in ("system", "developer") and self.enable_thinking:
-      head += "<|turn>system\n<|think|><turn|>\n"
-    return head
+  def preamble(self, messages) -> str:
+    """With thinking on, a conversation without a system turn gets one that only switches thinking on."""
+    needs_switch = self.enable_thinking and messages and messages[0]["role"] not in ("system", "developer")
+    return self.tokens.bos_token + (self.THINK_SYSTEM if needs_switch else "")
 
-  def _parse_tool(self, content: str) -> str:
-    return self.tokens.tool_response_start_token + content + self.tokens.tool_response_end_token
+  def body(self, role: str, content: str) -> str:
+    return content if role == "tool" else content.strip()
 
-  def _parse_system(self, content: str) -> str:
-    return self.tokens.system_token + content.strip() + self.tokens.eot_token
-
-  def _parse_user(self, content: str) -> str:
-    return self.tokens.user_token + content.strip() + self.tokens.eot_token
-
-  def _parse_assistant(self, content: str) -> str:
-    body = content.strip()
-    prefix = "<|turn>model\n" if self.enable_thinking else self.tokens.assistant_token
-    return prefix + body + ("\n" if body.endswith("<turn|>") else self.tokens.eot_token)
+  def render_turn(self, role: str, content: str) -> str:
+    if role != "assistant":
+      return super().render_turn(role, content)
+    # a past assistant turn is replayed without the empty-thought stub; one that already closed its turn gets
+    # only the newline
+    opener = "<|turn>model\n" if self.enable_thinking else self.tokens.assistant_token
+    return opener + content + ("\n" if content.endswith(self.TURN_END) else self.tokens.eot_token)
 
   @property
   def newline_tokens(self) -> List[int]:
@@ -216,13 +246,9 @@ class Gemma4ChatTemplateParser(BaseChatTemplateParser):
     except TypeError:
       ids = self.tokenizer.encode("\n")
     special = set()
-    for attr in ("bos_id", "eos_id"):
-      v = getattr(self.tokenizer, attr, None)
-      v = v() if callable(v) else v
-      if v is not None:
-        special.add(v)
+    for name in ("bos_id", "eos_id"):
+      value = getattr(self.tokenizer, name, None)
+      value = value() if callable(value) else value
+      if value is not None:
+        special.add(value)
     return [t for t in ids if t not in special]
-
-  def update_assistant_end_tokens(self, tokens: np.ndarray) -> Tuple[np.ndarray, int]:
-    nl = self.newline_tokens
-    return np.concatenate([tokens, np.asarray(nl, dtype=np.int32)], axis=0), len(nl)
