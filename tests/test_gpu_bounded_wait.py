@@ -37,3 +37,25 @@ def test_peer_barrier_gives_up_and_context_survives():
   torch.cuda.synchronize()
   _lib.check_status(dev)
   assert float((torch.ones(8, device=dev) * 2).sum()) == 16.0
+
+
+def test_device_lane_span_is_closed_by_a_cuda_timing_event(kernel_lib):
+  """A device-lane span over CUDA work ends at the device timestamp of an event recorded behind the work, mapped
+  onto the host clock; no waiter thread is involved."""
+  import time
+  from tunix_b200.perf.experimental import timeline
+  lane = timeline.AsyncTimeline("cuda0", time.perf_counter())
+  a = torch.randn(4096, 4096, device="cuda")
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  begin = time.perf_counter()
+  e0.record()
+  for _ in range(20):
+    a = a @ a * 1e-3
+  e1.record()
+  lane.span("work", begin, [a])
+  assert lane._resolver is None and not lane.cur_step          # nothing resolved, nothing blocked yet
+  lane.wait_pending_spans()
+  (span,) = lane.cur_step.values()
+  device_s = e0.elapsed_time(e1) * 1e-3
+  assert span.ended and span.duration >= 0.8 * device_s and span.duration < device_s + 0.05

@@ -7,11 +7,13 @@
       --process --process_main=a.main --discovery_id=door --discovery_port=12345 \
       --process --process_main=b.main --discovery_addrs=door:12345
 
-A "process" here is a logical one: several given in one invocation run as
-threads of this OS process and share the executor. Flags the launcher does not
-know are passed to the body untouched. A non-zero `SystemExit` from any body
-ends the whole OS process with that code, so an orchestration layer restarts
-the group rather than waiting on the survivors.
+A "process" here is a logical one: several given in one invocation run as threads of this OS process and share
+the executor. The command line is read in two passes: `LaunchPlan.from_argv` takes the launcher's own flag
+(`--process_executor`), cuts the rest at every `--process` marker and resolves each section's `--process_main`
+plus discovery flags; whatever a section's parser does not know goes to the process body untouched. `run_group`
+then starts the bodies and applies the group policy: the first body that leaves with a non-zero `SystemExit`, or
+raises, ends the whole OS process with that code, so an orchestration layer restarts the group rather than waiting
+on the survivors.
 
 Counterpart of tunix/experimental/distributed/runtime/main.py.
 """
@@ -19,96 +21,127 @@ Counterpart of tunix/experimental/distributed/runtime/main.py.
 from __future__ import annotations
 
 import argparse
-import concurrent.futures
 import dataclasses
 import importlib
 import logging
 import os
 import sys
-from typing import Any, Callable
+import threading
+from typing import Any, Callable, List, Optional, Sequence
 
-DEFAULT_EXECUTOR = (
-    "tunix_b200.experimental.distributed.runtime.executor.LocalExecutor")
-
-
-@dataclasses.dataclass(frozen=True)
-class PreparedProcess:
-  main_fn: Callable[..., Any]
-  argv: list[str]
-  context_args: argparse.Namespace
+DEFAULT_EXECUTOR = "tunix_b200.experimental.distributed.runtime.executor.LocalExecutor"
+PROCESS_MARKER = "--process"
+_LOG_FORMAT = "%(asctime)s [%(filename)s:%(lineno)d] %(levelname)s %(message)s"
 
 
 def import_symbol(fqn: str) -> Any:
   """Resolves ``pkg.mod.attr`` (or ``pkg.mod:attr``) to the object."""
   if not fqn:
     raise ValueError("empty symbol name")
-  mod_name, sep, attr = fqn.replace(":", ".").rpartition(".")
-  if not sep:
+  module, dot, attr = fqn.replace(":", ".").rpartition(".")
+  if not dot:
     raise ValueError(f"'{fqn}' is not a fully qualified name")
-  return getattr(importlib.import_module(mod_name), attr)
+  return getattr(importlib.import_module(module), attr)
 
 
-def split_process_argv(argv: list[str]) -> list[list[str]]:
-  if "--process" not in argv:
-    return [argv]
-  out, cur = [], []
+def split_process_argv(argv: Sequence[str]) -> List[List[str]]:
+  """Sections of the command line between `--process` markers (the whole line when there is no marker)."""
+  if PROCESS_MARKER not in argv:
+    return [list(argv)]
+  sections: List[List[str]] = [[]]
   for tok in argv:
-    if tok == "--process":
-      if cur:
-        out.append(cur)
-      cur = []
+    if tok == PROCESS_MARKER:
+      sections.append([])
     else:
-      cur.append(tok)
-  if cur:
-    out.append(cur)
-  return out
+      sections[-1].append(tok)
+  return [s for s in sections if s]
 
 
-def prepare_process(argv: list[str]) -> PreparedProcess:
+def _context_parser() -> argparse.ArgumentParser:
   p = argparse.ArgumentParser(allow_abbrev=False, add_help=False)
   p.add_argument("--process_main", type=str, default="")
   p.add_argument("--discovery_id", type=str, default="")
   p.add_argument("--discovery_port", type=int, default=0)
   p.add_argument("--discovery_addrs", type=str, default="")
-  ctx_args, rest = p.parse_known_args(argv)
+  return p
+
+
+@dataclasses.dataclass(frozen=True)
+class PreparedProcess:
+  main_fn: Callable[..., Any]
+  argv: List[str]
+  context_args: argparse.Namespace
+
+
+def prepare_process(argv: Sequence[str]) -> PreparedProcess:
+  context_args, body_argv = _context_parser().parse_known_args(list(argv))
   try:
-    fn = import_symbol(ctx_args.process_main)
+    body = import_symbol(context_args.process_main)
   except (AttributeError, ImportError, ValueError) as e:
-    raise ValueError(
-        f"Invalid --process_main={ctx_args.process_main}: {e}") from e
-  return PreparedProcess(fn, rest, ctx_args)
+    raise ValueError(f"Invalid --process_main={context_args.process_main}: {e}") from e
+  return PreparedProcess(body, body_argv, context_args)
 
 
-def main(argv: list[str]) -> None:
-  p = argparse.ArgumentParser(allow_abbrev=False, add_help=False)
-  p.add_argument("--process_executor", type=str, default=DEFAULT_EXECUTOR)
-  main_args, rest = p.parse_known_args(argv)
-  rest = rest[1:]
-  executor = import_symbol(main_args.process_executor)()
-  logging.basicConfig(
-      level=logging.INFO, force=True,
-      format="%(asctime)s [%(filename)s:%(lineno)d] %(levelname)s %(message)s")
-  prepared = [prepare_process(a) for a in split_process_argv(rest)]
-  if len(prepared) == 1:
-    one = prepared[0]
-    executor.run(one.main_fn, one.argv, one.context_args)
+@dataclasses.dataclass
+class LaunchPlan:
+  executor: Any
+  processes: List[PreparedProcess]
+
+  @classmethod
+  def from_argv(cls, argv: Sequence[str]) -> "LaunchPlan":
+    p = argparse.ArgumentParser(allow_abbrev=False, add_help=False)
+    p.add_argument("--process_executor", type=str, default=DEFAULT_EXECUTOR)
+    own, rest = p.parse_known_args(list(argv))
+    return cls(executor=import_symbol(own.process_executor)(),
+               processes=[prepare_process(section) for section in split_process_argv(rest[1:])])   # rest[0]: program
+
+
+def _exit_code(exit_: SystemExit) -> int:
+  if isinstance(exit_.code, int):
+    return exit_.code
+  return 0 if exit_.code is None else 1
+
+
+def run_group(plan: LaunchPlan) -> None:
+  """One body: runs on the calling thread. Several: one thread each; the first failure ends the OS process."""
+  if len(plan.processes) == 1:
+    only = plan.processes[0]
+    plan.executor.run(only.main_fn, only.argv, only.context_args)
     return
-  with concurrent.futures.ThreadPoolExecutor(len(prepared)) as pool:
-    futs = [pool.submit(executor.run, q.main_fn, q.argv, q.context_args)
-            for q in prepared]
+  failed = threading.Event()
+  verdict: List[Optional[int]] = [None]
+
+  def body(proc: PreparedProcess) -> None:
     try:
-      for f in concurrent.futures.as_completed(futs):
-        f.result()
+      plan.executor.run(proc.main_fn, proc.argv, proc.context_args)
     except SystemExit as e:
-      code = e.code if isinstance(e.code, int) else (0 if e.code is None else 1)
-      if code != 0:
-        logging.error("a process exited with code %d; ending the group", code)
-        logging.shutdown()
-        os._exit(code)
-    except BaseException:
+      if _exit_code(e) != 0 and verdict[0] is None:
+        logging.error("a process exited with code %d; ending the group", _exit_code(e))
+        verdict[0] = _exit_code(e)
+        failed.set()
+    except BaseException:     # noqa: BLE001
       logging.exception("a process raised; ending the group")
+      if verdict[0] is None:
+        verdict[0] = 1
+      failed.set()
+
+  threads = [threading.Thread(target=body, args=(proc,), name=f"process-{i}", daemon=True)
+             for i, proc in enumerate(plan.processes)]
+  for t in threads:
+    t.start()
+  while any(t.is_alive() for t in threads):
+    if failed.wait(timeout=0.05):
       logging.shutdown()
-      os._exit(1)
+      os._exit(verdict[0] or 1)
+  if failed.is_set():
+    logging.shutdown()
+    os._exit(verdict[0] or 1)
+
+
+def main(argv: Sequence[str]) -> None:
+  plan = LaunchPlan.from_argv(argv)
+  logging.basicConfig(level=logging.INFO, force=True, format=_LOG_FORMAT)
+  run_group(plan)
 
 
 if __name__ == "__main__":

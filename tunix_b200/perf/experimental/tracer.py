@@ -11,7 +11,6 @@ commits the step on every timeline and hands the timelines to the export functio
 """
 from __future__ import annotations
 
-import collections
 import contextlib
 import threading
 import time
@@ -70,89 +69,101 @@ class NoopTracer:
     yield AsyncWaitlist()
 
 
+class _Lanes:
+  """The tracer's timelines by kind: host threads, device lanes, and the queue lanes that receive the waiting
+  part of overlapping device spans. Lanes are created on first use; one lock guards the three tables."""
+
+  def __init__(self, born: float):
+    self.born = born
+    self.lock = threading.RLock()
+    self.host: Dict[str, Timeline] = {}
+    self.device: Dict[str, AsyncTimeline] = {}
+    self.queued: Dict[str, Timeline] = {}
+
+  def _get(self, table: Dict[str, Any], key: str, make: Callable[[str, float], Any]) -> Any:
+    with self.lock:
+      lane = table.get(key)
+      if lane is None:
+        lane = table[key] = make(key, self.born)
+      return lane
+
+  def host_lane(self, key: str) -> Timeline:
+    return self._get(self.host, key, Timeline)
+
+  def device_lane(self, key: str) -> AsyncTimeline:
+    return self._get(self.device, key, AsyncTimeline)
+
+  def queue_lane(self, key: str) -> Timeline:
+    return self._get(self.queued, key, Timeline)
+
+  def everything(self) -> Dict[str, Timeline]:
+    with self.lock:
+      return {**self.host, **self.device, **self.queued}
+
+  def device_lanes(self) -> List[AsyncTimeline]:
+    with self.lock:
+      return list(self.device.values())
+
+
 class PerfTracer(NoopTracer):
 
   def __init__(self, devices: Optional[Sequence[Any]] = None,
                export_fn: Optional[Callable[[Mapping[str, Timeline]], MetricsT]] = None,
                concurrent_spans: Union[None, str, Sequence[str]] = None,
                collect_on_first_device_per_mesh: bool = False):
-    """`concurrent_spans`: span names that really overlap on a device (or "all"): timelines that
-    contain them are not sequentialised."""
-    self._born = time.perf_counter()
+    """`concurrent_spans`: span names that really overlap on a device (or "all"): device lanes that contain them
+    are not split into active and queued parts."""
     self._export_fn = export_fn
     self._concurrent_spans = concurrent_spans
     self._collect_on_first_device_per_mesh = collect_on_first_device_per_mesh
-    self._timelines_lock = threading.RLock()
-    self._host_timelines: Dict[str, Timeline] = {}
-    self._device_timelines: Dict[str, AsyncTimeline] = {}
-    self._device_queue_timelines: Dict[str, Timeline] = collections.defaultdict(self._new_queue_timeline)
-    for d in timeline_utils.generate_device_timeline_ids(devices):
-      self._get_or_create_device_timeline(d)
-    self._get_or_create_host_timeline(timeline_utils.generate_host_timeline_id())
-
-  def _new_queue_timeline(self) -> Timeline:
-    return Timeline("queue", self._born)
+    self._lanes = _Lanes(time.perf_counter())
+    for lane_id in timeline_utils.generate_device_timeline_ids(devices):
+      self._lanes.device_lane(lane_id)
+    self._lanes.host_lane(timeline_utils.generate_host_timeline_id())
 
   def _get_timelines(self) -> Dict[str, Timeline]:
-    with self._timelines_lock:
-      out: Dict[str, Timeline] = {}
-      out.update(self._host_timelines)
-      out.update(self._device_timelines)
-      out.update(self._device_queue_timelines)
-      return out
+    return self._lanes.everything()
 
-  def _get_or_create_host_timeline(self, timeline_id: str) -> Timeline:
-    with self._timelines_lock:
-      if timeline_id not in self._host_timelines:
-        self._host_timelines[timeline_id] = Timeline(timeline_id, self._born)
-      return self._host_timelines[timeline_id]
+  @property
+  def all_devices(self) -> Sequence[str]:
+    with self._lanes.lock:
+      return list(self._lanes.device)
 
-  def _get_or_create_device_timeline(self, timeline_id: str) -> AsyncTimeline:
-    with self._timelines_lock:
-      if timeline_id not in self._device_timelines:
-        self._device_timelines[timeline_id] = AsyncTimeline(timeline_id, self._born)
-      return self._device_timelines[timeline_id]
-
-  def _get_or_create_device_timelines(self, devices: Any) -> BatchAsyncTimelines:
-    return BatchAsyncTimelines([self._get_or_create_device_timeline(i)
-                                for i in timeline_utils.generate_device_timeline_ids(devices)])
-
+  # ---- waiting and printing
   def synchronize(self) -> None:
     _synchronize_devices()
-    with self._timelines_lock:
-      tls = list(self._device_timelines.values())
-    for tl in tls:
-      tl.wait_pending_spans()
+    for lane in self._lanes.device_lanes():
+      lane.wait_pending_spans()
 
   def print(self) -> None:
     self.synchronize()
-    for tl in self._get_timelines().values():
-      print(repr(tl))
+    for lane in self._get_timelines().values():
+      print(repr(lane))
 
-  def _sequentialize_device_timeline(self, timeline_id: str, tl: AsyncTimeline) -> None:
-    with tl._lock:
-      ignore = self._concurrent_spans or []
-      if any(sp.name in ignore for sp in tl._cur_step.values()):
+  # ---- end of step
+  def _split_queued(self, lane_id: str, lane: AsyncTimeline) -> None:
+    """Overlapping spans of a device lane are work that waited behind other work: the waiting part moves to the
+    lane's queue timeline, the running parts stay and no longer overlap."""
+    declared = self._concurrent_spans or []
+    with lane._lock:
+      if any(span.name in declared for span in lane._cur_step.values()):
         return
-      active, queued = timeline_utils.sequentialize_overlapping_spans(tl._cur_step)
-      tl._cur_step = dict(active)
-    if queued:
-      qid = timeline_utils.generate_queued_timeline_id(timeline_id)
-      qtl = self._device_queue_timelines[qid]
-      qtl.id = qid
-      with qtl._lock:
-        qtl._cur_step.update(queued)
+      running, waiting = timeline_utils.sequentialize_overlapping_spans(lane._cur_step)
+      lane._cur_step = dict(running)
+    if waiting:
+      qlane = self._lanes.queue_lane(timeline_utils.generate_queued_timeline_id(lane_id))
+      with qlane._lock:
+        qlane._cur_step.update(waiting)
 
   def process_and_commit_timelines(self) -> None:
-    with self._timelines_lock:
-      for tl in self._device_timelines.values():
-        tl.wait_pending_spans()
+    with self._lanes.lock:
+      for lane in self._lanes.device.values():
+        lane.wait_pending_spans()
       if self._concurrent_spans != "all":
-        for tid, tl in list(self._device_timelines.items()):
-          self._sequentialize_device_timeline(tid, tl)
-      for group in (self._host_timelines, self._device_timelines, self._device_queue_timelines):
-        for tl in group.values():
-          tl.commit_step()
+        for lane_id, lane in list(self._lanes.device.items()):
+          self._split_queued(lane_id, lane)
+      for lane in self._lanes.everything().values():
+        lane.commit_step()
 
   def export(self) -> MetricsT:
     if self._export_fn is None:
@@ -160,28 +171,25 @@ class PerfTracer(NoopTracer):
     self.process_and_commit_timelines()
     return self._export_fn(self._get_timelines())
 
-  @property
-  def all_devices(self) -> Sequence[str]:
-    with self._timelines_lock:
-      return list(self._device_timelines.keys())
+  # ---- recording
+  def _lanes_for(self, devices: Any) -> BatchAsyncTimelines:
+    if self._collect_on_first_device_per_mesh and devices is not None:
+      flat = devices.flatten().tolist() if isinstance(devices, np.ndarray) else list(devices)
+      devices = flat[:1]
+    return BatchAsyncTimelines([self._lanes.device_lane(lane_id)
+                                for lane_id in timeline_utils.generate_device_timeline_ids(devices)])
 
   @contextlib.contextmanager
   def span(self, name: str, devices: Any = None, tags: Optional[Mapping[str, Any]] = None) -> Iterator[AsyncWaitlist]:
-    span_devices = devices
-    if self._collect_on_first_device_per_mesh and devices is not None:
-      flat = devices.flatten().tolist() if isinstance(devices, np.ndarray) else list(devices)
-      span_devices = flat[:1]
-    begin = time.perf_counter()
-    wl = AsyncWaitlist()
-    host_tl = None
+    issued_at = time.perf_counter()
+    pending = AsyncWaitlist()
+    host = self._lanes.host_lane(timeline_utils.generate_host_timeline_id())
+    host.start_span(name, issued_at, tags=tags)
     try:
-      host_tl = self._get_or_create_host_timeline(timeline_utils.generate_host_timeline_id())
-      host_tl.start_span(name, begin, tags=tags)
-      yield wl
+      yield pending
     finally:
-      if host_tl is not None:
-        host_tl.stop_span(time.perf_counter())
-        self._get_or_create_device_timelines(span_devices).span(name, begin, wl.waitlist, tags=tags)
+      host.stop_span(time.perf_counter())
+      self._lanes_for(devices).span(name, issued_at, pending.waitlist, tags=tags)
 
 
 Tracer = Union[PerfTracer, NoopTracer]
