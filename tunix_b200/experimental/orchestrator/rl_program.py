@@ -52,7 +52,58 @@ class RLProgram(abc.ABC):
           num_steps: Optional[int] = None, **kwargs: Any) -> None: ...
 
 
+class _DispatchWindow:
+  """Back-pressure between dispatch and training: prompt number i may be dispatched once
+  i < (policy_version + max_staleness + 1) * mini_batch_size, i.e. rollouts never run more than `max_staleness`
+  optimizer steps ahead of the policy that will train on them. The trainer calls `advance()` after every step;
+  the dispatcher sleeps on a condition in between (no polling)."""
+
+  def __init__(self, per_step: int, max_staleness: Optional[int]):
+    self.per_step, self.max_staleness = per_step, max_staleness
+    self.version = 0
+    self._moved = asyncio.Condition()
+
+  def _open_for(self, index: int) -> bool:
+    return self.max_staleness is None or index < (self.version + self.max_staleness + 1) * self.per_step
+
+  async def admit(self, index: int) -> None:
+    if self._open_for(index):
+      return
+    async with self._moved:
+      await self._moved.wait_for(lambda: self._open_for(index))
+
+  async def advance(self, version: int) -> None:
+    async with self._moved:
+      self.version = version
+      self._moved.notify_all()
+
+
+@dataclasses.dataclass
+class _StepLedger:
+  """What one optimizer step consumed."""
+  groups: List[List[Any]] = dataclasses.field(default_factory=list)
+  rewards: List[float] = dataclasses.field(default_factory=list)
+  micro_batches: int = 0
+  train_result: Any = None
+
+  def summary(self, step: int, version: int) -> RLStepResult:
+    r = np.asarray(self.rewards, dtype=np.float64)
+    return RLStepResult(step=step, policy_version=version, num_rollouts=len(self.rewards),
+                        num_microbatches=self.micro_batches, reward_mean=float(r.mean()) if r.size else 0.0,
+                        reward_std=float(r.std()) if r.size else 0.0, train_result=self.train_result)
+
+
+def _as_prompt_item(item: Any, index: int) -> Any:
+  """Every dispatched prompt needs an id; plain prompts and dicts without one get `prompt_<index>`."""
+  if isinstance(item, dict):
+    return {"prompt_id": f"prompt_{index}", **item}
+  if hasattr(item, "prompt_id"):
+    return item
+  return {"prompt": item, "prompt_id": f"prompt_{index}"}
+
+
 class StandardRLProgram(RLProgram):
+
   def __init__(self, algo: algorithm_adapter.AlgorithmAdapter, dataset: Optional[Iterable[Any]] = None,
                reward_fns: Optional[Sequence[Callable[..., Any]]] = None, assembler: Any = None, group_size: int = 8,
                mini_batch_size: int = 4, max_staleness: Optional[int] = None, sync_weights: bool = True,
@@ -72,120 +123,139 @@ class StandardRLProgram(RLProgram):
                                                    current_policy_version=lambda: self.policy_version)
     self.scored_q = tqm.TrajectoryQueueManager.create(group_size=self.group_size)
     self.history: List[RLStepResult] = []
+    self._window: Optional[_DispatchWindow] = None        # made inside the running loop
 
-  async def _wait_for_dispatch_window(self, prompt_idx: int) -> None:
-    if self.max_staleness is None:
-      return
-    ahead = self.mini_batch_size * (self.max_staleness + 1)
-    while prompt_idx - self.policy_version * self.mini_batch_size >= ahead:
-      await asyncio.sleep(0.005)
-
+  # ---- stage 1: dispatch
   async def rollout_dispatch_stage(self, engine, train_dataset=None) -> None:
-    ds = train_dataset if train_dataset is not None else self.dataset
-    if ds is None:
+    source = train_dataset if train_dataset is not None else self.dataset
+    if source is None:
       raise ValueError("StandardRLProgram requires a dataset either at init or in run().")
-    for i, item in enumerate(ds):
-      await self._wait_for_dispatch_window(i)
-      if isinstance(item, dict):
-        item = dict(item)
-        item.setdefault("prompt_id", f"prompt_{i}")
-      elif not hasattr(item, "prompt_id"):
-        item = {"prompt": item, "prompt_id": f"prompt_{i}"}
-      await engine.dispatch_rollouts([item], group_size=self.group_size, policy_version=self.policy_version)
+    window = self._window or _DispatchWindow(self.mini_batch_size, self.max_staleness)
+    for index, item in enumerate(source):
+      await window.admit(index)
+      await engine.dispatch_rollouts([_as_prompt_item(item, index)], group_size=self.group_size,
+                                     policy_version=self.policy_version)
 
+  # ---- stage 2: collect finished rollouts
   async def polling_stage(self, engine) -> None:
     while True:
       try:
-        for it in await engine.poll_rollouts(timeout_s=0.2) or []:
-          await self.raw_q.put(it)
+        finished = await engine.poll_rollouts(timeout_s=0.2)
       except asyncio.CancelledError:
-        break
-      except Exception as e:
+        return
+      except Exception as e:       # noqa: BLE001 - a flaky worker must not end the collection
         logging.warning("Error in polling_stage: %s", e)
         await asyncio.sleep(0.01)
+        continue
+      for item in finished or []:
+        await self.raw_q.put(item)
+
+  # ---- stage 3: score complete groups
+  def _score(self, item: Any) -> float:
+    if self.reward_fns:
+      return float(sum(fn(item) for fn in self.reward_fns))
+    return float(getattr(item.traj, "reward", 0.0))
 
   async def critique_stage(self, engine) -> None:
     while True:
       try:
         group = await self.raw_q.get_group()
       except asyncio.CancelledError:
-        break
+        return
       if not group:
+        return
+      rewards = [self._score(item) for item in group]
+      payloads = self.algo.create_trainer_payloads(group, rewards=rewards)
+      group_id = getattr(group[0], "group_id", "default")
+      for index, (source, payload, reward) in enumerate(zip(group, payloads, rewards)):
+        scored = datatypes.TrajectoryItem(pair_index=index, group_id=group_id, start_step=0,
+                                          traj=datatypes.Trajectory(reward=reward),
+                                          policy_version=getattr(source, "policy_version", 0))
+        scored.payload = payload
+        await self.scored_q.put(scored)
+
+  # ---- stage 4: train
+  async def _micro_batches(self, engine, items: List[Any]) -> List[Any]:
+    """One group's payloads packed into micro-batches, with reference log-probs when the algorithm has a KL term."""
+    batches = self.assembler.pack([item.payload for item in items])
+    if not getattr(self.algo, "requires_reference_kl", False):
+      return batches
+    with_ref = []
+    for batch in batches:
+      if not isinstance(batch, rl_common.TrainExample):
+        raise TypeError("Reference KL requires an assembler that returns rl_common.TrainExample microbatches; "
+                        f"got {type(batch).__name__}.")
+      ref_logps = await engine.per_token_logps(datatypes.Role.REFERENCE, items=batch)
+      with_ref.append(batch_assembly.with_ref_per_token_logps(batch, ref_logps))
+    return with_ref
+
+  async def _one_step(self, engine) -> _StepLedger:
+    """Accumulates gradients over `mini_batch_size` groups; the optimizer is applied with the very last
+    micro-batch. Returns early (fewer groups) when the scored queue is draining."""
+    ledger = _StepLedger()
+    for position in range(self.mini_batch_size):
+      items = await self.scored_q.get_batch(num_groups=1)
+      if not items:
         break
-      rewards = [float(sum(fn(it) for fn in self.reward_fns)) if self.reward_fns
-                 else float(getattr(it.traj, "reward", 0.0)) for it in group]
-      for idx, (payload, r) in enumerate(zip(self.algo.create_trainer_payloads(group, rewards=rewards), rewards)):
-        item = datatypes.TrajectoryItem(pair_index=idx, group_id=getattr(group[0], "group_id", "default"),
-                                        start_step=0, traj=datatypes.Trajectory(reward=r),
-                                        policy_version=getattr(group[idx], "policy_version", 0))
-        item.payload = payload
-        await self.scored_q.put(item)
+      ledger.groups.append(items)
+      ledger.rewards.extend(float(getattr(item.traj, "reward", 0.0)) for item in items)
+      batches = await self._micro_batches(engine, items)
+      ledger.micro_batches += len(batches)
+      closing_group = position == self.mini_batch_size - 1
+      for number, batch in enumerate(batches, start=1):
+        ledger.train_result = await engine.train_step(
+            batch, role=datatypes.Role.ACTOR, accumulate_gradients=True,
+            apply_optimizer=closing_group and number == len(batches))
+    return ledger
 
   async def train_stage(self, engine, num_steps: Optional[int] = None) -> None:
     step = 0
     while num_steps is None or step < num_steps:
       if self.on_step_begin:
         self.on_step_begin(self.step)
-      groups, rewards, n_micro, result = [], [], 0, None
-      for g in range(self.mini_batch_size):
-        items = await self.scored_q.get_batch(num_groups=1)
-        if not items:
-          break
-        groups.append(items)
-        rewards += [float(getattr(i.traj, "reward", 0.0)) for i in items]
-        batches = self.assembler.pack([i.payload for i in items])
-        if getattr(self.algo, "requires_reference_kl", False):
-          scored = []
-          for b in batches:
-            if not isinstance(b, rl_common.TrainExample):
-              raise TypeError("Reference KL requires an assembler that returns rl_common.TrainExample microbatches; "
-                              f"got {type(b).__name__}.")
-            scored.append(batch_assembly.with_ref_per_token_logps(
-                b, await engine.per_token_logps(datatypes.Role.REFERENCE, items=b)))
-          batches = scored
-        n_micro += len(batches)
-        last_group = g == self.mini_batch_size - 1
-        for bi, b in enumerate(batches):
-          result = await engine.train_step(b, role=datatypes.Role.ACTOR, accumulate_gradients=True,
-                                           apply_optimizer=last_group and bi == len(batches) - 1)
-      if not groups:
-        break
-      if self.sync_weights:
-        self.policy_version = (await engine.sync_weights(role=datatypes.Role.ACTOR)) or self.step + 1
-      else:
-        self.policy_version = self.step + 1
-      self.scored_q.commit(step, groups=groups)
-      self.last_step_result = RLStepResult(
-          step=step, policy_version=self.policy_version, num_rollouts=len(rewards), num_microbatches=n_micro,
-          reward_mean=float(np.mean(rewards)) if rewards else 0.0, reward_std=float(np.std(rewards)) if rewards else 0.0,
-          train_result=result)
+      ledger = await self._one_step(engine)
+      if not ledger.groups:
+        return
+      published = (await engine.sync_weights(role=datatypes.Role.ACTOR)) if self.sync_weights else None
+      self.policy_version = published or self.step + 1
+      if self._window is not None:
+        await self._window.advance(self.policy_version)
+      self.scored_q.commit(step, groups=ledger.groups)
+      self.last_step_result = ledger.summary(step, self.policy_version)
       self.history.append(self.last_step_result)
       if self.on_step_end:
         self.on_step_end(step, self.last_step_result)
       step += 1
 
+  # ---- supervision
   async def run_async(self, engine, train_dataset=None, num_steps: Optional[int] = None, **kwargs) -> None:
+    """Runs the four stages until the trainer has done `num_steps` (or the data ran out). A failure of the
+    dispatcher or the critic cancels training and is re-raised; the poller only logs."""
     self._is_running = True
-    side = [asyncio.create_task(self.rollout_dispatch_stage(engine, train_dataset)),
-            asyncio.create_task(self.polling_stage(engine)), asyncio.create_task(self.critique_stage(engine))]
+    self._window = _DispatchWindow(self.mini_batch_size, self.max_staleness)
+    self._window.version = self.policy_version
+    dispatch = asyncio.create_task(self.rollout_dispatch_stage(engine, train_dataset))
+    poll = asyncio.create_task(self.polling_stage(engine))
+    critique = asyncio.create_task(self.critique_stage(engine))
+    train = asyncio.create_task(self.train_stage(engine, num_steps))
+    watched = {train, dispatch, critique}
     try:
-      train = asyncio.create_task(self.train_stage(engine, num_steps))
-      watch = {train, side[0], side[2]}
       while not train.done():
-        done, _ = await asyncio.wait(watch, return_when=asyncio.FIRST_COMPLETED)
-        for t in done:
-          watch.discard(t)
-          if t is not train and not t.cancelled() and t.exception() is not None:
-            train.cancel()
-            raise t.exception()
+        finished, _ = await asyncio.wait(watched, return_when=asyncio.FIRST_COMPLETED)
+        watched -= finished
+        broken = next((t for t in finished if t is not train and not t.cancelled() and t.exception()), None)
+        if broken is not None:
+          train.cancel()
+          raise broken.exception()
       await train
     finally:
       self._is_running = False
       await self.raw_q.prepare_clear()
       await self.scored_q.prepare_clear()
-      for t in side:
-        t.cancel()
-      await asyncio.gather(*side, return_exceptions=True)
+      helpers = [dispatch, poll, critique]
+      for task in helpers:
+        task.cancel()
+      await asyncio.gather(*helpers, return_exceptions=True)
 
   def run(self, engine, train_dataset=None, num_steps: Optional[int] = None, **kwargs) -> None:
     asyncio.run(self.run_async(engine, train_dataset, num_steps, **kwargs))

@@ -313,6 +313,7 @@ class TunixTrajectoryMetadata(TrajectoryMetadata):
   total_reward: float | None = None
   hyperparams: dict[str, Any] | None = None
   env_time: dict[str, float] | None = None
+  reward_time: dict[str, float] | None = None
 
 
 def _parse_tunix_step(v):
