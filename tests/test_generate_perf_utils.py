@@ -359,3 +359,41 @@ def test_vllm_sampler_adapter_with_a_fake_engine():
   assert all(len(t) == 2 for t in out.tokens)             # the EOS was stripped
   assert out.logprobs[0] == [-0.5, -1.0]
   s.close()
+
+
+def test_direct_state_transfer_stacks_fusion_wrappers_and_chunks():
+  from tunix_b200.generate import utils as gu
+  assert gu.stacked_key("a.layers.7.b.w") == ("a.layers.b.w", 7) and gu.stacked_key("embed.w") is None
+  torch.manual_seed(0)
+  L, D, F = 3, 4, 6
+  # source: trainer state wrapped in "base", layers stacked, expert gate / up apart
+  src = {"base": {"embed": {"w": torch.randn(10, D)},
+                  "layers": {"attn": {"w": torch.randn(L, D, D)}, "mlp": {"gate_proj": {"w": torch.randn(L, F, D)},
+                                                                          "up_proj": {"w": torch.randn(L, F, D)}}},
+                  "rng": {"key": torch.zeros(2)}}}
+  # destination: serving wrapper nested twice, layers apart, gate|up fused, plus a KV cache the source lacks
+  inner = {"embed.w": torch.zeros(10, D, dtype=torch.bfloat16), "kv_cache": torch.ones(2)}
+  for i in range(L):
+    inner[f"layers.{i}.attn.w"] = torch.zeros(D, D)
+    inner[f"layers.{i}.mlp.gate_up_proj.w"] = torch.zeros(2 * F, D)
+  dst = {"model": {"model": inner}}
+  ptr_before = inner["layers.1.attn.w"].data_ptr()
+  gu.transfer_state_directly(src, dst, scan_axis=0, reshard_chunk_size=2)
+  base = src["base"]
+  assert torch.equal(inner["embed.w"], base["embed"]["w"].bfloat16()) and inner["kv_cache"].eq(1).all()
+  for i in range(L):
+    assert torch.equal(inner[f"layers.{i}.attn.w"], base["layers"]["attn"]["w"][i])
+    want = torch.cat((base["layers"]["mlp"]["gate_proj"]["w"][i], base["layers"]["mlp"]["up_proj"]["w"][i]))
+    assert torch.equal(inner[f"layers.{i}.mlp.gate_up_proj.w"], want)
+  assert inner["layers.1.attn.w"].data_ptr() == ptr_before            # in place by default
+  # the other direction: per-layer source, stacked destination; destination buffers dropped and re-created
+  stacked_dst = {"layers.attn.w": torch.zeros(L, D, D), "embed.w": torch.zeros(10, D)}
+  per_layer_src = {k: v.float() for k, v in inner.items() if "attn" in k or k == "embed.w"}
+  old = stacked_dst["embed.w"]
+  gu.transfer_state_directly(per_layer_src, stacked_dst, delete_dst_buffers=True)
+  assert torch.equal(stacked_dst["layers.attn.w"], base["layers"]["attn"]["w"])
+  assert torch.equal(old, inner["embed.w"].float())                    # same tensor object, new storage
+  inter = gu.fuse_moe_gate_up(torch.tensor([[1.0], [2.0]]), torch.tensor([[10.0], [20.0]]), interleave=True)
+  assert inter.flatten().tolist() == [1.0, 10.0, 2.0, 20.0]
+  with pytest.raises(ValueError, match="share no keys"):
+    gu.transfer_state_directly({"a": torch.zeros(1)}, {"b": torch.zeros(1)})

@@ -181,18 +181,151 @@ def transfer_state_with_mappings(src_state: Mapping[str, torch.Tensor], dst_stat
   return dst_state
 
 
+# ---- direct (same naming family) transfer -------------------------------------------------------
+_LAYER_INDEX = re.compile(r"(^|\.)(layers)\.(\d+)\.")
+_WRAPPERS_SRC = ("base",)          # a trainer state that wraps the parameters once
+_WRAPPERS_DST = ("model",)         # serving wrappers nest the model, possibly several times
+
+
+def flatten_state(tree: Mapping[str, Any], prefix: str = "") -> Dict[str, torch.Tensor]:
+  """Nested mappings of tensors -> {dotted key: tensor}. Already flat states pass through."""
+  flat: Dict[str, torch.Tensor] = {}
+  for k, v in tree.items():
+    key = f"{prefix}{k}"
+    if isinstance(v, Mapping):
+      flat.update(flatten_state(v, key + "."))
+    else:
+      flat[key] = v
+  return flat
+
+
+def _unwrap(tree: Mapping[str, Any], wrappers: Sequence[str], repeatedly: bool) -> Mapping[str, Any]:
+  while isinstance(tree, Mapping) and len(tree) >= 1:
+    hit = next((w for w in wrappers if w in tree and isinstance(tree[w], Mapping)), None)
+    if hit is None:
+      break
+    tree = tree[hit]
+    if not repeatedly:
+      break
+  return tree
+
+
+def stacked_key(per_layer_key: str) -> Optional[Tuple[str, int]]:
+  """`a.layers.7.b` -> (`a.layers.b`, 7): the key under which a layer-stacked ("scanned") state keeps the same
+  parameter, and the layer's index. None for keys outside the layer stack."""
+  m = _LAYER_INDEX.search(per_layer_key)
+  if m is None:
+    return None
+  return per_layer_key[:m.start(3)] + per_layer_key[m.end(3) + 1:], int(m.group(3))
+
+
+def unstack_scanned(stacked: torch.Tensor, layer: int, scan_axis: int) -> torch.Tensor:
+  """Layer `layer` of a parameter stacked along `scan_axis` (a view, no copy)."""
+  return stacked.select(scan_axis, layer)
+
+
+def fuse_moe_gate_up(gate: torch.Tensor, up: torch.Tensor, interleave: bool = False) -> torch.Tensor:
+  """Separate expert gate (`wi_0`) and up (`wi_1`) projections [..., F, D] -> one fused [..., 2 F, D] weight:
+  gate rows then up rows (the layout of this package's `gate_up_proj`), or row-interleaved g0,u0,g1,u1,... for
+  engines that want the pair adjacent."""
+  if gate.shape != up.shape:
+    raise ValueError(f"gate {tuple(gate.shape)} and up {tuple(up.shape)} projections differ in shape")
+  if not interleave:
+    return torch.cat((gate, up), dim=-2)
+  return torch.stack((gate, up), dim=-2).reshape(*gate.shape[:-2], 2 * gate.shape[-2], gate.shape[-1])
+
+
+def _lookup(key: str, rank: int, src: Mapping[str, torch.Tensor], scan_axis: int) -> Optional[torch.Tensor]:
+  """`key` in the source, or its layer's slice of a stacked source parameter of rank `rank + 1`."""
+  if key in src:
+    return src[key]
+  where = stacked_key(key)
+  if where is not None and where[0] in src:
+    stacked, layer = src[where[0]], where[1]
+    if stacked.dim() == rank + 1 and layer < stacked.shape[scan_axis]:
+      return unstack_scanned(stacked, layer, scan_axis)
+  return None
+
+
+_FUSED_FROM = (("gate_up_proj", ("gate_proj", "up_proj")), ("wi", ("wi_0", "wi_1")))
+
+
+def _source_for(key: str, dst_t: torch.Tensor, src: Mapping[str, torch.Tensor], scan_axis: int
+                ) -> Optional[torch.Tensor]:
+  """The source tensor that fills destination `key`: the same key (or the layer's slice where the source keeps
+  layers stacked); or, when the destination wants gate|up fused and the source has them apart, the fusion."""
+  found = _lookup(key, dst_t.dim(), src, scan_axis)
+  if found is not None:
+    return found
+  for fused, (gate_name, up_name) in _FUSED_FROM:
+    if fused in key:
+      gate = _lookup(key.replace(fused, gate_name), dst_t.dim(), src, scan_axis)
+      up = _lookup(key.replace(fused, up_name), dst_t.dim(), src, scan_axis)
+      if gate is not None and up is not None:
+        return fuse_moe_gate_up(gate, up)
+  return None
+
+
+def _stack_into(dst_t: torch.Tensor, key: str, src: Mapping[str, torch.Tensor], scan_axis: int) -> bool:
+  """Fills a layer-stacked destination from per-layer source keys. True if every layer was found."""
+  marker = ".layers."
+  if marker not in key and not key.startswith("layers."):
+    return False
+  head, _, tail = key.partition("layers.")
+  n = dst_t.shape[scan_axis]
+  parts = [src.get(f"{head}layers.{i}.{tail}") for i in range(n)]
+  if any(p is None for p in parts):
+    return False
+  for i, part in enumerate(parts):
+    dst_t.select(scan_axis, i).copy_(_align_shape(part, dst_t.select(scan_axis, i).shape, key).to(dst_t.dtype))
+  return True
+
+
 @torch.no_grad()
-def transfer_state_directly(src_state: Mapping[str, torch.Tensor], dst_state: Mapping[str, torch.Tensor],
-                            reshard_fn: Optional[Callable] = None) -> Mapping[str, torch.Tensor]:
-  """Copies every key present in both states (structural intersection)."""
-  common = [k for k in dst_state if k in src_state]
-  if not common:
+def transfer_state_directly(src_state: Mapping[str, Any], dst_state: Mapping[str, Any],
+                            reshard_fn: Optional[Callable] = None, scan_axis: int = 0,
+                            delete_dst_buffers: bool = False, reshard_chunk_size: Optional[int] = None
+                            ) -> Mapping[str, Any]:
+  """Copies a state into another one of the same naming family by structure, without a key mapping.
+
+  * wrappers are stripped: one `base` level on the source (a trainer state), any depth of `model` on the
+    destination (serving wrappers); nested mappings are matched by dotted key;
+  * keys only one side has (KV caches, RNG state) are skipped; no common key at all is an error;
+  * layer stacks: if one side keeps a parameter stacked over layers (`layers.w`, [L, ...] along `scan_axis`) and
+    the other per layer (`layers.3.w`), slices are taken or filled accordingly;
+  * separate expert gate / up projections on the source are fused for a destination that holds `gate_up_proj`;
+  * `reshard_chunk_size` bounds how many keys are in flight at once: the copies of a chunk are issued, then the
+    stream is drained before the next chunk, so temporaries (casts, fused or re-laid-out tensors) of at most one
+    chunk are alive at a time;
+  * `delete_dst_buffers` frees each destination tensor's storage right before it is re-created from the source
+    (not when the two alias), which lowers the peak when source and destination share a GPU.
+  """
+  src = flatten_state(_unwrap(src_state, _WRAPPERS_SRC, repeatedly=False))
+  dst = flatten_state(_unwrap(dst_state, _WRAPPERS_DST, repeatedly=True))
+  keys = list(dst)
+  step = max(1, reshard_chunk_size or len(keys) or 1)
+  moved = 0
+  for start in range(0, len(keys), step):
+    for key in keys[start:start + step]:
+      dst_t = dst[key]
+      value = _source_for(key, dst_t, src, scan_axis)
+      if value is None:
+        moved += int(_stack_into(dst_t, key, src, scan_axis))
+        continue
+      if reshard_fn is not None:
+        value = reshard_fn(value, None)
+      value = _align_shape(value, dst_t.shape, key)
+      if delete_dst_buffers and value.data_ptr() != dst_t.data_ptr():
+        shape, dtype, device = dst_t.shape, dst_t.dtype, dst_t.device
+        dst_t.data = torch.empty(0, dtype=dtype, device=device)              # release before re-creating
+        dst_t.data = value.to(device=device, dtype=dtype, copy=True).reshape(shape)
+      else:
+        dst_t.copy_(value.to(dst_t.dtype))
+      moved += 1
+    if reshard_chunk_size and torch.cuda.is_available() and any(t.is_cuda for t in dst.values()):
+      torch.cuda.synchronize()
+  if moved == 0:
     raise ValueError("source and destination states share no keys")
-  for k in common:
-    v = src_state[k]
-    if reshard_fn is not None:
-      v = reshard_fn(v, None)
-    dst_state[k].copy_(_align_shape(v, dst_state[k].shape, k).to(dst_state[k].dtype))
   return dst_state
 
 
