@@ -153,3 +153,38 @@ def test_grpo_main_end_to_end(tmp_path, sp_model):
             "rl_training_config.actor_optimizer_config.learning_rate=0.001"]
   learner = grpo_main.main(argv("grpo_main", sp_model, tmp_path, *common, "rollout_engine=native"))
   assert learner.rl_engine.global_steps == 2
+
+
+def test_deepscaler_recipe_and_vllm_entry_arguments(tmp_path):
+  import json
+  from tunix_b200.cli import grpo_vllm_main
+  from tunix_b200.cli.recipes import deepscaler_data
+  train = tmp_path / "deepscaler.json"
+  train.write_text(json.dumps([{"problem": "1+1?", "answer": "2"}, {"problem": "2+2?", "answer": "4"}]))
+  evalf = tmp_path / "aime.jsonl"
+  evalf.write_text(json.dumps({"question": "3+3?", "ground_truth": "6"}) + "\n")
+  ds = deepscaler_data.create_dataset(str(train), str(evalf))
+  assert len(ds) == 2 and ds[0]["question"] == "1+1?" and ds[0]["answer"] == "2"
+  assert ds[1]["prompts"].startswith("2+2? Let's think step by step") and "\\boxed{}" in ds[1]["prompts"]
+  assert deepscaler_data.create_eval_dataset(str(evalf))[0] == {
+      "prompts": "3+3? " + deepscaler_data.INSTRUCTION, "question": "3+3?", "answer": "6"}
+  assert {r["question"] for r in deepscaler_data.create_dataset(str(train), shuffle=True, seed=1)} == {"1+1?", "2+2?"}
+  with pytest.raises(FileNotFoundError):
+    deepscaler_data.create_dataset(str(train), str(tmp_path / "missing.parquet"))
+  ds2 = data_lib.get_dataset_from_module(
+      f"tunix_b200.cli.recipes.deepscaler_data:create_dataset(train_data_path={str(train)!r})")
+  assert len(ds2) == 2
+  assert grpo_vllm_main.with_vllm_engine(["p", "a=1"]) == ["p", "a=1", "rollout_engine=vllm"]
+  assert grpo_vllm_main.with_vllm_engine(["p", "rollout_engine=native"]) == ["p", "rollout_engine=native"]
+
+
+def test_example_scripts_run_on_cpu():
+  import subprocess
+  import sys
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
+  for script, args in (("examples/sft/sft_synthetic.py", ["--steps", "3"]),
+                       ("examples/model_load/from_safetensors.py", [])):
+    r = subprocess.run([sys.executable, os.path.join(root, script), *args], env=env, capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
