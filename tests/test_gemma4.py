@@ -93,3 +93,90 @@ def test_automodel_builds_a_random_gemma4():
   assert isinstance(m, Gemma4) and path is None
   logits, _ = m(torch.randint(0, 64, (1, 5)))
   assert logits.shape == (1, 5, 64) and bool(torch.isfinite(logits).all())
+
+
+# ------------------------------------------------------------------------------------------ vision tower
+def _grid_positions(cols, rows, pad_to):
+  xy = [(c, r) for r in range(rows) for c in range(cols)]
+  xy += [(-1, -1)] * (pad_to - len(xy))
+  return torch.tensor(xy)
+
+
+def test_vision_pieces_against_plain_restatements():
+  from tunix_b200.models.gemma4 import vision as v
+  torch.manual_seed(0)
+  # factorised position embedding = one-hot contraction over both coordinates
+  table = torch.randn(6, 2, 5)
+  pos = torch.stack([_grid_positions(3, 2, 8), _grid_positions(2, 3, 8)])
+  got = v.factorized_posemb(table, pos)
+  onehot = torch.nn.functional.one_hot(pos.clamp(min=0), 6).float() * (pos >= 0)[..., None]
+  want = torch.einsum("blis,sid->bld", onehot, table)
+  assert torch.allclose(got, want, atol=1e-6) and got[0, 7].abs().sum() == 0
+  assert torch.isnan(v.factorized_posemb(table, torch.tensor([[[9, 0]]]))).all()
+  # pooling by coordinates: a 4 x 2 grid (+ padding) pooled 2 x 2 into 2 cells (of 3 slots)
+  x = torch.randn(1, 12, 4)
+  p = _grid_positions(4, 2, 12)[None]
+  pooled, mask = v.avg_pool_by_positions(x, p, 3)
+  cell0 = x[0, [0, 1, 4, 5]].mean(0)
+  cell1 = x[0, [2, 3, 6, 7]].mean(0)
+  assert torch.allclose(pooled[0, 0], cell0, atol=1e-6) and torch.allclose(pooled[0, 1], cell1, atol=1e-6)
+  assert mask.tolist() == [[True, True, False]] and pooled[0, 2].abs().sum() == 0
+  # 2-D rotary: norm-preserving, identity at the origin, first half depends on x only, second half on y only
+  h = torch.randn(1, 3, 2, 8)
+  xy = torch.tensor([[[0, 0], [3, 0], [0, 5]]])
+  r = v.rope_2d(h, xy)
+  assert torch.allclose(r.norm(dim=-1), h.norm(dim=-1), atol=1e-5) and torch.allclose(r[0, 0], h[0, 0])
+  assert torch.allclose(r[0, 1, :, 4:], h[0, 1, :, 4:]) and not torch.allclose(r[0, 1, :, :4], h[0, 1, :, :4])
+  assert torch.allclose(r[0, 2, :, :4], h[0, 2, :, :4]) and not torch.allclose(r[0, 2, :, 4:], h[0, 2, :, 4:])
+  # relative property: <rope(q, p), rope(k, p')> depends on p - p' only
+  q, k = torch.randn(1, 1, 1, 8), torch.randn(1, 1, 1, 8)
+  dot = lambda a, b: (v.rope_2d(q, torch.tensor([[a]])) * v.rope_2d(k, torch.tensor([[b]]))).sum()
+  assert torch.allclose(dot([5, 7], [2, 3]), dot([4, 9], [1, 5]), atol=1e-4)
+
+
+def test_vision_encoder_ignores_padding_and_feeds_the_decoder():
+  from tunix_b200.models.gemma4 import vision as v
+  torch.manual_seed(1)
+  vc = v.VisionEncoderConfig(d_model=16, num_layers=2, num_heads=2, ffw_hidden=32, patch_size=2, output_length=4,
+                             pos_emb_shape_yx=(16, 2), pooling_kernel_size=2, standardize_embeddings=True)
+  assert vc.max_patches == 16 and vc.image_height == 8
+  enc = v.VisionEncoder(vc).init_weights(seed=2, scale=0.2)
+  patches = torch.rand(2, 16, 12)
+  pos = torch.stack([_grid_positions(4, 4, 16), _grid_positions(4, 2, 16)])           # the second image is half size
+  (emb, mask), = enc(patches, pos)
+  assert emb.shape == (2, 4, 16) and mask.tolist() == [[True] * 4, [True, True, False, False]]
+  # padding content does not leak into valid outputs
+  noisy = patches.clone()
+  noisy[1, 8:] = torch.rand(8, 12) * 50
+  (emb2, _), = enc(noisy, pos)
+  assert torch.allclose(emb2[1, :2], emb[1, :2], atol=1e-5) and torch.allclose(emb2[0], emb[0], atol=1e-5)
+  # clipped linears: finite bounds clamp, infinite ones are the plain linear
+  lin = v.ClippedLinear(3, 4, True, torch.float32)
+  with torch.no_grad():
+    lin.w.copy_(torch.ones(3, 4))
+  xx = torch.tensor([[1.0, 2.0, 3.0, 4.0]])
+  assert lin(xx).tolist() == [[10.0] * 3]
+  lin.clip_input_max.fill_(2.0); lin.clip_output_max.fill_(6.5)
+  assert lin(xx).tolist() == [[6.5] * 3]
+
+  # decoder side: placeholders are replaced in order, each row by its own images; text positions untouched
+  cfg = tiny(vision_encoder=vc, use_bidirectional_attention="vision")
+  model = Gemma4(cfg).init_weights(seed=3, scale=0.1)
+  with torch.no_grad():
+    model.vision_encoder.load_state_dict(enc.state_dict())
+  I = g4.IMAGE_SOFT_TOKEN_PLACEHOLDER
+  tokens = torch.tensor([[5, I, I, I, I, 6, 7, 8], [9, I, I, 10, 11, 12, 13, 14]])
+  images = v.PreprocessedVisionInput(patches=patches, positions_xy=pos, soft_token_counts=[[4], [2]])
+  x_text = model.embedder.encode(tokens)
+  x = model._merge_modalities(x_text, tokens, images, None)
+  proj = model.embedder.encode_vision(emb)
+  assert torch.allclose(x[0, 1:5], proj[0], atol=1e-5) and torch.allclose(x[1, 1:3], proj[1, :2], atol=1e-5)
+  assert torch.equal(x[0, 5:], x_text[0, 5:]) and torch.equal(x[1, 3:], x_text[1, 3:]) and torch.equal(x[:, 0], x_text[:, 0])
+  causal = torch.ones(8, 8, dtype=torch.bool).tril()[None].expand(2, 8, 8)
+  opened = g4.add_bidirectional_blocks(causal, tokens == I)
+  assert opened[0, 1, 4] and opened[0, 2, 3] and not opened[0, 0, 1] and not opened[0, 5, 6] and not opened[1, 1, 3]
+  logits, _ = model(tokens, None, None, causal, images=images)
+  logits_text, _ = model(tokens, None, None, causal)
+  assert logits.shape == (2, 8, 64) and torch.isfinite(logits).all()
+  assert not torch.allclose(logits[0, 5], logits_text[0, 5])              # later text positions see the image
+  assert torch.allclose(logits[0, 0], logits_text[0, 0], atol=1e-5)       # earlier ones do not

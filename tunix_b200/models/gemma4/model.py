@@ -55,6 +55,9 @@ class ModelConfig:
   head_dim: int
   num_kv_heads: int
   final_logit_softcap: Optional[float] = 30.0
+  vision_encoder: Optional[object] = None          # vision.VisionEncoderConfig: adds the image tower
+  audio_encoder: Optional[object] = None           # audio.ConformerConfig: adds the audio tower
+  use_bidirectional_attention: Optional[str] = None   # "vision": image tokens of one image see each other in local layers
   sliding_window_size: Optional[int] = None
   per_layer_input_dim: int = 0
   num_global_kv_heads: Optional[int] = None
@@ -328,6 +331,23 @@ class DecoderLayer(nn.Module):
     return new_cache, f * self.skip_scale, kv
 
 
+IMAGE_SOFT_TOKEN_PLACEHOLDER = -2
+AUDIO_SOFT_TOKEN_PLACEHOLDER = -4
+
+
+def add_bidirectional_blocks(attn_mask: torch.Tensor, member: torch.Tensor) -> torch.Tensor:
+  """Opens `attn_mask` [B, T, S] between positions of the same run of consecutive `member` tokens ([B, T]): the
+  soft tokens of one image attend to each other in both directions; different images stay causal."""
+  starts = member & ~torch.nn.functional.pad(member, (1, 0))[:, :-1]
+  block = torch.where(member, starts.long().cumsum(dim=1), torch.zeros_like(starts, dtype=torch.long))    # 0 = not a member
+  q = block
+  S = attn_mask.shape[-1]
+  k = block if S == block.shape[1] else (torch.nn.functional.pad(block, (0, S - block.shape[1]))
+                                          if S > block.shape[1] else block[:, -S:])
+  same = (q[:, :, None] == k[:, None, :]) & (q[:, :, None] > 0)
+  return attn_mask | same
+
+
 class Embedder(nn.Module):
 
   def __init__(self, cfg: ModelConfig, device=None):
@@ -340,9 +360,23 @@ class Embedder(nn.Module):
       self.per_layer_model_projection = _param(LP, cfg.embed_dim, **kw)
       self.per_layer_projection_norm = _param(cfg.per_layer_input_dim, ones=True, **kw)
       self.per_layer_input_embedding = _param(cfg.num_embed, LP, **kw)
+    if cfg.vision_encoder is not None:
+      self.mm_input_projection = _param(cfg.embed_dim, cfg.vision_encoder.d_model, **kw)
+    if cfg.audio_encoder is not None:
+      self.audio_input_projection = _param(cfg.embed_dim, cfg.audio_encoder.lm_model_dims, **kw)
 
   def encode(self, tokens):
-    return F.embedding(tokens, self.input_embedding, math.sqrt(self.cfg.embed_dim))
+    # multimodal placeholders are negative ids: they embed as token 0 and are overwritten by soft tokens
+    safe = torch.where(tokens >= 0, tokens, torch.zeros_like(tokens))
+    return F.embedding(safe, self.input_embedding, math.sqrt(self.cfg.embed_dim))
+
+  def encode_vision(self, soft):
+    """Tower output -> text embedding space: scale-free RMS norm, then a linear map."""
+    return F.linear(rms(soft, None, self.cfg.norm_eps).to(self.mm_input_projection.dtype), self.mm_input_projection)
+
+  def encode_audio(self, soft):
+    """Audio tower output -> text embedding space: linear map, then a scale-free RMS norm."""
+    return rms(F.linear(soft.to(self.audio_input_projection.dtype), self.audio_input_projection), None, self.cfg.norm_eps)
 
   def encode_per_layer_input(self, x, tokens):
     """[B, T, L, P]: (norm(proj(x) / sqrt(D)) + sqrt(P) * table[token]) / sqrt(2)."""
@@ -381,6 +415,12 @@ class Gemma4(nn.Module):
       layers.append(DecoderLayer(config, t, hidden, owns_kv=not shared, device=device))
     self.layers = nn.ModuleList(layers)
     self.final_norm = _param(config.embed_dim, ones=True, dtype=config.dtype, device=device)
+    if config.vision_encoder is not None:
+      from . import vision
+      self.vision_encoder = vision.VisionEncoder(config.vision_encoder, dtype=config.dtype, device=device)
+    if config.audio_encoder is not None:
+      from . import audio
+      self.audio_encoder = audio.AudioTokenizer(config.audio_encoder, dtype=config.dtype, device=device)
 
   def init_weights(self, seed: int = 0, scale: float = 0.02) -> "Gemma4":
     g = torch.Generator().manual_seed(seed)
@@ -412,13 +452,32 @@ class Gemma4(nn.Module):
     cap = self.config.final_logit_softcap
     return torch.tanh(logits / cap) * cap if cap else logits
 
+  def _merge_modalities(self, x, tokens, images, audios):
+    """Overwrites the embeddings at image / audio placeholder tokens with the towers' soft tokens."""
+    from . import vision as vision_lib
+    if images is not None and self.config.vision_encoder is not None:
+      soft = vision_lib.soft_tokens_per_row(self.vision_encoder, images)
+      if soft is not None:
+        x = vision_lib.merge_soft_tokens(x, self.embedder.encode_vision(soft), tokens == IMAGE_SOFT_TOKEN_PLACEHOLDER)
+    if audios is not None and self.config.audio_encoder is not None:
+      from . import audio as audio_lib
+      soft = audio_lib.soft_tokens_per_row(self.audio_encoder, audios)
+      if soft is not None:
+        x = vision_lib.merge_soft_tokens(x, self.embedder.encode_audio(soft), tokens == AUDIO_SOFT_TOKEN_PLACEHOLDER)
+    return x
+
   def forward(self, input_tokens, positions=None, cache=None, attention_mask=None, output_hidden_states: bool = False,
-              segment_ids=None, skip_lm_head: bool = False):
+              segment_ids=None, skip_lm_head: bool = False, images=None, audios=None):
     del output_hidden_states, segment_ids
     B, T = input_tokens.shape
     if positions is None:
       positions = torch.arange(T, device=input_tokens.device)[None].expand(B, T)
     x = self.embedder.encode(input_tokens)
+    x = self._merge_modalities(x, input_tokens, images, audios)
+    local_mask = attention_mask
+    if (T > 1 and images is not None and attention_mask is not None
+        and self.config.use_bidirectional_attention == "vision"):
+      local_mask = add_bidirectional_blocks(attention_mask, input_tokens == IMAGE_SOFT_TOKEN_PLACEHOLDER)
     per_layer = self.embedder.encode_per_layer_input(x, input_tokens) if self.config.per_layer_input_dim > 0 else None
     new_cache = {} if cache is not None else None
     fresh: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
@@ -436,7 +495,8 @@ class Gemma4(nn.Module):
       else:
         shared_kv = None
         layer_cache = cache[f"layer_{i}"] if cache is not None else None
-      lc, x, kv = layer(x, positions, layer_cache, attention_mask,
+      lc, x, kv = layer(x, positions, layer_cache,
+                        local_mask if layer.attn.attn_type == AttentionType.LOCAL_SLIDING else attention_mask,
                         per_layer[:, :, i, :] if per_layer is not None else None, shared_kv,
                         slot_keys=cache is not None)
       if i in self.shared_origins and cache is None:
