@@ -180,3 +180,110 @@ def test_vision_encoder_ignores_padding_and_feeds_the_decoder():
   assert logits.shape == (2, 8, 64) and torch.isfinite(logits).all()
   assert not torch.allclose(logits[0, 5], logits_text[0, 5])              # later text positions see the image
   assert torch.allclose(logits[0, 0], logits_text[0, 0], atol=1e-5)       # earlier ones do not
+
+
+# ------------------------------------------------------------------------------------------ audio tower
+def _blocked_local_attention(att, x, mask, block=4):
+  """The block formulation: queries in blocks of `block`, keys gathered with left context per block, relative
+  logits aligned by the pad-and-reshape shift, band + validity mask per block. Oracle for the band kernel."""
+  import math
+  from tunix_b200.models.gemma4 import audio as a
+  B, T, _ = x.shape
+  N, H, L = att.N, att.H, att.L
+  q, k, v = (proj(x).float().view(B, T, N, H) for proj in att.qkv)
+  q = q * (a._R_SOFTPLUS_0 / math.sqrt(H)) * torch.nn.functional.softplus(att.per_dim_scale.float())
+  k = k * (a._R_SOFTPLUS_0 * math.log1p(math.e))
+  U = (T + block - 1) // block
+  C = block + L
+
+  def ctx(t, fill):
+    tp = torch.nn.functional.pad(t.float(), [0, 0] * (t.dim() - 2) + [L, block - 1], value=fill)
+    idx = (torch.arange(U) * block)[:, None] + torch.arange(C)[None, :]
+    return tp[:, idx]
+
+  qb = torch.nn.functional.pad(q, [0, 0, 0, 0, 0, U * block - T]).view(B, U, block, N, H)
+  kb, vb = ctx(k, 0.0), ctx(v, 0.0)
+  ac = torch.einsum("buwnh,bucnh->bnuwc", qb, kb)
+  E = torch.nn.functional.linear(a.sinusoid(torch.arange(L, -1, -1), N * H), att.pos_proj.float()).view(L + 1, N, H)
+  bd = torch.einsum("buwnh,fnh->bnuwf", qb, E)
+  bd = torch.nn.functional.pad(bd, (0, (C + 1) - (L + 1))).reshape(B, N, U, block * (C + 1))[..., :block * C]
+  logits = a._SOFTCAP * torch.tanh((ac + bd.view(B, N, U, block, C)) / a._SOFTCAP)
+  w_, c_ = torch.arange(block)[:, None], torch.arange(C)[None, :]
+  band = (c_ >= w_) & (c_ - w_ <= L)
+  valid = ctx(mask, 0.0).bool()[:, None, :, None, :] & band[None, None, None]
+  probs = torch.softmax(torch.where(valid, logits, torch.full_like(logits, -1e9)), dim=-1)
+  out = torch.einsum("bnuwc,bucnh->buwnh", probs, vb)
+  return out.reshape(B, U * block, N, H)[:, :T]
+
+
+def test_audio_front_end_and_band_attention():
+  import numpy as np
+  from tunix_b200.models.gemma4 import audio as a
+  torch.manual_seed(0)
+  mel = a.MelFilterbank()
+  wave = torch.randn(2, 16000) * 0.1
+  got = mel(wave)
+  assert got.shape == (2, mel.num_frames(16000), 128) and mel.num_frames(16000) == 98 and mel.num_frames(320) == 0
+  # first frame, spelled out: 320 samples x window -> 512-point spectrum magnitude -> triangles -> log
+  frame = wave[0, :320].numpy() * mel.window.numpy()
+  spec = np.abs(np.fft.rfft(frame, n=512))
+  assert np.allclose(got[0, 0].numpy(), np.log(spec @ mel.mel_basis.numpy() + 1e-3), atol=1e-4)
+  assert mel.window.min() > 0 and (mel.mel_basis >= 0).all() and float(mel.mel_basis.max()) <= 1.0
+  assert a.to_float32(torch.tensor([16384], dtype=torch.int16)).item() == 0.5
+
+  cfg = a.ConformerConfig(num_layers=2, model_dims=32, lm_model_dims=24, atten_num_heads=4, atten_left_context=6,
+                          conv_kernel_size=3)
+  att = a.BandAttention(cfg, torch.float32)
+  with torch.no_grad():
+    for p in att.parameters():
+      p.copy_(torch.randn(p.shape) * 0.3)
+  x = torch.randn(2, 11, 32)
+  mask = torch.ones(2, 11, dtype=torch.bool)
+  mask[1, 7:] = False
+  band = att(x, mask)
+  for block in (4, 12):
+    ref = _blocked_local_attention(att, x, mask, block=block)
+    assert torch.allclose(band[0], ref[0], atol=1e-5) and torch.allclose(band[1, :7], ref[1, :7], atol=1e-5)
+  # a frame never sees beyond its left context nor the future
+  x2 = x.clone()
+  x2[0, 0] += 5.0
+  x2[0, 10] += 5.0
+  moved = (att(x2, mask)[0] - band[0]).abs().amax(dim=(-1, -2)) > 1e-6
+  assert moved.tolist() == [True] * 6 + [False] * 4 + [True]
+
+
+def test_audio_tokenizer_lengths_padding_and_decoder_merge():
+  from tunix_b200.models.gemma4 import audio as a, vision as v
+  torch.manual_seed(1)
+  cfg = a.ConformerConfig(num_layers=2, model_dims=32, lm_model_dims=24, atten_num_heads=4, atten_left_context=5,
+                          conv_kernel_size=3)
+  tok = a.AudioTokenizer(cfg).init_weights(seed=4, scale=0.2)
+  samples = 4000
+  waves = torch.randn(2, samples) * 0.1
+  lengths = torch.tensor([samples, 2400])
+  emb, pad = tok(waves, lengths)
+  assert emb.shape == (2, tok.get_num_soft_tokens(samples), 24) and tok.get_num_soft_tokens(100) == 0
+  assert not pad[0].any() and pad[1].sum() > 0 and emb[1][pad[1]].abs().sum() == 0
+  n_valid = int((~pad[1]).sum())
+  assert abs(n_valid - tok.get_num_soft_tokens(2400)) <= 1
+  # what lies beyond a clip's length does not change its earlier tokens (streaming model: past-only context)
+  noisy = waves.clone()
+  noisy[1, 2400:] = torch.randn(samples - 2400) * 3
+  emb2, pad2 = tok(noisy, lengths)
+  assert torch.equal(pad, pad2) and torch.allclose(emb2[1, :n_valid - 2], emb[1, :n_valid - 2], atol=1e-4)
+
+  model_cfg = tiny(audio_encoder=cfg)
+  model = Gemma4(model_cfg).init_weights(seed=5, scale=0.1)
+  with torch.no_grad():
+    model.audio_encoder.load_state_dict(tok.state_dict())
+  A = g4.AUDIO_SOFT_TOKEN_PLACEHOLDER
+  T = emb.shape[1]
+  tokens = torch.tensor([[5] + [A] * T + [6, 7], [9] + [A] * n_valid + [3] * (T - n_valid) + [10, 11]])
+  audios = a.PreprocessedAudioInput(audios=waves[:, None], sequence_lengths=lengths[:, None])
+  x_text = model.embedder.encode(tokens)
+  x = model._merge_modalities(x_text, tokens, None, audios)
+  want = model.embedder.encode_audio(emb)
+  assert torch.allclose(x[0, 1:1 + T], want[0], atol=1e-5) and torch.allclose(x[1, 1:1 + n_valid], want[1, :n_valid], atol=1e-5)
+  assert torch.equal(x[1, 1 + n_valid:], x_text[1, 1 + n_valid:])
+  logits, _ = model(tokens, None, None, None, audios=audios)
+  assert torch.isfinite(logits).all() and logits.shape[:2] == tokens.shape
