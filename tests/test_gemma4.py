@@ -158,6 +158,11 @@ def test_vision_encoder_ignores_padding_and_feeds_the_decoder():
   assert lin(xx).tolist() == [[10.0] * 3]
   lin.clip_input_max.fill_(2.0); lin.clip_output_max.fill_(6.5)
   assert lin(xx).tolist() == [[6.5] * 3]
+  seg = v.ClippedLinear((1, 2), 4, True, torch.float32)               # two segments with their own clamps
+  with torch.no_grad():
+    seg.w.copy_(torch.ones(3, 4))
+  seg.clip_input_max[1] = 1.0; seg.clip_output_min[0] = 20.0
+  assert seg(xx).tolist() == [[20.0, 4.0, 4.0]]
 
   # decoder side: placeholders are replaced in order, each row by its own images; text positions untouched
   cfg = tiny(vision_encoder=vc, use_bidirectional_attention="vision")
@@ -287,3 +292,46 @@ def test_audio_tokenizer_lengths_padding_and_decoder_merge():
   assert torch.equal(x[1, 1 + n_valid:], x_text[1, 1 + n_valid:])
   logits, _ = model(tokens, None, None, None, audios=audios)
   assert torch.isfinite(logits).all() and logits.shape[:2] == tokens.shape
+
+
+def test_checkpoint_names_round_trip_for_text_vision_audio(tmp_path):
+  from tunix_b200.models.gemma4 import audio as a, params_safetensors as ps, vision as v
+  torch.manual_seed(3)
+  vc = v.VisionEncoderConfig(d_model=16, num_layers=2, num_heads=2, ffw_hidden=32, patch_size=2, output_length=4,
+                             pos_emb_shape_yx=(16, 2), pooling_kernel_size=2, standardize_embeddings=True,
+                             use_clipped_linears=True)
+  ac = a.ConformerConfig(num_layers=2, model_dims=32, lm_model_dims=24, atten_num_heads=4, atten_left_context=5,
+                         conv_kernel_size=3)
+  cfg = tiny(vision_encoder=vc, audio_encoder=ac, enable_moe=True, num_experts=4, num_experts_per_tok=2, expert_dim=16)
+  src = Gemma4(cfg)
+  with torch.no_grad():
+    for t in src.state_dict().values():
+      t.copy_(torch.randn(t.shape) if t.is_floating_point() else t)
+  # in a checkpoint v shares k's clamps and up shares gate's: make the source consistent with that
+  for blk in src.vision_encoder.layers:
+    for name in ("clip_input_min", "clip_input_max", "clip_output_min", "clip_output_max"):
+      getattr(blk.attn.qkv_proj, name)[2] = getattr(blk.attn.qkv_proj, name)[1]
+      getattr(blk.mlp.gate_up_proj, name)[1] = getattr(blk.mlp.gate_up_proj, name)[0]
+  hf = ps.to_hf(cfg, src.state_dict())
+  assert "model.language_model.layers.0.mlp.gate_proj.weight" in hf and "model.language_model.layers.3.self_attn.q_proj.weight" in hf
+  assert "model.language_model.layers.3.self_attn.k_proj.weight" not in hf          # layer 3 shares K/V
+  assert hf["model.vision_tower.patch_embedder.position_embedding_table"].shape == (2, 16, 16)
+  assert "model.vision_tower.encoder.layers.1.self_attn.k_proj.input_max" in hf
+  assert "model.vision_tower.encoder.layers.1.self_attn.v_proj.input_max" not in hf
+  assert hf["model.audio_tower.layers.1.self_attn.post.linear.weight"].shape == (32, 32)
+  assert hf["model.language_model.layers.0.experts.gate_up_proj"].shape == (4, 32, 32)
+  path = ps.save_checkpoint(src, str(tmp_path))
+  assert path.endswith("model.safetensors")
+  dst = ps.load_checkpoint(Gemma4(cfg), str(tmp_path))
+  for (n, p), (_, q) in zip(src.state_dict().items(), dst.state_dict().items()):
+    assert torch.equal(p, q), n
+  # keys without the prefixes load as well; a missing tensor is named
+  bare = {k.replace("model.language_model.", "").replace("model.", ""): t for k, t in hf.items()}
+  again = ps.from_hf(cfg, bare, src.state_dict().keys())
+  assert torch.equal(again["layers.2.mlp.gate_up_proj"], src.state_dict()["layers.2.mlp.gate_up_proj"])
+  del bare["norm.weight"]
+  try:
+    ps.from_hf(cfg, bare, src.state_dict().keys())
+    raise AssertionError("expected KeyError")
+  except KeyError as e:
+    assert "final_norm" in str(e)

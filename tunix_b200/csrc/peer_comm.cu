@@ -91,6 +91,40 @@ reduce_scatter_sum_kernel(PeerTable grads, float* __restrict__ out, long long sh
   }
 }
 
+// The same sum for use BESIDE compute kernels: few, long-lived CTAs (so they take a slot on a handful of SMs once
+// and stay there instead of queueing wave after wave behind a persistent GEMM) with eight independent 16-byte
+// loads per peer in flight per thread to keep the links busy from so few threads.
+__global__ void __launch_bounds__(512)
+reduce_scatter_sum_bg_kernel(PeerTable grads, float* __restrict__ out, long long shard_off, long long n, int world,
+                             int rank) {
+  constexpr int U = 8;
+  const long long n4 = n / 4;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long base = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; base < n4; base += stride * U) {
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < world; ++k) {
+      int r = rank + k;
+      if (r >= world) r -= world;
+      const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + shard_off);
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = base + u * stride;
+        v[u] = i < n4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) { acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w; }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = base + u * stride;
+      if (i < n4) reinterpret_cast<float4*>(out)[i] = acc[u];
+    }
+  }
+}
+
 struct AdamArgs {
   float lr, beta1, beta2, eps, weight_decay, bc1, bc2;
 };
@@ -227,6 +261,17 @@ extern "C" int tx_reduce_scatter_sum_f32(void* const* grad_ptrs, float* out_shar
   for (int i = 0; i < world; ++i) t.p[i] = grad_ptrs[i];
   reduce_scatter_sum_kernel<<<tx_reduce_scatter_grid(), 256, 0, s>>>(t, out_shard, shard_off, n, world, rank,
                                                                      sumsq_partials);
+  return cudaGetLastError() == cudaSuccess ? 0 : 400;
+}
+
+// Background variant (no sum of squares): `ctas` CTAs of 512 threads, meant for a side stream next to compute.
+extern "C" int tx_reduce_scatter_sum_f32_bg(void* const* grad_ptrs, float* out_shard, long long shard_off, long long n,
+                                            int world, int rank, int ctas, cudaStream_t s) {
+  if (world > kMaxPeers || (n & 3) || (shard_off & 3) || ctas <= 0) return 1;
+  if (n == 0) return 0;
+  PeerTable t;
+  for (int i = 0; i < world; ++i) t.p[i] = grad_ptrs[i];
+  reduce_scatter_sum_bg_kernel<<<ctas, 512, 0, s>>>(t, out_shard, shard_off, n, world, rank);
   return cudaGetLastError() == cudaSuccess ? 0 : 400;
 }
 

@@ -46,6 +46,7 @@ from . import mesh as mesh_lib
 log = logging.getLogger(__name__)
 
 _ALIGN = 2048   # elements; keeps every shard boundary 16-byte aligned for any dtype and vector width
+_BACKGROUND_CTAS = int(os.environ.get("TUNIX_FSDP_BACKGROUND_CTAS", "48"))    # 0: the full-grid kernel
 _BUCKET_ALIGN = _ALIGN * 16   # bucket boundaries: divisible into 16-byte aligned pieces for up to 16 ranks
 
 
@@ -258,14 +259,15 @@ class FlatParamStore:
     from ..ops import _lib
     _lib.bind_thread()
     if self._side is None:
-      self._side = torch.cuda.Stream(device=self.device)
+      self._side = torch.cuda.Stream(device=self.device, priority=-1)   # its few CTAs go first at kernel boundaries
     ev = torch.cuda.Event()
     ev.record(torch.cuda.current_stream(self.device))
     self._side.wait_event(ev)
     self.symm.barrier(channel=1, stream=self._side)        # every rank's gradients of these buckets are final
     for x in sorted(due):
       lo, n, so = self.pieces[x]
-      self.symm.reduce_scatter_piece(self.flat_grad, self.grad_shard[so:so + n], lo, stream=self._side)
+      self.symm.reduce_scatter_piece(self.flat_grad, self.grad_shard[so:so + n], lo, stream=self._side,
+                                     background_ctas=_BACKGROUND_CTAS)
       self._reduced.add(x)
 
   # ---- the optimizer step ------------------------------------------------------------------

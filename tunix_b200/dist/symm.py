@@ -38,6 +38,8 @@ def _declare():
   lib.tx_reduce_scatter_grid.restype = _I
   lib.tx_reduce_scatter_sum_f32.argtypes = [ctypes.POINTER(_P), _P, _L, _L, _I, _I, _P, _P]
   lib.tx_reduce_scatter_sum_f32.restype = _I
+  lib.tx_reduce_scatter_sum_f32_bg.argtypes = [ctypes.POINTER(_P), _P, _L, _L, _I, _I, _I, _P]
+  lib.tx_reduce_scatter_sum_f32_bg.restype = _I
   lib.tx_adamw_allgather.argtypes = [_P, _P, _P, _P, ctypes.POINTER(_P), _L, _L, _F, _F, _F, _F, _F, _F, _F, _P, _I, _I, _P]
   lib.tx_adamw_allgather.restype = _I
   lib.tx_peer_copy_2d.argtypes = [_P, _P, _L, _L, _L, _L, _P]
@@ -117,10 +119,17 @@ class SymmetricBuffers:
                                   self.wait_limit_ms, _lib.status_word(self.device).data_ptr(), sp)
     _lib.check_rc(rc, "tx_peer_barrier")
 
-  def reduce_scatter_piece(self, full_fp32: torch.Tensor, out_piece: torch.Tensor, flat_start: int, stream=None) -> None:
+  def reduce_scatter_piece(self, full_fp32: torch.Tensor, out_piece: torch.Tensor, flat_start: int, stream=None,
+                           background_ctas: int = 0) -> None:
     """out_piece = sum over ranks of full_fp32[flat_start : flat_start + n], read over NVLink. The caller has
-    made sure (a barrier) that every rank's values in that range are final."""
+    made sure (a barrier) that every rank's values in that range are final. With `background_ctas` the sum runs
+    on that many long-lived CTAs, the form to use on a side stream while compute kernels own the machine."""
     sp = _lib.stream_ptr() if stream is None else stream.cuda_stream
+    if background_ctas > 0:
+      rc = self.lib.tx_reduce_scatter_sum_f32_bg(_ptr_array(self.ptrs_for(full_fp32)), out_piece.data_ptr(), flat_start,
+                                                 out_piece.numel(), self.world, self.rank, background_ctas, sp)
+      _lib.check_rc(rc, "tx_reduce_scatter_sum_f32_bg")
+      return
     rc = self.lib.tx_reduce_scatter_sum_f32(_ptr_array(self.ptrs_for(full_fp32)), out_piece.data_ptr(), flat_start,
                                             out_piece.numel(), self.world, self.rank, None, sp)
     _lib.check_rc(rc, "tx_reduce_scatter_sum_f32")

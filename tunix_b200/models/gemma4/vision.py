@@ -124,23 +124,32 @@ def avg_pool_by_positions(x: torch.Tensor, positions_xy: torch.Tensor, length: i
 
 # ------------------------------------------------------------------------------------------ modules
 class ClippedLinear(nn.Module):
-  """y = clamp(W clamp(x)); the four bounds are checkpoint values (+-inf = no clamp)."""
+  """A linear map whose output rows are grouped in *segments* (q | k | v, gate | up, or a single one), each with
+  its own clamps on the input it reads and the output it writes: y_s = clamp(W_s clamp(x)). The bounds are
+  checkpoint values (+-inf = no clamp). A model without clamps runs one GEMM over the fused weight; a model with
+  clamps runs one GEMM per segment, since segments may clamp the input differently."""
 
-  def __init__(self, out_features: int, in_features: int, clipped: bool, dtype, device=None):
+  def __init__(self, out_segments, in_features: int, clipped: bool, dtype, device=None):
     super().__init__()
-    self.w = nn.Parameter(torch.zeros(out_features, in_features, dtype=dtype, device=device))
+    self.segments = tuple(out_segments) if isinstance(out_segments, (tuple, list)) else (int(out_segments),)
+    self.w = nn.Parameter(torch.zeros(sum(self.segments), in_features, dtype=dtype, device=device))
     self.clipped = clipped
     if clipped:
+      S = len(self.segments)
       for name, value in (("clip_input_min", -math.inf), ("clip_input_max", math.inf),
                           ("clip_output_min", -math.inf), ("clip_output_max", math.inf)):
-        self.register_buffer(name, torch.tensor(value, dtype=torch.float32, device=device))
+        self.register_buffer(name, torch.full((S,), value, dtype=torch.float32, device=device))
 
   def forward(self, x: torch.Tensor) -> torch.Tensor:
     if not self.clipped:
       return F.linear(x, self.w)
-    x = torch.clamp(x, self.clip_input_min.to(x.dtype), self.clip_input_max.to(x.dtype))
-    y = F.linear(x, self.w)
-    return torch.clamp(y, self.clip_output_min.to(y.dtype), self.clip_output_max.to(y.dtype))
+    outs, row = [], 0
+    for s, n in enumerate(self.segments):
+      xs = torch.clamp(x, self.clip_input_min[s].to(x.dtype), self.clip_input_max[s].to(x.dtype))
+      ys = F.linear(xs, self.w[row:row + n])
+      outs.append(torch.clamp(ys, self.clip_output_min[s].to(ys.dtype), self.clip_output_max[s].to(ys.dtype)))
+      row += n
+    return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
 
 
 class VisionAttention(nn.Module):
@@ -149,7 +158,7 @@ class VisionAttention(nn.Module):
     super().__init__()
     self.N, self.H = cfg.num_heads, cfg.d_model // cfg.num_heads
     D = cfg.d_model
-    self.qkv_proj = ClippedLinear(3 * self.N * self.H, D, cfg.use_clipped_linears, dtype, device)
+    self.qkv_proj = ClippedLinear((self.N * self.H,) * 3, D, cfg.use_clipped_linears, dtype, device)
     self.o_proj = ClippedLinear(D, self.N * self.H, cfg.use_clipped_linears, dtype, device)
     self.query_norm = nn.Parameter(torch.ones(self.H, dtype=dtype, device=device))
     self.key_norm = nn.Parameter(torch.ones(self.H, dtype=dtype, device=device))
@@ -170,7 +179,7 @@ class VisionMLP(nn.Module):
 
   def __init__(self, cfg: VisionEncoderConfig, dtype, device=None):
     super().__init__()
-    self.gate_up_proj = ClippedLinear(2 * cfg.ffw_hidden, cfg.d_model, cfg.use_clipped_linears, dtype, device)
+    self.gate_up_proj = ClippedLinear((cfg.ffw_hidden,) * 2, cfg.d_model, cfg.use_clipped_linears, dtype, device)
     self.down_proj = ClippedLinear(cfg.d_model, cfg.ffw_hidden, cfg.use_clipped_linears, dtype, device)
 
   def forward(self, x: torch.Tensor) -> torch.Tensor:

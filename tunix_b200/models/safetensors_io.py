@@ -106,5 +106,5 @@ def save_file(tensors: Mapping[str, torch.Tensor], path: str, metadata: Optional
     f.write(struct.pack("<Q", len(hj)))
     f.write(hj)
     for t in blobs:
-      f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+      f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")   # reshape: 0-dim scalars too
   os.replace(tmp, path)
