@@ -335,3 +335,28 @@ def test_checkpoint_names_round_trip_for_text_vision_audio(tmp_path):
     raise AssertionError("expected KeyError")
   except KeyError as e:
     assert "final_norm" in str(e)
+
+
+def test_window_sized_ring_cache_matches_the_full_cache():
+  """Local layers that keep only `sliding_window_size` keys give the same logits as a full-length cache: a prompt
+  longer than the window, then decode steps that wrap the ring several times; shared layers read the ring too."""
+  torch.manual_seed(5)
+  full_cfg, ring_cfg = tiny(), tiny(use_sliding_window_kv_cache=True)
+  full = Gemma4(full_cfg).init_weights(seed=7, scale=0.2)
+  ring = Gemma4(ring_cfg).init_weights(seed=7, scale=0.2)
+  B, P, steps, size = 2, 7, 9, 24
+  tokens = torch.randint(1, 60, (B, P + steps))
+  cf, cr = full.init_cache(B, size), ring.init_cache(B, size)
+  assert cr["layer_0"]["k"].shape[1] == 4 and cr["layer_2"]["k"].shape[1] == size and cf["layer_0"]["k"].shape[1] == size
+  pos = torch.arange(P)[None].expand(B, P)
+  causal = torch.ones(P, size, dtype=torch.bool).tril()[None].expand(B, P, size)
+  lf, cf = full(tokens[:, :P], pos, cf, causal)
+  lr, cr = ring(tokens[:, :P], pos, cr, causal)
+  assert torch.allclose(lf, lr, atol=1e-5)
+  for t in range(P, P + steps):
+    step_mask = (torch.arange(size) <= t)[None, None, :].expand(B, 1, size)
+    p1 = torch.full((B, 1), t)
+    lf, cf = full(tokens[:, t:t + 1], p1, cf, step_mask)
+    lr, cr = ring(tokens[:, t:t + 1], p1, cr, step_mask)
+    assert torch.allclose(lf, lr, atol=1e-5), t
+  assert int(cr["layer_0"]["end_index"][0]) == P + steps

@@ -59,6 +59,7 @@ class ModelConfig:
   audio_encoder: Optional[object] = None           # audio.ConformerConfig: adds the audio tower
   use_bidirectional_attention: Optional[str] = None   # "vision": image tokens of one image see each other in local layers
   sliding_window_size: Optional[int] = None
+  use_sliding_window_kv_cache: bool = False    # local layers keep only a window-sized ring of keys / values
   per_layer_input_dim: int = 0
   num_global_kv_heads: Optional[int] = None
   global_key_size: Optional[int] = 512
@@ -211,28 +212,49 @@ class Attention(nn.Module):
     q = partial_rope(rms(q, self.q_norm, cfg.norm_eps), positions, self.rope_base, self.rope_scale,
                      self.rope_proportion)
     new_cache = None
+    ring = (cfg.use_sliding_window_kv_cache and self.attn_type == AttentionType.LOCAL_SLIDING
+            and bool(cfg.sliding_window_size))
+    newest = None                      # ring decode: absolute position of the token being decoded, [B]
     if shared_kv is not None:
       k, v = shared_kv["k"], shared_kv["v"]
+      if ring and T == 1 and "end_index" in shared_kv:
+        newest = shared_kv["end_index"] - 1          # the owner of these keys has already counted this token
     else:
       k, v = self.project_kv(x, positions)
       if cache is not None:
         S = cache["k"].shape[1]
-        idx = (cache["end_index"][:, None] + torch.arange(T, device=x.device)[None]) % S
-        bidx = torch.arange(B, device=x.device)[:, None].expand(B, T)
-        ck = cache["k"].index_put((bidx, idx), k.to(cache["k"].dtype))
-        cv = cache["v"].index_put((bidx, idx), v.to(cache["v"].dtype))
+        keep = min(T, S)                             # a prompt longer than the ring leaves its last S tokens
+        idx = (cache["end_index"][:, None] + torch.arange(T - keep, T, device=x.device)[None]) % S
+        bidx = torch.arange(B, device=x.device)[:, None].expand(B, keep)
+        ck = cache["k"].index_put((bidx, idx), k[:, T - keep:].to(cache["k"].dtype))
+        cv = cache["v"].index_put((bidx, idx), v[:, T - keep:].to(cache["v"].dtype))
         new_cache = {"k": ck, "v": cv, "end_index": cache["end_index"] + T}
-        k, v = ck, cv
+        if ring and T > 1:
+          slot_keys = False                          # prefill attends this call's own keys; the ring only records
+        else:
+          k, v = ck, cv
+          if ring:
+            newest = cache["end_index"]
     S = k.shape[1]
     mask = attn_mask
-    slot_keys = slot_keys or cache is not None
-    kpos = torch.arange(S, device=x.device)[None, None, :] if slot_keys else positions[:, None, :]
-    qpos = positions[:, :, None]
-    if slot_keys and mask is None:
-      mask = kpos <= qpos                    # written slots up to the query's own position
-    if self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size:
-      win = (kpos > qpos - cfg.sliding_window_size) & (kpos <= qpos)     # the window behind the query
-      mask = win if mask is None else (mask[..., :S] & win)
+    if newest is not None:
+      # ring decode: slot p holds absolute position newest - ((newest - p) mod S); slots never written are < 0
+      slots = torch.arange(S, device=x.device)[None, :]
+      logical = newest[:, None] - ((newest[:, None] - slots) % S)                       # [B, S]
+      written = logical >= 0
+      seen = written & (logical > newest[:, None] - cfg.sliding_window_size)
+      if mask is not None:                           # the caller's mask speaks about absolute positions
+        seen = seen & torch.gather(mask[:, 0, :], 1, logical.clamp(min=0, max=mask.shape[-1] - 1))
+      mask = seen[:, None, :]
+    else:
+      slot_keys = slot_keys or (cache is not None and not (ring and T > 1))
+      kpos = torch.arange(S, device=x.device)[None, None, :] if slot_keys else positions[:, None, :]
+      qpos = positions[:, :, None]
+      if slot_keys and mask is None:
+        mask = kpos <= qpos                    # written slots up to the query's own position
+      if self.attn_type == AttentionType.LOCAL_SLIDING and cfg.sliding_window_size:
+        win = (kpos > qpos - cfg.sliding_window_size) & (kpos <= qpos)     # the window behind the query
+        mask = win if mask is None else (mask[..., :S] & win)
     causal = mask is None
     o = F.attention(q, k, v, mask=mask, causal=causal, scale=1.0)
     out = F.linear(o.reshape(B, T, N * H), self.o_proj)
@@ -441,7 +463,11 @@ class Gemma4(nn.Module):
       if self.kv_sharing[i] != i:
         continue
       a = layer.attn
-      shape = (batch_size, cache_size, a.num_kv_heads, a.head_dim)
+      length = cache_size
+      if (self.config.use_sliding_window_kv_cache and a.attn_type == AttentionType.LOCAL_SLIDING
+          and self.config.sliding_window_size):
+        length = min(cache_size, self.config.sliding_window_size)
+      shape = (batch_size, length, a.num_kv_heads, a.head_dim)
       cache[f"layer_{i}"] = {"k": torch.zeros(shape, dtype=dtype, device=device),
                              "v": torch.zeros(shape, dtype=dtype, device=device),
                              "end_index": torch.zeros(batch_size, dtype=torch.long, device=device)}
@@ -484,11 +510,14 @@ class Gemma4(nn.Module):
     for i, layer in enumerate(self.layers):
       origin = self.kv_sharing[i]
       shared = origin != i
+      ring_prefill = (cache is not None and T > 1 and self.config.use_sliding_window_kv_cache
+                      and layer.attn.attn_type == AttentionType.LOCAL_SLIDING and bool(self.config.sliding_window_size))
       if shared:
-        # with a cache the origin layer's updated cache holds all keys so far; without one, this call's keys
-        if cache is not None:
+        # with a cache the origin layer's updated cache holds all keys so far; without one - or while a prompt is
+        # prefilled into a window-sized ring, which cannot hold it - this call's own keys
+        if cache is not None and not ring_prefill:
           oc = new_cache[f"layer_{origin}"]
-          shared_kv = {"k": oc["k"], "v": oc["v"]}
+          shared_kv = {"k": oc["k"], "v": oc["v"], "end_index": oc["end_index"]}
         else:
           shared_kv = {"k": fresh[origin][0], "v": fresh[origin][1]}
         layer_cache = None
@@ -498,8 +527,8 @@ class Gemma4(nn.Module):
       lc, x, kv = layer(x, positions, layer_cache,
                         local_mask if layer.attn.attn_type == AttentionType.LOCAL_SLIDING else attention_mask,
                         per_layer[:, :, i, :] if per_layer is not None else None, shared_kv,
-                        slot_keys=cache is not None)
-      if i in self.shared_origins and cache is None:
+                        slot_keys=cache is not None and not ring_prefill)
+      if i in self.shared_origins and (cache is None or ring_prefill):
         fresh[i] = kv
       if not shared and new_cache is not None:
         new_cache[f"layer_{i}"] = lc
