@@ -27,6 +27,7 @@ def main():
   ap.add_argument("--out", required=True)
   ap.add_argument("--root", required=True)
   ap.add_argument("--moe", type=int, default=1)
+  ap.add_argument("--ocdbt", type=int, default=0)
   a = ap.parse_args()
   import torch.distributed as dist
   from tunix_b200 import optim
@@ -40,7 +41,7 @@ def main():
   mesh_lib.set_current_mesh(mesh)
   opts = co.TunixCheckpointingOptions(save_decision_policy=co.ContinuousCheckpointingPolicy(minimum_interval_secs=0.25),
                                       preservation_policy=co.LatestN(n=10), enable_async_checkpointing=True,
-                                      async_options=co.AsyncOptions(timeout_secs=60))
+                                      async_options=co.AsyncOptions(timeout_secs=60), use_ocdbt=bool(a.ocdbt))
   tc = TrainingConfig(eval_every_n_steps=100, max_grad_norm=1.0, pbar_description=None, data_sharding_axis=(),
                       checkpoint_root_directory=a.root, checkpointing_options=opts)
 

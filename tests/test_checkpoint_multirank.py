@@ -9,11 +9,11 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(tmp_path, moe: int, port: int):
+def _run(tmp_path, moe: int, port: int, ocdbt: int = 0):
   out, root = str(tmp_path / "res.pt"), str(tmp_path / "ckpt")
   cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
          "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_ckpt_worker.py"), "--out", out, "--root", root,
-         "--moe", str(moe)]
+         "--moe", str(moe), "--ocdbt", str(ocdbt)]
   r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2"), capture_output=True, text=True, timeout=600)
   assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
   return torch.load(out, weights_only=False), root
@@ -54,3 +54,19 @@ def test_flat_state_restores_at_another_job_size(tmp_path):
   n = got["index"]["used"]
   assert float((mu[:n] - got["full_mu"][:n]).abs().max()) == 0.0
   tr.checkpoint_manager.close()
+
+
+def test_per_process_key_value_stores_hold_the_same_checkpoint(tmp_path):
+  """With `use_ocdbt` every rank writes one store `ocdbt.process_<r>` per item instead of a file per array chunk;
+  the restore reads the union of the stores and every rank still gets its own shards back."""
+  got, root = _run(tmp_path, 1, 29683, ocdbt=1)
+  for r in got["ranks"]:
+    assert r["restored_step"] == 6 and r["param_err"] == 0.0 and r["mu_err"] == 0.0 and r["local_err"] == 0.0
+  assert got["ranks"][0]["expert_sig"] != got["ranks"][1]["expert_sig"]
+  item = os.path.join(root, "6", "optimizer_state")
+  names = sorted(os.listdir(item))
+  assert "ocdbt.process_0" in names and "ocdbt.process_1" in names and "mu.flat.value" not in names
+  assert sorted(os.listdir(os.path.join(item, "ocdbt.process_1"))) == ["d", "manifest.ocdbt"]
+  from tunix_b200.ckpt import orbax_layout
+  kv = orbax_layout.open_kv(item)
+  assert kv.get("mu.flat.value/.zarray") is not None and kv.get("mu.flat.value/0") and kv.get("mu.flat.value/1")

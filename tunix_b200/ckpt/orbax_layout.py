@@ -130,9 +130,33 @@ def _write_file(path: str, data: bytes) -> None:
   os.replace(tmp, path)
 
 
+class _StoreWriter:
+  """Collects what a process writes (array chunks, `.zarray` descriptors) and commits it as one OCDBT store under
+  `ocdbt.process_<r>/` - the per-process layout Orbax uses before it merges manifests. Same interface as the
+  native file writer pool (`submit`, `wait`, `close`)."""
+
+  def __init__(self, directory: str, process_index: int):
+    self.target = os.path.join(directory, f"ocdbt.process_{process_index}")
+    self.root = directory
+    self.items: Dict[str, bytes] = {}
+
+  def submit(self, path: str, data: bytes) -> None:
+    self.items[os.path.relpath(path, self.root).replace(os.sep, "/")] = bytes(data)
+
+  def wait(self) -> None:
+    from . import ocdbt
+    if self.items:
+      ocdbt.write_store(self.target, self.items)
+
+  def close(self) -> None:
+    self.items = {}
+
+
 def write_tree(directory: str, tree: Mapping[Key, Any], process_index: int = 0,
-               sharding_desc: Optional[Mapping[Key, Mapping[str, Any]]] = None) -> None:
-  """Writes `{key tuple: tensor | ShardedArray}` under `directory` in the Orbax plain-zarr layout.
+               sharding_desc: Optional[Mapping[Key, Mapping[str, Any]]] = None, use_ocdbt: bool = False) -> None:
+  """Writes `{key tuple: tensor | ShardedArray}` under `directory` in the Orbax plain-zarr layout, or - with
+  `use_ocdbt` - with all array data of a process inside one OCDBT store `ocdbt.process_<r>/` (two files per
+  process instead of two per array; `open_kv` reads the union of the stores).
 
   Called by every process of a job with the same keys. Plain tensors are replicated state: process 0
   writes them. A `ShardedArray` leaf is written by every process - its own chunk file - while process 0
@@ -144,16 +168,18 @@ def write_tree(directory: str, tree: Mapping[Key, Any], process_index: int = 0,
   shard_md: Dict[str, str] = {}
   # array chunks go through the native writer pool (temp file + rename on worker threads)
   from ..runtime import native
-  writer = native.AsyncWriter(threads=8)
+  writer = _StoreWriter(directory, process_index) if use_ocdbt else native.AsyncWriter(threads=8)
   try:
-    _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index)
+    _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index,
+                       descriptor_sink=writer.submit if use_ocdbt else None)
     writer.wait()
   finally:
     writer.close()
   _write_tree_metadata(directory, process_index, tree_md, arr_md, shard_md)
 
 
-def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index=0) -> None:
+def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, shard_md, process_index=0,
+                       descriptor_sink=None) -> None:
   for key, t in tree.items():
     sharded = isinstance(t, ShardedArray)
     if not sharded and not isinstance(t, torch.Tensor):
@@ -173,14 +199,18 @@ def _write_tree_arrays(directory, tree, sharding_desc, writer, tree_md, arr_md, 
       chunk_name = ".".join("0" for _ in shape) if shape else "0"
       sharding_type = "SingleDeviceSharding"
     if sharded or process_index == 0:
-      os.makedirs(pdir, exist_ok=True)
+      if descriptor_sink is None:
+        os.makedirs(pdir, exist_ok=True)
       writer.submit(os.path.join(pdir, chunk_name), data)
     if process_index == 0:
       zarray = {
           "chunks": chunks if chunks else [], "compressor": None, "dimension_separator": ".", "dtype": zdtype,
           "fill_value": None, "filters": None, "order": "C", "shape": shape, "zarr_format": 2,
       }
-      _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
+      if descriptor_sink is None:
+        _write_file(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
+      else:
+        descriptor_sink(os.path.join(pdir, ".zarray"), json.dumps(zarray).encode())
     tree_md[key_to_str(key)] = {
         "key_metadata": [{"key": str(k), "key_type": 1 if isinstance(k, int) else 2} for k in key],
         "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False, "write_shape": chunks},
@@ -243,11 +273,30 @@ class _DirKV:
       return f.read()
 
 
+class _UnionKV:
+  """Several stores read as one: the first that has a key answers (per-process stores hold disjoint keys)."""
+
+  def __init__(self, stores):
+    self.stores = list(stores)
+
+  def get(self, key: str) -> Optional[bytes]:
+    for store in self.stores:
+      value = store.get(key)
+      if value is not None:
+        return value
+    return None
+
+
 def open_kv(directory: str):
-  """Directory-backed store, or the OCDBT store when `manifest.ocdbt` is present."""
+  """Directory-backed store; the OCDBT store when `manifest.ocdbt` is present; the union of the per-process
+  stores `ocdbt.process_<r>/` (plus loose files) when a checkpoint was written that way and never merged."""
+  from . import ocdbt
   if os.path.exists(os.path.join(directory, "manifest.ocdbt")):
-    from . import ocdbt
     return ocdbt.OcdbtStore(directory)
+  per_process = sorted(d for d in (os.listdir(directory) if os.path.isdir(directory) else [])
+                       if d.startswith("ocdbt.process_") and os.path.exists(os.path.join(directory, d, "manifest.ocdbt")))
+  if per_process:
+    return _UnionKV([ocdbt.OcdbtStore(os.path.join(directory, d)) for d in per_process] + [_DirKV(directory)])
   return _DirKV(directory)
 
 

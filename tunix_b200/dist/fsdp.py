@@ -46,7 +46,7 @@ from . import mesh as mesh_lib
 log = logging.getLogger(__name__)
 
 _ALIGN = 2048   # elements; keeps every shard boundary 16-byte aligned for any dtype and vector width
-_BACKGROUND_CTAS = int(os.environ.get("TUNIX_FSDP_BACKGROUND_CTAS", "48"))    # 0: the full-grid kernel
+_BACKGROUND_CTAS = int(os.environ.get("TUNIX_FSDP_BACKGROUND_CTAS", "0"))    # 0: the full-grid kernel (measured best); n > 0: n long-lived CTAs
 _BUCKET_ALIGN = _ALIGN * 16   # bucket boundaries: divisible into 16-byte aligned pieces for up to 16 ranks
 
 

@@ -120,7 +120,8 @@ class CheckpointManager:
     tmp = f"{final}.tmp-{init_ns}"
     try:
       for name, tree in items.items():
-        orbax_layout.write_tree(os.path.join(tmp, name), tree, process_index=rank)
+        orbax_layout.write_tree(os.path.join(tmp, name), tree, process_index=rank,
+                                use_ocdbt=bool(getattr(self._options, "use_ocdbt", False)))
       with open(os.path.join(tmp, f"_rank_{rank}.done"), "w") as f:
         f.write("ok")
       if rank != 0:

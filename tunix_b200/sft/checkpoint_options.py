@@ -68,6 +68,7 @@ class TunixCheckpointingOptions:
   step_name_format: Any = None
   enable_async_checkpointing: Optional[bool] = None
   async_options: Optional[AsyncOptions] = None
+  use_ocdbt: bool = False      # array data of each process in one key-value store file instead of a file per array
 
 
 DEFAULT_CHECKPOINTING_OPTIONS = TunixCheckpointingOptions(
@@ -105,6 +106,7 @@ def resolve_checkpointing_defaults(options: Any = None) -> TunixCheckpointingOpt
       step_name_format=getattr(options, "step_name_format", None),
       enable_async_checkpointing=d.enable_async_checkpointing if en is None else en,
       async_options=ao or d.async_options,
+      use_ocdbt=bool(getattr(options, "use_ocdbt", False)),
   )
 
 
