@@ -211,6 +211,23 @@ def make_round(**dest_kw):
   return h, src, dests, co
 
 
+def test_weight_sync_preflight_catches_name_and_shape_mismatches_before_any_downtime():
+  h, src, dests, co = make_round()
+  dests[1].serving = {"w": torch.full((4, 3), -1.0), "bias": torch.full((3,), -1.0)}        # a misspelt name
+  dests[1].staging = {k: torch.zeros_like(v) for k, v in dests[1].serving.items()}
+  res = asyncio.run(co.sync(1, raise_on_failure=False))
+  assert res.state == wsc.RoundState.ABORTED and not co.poisoned
+  text = " ".join(res.failures)
+  assert "destination units disagree" in text or "'bias' has no source counterpart" in text
+  assert all("pre_weight_sync" not in d.calls for d in dests) and all(d.admitting for d in dests)
+  assert src.released == 1
+  m_src = wsc.Manifest("source", [peer_memory_handler.manifest_of(src.unit, {"w": torch.zeros(4, 3)})])
+  m_dst = wsc.Manifest("destination", [peer_memory_handler.manifest_of(dests[0].unit, {"w": torch.zeros(4, 3).half()})])
+  assert m_src.differences(m_dst) == ["preflight: 'w' item_size differs: source 4, destination 2"]
+  m_dst2 = wsc.Manifest("destination", [peer_memory_handler.manifest_of(dests[0].unit, {"w": torch.zeros(2, 3)})])
+  assert "global shape differs" in m_src.differences(m_dst2)[0]
+
+
 def test_weight_sync_commits_and_versions_advance():
   h, src, dests, co = make_round()
   src.weights["w"].fill_(2.0)

@@ -179,6 +179,48 @@ class WeightSyncError(RuntimeError):
     self.result = result
 
 
+class Manifest:
+  """What one side of a round says it holds: variable name -> (global shape, bytes per element).
+
+  Built from the work-unit metadata of every member of the side. Units of one side describe the same global
+  tensors (one unit per host), so two units that disagree about a name are a problem of their own, recorded
+  rather than silently overwritten. Multi-tensor units list their variables; a single-tensor unit goes under its
+  `data_name`."""
+
+  def __init__(self, side: str, metadata: Sequence[weight_sync.WorkUnitMetadata]):
+    self.side = side
+    self.entries: Dict[str, Tuple[Optional[Tuple[int, ...]], Optional[int]]] = {}
+    self.problems: List[str] = []
+    for md in metadata:
+      if md.variables:
+        for var in md.variables:
+          self._add(var.name, tuple(var.shape), var.item_size)
+      else:
+        self._add(md.unit.data_name, tuple(md.global_shape) if md.global_shape else None, md.item_size)
+
+  def _add(self, name: str, shape, item_size) -> None:
+    seen = self.entries.get(name)
+    if seen is not None and seen != (shape, item_size):
+      self.problems.append(f"preflight: {self.side} units disagree on {name!r}: {seen} vs {(shape, item_size)}")
+    self.entries[name] = (shape, item_size)
+
+  def differences(self, other: "Manifest") -> List[str]:
+    """Everything that would make a transfer between the two sides lose or corrupt a tensor. The transport pairs
+    variables by exact name, so a misspelt name does not fail - it just is not copied; this check costs one
+    comparison and runs before any destination stops serving."""
+    out = list(self.problems) + list(other.problems)
+    mine, theirs = set(self.entries), set(other.entries)
+    out += [f"preflight: {self.side} variable {n!r} has no {other.side} counterpart" for n in sorted(mine - theirs)]
+    out += [f"preflight: {other.side} variable {n!r} has no {self.side} counterpart" for n in sorted(theirs - mine)]
+    for n in sorted(mine & theirs):
+      (s_shape, s_item), (d_shape, d_item) = self.entries[n], other.entries[n]
+      if s_shape != d_shape:
+        out.append(f"preflight: {n!r} global shape differs: {self.side} {s_shape}, {other.side} {d_shape}")
+      if s_item != d_item:
+        out.append(f"preflight: {n!r} item_size differs: {self.side} {s_item}, {other.side} {d_item}")
+    return out
+
+
 def _worker_id(member: Any) -> str:
   try:
     info = member.info()
@@ -356,6 +398,9 @@ class WeightSyncCoordinator:
       for s in sources:
         prepared_sources.append(s)
         src_meta += list(await _call(s, "prepare_weight_sync", req, timeout=t.source_prepare))
+      mismatches = Manifest("source", src_meta).differences(Manifest("destination", dst_meta))
+      if mismatches:
+        raise ValueError("; ".join(mismatches[:8]) + (f" (+{len(mismatches) - 8} more)" if len(mismatches) > 8 else ""))
       for m in src_meta + dst_meta:
         self._handler.register_work_unit(m)
       src_units[:] = [m.unit for m in src_meta]
