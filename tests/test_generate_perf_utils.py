@@ -397,3 +397,27 @@ def test_direct_state_transfer_stacks_fusion_wrappers_and_chunks():
   assert inter.flatten().tolist() == [1.0, 10.0, 2.0, 20.0]
   with pytest.raises(ValueError, match="share no keys"):
     gu.transfer_state_directly({"a": torch.zeros(1)}, {"b": torch.zeros(1)})
+
+
+def test_stateful_device_allocation_over_pools_with_holes():
+  from tunix_b200.utils import mesh as m
+  st = m.DeviceAllocationState(range(16))
+  assert st.allocate("trainer", 8) == list(range(8))                       # a whole node
+  assert st.allocate("rollout", 4, "PERFORMANCE") == [8, 9, 10, 11]         # one socket of the other node
+  assert st.allocate("ref", 2) == [12, 13] and st.allocate("rm", 2) == [14, 15]
+  assert "node 1" in st.summary() and "(0 free)" in st.summary()
+  with pytest.raises(ValueError, match="0 free"):
+    st.allocate("late", 1)
+  st.release("rollout")
+  assert st.allocate("x", 3) == [8, 9, 10] and st.free == [11]
+  # a pool with a hole on node 1: the 12-GPU request takes whole node 0 and finishes on the damaged node 1,
+  # leaving node 2 whole for the next large request (COMPACT); names keep their request order in the answer
+  pool = [r for r in range(24) if r != 14]
+  got = m.allocate_devices([("small", 3), ("big", 12)], pool)
+  assert got["big"] == list(range(8)) + [8, 9, 10, 11] and list(got) == ["small", "big"]
+  assert got["small"] == [12, 13, 15]                                      # the rest of the damaged node's socket
+  assert m.allocate_devices([("whole", 8)], pool)["whole"] == list(range(8))
+  perf = m.allocate_devices([("a", 2), ("b", 2)], range(8), "PERFORMANCE")
+  assert perf["a"] == [0, 1] and perf["b"][0] % 2 == 0
+  with pytest.raises(ValueError, match="duplicate"):
+    m.DeviceAllocationState([0, 0, 1])
