@@ -136,3 +136,22 @@ def test_top_k_and_top_p_in_the_paged_engine():
       assert int(t) in torch.topk(z, 3).indices.tolist()
       np.testing.assert_allclose(float(torch.log_softmax(z, -1)[int(t)]), float(lp), atol=2e-4)
       ids.append(int(t))
+
+
+def test_sglang_jax_configuration_is_translated_to_engine_geometry():
+  import types
+  from tunix_b200.common.configs import RolloutConfig
+  from tunix_b200.rl.rollout import sglang_jax_rollout as sg
+  mc = types.SimpleNamespace(num_layers=4, num_kv_heads=2, head_dim=64)
+  rc = RolloutConfig(max_tokens_to_generate=64, max_prompt_length=64, kv_cache_size=96,
+                     rollout_sglang_jax_page_size=128, rollout_sglang_jax_context_length=512,
+                     rollout_sglang_jax_max_running_requests=48, rollout_sglang_jax_chunked_prefill_size=2048,
+                     rollout_sglang_jax_precompile_bs_paddings=[8, 16, 64], rollout_sglang_jax_mem_fraction_static=0.5)
+  g = sg.engine_geometry(rc, mc, device_memory_bytes=1 << 30)
+  assert g["page_size"] == 64 and g["max_seq_len"] == 512 and g["max_batch"] == 48
+  assert g["max_prefill_tokens"] == 2048 and g["warm_buckets"] == [8, 16, 48]
+  per_page = 64 * 2 * 4 * 2 * 64 * 2
+  assert g["num_pages"] == min(48 * 8, (1 << 29) // per_page)
+  small = sg.engine_geometry(RolloutConfig(max_tokens_to_generate=8, max_prompt_length=8, kv_cache_size=16,
+                                           rollout_sglang_jax_page_size=4, rollout_sglang_jax_chunked_prefill_size=-1), mc)
+  assert small["page_size"] == 8 and small["max_seq_len"] == 16 and "max_prefill_tokens" not in small

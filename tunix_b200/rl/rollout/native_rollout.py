@@ -34,7 +34,8 @@ DEFAULT_PAGE_SIZE = 64       # one TMA box per 64-key tile in the decode kernel
 
 class NativeRollout(base_rollout.BaseRollout):
   def __init__(self, model: torch.nn.Module, tokenizer: Any, rollout_config: base_rollout.RolloutConfig, mesh=None,
-               page_size: Optional[int] = None, max_batch: Optional[int] = None):
+               page_size: Optional[int] = None, max_batch: Optional[int] = None,
+               engine_overrides: Optional[dict] = None):
     page_size = page_size or DEFAULT_PAGE_SIZE
     max_batch = max_batch or DEFAULT_MAX_BATCH
     self._model = model
@@ -57,8 +58,10 @@ class NativeRollout(base_rollout.BaseRollout):
       self._engine = None
     else:
       max_seq = max(rc.kv_cache_size, rc.max_prompt_length + rc.max_tokens_to_generate)
+      extra = {k: v for k, v in (engine_overrides or {}).items() if k in ("max_prefill_tokens", "num_pages", "share_prefix")}
+      max_seq = max(max_seq, int((engine_overrides or {}).get("max_seq_len", 0)))
       self._engine = PagedEngine(model, EngineConfig(page_size=page_size, max_batch=max_batch, max_seq_len=max_seq,
-                                                     use_cuda_graphs=next(model.parameters()).is_cuda))
+                                                     use_cuda_graphs=next(model.parameters()).is_cuda, **extra))
 
   def _build_replica(self, trainer_model: torch.nn.Module, tp: int, mesh):
     """This rank's tensor-parallel slice of the trainer's weights, as a model of its own."""
