@@ -655,6 +655,13 @@ int launch_skinny(const void* X, const void* W, SkinnyParams p, long long ldx, l
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = s; best_nc = nc; }
   }
   if (best_cost < 0) return 301;
+  static const bool verbose = [] { const char* e = getenv("TUNIX_B200_SKINNY_VERBOSE"); return e && e[0] == '1'; }();
+  if (verbose) {
+    fprintf(stderr, "[gemm_skinny] rows<=%d glu=%d N=%d K=%d slabs=%d kblocks=%d -> split %d x %d clusters; resident clusters by split:",
+            BNX, GLU ? 1 : 0, p.Nw, p.K, slabs, num_kb, best_s, best_nc);
+    for (int s = 1; s <= 8; ++s) fprintf(stderr, " %d:%d", s, fit.known[s] ? fit.max_clusters[s] : -1);
+    fprintf(stderr, "\n");
+  }
   p.split = best_s;
   p.n_clusters = best_nc;
   p.stages = fit.stages[best_s];
