@@ -40,3 +40,22 @@ def test_graph_decode_matches_eager_and_training_logprobs(kernel_lib):
     ref = torch.log_softmax(logits[0, len(p) - 1:-1].float(), -1).gather(-1, seq[0, len(p):, None])[:, 0]
     np.testing.assert_allclose(lp, ref.cpu().numpy(), rtol=0, atol=0.08)
   assert len({tuple(t.tolist()) for t in outs[1].tokens[-3:]}) > 1     # samples of one prompt differ
+
+
+def test_decode_of_96_sequences_matches_training_logprobs(kernel_lib):
+  """Above 64 rows the plain decode products take the general GEMM (residual through accumulate), gate|up keeps
+  the fused-GLU skinny kernel: same log-probs as the training forward."""
+  from tunix_b200.ops import _lib
+  from tunix_b200.rollout import EngineConfig, PagedEngine
+  m = model()
+  rng = np.random.default_rng(1)
+  prompts = [rng.integers(3, 500, size=int(n)).tolist() for n in rng.integers(4, 40, size=96)]
+  eng = PagedEngine(m, EngineConfig(page_size=16, max_batch=96, max_seq_len=128, use_cuda_graphs=True))
+  out = eng.generate(prompts, 8, temperature=1.0, seed=3)
+  _lib.check_status()
+  for p, t, lp in list(zip(prompts, out.tokens, out.logprobs))[::7]:
+    seq = torch.tensor([p + t.tolist()], device="cuda")
+    with torch.no_grad():
+      logits, _ = m(seq, None, None, None)
+    ref = torch.log_softmax(logits[0, len(p) - 1:-1].float(), -1).gather(-1, seq[0, len(p):, None])[:, 0]
+    np.testing.assert_allclose(lp, ref.cpu().numpy(), rtol=0, atol=0.08)

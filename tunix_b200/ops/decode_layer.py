@@ -22,6 +22,8 @@ tolerance the rollout tests state.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import kernels, paged
@@ -65,6 +67,25 @@ def _w(lin) -> torch.Tensor:
   return getattr(lin, "inner", lin).w
 
 
+# Above this many rows the plain products (q|k|v, o_proj, down) take the general GEMM: the skinny kernel's 128-row
+# variant halves its ring depth and was measured slower there (31.7 / 29.6 / 64.5 us against 25.6 / 27.6 / 45.9 at
+# 128 rows), while gate|up keeps it for the fused GLU. Tensor-parallel exits always use the skinny kernel, which
+# carries the all-reduce.
+_SKINNY_PLAIN_MAX_ROWS = int(os.environ.get("TUNIX_B200_SKINNY_PLAIN_MAX_ROWS", "64"))
+
+
+def _project(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, tp=None) -> torch.Tensor:
+  """x Wᵀ (+ bias) (+ residual) for a decode batch, on whichever kernel is faster at this row count."""
+  if tp is not None or x.shape[0] <= _SKINNY_PLAIN_MAX_ROWS:
+    return kernels.gemm_skinny(x, w, bias=bias, residual=residual, tp=tp)
+  if residual is not None:
+    out = residual.clone()
+    kernels.gemm(x, w, out=out, accumulate=True)
+    return out
+  out = kernels.gemm(x, w)
+  return out if bias is None else out.add_(bias)
+
+
 def run(layer, h: torch.Tensor, positions: torch.Tensor, cache) -> torch.Tensor:
   """h [B, 1, D] -> [B, 1, D]; K/V of the new tokens are written into `cache`'s pages."""
   cfg = layer.cfg
@@ -76,7 +97,7 @@ def run(layer, h: torch.Tensor, positions: torch.Tensor, cache) -> torch.Tensor:
     h2 = h2.contiguous()
   x, _, _ = kernels.rmsnorm_fwd(h2, layer.input_layernorm.w, cfg.norm_eps, cfg.norm_offset, want_rstd=False)
   qkv_lin = getattr(a.qkv_proj, "inner", a.qkv_proj)
-  qkv = kernels.gemm_skinny(x, qkv_lin.w, bias=qkv_lin.b)
+  qkv = _project(x, qkv_lin.w, bias=qkv_lin.b)
   theta, rscale = a._theta_scale()
   table = F.rope_table(H, theta, cfg.max_position or F._position_bound() or 4096, h.device, rscale)
   pos = positions.reshape(-1).to(torch.int32)
@@ -86,9 +107,9 @@ def run(layer, h: torch.Tensor, positions: torch.Tensor, cache) -> torch.Tensor:
   q = qkv[:, :N * H].view(B, N, H)
   o = paged.paged_decode_attention(q, cache.k_pages, cache.v_pages, cache.block_tables, cache.seq_lens,
                                    cfg.attn_scale, cache.num_splits, cache.max_len)
-  h_mid = kernels.gemm_skinny(o.view(B, N * H), _w(a.o_proj), residual=h2, tp=getattr(a.o_proj, "tp_exit", None))
+  h_mid = _project(o.view(B, N * H), _w(a.o_proj), residual=h2, tp=getattr(a.o_proj, "tp_exit", None))
   x2, _, _ = kernels.rmsnorm_fwd(h_mid, layer.post_attention_layernorm.w, cfg.norm_eps, cfg.norm_offset,
                                  want_rstd=False)
   act = kernels.gemm_skinny(x2, _w(m.gate_up_proj), glu="gelu" if m.kind == "gelu" else "silu")
-  out = kernels.gemm_skinny(act, _w(m.down_proj), residual=h_mid, tp=getattr(m.down_proj, "tp_exit", None))
+  out = _project(act, _w(m.down_proj), residual=h_mid, tp=getattr(m.down_proj, "tp_exit", None))
   return out.view(B, 1, D)
