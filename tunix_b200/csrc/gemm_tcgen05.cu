@@ -312,14 +312,11 @@ static int g_deterministic = 0;
 // is then reduced in one fixed order and repeated launches give identical bits.
 extern "C" void tx_gemm_set_deterministic(int v) { g_deterministic = v; }
 
-// Skinny-GEMM policy knobs (decode shapes, M <= 128): tile width 64 or 32 for the plain K-major product, and the
-// tile count below which K is split over several CTAs. Settable for measurements; the defaults are the measured best.
-static int g_skinny_bn32 = 0;
-static int g_split_limit = 96;
-extern "C" void tx_gemm_set_tuning(int skinny_bn32, int split_limit) {
-  g_skinny_bn32 = skinny_bn32;
-  if (split_limit > 0) g_split_limit = split_limit;
-}
+// Policy of the general kernel for products with few rows (M <= 128; the decode path proper uses gemm_skinny.cu):
+// 64-column tiles (32-column ones were measured slower on every decode shape but 4096 x 4096), and K split over
+// several CTAs when fewer than 96 tiles exist.
+constexpr int g_skinny_bn32 = 0;
+constexpr int g_split_limit = 96;
 
 static int g_disable_pair = 0;
 // Test hook: 1 forces the single-CTA kernels for every shape.
