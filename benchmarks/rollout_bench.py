@@ -52,6 +52,8 @@ def main():
   n = sum(len(t) for t in res.tokens)
   print(json.dumps({"metric": "rollout generated tokens/s", "value": round(n / ms * 1e3, 1), "ms": round(ms, 1),
                     "generated": n, "decode_steps": res.steps, "ms_per_decode_step": round(ms / max(res.steps, 1), 3),
+                    "prefill_ms": round(res.prefill_ms, 1),
+                    "decode_only_ms_per_step": round((ms - res.prefill_ms) / max(res.steps, 1), 3),
                     "sequences": len(prompts), "model": a.model, "layers": cfg.num_layers,
                     "cuda_graphs": not a.no_graphs, "page_size": a.page_size, "kv_cache_gb": round(eng.cache.bytes() / 2 ** 30, 1),
                     "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)}))

@@ -72,6 +72,20 @@ def main():
                                  for p, t, lp in zip(prompts, got.tokens, got.logprobs))
       res[f"captured_{key}"] = bool(graphs and any(v is not False for v in eng._graphs.values()))
     del rep, eng, ref
+  # 96 sequences: above 64 rows the tensor-parallel exits run as two chunks of the skinny kernel and the plain
+  # products take the general GEMM; tokens still agree across the group and with the unsharded model
+  rep = weight_sync.RolloutReplica(trainer, tp_mesh, "tp")
+  rep.sync()
+  many = [rng.integers(3, 500, size=int(n)).tolist() for n in rng.integers(4, 40, size=96)]
+  eng = PagedEngine(rep.model, EngineConfig(page_size=16, max_batch=96, max_seq_len=128, use_cuda_graphs=True))
+  got = eng.generate(many, 8, temperature=1.0, seed=5)
+  toks = torch.tensor([t.tolist() for t in got.tokens], device=dev)
+  peer_toks = [torch.empty_like(toks) for _ in range(world)]
+  dist.all_gather(peer_toks, toks)
+  res["same_tokens_96"] = all(torch.equal(peer_toks[0], t) for t in peer_toks)
+  res["lp_err_96"] = max(float(np.abs(lp - reference_logprobs(p, t)).max())
+                         for p, t, lp in list(zip(many, got.tokens, got.logprobs))[::9])
+  del rep, eng
   # a weight change reaches the replica through the next sync
   rep = weight_sync.RolloutReplica(trainer, tp_mesh, "tp")
   rep.sync()

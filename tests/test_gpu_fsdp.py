@@ -105,6 +105,7 @@ def test_tensor_parallel_rollout_with_kernel_weight_sync_two_gpus(kernel_lib, tm
       assert res[f"same_tokens_{key}"], res                # reduced logits are bitwise equal on the ranks of a group
       assert res[f"lp_err_{key}"] < 0.08, res
     assert res["captured_own_graph"] and res["captured_peer_graph"], res
+    assert res["same_tokens_96"] and res["lp_err_96"] < 0.08, res
     assert abs(res["update_ratio"] - 1.5) < 0.02, res
 
 

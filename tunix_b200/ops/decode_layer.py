@@ -76,8 +76,19 @@ _SKINNY_PLAIN_MAX_ROWS = int(os.environ.get("TUNIX_B200_SKINNY_PLAIN_MAX_ROWS", 
 
 def _project(x: torch.Tensor, w: torch.Tensor, *, bias=None, residual=None, tp=None) -> torch.Tensor:
   """x Wᵀ (+ bias) (+ residual) for a decode batch, on whichever kernel is faster at this row count."""
-  if tp is not None or x.shape[0] <= _SKINNY_PLAIN_MAX_ROWS:
+  rows = x.shape[0]
+  if rows <= _SKINNY_PLAIN_MAX_ROWS:
     return kernels.gemm_skinny(x, w, bias=bias, residual=residual, tp=tp)
+  if tp is not None:
+    # a tensor-parallel exit stays on the skinny kernel (it carries the all-reduce) but runs in chunks of at most
+    # 64 rows, the kernel's fast variant; the weight slice of a TP rank is re-read from L2 by the second chunk.
+    # Every rank of the group sees the same row count, so all of them issue the same sequence of exits.
+    out = torch.empty((rows, w.shape[0]), dtype=x.dtype, device=x.device)
+    for lo in range(0, rows, _SKINNY_PLAIN_MAX_ROWS):
+      hi = min(rows, lo + _SKINNY_PLAIN_MAX_ROWS)
+      kernels.gemm_skinny(x[lo:hi], w, out=out[lo:hi], bias=bias, tp=tp,
+                          residual=None if residual is None else residual[lo:hi])
+    return out
   if residual is not None:
     out = residual.clone()
     kernels.gemm(x, w, out=out, accumulate=True)

@@ -41,6 +41,7 @@ class GenerationResult:
   logprobs: Optional[List[np.ndarray]]
   finish_reasons: List[str]                # "eos" | "length"
   steps: int = 0                           # decode forwards that were run
+  prefill_ms: float = 0.0                  # device time spent in prompt forwards (CUDA events; 0 on CPU)
 
 
 @dataclasses.dataclass
@@ -310,13 +311,22 @@ class PagedEngine:
     running: List[_Seq] = []
     results: Dict[int, _Seq] = {}
     steps = 0
+    timed = self.device.type == "cuda"
+    prefill_marks = []
     try:
       while waiting or running:
         groups = self._admit(waiting, running)
         if not groups and not running:
           raise OutOfPages(f"a request needs {self._pages_needed(waiting[0])} pages but the cache has only "
                            f"{self.cache.num_pages}")
-        self._prefill_groups(groups, sampling, results)
+        if groups and timed:
+          marks = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          marks[0].record()
+          self._prefill_groups(groups, sampling, results)
+          marks[1].record()
+          prefill_marks.append(marks)
+        else:
+          self._prefill_groups(groups, sampling, results)
         running = self._retire(running, results)
         if not running:
           continue
@@ -333,6 +343,10 @@ class PagedEngine:
       from ..ops import _lib
       _lib.check_status(self.device)     # a kernel that gave up a bounded wait or met a bad argument: not a result
     order = [results[i] for i in range(len(prompts))]
-    return GenerationResult(tokens=[np.asarray(s.out, dtype=np.int64) for s in order],
+    prefill_ms = 0.0
+    if prefill_marks:
+      prefill_marks[-1][1].synchronize()
+      prefill_ms = float(sum(a.elapsed_time(b) for a, b in prefill_marks))
+    return GenerationResult(prefill_ms=prefill_ms, tokens=[np.asarray(s.out, dtype=np.int64) for s in order],
                             logprobs=[np.asarray(s.lps, dtype=np.float32) for s in order] if return_logprobs else None,
                             finish_reasons=[s.reason for s in order], steps=steps)
