@@ -1,89 +1,83 @@
-"""Thread-safe registry of named functions per category: policy / value loss functions,
-advantage estimators, reward managers (tunix/rl/function_registry.py:26-168). Configs refer to
-these by string name."""
+"""Named functions that configs refer to by string: policy / value loss functions, advantage estimators, reward
+managers (tunix/rl/function_registry.py:26-168).
+
+A `FunctionRegistry` is a set of *categories*, each a name -> callable table. Entries are immutable once added
+(registering a name twice is an error), tables are copy-on-write under one lock so that lookups - which happen on the
+training path - take no lock, and the category-specific helpers at the bottom (`register_policy_loss_fn`, ...) are
+generated from one list instead of being spelled out four times.
+"""
 from __future__ import annotations
 
 import threading
-from typing import Any, Callable, Dict, FrozenSet, Iterable, List, Optional
+from typing import Any, Callable, Dict, FrozenSet, Iterable, List, Mapping, Optional
+
+Fn = Callable[..., Any]
 
 _POLICY_LOSS_FN_CATEGORY = "policy_loss_fn"
 _VALUE_LOSS_FN_CATEGORY = "value_loss_fn"
 _ADVANTAGE_ESTIMATOR_CATEGORY = "advantage_estimator"
 _REWARD_MANAGER_CATEGORY = "reward_manager"
+_BUILT_IN = (_POLICY_LOSS_FN_CATEGORY, _VALUE_LOSS_FN_CATEGORY, _ADVANTAGE_ESTIMATOR_CATEGORY, _REWARD_MANAGER_CATEGORY)
 
 
 class FunctionRegistry:
-  DEFAULT_ALLOWED_CATEGORIES: FrozenSet[str] = frozenset({
-      _POLICY_LOSS_FN_CATEGORY, _VALUE_LOSS_FN_CATEGORY, _ADVANTAGE_ESTIMATOR_CATEGORY, _REWARD_MANAGER_CATEGORY})
+  DEFAULT_ALLOWED_CATEGORIES: FrozenSet[str] = frozenset(_BUILT_IN)
 
   def __init__(self, allowed_categories: Optional[Iterable[str]] = None):
-    self._allowed_categories = (frozenset(allowed_categories) if allowed_categories is not None
-                                else self.DEFAULT_ALLOWED_CATEGORIES)
-    self._registry: Dict[str, Dict[str, Callable[..., Any]]] = {c: {} for c in self._allowed_categories}
-    self._lock = threading.Lock()
+    self._allowed_categories = (self.DEFAULT_ALLOWED_CATEGORIES if allowed_categories is None
+                                else frozenset(allowed_categories))
+    self._tables: Mapping[str, Mapping[str, Fn]] = {c: {} for c in self._allowed_categories}
+    self._write = threading.Lock()
 
-  def _validate_category(self, category: str) -> None:
-    if category not in self._allowed_categories:
-      raise ValueError(f"Invalid category: '{category}'. Allowed categories are: {sorted(self._allowed_categories)}")
+  def _table(self, category: str) -> Mapping[str, Fn]:
+    try:
+      return self._tables[category]
+    except KeyError:
+      raise ValueError(f"Invalid category: '{category}'. Allowed categories are: "
+                       f"{sorted(self._allowed_categories)}") from None
 
-  def register(self, category: str, name: str) -> Callable[[Callable[..., Any]], Callable[..., Any]]:
-    self._validate_category(category)
+  def add(self, category: str, name: str, func: Fn) -> Fn:
+    self._table(category)                                   # validates before taking the lock
+    with self._write:
+      table = self._tables[category]
+      if name in table:
+        raise ValueError(f"'{name}' is already registered in category '{category}'.")
+      self._tables = {**self._tables, category: {**table, name: func}}
+    return func
 
-    def decorator(func: Callable[..., Any]) -> Callable[..., Any]:
-      with self._lock:
-        if name in self._registry[category]:
-          raise ValueError(f"'{name}' is already registered in category '{category}'.")
-        self._registry[category][name] = func
-      return func
-    return decorator
+  def register(self, category: str, name: str) -> Callable[[Fn], Fn]:
+    """Decorator form of `add`."""
+    self._table(category)
+    return lambda func: self.add(category, name, func)
 
-  def get(self, category: str, name: str) -> Callable[..., Any]:
-    self._validate_category(category)
-    with self._lock:
-      if name not in self._registry[category]:
-        raise LookupError(f"'{name}' not found in category '{category}'. Available: "
-                          f"{sorted(self._registry[category])}")
-      return self._registry[category][name]
+  def get(self, category: str, name: str) -> Fn:
+    table = self._table(category)
+    if name not in table:
+      raise LookupError(f"'{name}' not found in category '{category}'. Available: {sorted(table)}")
+    return table[name]
 
   def list_categories(self) -> List[str]:
     return sorted(self._allowed_categories)
 
   def list_functions(self, category: str) -> List[str]:
-    self._validate_category(category)
-    with self._lock:
-      return sorted(self._registry[category])
+    return sorted(self._table(category))
 
 
 default_registry = FunctionRegistry()
 
 
-def get_policy_loss_fn(name: str):
-  return default_registry.get(_POLICY_LOSS_FN_CATEGORY, name)
+def _helpers(category: str):
+  def getter(name: str) -> Fn:
+    return default_registry.get(category, name)
+
+  def registrar(name: str) -> Callable[[Fn], Fn]:
+    return default_registry.register(category, name)
+  getter.__doc__ = f"The `{category}` registered under `name` in the default registry."
+  registrar.__doc__ = f"Decorator: registers a `{category}` under `name` in the default registry."
+  return getter, registrar
 
 
-def register_policy_loss_fn(name: str):
-  return default_registry.register(_POLICY_LOSS_FN_CATEGORY, name)
-
-
-def get_advantage_estimator(name: str):
-  return default_registry.get(_ADVANTAGE_ESTIMATOR_CATEGORY, name)
-
-
-def register_advantage_estimator(name: str):
-  return default_registry.register(_ADVANTAGE_ESTIMATOR_CATEGORY, name)
-
-
-def get_reward_manager(name: str):
-  return default_registry.get(_REWARD_MANAGER_CATEGORY, name)
-
-
-def register_reward_manager(name: str):
-  return default_registry.register(_REWARD_MANAGER_CATEGORY, name)
-
-
-def get_value_loss_fn(name: str):
-  return default_registry.get(_VALUE_LOSS_FN_CATEGORY, name)
-
-
-def register_value_loss_fn(name: str):
-  return default_registry.register(_VALUE_LOSS_FN_CATEGORY, name)
+get_policy_loss_fn, register_policy_loss_fn = _helpers(_POLICY_LOSS_FN_CATEGORY)
+get_value_loss_fn, register_value_loss_fn = _helpers(_VALUE_LOSS_FN_CATEGORY)
+get_advantage_estimator, register_advantage_estimator = _helpers(_ADVANTAGE_ESTIMATOR_CATEGORY)
+get_reward_manager, register_reward_manager = _helpers(_REWARD_MANAGER_CATEGORY)
