@@ -59,3 +59,32 @@ def test_device_lane_span_is_closed_by_a_cuda_timing_event(kernel_lib):
   (span,) = lane.cur_step.values()
   device_s = e0.elapsed_time(e1) * 1e-3
   assert span.ended and span.duration >= 0.8 * device_s and span.duration < device_s + 0.05
+
+
+def test_own_peer_allocator_single_rank(kernel_lib, tmp_path):
+  """`dist/vmm.py` with a group of one: the buffer is a real tensor over driver-allocated memory, and the 2-D peer
+  copy kernel reads it through the pointer the heap reports."""
+  import torch.distributed as dist
+  from tunix_b200.dist import symm, vmm
+  assert vmm.available() is None
+  created = not dist.is_initialized()
+  if created:
+    dist.init_process_group("gloo", init_method=f"file://{tmp_path}/rdv", rank=0, world_size=1)
+  try:
+    dev = torch.device("cuda", 0)
+    heap = vmm.PeerHeap(None, dev)
+    buf = heap.alloc(4096 * 2)
+    t = buf.local.view(torch.bfloat16)
+    assert t.numel() == 4096 and t.data_ptr() == buf.ptrs[0] and float(t.float().abs().sum()) == 0.0
+    t.copy_(torch.arange(4096, device=dev).to(torch.bfloat16))
+    lib = symm._declare()
+    from tunix_b200.ops import _lib
+    dst = torch.zeros(8, 256, dtype=torch.bfloat16, device=dev)
+    rc = lib.tx_peer_copy_2d(buf.ptrs[0] + 2 * 256, dst.data_ptr(), 8, 256, 512, 256, _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, t.view(8, 512)[:, 256:])
+    heap.close()
+  finally:
+    if created:
+      dist.destroy_process_group()

@@ -11,8 +11,8 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, out, transport, port):
-  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000")
+def _run(nproc, out, transport, port, **extra_env):
+  env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000", **extra_env)
   if nproc == 1:
     cmd = [sys.executable, os.path.join(HERE, "_fsdp_worker.py"), "--out", out, "--transport", transport]
   else:
@@ -33,6 +33,19 @@ def test_fsdp2_matches_single_gpu(kernel_lib, tmp_path, transport):
   for n, p in ref["params"].items():
     q = got["params"][n]
     rel = (p - q).norm() / (p.norm() + 1e-6)
+    assert rel < 2e-2, (n, rel.item())
+  assert abs(ref["loss"][-1] - got["loss"][-1]) < 0.05
+
+
+def test_fsdp2_on_the_own_peer_allocator(kernel_lib, tmp_path):
+  """The same equivalence with the symmetric buffers coming from `dist/vmm.py` (cuMemCreate, descriptors over Unix
+  sockets, cuMemMap) instead of torch's symmetric-memory plumbing."""
+  if torch.cuda.device_count() < 2:
+    pytest.skip("needs 2 GPUs")
+  ref = _run(1, str(tmp_path / "ref.pt"), "local", 0)
+  got = _run(2, str(tmp_path / "vmm.pt"), "p2p", 29613, TUNIX_B200_SYMM_BACKEND="vmm")
+  for n, p in ref["params"].items():
+    rel = (p - got["params"][n]).norm() / (p.norm() + 1e-6)
     assert rel < 2e-2, (n, rel.item())
   assert abs(ref["loss"][-1] - got["loss"][-1]) < 0.05
 

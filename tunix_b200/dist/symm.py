@@ -1,10 +1,12 @@
 """Symmetric (peer-mapped) buffers and the collectives built on them.
 
-`torch.distributed._symmetric_memory` does the plumbing only: it allocates a buffer on every
-rank of a group and exchanges the handles, so each process holds a device pointer to every
-peer's copy (NVLink / NVSwitch peer access). The data movement itself is done by this package's
-own kernels (`csrc/peer_comm.cu`), which read and write the peers' buffers with plain loads and
-stores from inside the compute kernel:
+Two interchangeable backends provide the buffers, so that each process holds a device pointer to every peer's
+copy (NVLink / NVSwitch peer access): `TUNIX_B200_SYMM_BACKEND=vmm` is this package's own allocator
+(`dist/vmm.py`: `cuMemCreate` + descriptor passing over Unix sockets + `cuMemMap` of every peer's allocation);
+`torch` delegates allocation and handle exchange to `torch.distributed._symmetric_memory` (a private torch API,
+used for nothing else). The data movement itself is done by this package's own kernels
+(`csrc/peer_comm.cu`), which read and write the peers' buffers with plain loads and stores from inside
+the compute kernel:
 
   * `reduce_scatter_sum`  - pull-and-sum of the peers' fp32 gradient shards,
   * `adamw_allgather`     - AdamW on the local master shard, result pushed to every peer,
@@ -24,6 +26,8 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
+
+_DEFAULT_BACKEND = "torch"       # "vmm": the own allocator of dist/vmm.py
 
 _P, _I, _L, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
@@ -59,9 +63,18 @@ class SymmetricBuffers:
   """A set of named buffers allocated symmetrically on every rank of `group`."""
 
   def __init__(self, group, device: torch.device):
-    import torch.distributed._symmetric_memory as symm_mem
-    self._sm = symm_mem
+    from . import vmm
+    backend = os.environ.get("TUNIX_B200_SYMM_BACKEND", _DEFAULT_BACKEND)
+    if backend == "vmm" and vmm.available() is not None:
+      raise RuntimeError(f"TUNIX_B200_SYMM_BACKEND=vmm: {vmm.available()}")
+    self._heap = None
+    self._sm = None
     self.group = group if group is not None else dist.group.WORLD
+    if backend == "vmm":
+      self._heap = vmm.PeerHeap(self.group, device)
+    else:
+      import torch.distributed._symmetric_memory as symm_mem
+      self._sm = symm_mem
     self.world = dist.get_world_size(self.group)
     self.rank = dist.get_rank(self.group)
     self.device = device
@@ -77,6 +90,16 @@ class SymmetricBuffers:
     self._epoch1 = 0
 
   def alloc(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    """Collective: every rank allocates the same buffers in the same order. Peer pointers are known at once with
+    the own allocator, after `rendezvous()` with the torch backend; callers always rendezvous before use."""
+    if self._heap is not None:
+      itemsize = torch.empty((), dtype=dtype).element_size()
+      buf = self._heap.alloc(numel * itemsize)
+      t = buf.local.view(dtype)[:numel]
+      self.tensors[name] = t
+      self._pending_ptrs = getattr(self, "_pending_ptrs", {})
+      self._pending_ptrs[name] = buf.ptrs
+      return t
     t = self._sm.empty(numel, dtype=dtype, device=self.device)
     self.tensors[name] = t
     return t
@@ -88,6 +111,10 @@ class SymmetricBuffers:
         continue
       if name in ("_flags", "_flags1"):
         t.zero_()
+      if self._heap is not None:
+        self.handles[name] = self._heap
+        self.peer_ptrs[name] = [int(p) for p in self._pending_ptrs.pop(name)]
+        continue
       h = self._sm.rendezvous(t, self.group)
       self.handles[name] = h
       self.peer_ptrs[name] = [int(p) for p in h.buffer_ptrs]
