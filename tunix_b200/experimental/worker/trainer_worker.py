@@ -3,6 +3,7 @@
 lifecycle state, and is the SOURCE side of weight-sync rounds."""
 from __future__ import annotations
 
+import functools
 from typing import Any, Callable, Dict, Optional, Sequence
 
 from ..common import datatypes
@@ -13,7 +14,32 @@ from . import abstract_worker
 WorkerState = datatypes.WorkerState
 
 
+def _serving(method):
+  """An API call that needs a READY worker (a PENDING one is initialised on the way) and whose failure puts the
+  worker into ERROR with the message kept for the next heartbeat."""
+  @functools.wraps(method)
+  def guarded(self: "TrainerWorker", *args, **kwargs):
+    if self.state == WorkerState.PENDING:
+      self.initialize()
+    if self.state != WorkerState.READY:
+      raise RuntimeError(f"TrainerWorker is not ready: {self.state.value}.")
+    try:
+      result = method(self, *args, **kwargs)
+    except Exception as e:
+      self._last_error = str(e)
+      self._state = WorkerState.ERROR
+      raise
+    self._last_error = None
+    return result
+  return guarded
+
+
 class TrainerWorker(abstract_worker.Worker):
+  """Everything a caller learns comes back as a `Response` whose metadata carries the worker id, its state and the
+  policy version next to the call's own fields (`_reply`); trainer return values that are dicts are merged in."""
+
+  ROLES = frozenset({"trainer", "actor", "weight_sync"})
+
   def __init__(self, trainer_factory: Callable[[], abstract_trainer.AbstractTrainer], *,
                worker_id: str = "trainer_worker", handler: Optional[weight_sync.WeightSyncHandler] = None,
                rank: int = 0):
@@ -27,113 +53,106 @@ class TrainerWorker(abstract_worker.Worker):
   def trainer(self) -> abstract_trainer.AbstractTrainer:
     return self._trainer
 
-  def _version(self) -> int:
+  @property
+  def policy_version(self) -> int:
     return int(getattr(self._trainer, "policy_version", 0))
 
-  def _response(self, **md) -> datatypes.Response:
+  def _reply(self, returned: Any = None, **fields) -> datatypes.Response:
+    extra = returned if isinstance(returned, dict) else {}
     return datatypes.Response(metadata={"worker_id": self._worker_id, "state": self.state.value,
-                                        "policy_version": self._version(), **md})
-
-  def _ensure_ready(self) -> None:
-    if self.state == WorkerState.PENDING:
-      self.initialize()
-    if self.state != WorkerState.READY:
-      raise RuntimeError(f"TrainerWorker is not ready: {self.state.value}.")
-
-  def _guard(self, fn, *a, **k):
-    try:
-      out = fn(*a, **k)
-      self._last_error = None
-      return out
-    except Exception as e:
-      self._last_error = str(e)
-      self._state = WorkerState.ERROR
-      raise
+                                        "policy_version": self.policy_version, **fields, **extra})
 
   # ---- lifecycle -----------------------------------------------------------------------------
   def initialize(self) -> datatypes.Response:
     if self.state == WorkerState.READY:
-      return self._response(initialized=True, already_ready=True)
+      return self._reply(initialized=True, already_ready=True)
     self.state = WorkerState.INITIALIZING
     self.state = WorkerState.READY
-    return self._response(initialized=True)
+    return self._reply(initialized=True)
 
   def compile(self, dummy_data: Any = None) -> datatypes.Response:
     if self.state == WorkerState.PENDING:
       self.initialize()
     with self._phase(WorkerState.COMPILING):
-      self._guard(self._trainer.compile, dummy_data)
-    return self._response(compiled=True)
+      try:
+        self._trainer.compile(dummy_data)
+      except Exception as e:
+        self._last_error = str(e)
+        raise
+    return self._reply(compiled=True)
 
   def start(self) -> datatypes.Response:
     if self.state == WorkerState.PENDING:
       self.initialize()
     if self.state != WorkerState.READY:
       raise RuntimeError(f"Cannot start TrainerWorker from {self.state.value}.")
-    return self._response(started=True)
+    return self._reply(started=True)
 
   def stop(self) -> datatypes.Response:
     if self.state == WorkerState.STOPPED:
-      return self._response(stopped=True, already_stopped=True)
+      return self._reply(stopped=True, already_stopped=True)
     if self.state == WorkerState.READY:
       self.state = WorkerState.DRAINING
     try:
       self._trainer.close()
     finally:
       self._state = WorkerState.STOPPED
-    return self._response(stopped=True)
+    return self._reply(stopped=True)
 
   def info(self) -> datatypes.WorkerInfo:
-    return datatypes.WorkerInfo(worker_id=self._worker_id, roles=frozenset({"trainer", "actor", "weight_sync"}),
-                                resources={"trainer": type(self._trainer).__name__, "policy_version": self._version()})
+    return datatypes.WorkerInfo(worker_id=self._worker_id, roles=self.ROLES,
+                                resources={"trainer": type(self._trainer).__name__, "policy_version": self.policy_version})
 
   def heartbeat(self) -> datatypes.HealthReport:
-    return datatypes.HealthReport(state=self.state, policy_version=self._version(), last_error=self._last_error)
+    return datatypes.HealthReport(state=self.state, policy_version=self.policy_version, last_error=self._last_error)
 
-  # ---- training API --------------------------------------------------------------------------
+  # ---- configuration -------------------------------------------------------------------------
   def with_loss_fn(self, loss_fn, has_aux: bool = False) -> datatypes.Response:
     self._trainer.with_loss_fn(loss_fn, has_aux)
-    return self._response(loss_fn_configured=True)
+    return self._reply(loss_fn_configured=True)
 
   def with_gen_model_input_fn(self, fn) -> datatypes.Response:
     self._trainer.with_gen_model_input_fn(fn)
-    return self._response(gen_model_input_fn_configured=True)
+    return self._reply(gen_model_input_fn_configured=True)
 
+  # ---- training API --------------------------------------------------------------------------
+  @_serving
   def fwd_bwd(self, payload: Any, **kwargs) -> datatypes.Response:
-    self._ensure_ready()
-    kwargs.pop("skip_jit", None)
-    out = self._guard(self._trainer.fwd_bwd, payload, **kwargs)
-    return self._response(queued=True, **(out if isinstance(out, dict) else {}))
+    kwargs.pop("skip_jit", None)                 # a tracing-compiler switch of the reference's API; nothing to skip here
+    return self._reply(self._trainer.fwd_bwd(payload, **kwargs), queued=True)
 
+  @_serving
   def update(self, **kwargs) -> int:
-    self._ensure_ready()
-    return self._guard(self._trainer.update, **kwargs)
+    return self._trainer.update(**kwargs)
 
   def train_step(self, payload: Any, accumulate_gradients: bool = False, apply_optimizer: bool = True,
                  **kwargs) -> datatypes.Response:
     """`fwd_bwd` on the payload, then `update` when `apply_optimizer`."""
-    r = self.fwd_bwd(payload, **kwargs)
+    reply = self.fwd_bwd(payload, **kwargs)
     if apply_optimizer:
-      r.metadata["train_steps"] = self.update()
-      r.metadata["policy_version"] = self._version()
-    return r
+      reply.metadata["train_steps"] = self.update()
+      reply.metadata["policy_version"] = self.policy_version
+    return reply
 
+  @_serving
   def eval_step(self, payload: Any, **kwargs) -> datatypes.Response:
-    self._ensure_ready()
-    out = self._guard(self._trainer.eval_step, payload, **kwargs)
-    return self._response(evaluated=True, **(out if isinstance(out, dict) else {}))
+    return self._reply(self._trainer.eval_step(payload, **kwargs), evaluated=True)
 
+  @_serving
   def run_eval(self, eval_ds: Any, **kwargs) -> datatypes.Response:
-    self._ensure_ready()
     if eval_ds is None:
-      return self._response(evaluated=True, eval_batches=0)
-    fn = getattr(self._trainer, "run_eval", None)
-    out = self._guard(fn, eval_ds, **kwargs) if callable(fn) else {"batches": sum(1 for b in eval_ds
-                                                                                  if self._trainer.eval_step(b) or True)}
-    return self._response(evaluated=True, **(out if isinstance(out, dict) else {}))
+      return self._reply(evaluated=True, eval_batches=0)
+    own = getattr(self._trainer, "run_eval", None)
+    if callable(own):
+      return self._reply(own(eval_ds, **kwargs), evaluated=True)
+    batches = 0
+    for batch in eval_ds:
+      self._trainer.eval_step(batch)
+      batches += 1
+    return self._reply(evaluated=True, batches=batches)
 
   def save_checkpoint(self, force: bool = False) -> datatypes.Response:
-    return self._response(saved=bool(self._trainer.save_checkpoint(force)))
+    return self._reply(saved=bool(self._trainer.save_checkpoint(force)))
 
   # ---- weight-sync source --------------------------------------------------------------------
   @property
@@ -141,11 +160,12 @@ class TrainerWorker(abstract_worker.Worker):
     return weight_sync.WorkUnitId(job_name="trainer", job_replica_id=self._worker_id, data_replica_idx=self._rank)
 
   async def prepare_weight_sync(self, sync_request: Any = None, **kwargs) -> Sequence[weight_sync.WorkUnitMetadata]:
-    state = self._trainer.state_for_weight_sync()
-    self._staged = state
-    if self._handler is not None and hasattr(self._handler, "attach"):
-      self._handler.attach(self.work_unit, state)
-    return [peer_memory_handler.manifest_of(self.work_unit, state)]
+    """Exposes the current weights to the transport and describes them."""
+    self._staged = self._trainer.state_for_weight_sync()
+    attach = getattr(self._handler, "attach", None)
+    if callable(attach):
+      attach(self.work_unit, self._staged)
+    return [peer_memory_handler.manifest_of(self.work_unit, self._staged)]
 
   async def release_weight_sync(self, sync_request: Any = None, **kwargs) -> None:
     self._staged = None
