@@ -128,6 +128,34 @@ def test_perf_tracer_export_and_perfetto(tmp_path):
   assert noop.export() == {}
 
 
+def test_span_query_steps_and_option_checks(caplog):
+  import types as pytypes
+  from tunix_b200.perf import metrics as pm
+  from tunix_b200.perf.span import SpanGroup
+  root = SpanGroup("root")
+  steps = [SpanGroup("global_step", root) for _ in range(3)]
+  for k, step in enumerate(steps):
+    for _ in range(k + 1):
+      SpanGroup("mini_batch_step", step)
+  SpanGroup("other", root)
+  q = pm.PerfSpanQuery({"main": pytypes.SimpleNamespace(root=root)}, "main")
+  assert q().main().first_group("global_step").get() == [steps[0]]
+  assert q().main().last_group("global_step").get() == [steps[2]]
+  assert q().main().nth_group("global_step", 1).get() == [steps[1]] == q().main().nth_group("global_step", -2).get()
+  assert q().main().nth_group("global_step", 3).get() == [] == q().main().nth_group("global_step", -4).get()
+  assert len(q().main().all_groups("global_step").all_groups("mini_batch_step").get()) == 6
+  # the second mini batch exists only in steps 1 and 2
+  assert len(q().main().all_groups("global_step").nth_group("mini_batch_step", 1).get()) == 2
+  assert q().timeline("nope").all_groups("global_step").get() == [] and q.get_timeline_ids() == ["main"]
+  with pytest.raises(ValueError, match="custom_export_fn_path_v2"):
+    pm.PerfMetricsOptions(custom_export_fn_path_v2="a.b")
+  with pytest.raises(ValueError, match="enable_trace_writer"):
+    pm.PerfMetricsOptions(enable_perf_v1=False)
+  with caplog.at_level("WARNING"):
+    pm.PerfMetricsOptions(enable_trace_writer=False, trace_dir="/tmp/x")
+  assert "trace_dir" in caplog.text
+
+
 def test_mesh_allocation_policies():
   devs = list(range(16))
   out = mesh_utils.allocate_named_mesh_device_slices([("actor", 8), ("rollout", 4), ("ref", 4)], devs, "performance")
