@@ -42,6 +42,9 @@ def parse_args():
   ap.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the number)")
   ap.add_argument("--remat", default="auto", choices=["auto", "none", "block"])
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--fsdp-mode", default="resident", choices=["resident", "sharded"],
+                  help="sharded: decoder-layer parameters and gradients exist per rank only as 1/N slices, gathered "
+                       "layer by layer (tunix_b200/dist/fsdp_sharded.py); resident: whole bf16 replica per rank")
   ap.add_argument("--workload", default="sft", choices=["sft", "grpo", "dpo", "moe"],
                   help="sft: Llama-3.1-8B full-weight SFT (default, the headline); grpo: Qwen3-8B GRPO step; "
                        "dpo: Qwen3-4B DPO with LoRA")
@@ -235,7 +238,8 @@ def main():
     for mod in model.modules():
       if hasattr(mod, "ep_group"):
         mod.ep_capacity_factor = args.moe_capacity_factor
-  model = fsdp.shard_model(model, mesh)     # flat bf16 params + fp32 grads, sharded optimizer state
+  sharded = args.fsdp_mode == "sharded" and not moe
+  model = fsdp.shard_model(model, mesh, mode="sharded" if sharded else "resident")
   trainer = PeftTrainer(model, tx, tcfg)
   trainer.with_grad_sync(fsdp.GradSync(model, mesh))
   trainer.is_managed_externally = True
@@ -343,8 +347,13 @@ def main():
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
         "impl": "ours",
         "config": {"model": args.model, "layers": cfg.num_layers, "global_batch": GB, "seq_len": S,
-                   "parallelism": f"ep{world}+fsdp{world}" if moe else f"fsdp{world}",
-                   "sharding": ("fp32 master / Adam moments and the reduced gradient are sharded over the ranks (interleaved by "
+                   "parallelism": f"ep{world}+fsdp{world}" if moe else f"fsdp{world}" + ("-sharded-params" if sharded else ""),
+                   "fsdp_mode": "sharded" if sharded else "resident",
+                   "sharding": ("decoder-layer parameters (bf16), gradient accumulators (fp32), fp32 master and Adam moments "
+                                "all sharded over the ranks; a layer is gathered for its forward and again for its backward "
+                                "(NCCL all-gather prefetched on a side stream), its gradients reduce-scattered as soon as its "
+                                "backward has run; embedding / final norm / head stay whole on every rank" if sharded else
+                                "fp32 master / Adam moments and the reduced gradient are sharded over the ranks (interleaved by "
                                 "bucket); every rank keeps a resident bf16 parameter replica and its own fp32 gradient "
                                 "accumulator" if world > 1 else "single GPU"),
                    "micro_batch_per_gpu": micro, "grad_accum": ga, "remat": remat,

@@ -3,6 +3,7 @@
 Trains a tiny decoder for a few optimizer steps with the flat sharded store and writes the final
 parameters of rank 0 to `--out`. With WORLD_SIZE=1 it produces the unsharded reference run."""
 import argparse
+import contextlib
 import os
 import sys
 
@@ -17,6 +18,9 @@ def main():
   ap.add_argument("--transport", default="nccl")
   ap.add_argument("--device", default="cuda")
   ap.add_argument("--steps", type=int, default=3)
+  ap.add_argument("--mode", default="")           # resident | sharded; "" = resident on CUDA, no store on CPU
+  ap.add_argument("--layers", type=int, default=2)
+  ap.add_argument("--remat", type=int, default=0)
   a = ap.parse_args()
   from tunix_b200 import optim
   from tunix_b200.common.configs import TrainingConfig
@@ -37,11 +41,12 @@ def main():
   dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if cuda else torch.device("cpu")
   if cuda:
     torch.cuda.set_device(dev)
-  cfg = ModelConfig(num_layers=2, vocab_size=512, embed_dim=256, hidden_dim=512, num_heads=4, head_dim=64,
+  from tunix_b200.models.transformer import RematConfig
+  cfg = ModelConfig(num_layers=a.layers, remat_config=RematConfig.BLOCK if a.remat else RematConfig.NONE, vocab_size=512, embed_dim=256, hidden_dim=512, num_heads=4, head_dim=64,
                     num_kv_heads=2, dtype=torch.bfloat16 if cuda else torch.float32, max_position=64)
   model = Transformer(cfg, device=dev).init_weights(seed=0)
-  if cuda:
-    model = fsdp.shard_model(model, mesh, transport=a.transport)
+  if cuda or a.mode:
+    model = fsdp.shard_model(model, mesh, transport=a.transport, mode=a.mode or None)
   tc = TrainingConfig(eval_every_n_steps=100, gradient_accumulation_steps=2, max_grad_norm=1.0, pbar_description=None)
   tr = PeftTrainer(model, optim.adamw(2e-3, weight_decay=0.01), tc)
   tr.with_grad_sync(fsdp.GradSync(model, mesh))
@@ -56,9 +61,12 @@ def main():
   if cuda:
     torch.cuda.synchronize()
     _lib.check_status()
+  store = getattr(model, "flat_store", None)
+  with (store.summon_full_params() if store is not None else contextlib.nullcontext()):
+    params = {n: p.detach().float().cpu() for n, p in model.named_parameters()}
   if rank == 0:
-    torch.save({"params": {n: p.detach().float().cpu() for n, p in model.named_parameters()},
-                "loss": tr.metrics_logger.get_metric_history("", "loss", "train")}, a.out)
+    torch.save({"params": params, "loss": tr.metrics_logger.get_metric_history("", "loss", "train"),
+                "memory": store.memory_report() if hasattr(store, "memory_report") else None}, a.out)
   if world > 1:
     torch.distributed.barrier()
     torch.distributed.destroy_process_group()

@@ -11,14 +11,14 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _run(nproc, out, transport, port, **extra_env):
+def _run(nproc, out, transport, port, args=(), **extra_env):
   env = dict(os.environ, NCCL_NVLS_ENABLE="0", TUNIX_PEER_WAIT_MS="20000", **extra_env)
   if nproc == 1:
-    cmd = [sys.executable, os.path.join(HERE, "_fsdp_worker.py"), "--out", out, "--transport", transport]
+    cmd = [sys.executable, os.path.join(HERE, "_fsdp_worker.py"), "--out", out, "--transport", transport, *args]
   else:
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "_fsdp_worker.py"),
-           "--out", out, "--transport", transport]
+           "--out", out, "--transport", transport, *args]
   r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
   assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
   return torch.load(out, weights_only=False)
@@ -35,6 +35,26 @@ def test_fsdp2_matches_single_gpu(kernel_lib, tmp_path, transport):
     rel = (p - q).norm() / (p.norm() + 1e-6)
     assert rel < 2e-2, (n, rel.item())
   assert abs(ref["loss"][-1] - got["loss"][-1]) < 0.05
+
+
+def test_sharded_parameters_match_the_resident_store_on_gpus(kernel_lib, tmp_path):
+  """Parameters, gradients and optimizer state all sharded (`dist/fsdp_sharded.py`): layers gathered on a side
+  stream for forward and backward, gradients reduce-scattered per layer. One GPU must reproduce the resident
+  store (same kernels, same order); two GPUs must agree with it like the resident 2-GPU run does."""
+  args = ("--layers", "4")
+  ref = _run(1, str(tmp_path / "ref.pt"), "local", 0, args)
+  one = _run(1, str(tmp_path / "one.pt"), "local", 0, args + ("--mode", "sharded"))
+  for n, p in ref["params"].items():      # same kernels; only the grouping of the norm's partial sums may differ
+    rel = (p - one["params"][n]).norm() / (p.norm() + 1e-6)
+    assert rel < 2e-3, (n, rel.item())
+  if torch.cuda.device_count() < 2:
+    return
+  two = _run(2, str(tmp_path / "two.pt"), "nccl", 29616, args + ("--mode", "sharded"))
+  for n, p in ref["params"].items():
+    rel = (p - two["params"][n]).norm() / (p.norm() + 1e-6)
+    assert rel < 2e-2, (n, rel.item())
+  assert abs(ref["loss"][-1] - two["loss"][-1]) < 0.05
+  assert two["memory"]["param_shard"] < 0.6 * one["memory"]["param_shard"]
 
 
 def test_fsdp2_on_the_own_peer_allocator(kernel_lib, tmp_path):

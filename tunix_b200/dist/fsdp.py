@@ -33,6 +33,7 @@ applies AdamW and pushes the updated bf16 values straight into every peer's para
 """
 from __future__ import annotations
 
+import contextlib
 import logging
 import math
 import os
@@ -69,6 +70,8 @@ def _bucket_id(name: str, layers_per_bucket: int) -> int:
 class FlatParamStore:
   """Flat bf16 parameters + flat fp32 gradients, sharded optimizer state."""
 
+  resident = True          # the whole bf16 model stays on every rank (`fsdp_sharded.ShardedParamStore`: False)
+
   def __init__(self, model: torch.nn.Module, mesh: Optional[mesh_lib.Mesh] = None, axis: str = "fsdp",
                transport: Optional[str] = None, only_trainable: bool = True):
     self.mesh = mesh
@@ -92,7 +95,7 @@ class FlatParamStore:
     self.offsets: Dict[str, int] = {}
     # buckets: consecutive parameters grouped by decoder layer; a bucket starts on a boundary that does not
     # depend on the number of ranks, so a checkpoint's flat offsets are valid for any power-of-two job size
-    per_bucket = int(os.environ.get("TUNIX_FSDP_BUCKET_LAYERS", "4"))
+    per_bucket = self._layers_per_bucket()
     pow2 = self.world & (self.world - 1) == 0 and self.world <= 16
     ids = [_bucket_id(n, per_bucket) for n, _ in params] if (pow2 and per_bucket > 0) else None
     if ids is not None and any(b < a for a, b in zip(ids, ids[1:])):
@@ -118,6 +121,15 @@ class FlatParamStore:
       self.pieces.append((lo + self.rank * per, per, so))
       so += per
     self.shard_numel = so
+    self._bucket_ids = ids
+    self._allocate(model, params, local, transport)
+
+  def _layers_per_bucket(self) -> int:
+    return int(os.environ.get("TUNIX_FSDP_BUCKET_LAYERS", "4"))
+
+  def _allocate(self, model: torch.nn.Module, params, local, transport: Optional[str]) -> None:
+    """Resident layout: whole flat bf16 parameter and fp32 gradient buffers on every rank."""
+    dev, dtype, ids = self.device, self.dtype, self._bucket_ids
     self.transport = transport or os.environ.get("TUNIX_FSDP_TRANSPORT", "p2p" if self.world > 1 else "local")
     self.symm = None
     if self.world > 1 and self.transport == "p2p":
@@ -237,6 +249,15 @@ class FlatParamStore:
       if w is not None and i in self._bucket_of_layer:
         w.grad_ready_hook = functools.partial(self._layer_backward_done, i)
 
+  def after_backward(self) -> None:
+    """Called by the trainer when a backward pass has returned (the sharded-parameter store closes its last
+    unit here)."""
+
+  @contextlib.contextmanager
+  def summon_full_params(self, writeback: bool = False):
+    """Every parameter is whole inside the block: always true for this store."""
+    yield self
+
   def arm_overlap(self) -> None:
     """Called by the trainer before the backward pass of the LAST micro-batch of an optimizer step: from now on
     a bucket whose layers have all run backward holds final gradients and may be reduced."""
@@ -271,6 +292,41 @@ class FlatParamStore:
       self._reduced.add(x)
 
   # ---- the optimizer step ------------------------------------------------------------------
+  def _norm_and_scale(self, g: torch.Tensor, ss: torch.Tensor, d: torch.Tensor, max_grad_norm: Optional[float]):
+    """fp32 global norm of the summed gradient (`g`: this rank's reduced shard) and the factor the update
+    multiplies it by: 1 / sum of denominators, times max_norm / norm when clipping applies. Both are
+    device scalars; one small all-reduce carries the sum of squares and the denominator together."""
+    from ..ops import kernels
+    if self.device.type == "cuda":
+      kernels.sumsq(g, ss, accumulate=False)
+    else:
+      ss.copy_(g.double().pow(2).sum().float().reshape(1))
+    if getattr(self, "local_grad", None) is not None:
+      # every rank's expert gradients are distinct, so their squares simply join the sum over ranks
+      if self.device.type == "cuda":
+        kernels.sumsq(self.local_grad, ss, accumulate=True)
+      else:
+        ss.add_(self.local_grad.double().pow(2).sum().float())
+    if self.world > 1:
+      pack = self._buf("pack", 2)
+      pack[0:1].copy_(ss)
+      pack[1:2].copy_(d)
+      dist.all_reduce(pack, op=dist.ReduceOp.SUM, group=self.group)
+      ss.copy_(pack[0:1])
+      d.copy_(pack[1:2])
+    inv = self._buf("inv")
+    torch.where(d == 0, torch.zeros_like(d), 1.0 / torch.where(d == 0, torch.ones_like(d), d), out=inv)
+    norm, scale = self._buf("norm"), self._buf("scale")
+    if self.device.type == "cuda":
+      kernels.clip_scale(ss, inv, max_grad_norm or 0.0, norm, scale)
+    else:
+      # norm of the mean gradient; scale = 1/denom, times max_norm/norm when clipping applies
+      norm.copy_(ss.sqrt() * inv)
+      scale.copy_(inv)
+      if max_grad_norm and float(norm) > max_grad_norm:
+        scale.mul_(max_grad_norm / (float(norm) + 1e-6))
+    return norm, scale
+
   @torch.no_grad()
   def step(self, tx, state: Dict[str, Any], denom: torch.Tensor, max_grad_norm: Optional[float]) -> torch.Tensor:
     """Reduces gradients and denominators over the data-parallel group, applies the fused AdamW
@@ -304,34 +360,7 @@ class FlatParamStore:
       dist.all_reduce(self.flat_grad, op=dist.ReduceOp.SUM, group=self.group)
       self.grad_shard.copy_(self._my_part(self.flat_grad))
       g = self.grad_shard
-    if self.device.type == "cuda":
-      kernels.sumsq(g, ss, accumulate=False)
-    else:
-      ss.copy_(g.double().pow(2).sum().float().reshape(1))
-    if self.local_grad is not None:
-      # every rank's expert gradients are distinct, so their squares simply join the sum over ranks
-      if self.device.type == "cuda":
-        kernels.sumsq(self.local_grad, ss, accumulate=True)
-      else:
-        ss.add_(self.local_grad.double().pow(2).sum().float())
-    if self.world > 1:
-      pack = self._buf("pack", 2)
-      pack[0:1].copy_(ss)
-      pack[1:2].copy_(d)
-      dist.all_reduce(pack, op=dist.ReduceOp.SUM, group=self.group)
-      ss.copy_(pack[0:1])
-      d.copy_(pack[1:2])
-    inv = self._buf("inv")
-    torch.where(d == 0, torch.zeros_like(d), 1.0 / torch.where(d == 0, torch.ones_like(d), d), out=inv)
-    norm, scale = self._buf("norm"), self._buf("scale")
-    if self.device.type == "cuda":
-      kernels.clip_scale(ss, inv, max_grad_norm or 0.0, norm, scale)
-    else:
-      # norm of the mean gradient; scale = 1/denom, times max_norm/norm when clipping applies
-      norm.copy_(ss.sqrt() * inv)
-      scale.copy_(inv)
-      if max_grad_norm and float(norm) > max_grad_norm:
-        scale.mul_(max_grad_norm / (float(norm) + 1e-6))
+    norm, scale = self._norm_and_scale(g, ss, d, max_grad_norm)
     inner = getattr(tx, "inner", tx)
     if self.local_grad is not None:
       self._local_update(inner, state, scale)
@@ -485,11 +514,18 @@ class FlatParamStore:
 
 
 def shard_model(model: torch.nn.Module, mesh: Optional[mesh_lib.Mesh] = None, axis: str = "fsdp",
-                transport: Optional[str] = None) -> torch.nn.Module:
+                transport: Optional[str] = None, mode: Optional[str] = None) -> torch.nn.Module:
   """Moves the trainable parameters of `model` into a `FlatParamStore` (attached as
   `model.flat_store`). With `mesh=None` the store is single-rank: same flat layout, fused
   one-kernel optimizer step, no communication. All ranks must start from identical weights
-  (same seed) or call `broadcast_params` afterwards."""
+  (same seed) or call `broadcast_params` afterwards. `mode="sharded"` (or `TUNIX_FSDP_MODE=sharded`) shards the
+  decoder layers' parameters and gradients too (`fsdp_sharded.ShardedParamStore`)."""
+  mode = mode or os.environ.get("TUNIX_FSDP_MODE", "resident")
+  if mode == "sharded":
+    from . import fsdp_sharded
+    return fsdp_sharded.shard_model(model, mesh, axis)
+  if mode != "resident":
+    raise ValueError(f"unknown FSDP mode {mode!r}: 'resident' or 'sharded'")
   store = FlatParamStore(model, mesh, axis, transport)
   model.flat_store = store
   return model
@@ -497,9 +533,15 @@ def shard_model(model: torch.nn.Module, mesh: Optional[mesh_lib.Mesh] = None, ax
 
 def broadcast_params(model: torch.nn.Module, src: int = 0) -> None:
   store: FlatParamStore = model.flat_store
-  if store.world > 1:
-    ranks = store.mesh.ranks()
+  if store.world == 1:
+    return
+  ranks = store.mesh.ranks()
+  if store.resident:
     dist.broadcast(store.flat_param, src=ranks[src], group=store.mesh.all_group())
+    return
+  with store.summon_full_params(writeback=True):
+    for p in store.params.values():
+      dist.broadcast(p.data, src=ranks[src], group=store.mesh.all_group())
 
 
 class GradSync:

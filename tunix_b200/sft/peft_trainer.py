@@ -92,6 +92,9 @@ class GradientAccumulator:
     self.acc: Dict[str, torch.Tensor] = {}
     dev = None
     for n, p in self.params.items():
+      dev = p.device
+      if getattr(p, "grad_managed", False):
+        continue                      # a sharded-parameter store collects and reduces this gradient itself
       buf = getattr(p, "main_grad", None)
       if buf is None:
         buf = torch.zeros(p.shape, dtype=torch.float32, device=p.device)
@@ -102,9 +105,10 @@ class GradientAccumulator:
     self.denom = torch.zeros((), dtype=torch.float32, device=dev or "cpu")
 
   def collect(self, denom: Any) -> None:
-    for n, p in self.params.items():
+    for n, buf in self.acc.items():
+      p = self.params[n]
       if p.grad is not None:
-        self.acc[n].add_(p.grad.to(torch.float32))
+        buf.add_(p.grad.to(torch.float32))
         p.grad = None
     if isinstance(denom, torch.Tensor):
       self.denom.add_(denom.detach().to(self.denom.device, torch.float32))
@@ -331,6 +335,8 @@ class PeftTrainer:
     if is_update_step and self.optimizer.flat is not None:
       self.optimizer.flat.arm_overlap()      # gradients of this backward pass are final: reduce buckets as they finish
     loss_t.backward()
+    if self.optimizer.flat is not None:
+      self.optimizer.flat.after_backward()
     loss_val = aux.primary_loss.compute().detach() if isinstance(aux, LossOutput) else loss_t.detach()
     acc = self.grad_accumulator
     acc.collect(denom)
