@@ -224,3 +224,63 @@ def test_deployment_yaml(tmp_path):
     yaml_generator.parse_gpu_slice("tpu7x:4x4")
   with pytest.raises(ValueError):
     yaml_generator.parse_gpu_slice("b200:2x4")
+
+
+def test_mock_parts_drive_collect_train_sync():
+  """`experimental/common/test_utils.py`: the stand-ins behave like the parts they replace."""
+  import asyncio
+  import threading
+  from tunix_b200.experimental.common import test_utils as tu
+  from tunix_b200.experimental.rollout import sampler as sampler_lib
+  tok = tu.MockTokenizer()
+  assert tok.decode(tok.encode("héllo", add_special_tokens=True)) == "héllo"
+  assert tok.dedup_bos_ids([1, 1, 1, 7]) == [1, 7] and tok.dedup_bos_ids([1, 7]) == [1, 7]
+  parser = tu.MockChatParser()
+  assert parser.parse([{"role": "user", "content": "hi"}], add_generation_prompt=True) == "<user>hi</user><assistant>"
+  # the pool blocks when empty and refuses a double release
+  pool = tu.MockEnvironmentPool(1)
+  env = pool.acquire_env()
+  with pytest.raises(TimeoutError):
+    pool.acquire_env(timeout=0.05)
+  threading.Timer(0.05, pool.release_env, args=(env,)).start()
+  assert pool.acquire_env(timeout=2.0) is env
+  pool.release_env(env)
+  with pytest.raises(ValueError):
+    pool.release_env(env)
+  # an episode: keywords rewarded turn by turn, done after `turns`
+  e = tu.MockEnvironment(delay_seconds=0.0, turns=2)
+  obs, _ = e.reset()
+  assert "alpha" in obs["question"]
+  obs, r, done, info = e.step("alpha please")
+  assert r == 1.0 and not done and "beta" in obs["question"]
+  _, r, done, _ = e.step("wrong")
+  assert r == 0.0 and done
+  # the sampler follows the protocol, truncates at max_tokens and answers "cancelled" while paused
+  s = tu.MockSampler()
+  assert isinstance(s, sampler_lib.Sampler)
+
+  async def sampling():
+    full = (await s.sample([sampler_lib.SamplingRequest(prompt="x")]))[0]
+    short = (await s.sample([sampler_lib.SamplingRequest(
+        prompt="x", sampling_params=sampler_lib.SamplingParams(max_tokens=3, return_logprobs=True))]))[0]
+    await s.pause()
+    cancelled = (await s.sample([sampler_lib.SamplingRequest(prompt="x")]))[0]
+    await s.resume()
+    return full, short, cancelled
+  full, short, cancelled = asyncio.run(sampling())
+  assert full.finish_reason == "stop" and short.finish_reason == "length" and len(short.token_ids) == 3
+  assert short.logprobs.shape == (3,) and cancelled.finish_reason == "cancelled"
+  # collect -> train -> sync, twice: rewards are earned, versions advance, the sampler saw every phase
+  orch = tu.MockGlobalOrchestrator(num_envs=2)
+  with pytest.raises(RuntimeError):
+    asyncio.run(orch.collect_rollout_batch(1))
+  orch.start_workers()
+  for round_ in (1, 2):
+    batch = asyncio.run(orch.collect_rollout_batch(4))
+    assert len(batch) == 4 and all(ep.steps == 2 and ep.reward == 2.0 for ep in batch)
+    assert all(ep.policy_version == round_ - 1 for ep in batch)
+    assert asyncio.run(orch.run_training_step(batch)) == round_
+    assert orch.synchronize_weights(["rollout:0"]) == round_
+  assert orch.sampler.policy_version == 2 and orch.trainer.mean_reward == 2.0
+  assert orch.sampler.phases == ["pre", "transfer", "post"] * 2 and orch.pool.available == 2
+  orch.stop_workers()

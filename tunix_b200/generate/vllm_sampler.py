@@ -67,6 +67,13 @@ def hf_config_dict(cfg) -> Dict[str, Any]:
   return d
 
 
+def _in_process_engine() -> None:
+  """Weight sync hands device tensors to the engine's model without a copy through a pipe, which needs the
+  engine core in this process: vLLM's switch for that is an environment variable read at engine start-up.
+  A value the user has set wins."""
+  os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
+
+
 @dataclasses.dataclass
 class VllmConfig:
   model_path: Optional[str] = None
@@ -198,6 +205,7 @@ class VllmSampler(base_sampler.BaseSampler):
     self._model = model
     self._tmp = None
     if llm is None:
+      _in_process_engine()
       import vllm
       llm = vllm.LLM(**config.engine_args(self._model_dir()))
     self.llm = llm
@@ -254,9 +262,13 @@ class VllmSampler(base_sampler.BaseSampler):
     if callable(loader):                     # injected engines and thin wrappers
       loader(weights)
       return
-    # in-process engine: hand the (name, tensor) stream to every worker's model
-    self.llm.collective_rpc("load_weights", args=(weights,)) if hasattr(self.llm, "collective_rpc") else \
-        self.llm.llm_engine.model_executor.driver_worker.model_runner.model.load_weights(weights)
+    # in-process engine: run the model's own `load_weights` on the (name, tensor) stream inside every worker. The
+    # closure holds device tensors, so the engine core must live in this process (see `_in_process_engine`).
+    apply = getattr(self.llm, "apply_model", None)
+    if callable(apply):
+      apply(lambda module: module.load_weights(iter(weights)) and None)
+    else:
+      self.llm.llm_engine.model_executor.driver_worker.model_runner.model.load_weights(weights)
     reset = getattr(self.llm, "reset_prefix_cache", None)
     if callable(reset):
       reset()
