@@ -449,3 +449,92 @@ def test_stateful_device_allocation_over_pools_with_holes():
   assert perf["a"] == [0, 1] and perf["b"][0] % 2 == 0
   with pytest.raises(ValueError, match="duplicate"):
     m.DeviceAllocationState([0, 0, 1])
+
+
+class _FakeStepEngine:
+  """The four `LLMEngine` methods the step driver uses; a request finishes after `params` steps."""
+
+  def __init__(self):
+    self.left, self.added, self.aborted, self.fail_next = {}, [], [], False
+    self.batch_sizes = []
+
+  def add_request(self, request_id, prompt, params):
+    self.added.append(request_id)
+    self.left[request_id] = int(params)
+
+  def has_unfinished_requests(self):
+    return bool(self.left)
+
+  def abort_request(self, ids):
+    for i in ids:
+      self.aborted.append(i)
+      self.left.pop(i, None)
+
+  def step(self):
+    import types as pytypes
+    if self.fail_next:
+      self.fail_next = False
+      raise RuntimeError("engine fell over")
+    self.batch_sizes.append(len(self.left))
+    time.sleep(0.002)
+    outs = []
+    for rid in list(self.left):
+      self.left[rid] -= 1
+      done = self.left[rid] <= 0
+      if done:
+        del self.left[rid]
+      outs.append(pytypes.SimpleNamespace(request_id=rid, finished=done))
+    return outs
+
+
+def test_vllm_step_driver_batches_streams_cancels_and_survives_errors():
+  import concurrent.futures
+  from tunix_b200.generate import vllm_async_driver as vad
+  eng = _FakeStepEngine()
+  streamed = []
+  with vad.VLLMInProcessDriver(eng, stream_callback=lambda out: streamed.append(out.request_id)) as drv:
+    futs = drv.submit_requests([{"prompt_token_ids": [1]}] * 3, [1, 3, 2])
+    outs = [f.result(timeout=5) for f in futs]
+    assert [o.request_id for o in outs] == [f.request_id for f in futs] and all(o.finished for o in outs)
+    assert streamed and set(streamed) <= {futs[1].request_id, futs[2].request_id}
+    with pytest.raises(ValueError):
+      drv.submit_requests([1, 2], [1])
+    # cancel inside the engine: aborted there, future cancelled, the others unaffected
+    slow = drv.submit({"prompt_token_ids": [2]}, 10_000, request_id="slow")
+    quick = drv.submit({"prompt_token_ids": [3]}, 2)
+    assert quick.result(timeout=5).finished
+    assert drv.cancel("slow") and slow.cancelled() and not drv.cancel("slow")
+    deadline = time.time() + 5
+    while "slow" not in eng.aborted and time.time() < deadline:
+      time.sleep(0.01)
+    assert "slow" in eng.aborted
+    # pause: nothing is stepped, nothing is lost
+    drv.pause()
+    steps = drv.steps
+    held = drv.submit({"prompt_token_ids": [4]}, 1)
+    time.sleep(0.1)
+    assert drv.steps == steps and not held.done()
+    drv.resume()
+    assert held.result(timeout=5).finished
+    # an engine error fails what is in flight and is remembered; the driver keeps serving
+    eng.fail_next = True
+    doomed = drv.submit({"prompt_token_ids": [5]}, 2)
+    with pytest.raises(RuntimeError, match="fell over"):
+      doomed.result(timeout=5)
+    assert isinstance(drv.last_error, RuntimeError)
+    assert drv.submit({"prompt_token_ids": [6]}, 1).result(timeout=5).finished
+  with pytest.raises(RuntimeError):
+    drv.submit({"prompt_token_ids": [7]}, 1)
+  # the waiting room: with a threshold of 3 two requests wait for the timeout, three go in together
+  eng2 = _FakeStepEngine()
+  with vad.VLLMInProcessDriver(eng2, submission_threshold=3, submission_timeout_s=0.3) as drv2:
+    t0 = time.time()
+    two = drv2.submit_requests([1, 2], 1)
+    concurrent.futures.wait(two, timeout=5)
+    assert time.time() - t0 >= 0.25 and eng2.batch_sizes[0] == 2
+    t0 = time.time()
+    three = drv2.submit_requests([1, 2, 3], 1)
+    concurrent.futures.wait(three, timeout=5)
+    assert time.time() - t0 < 0.25 and eng2.batch_sizes[-1] == 3
+    waiting = drv2.submit(9, 1, request_id="w")
+    assert drv2.cancel("w") and waiting.cancelled() and "w" not in eng2.added

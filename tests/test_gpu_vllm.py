@@ -25,7 +25,7 @@ def test_real_vllm_engine_generates_with_synced_weights():
   dev = torch.device("cuda", 0)
   cfg = ModelConfig(num_layers=2, vocab_size=512, embed_dim=256, hidden_dim=512, num_heads=4, head_dim=64,
                     num_kv_heads=2, dtype=torch.bfloat16, max_position=128)
-  model = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.08)
+  model = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.15)
   tok = ToyTokenizer(vocab=512)
   conf = vs.VllmConfig(max_model_len=128, hbm_utilization=0.08, seed=0,
                        engine_kwargs={"enforce_eager": True, "attention_backend": "TRITON_ATTN", "dtype": "bfloat16"})
@@ -38,21 +38,35 @@ def test_real_vllm_engine_generates_with_synced_weights():
     b = own(input_strings=prompts, max_generation_steps=12, temperature=0.0, echo=False, pad_output=False,
             eos_tokens=[511], return_logprobs=True)
     same = total = 0
-    for x, y in zip(a.tokens, b.tokens):
+    gaps = []
+    for x, y, lx, ly in zip(a.tokens, b.tokens, a.logprobs, b.logprobs):
       n = min(len(x), len(y))
-      # greedy decoding in bf16 through two attention implementations: count until the first divergence
+      # greedy decoding in bf16 through two attention implementations: near-ties of a random model flip, and
+      # everything after a flip differs, so only the common prefix counts
       k = next((i for i in range(n) if int(x[i]) != int(y[i])), n)
       same, total = same + k, total + n
-    return same / max(total, 1), a
+      gaps += [abs(float(lx[i]) - float(ly[i])) for i in range(k)]
+    return same / max(total, 1), float(np.mean(gaps)) if gaps else float("inf"), a
 
-  first, out = agreement()
-  assert first >= 0.8, first
+  first, gap, out = agreement()
+  assert first >= 0.5 and gap < 0.15, (first, gap)      # dummy weights would agree on about 1 token in 512
   assert out.logprobs is not None and all(len(lp) == len(t) for lp, t in zip(out.logprobs, out.tokens))
   with torch.no_grad():
     for p in model.parameters():
       p.add_(0.05 * torch.randn_like(p))
-  stale, _ = agreement()                      # the engine still holds the old weights
+  stale, _, _ = agreement()                   # the engine still holds the old weights
   engine.update_params(dict(model.named_parameters()))
-  fresh, _ = agreement()
-  assert fresh >= 0.8 and fresh >= stale, (stale, fresh)
+  fresh, gap, _ = agreement()
+  assert fresh >= 0.5 and gap < 0.15 and fresh >= stale, (stale, fresh, gap)
+  print(f"vllm agreement: first {first:.2f}, stale {stale:.2f}, fresh {fresh:.2f}, logprob gap {gap:.3f}")
+  # server mode on the same engine: requests go through the step-level driver (add_request / step / futures)
+  import dataclasses
+  served = vs.VllmSampler(tok, dataclasses.replace(conf, server_mode=True, submission_threshold=2,
+                                                   submission_timeout_s=0.05), model=None, llm=engine.llm)
+  assert served._step_driver is not None
+  batch = engine(prompts, max_generation_steps=12, temperature=0.0, eos_tokens=[511])
+  stepped = served(prompts, max_generation_steps=12, temperature=0.0, eos_tokens=[511])
+  assert all(np.array_equal(x, y) for x, y in zip(batch.tokens, stepped.tokens))
+  assert served._step_driver.steps >= 12 and served._step_driver.last_error is None
+  served.close()
   engine.close()

@@ -141,8 +141,9 @@ class _Request:
   error: Optional[BaseException] = None
 
 
-class VLLMInProcessDriver:
-  """Owns the engine on one thread; batches queued requests by count or age before submitting them."""
+class GenerateBatchDriver:
+  """Owns an object that only offers a blocking `generate` on one thread; batches queued requests by count or age
+  before submitting them. Engines that can be stepped get `vllm_async_driver.VLLMInProcessDriver` instead."""
 
   def __init__(self, llm, threshold: int = 0, timeout_s: float = 0.0):
     self._llm = llm
@@ -209,8 +210,15 @@ class VllmSampler(base_sampler.BaseSampler):
       import vllm
       llm = vllm.LLM(**config.engine_args(self._model_dir()))
     self.llm = llm
-    self._driver = VLLMInProcessDriver(llm, config.submission_threshold, config.submission_timeout_s) \
-        if config.server_mode else None
+    self._driver = self._step_driver = None
+    if config.server_mode:
+      engine = getattr(llm, "llm_engine", None)
+      if all(hasattr(engine, m) for m in ("add_request", "step", "has_unfinished_requests", "abort_request")):
+        from . import vllm_async_driver
+        self._step_driver = vllm_async_driver.VLLMInProcessDriver(
+            engine, submission_threshold=config.submission_threshold, submission_timeout_s=config.submission_timeout_s)
+      else:
+        self._driver = GenerateBatchDriver(llm, config.submission_threshold, config.submission_timeout_s)
     if model is not None and not config.model_path and config.init_with_random_weights:
       self.update_params(dict(model.named_parameters()))
 
@@ -258,6 +266,16 @@ class VllmSampler(base_sampler.BaseSampler):
   def update_params(self, params: Dict[str, torch.Tensor], filter_types: Optional[Tuple[Any, ...]] = None) -> None:
     del filter_types
     weights = self.hf_named_weights(params)
+    if self._step_driver is not None:          # no engine step while the weights change
+      self._step_driver.pause()
+      try:
+        self._push(weights)
+      finally:
+        self._step_driver.resume()
+    else:
+      self._push(weights)
+
+  def _push(self, weights) -> None:
     loader = getattr(self.llm, "load_weights", None)
     if callable(loader):                     # injected engines and thin wrappers
       loader(weights)
@@ -298,7 +316,9 @@ class VllmSampler(base_sampler.BaseSampler):
     ids = [t[-P:] for t in ids]
     params = self._sampling_params(max_generation_steps, temperature, top_p, top_k, seed, eos_tokens,
                                    return_logprobs)
-    if self._driver is not None:
+    if self._step_driver is not None:
+      outs = [f.result() for f in self._step_driver.submit_requests([{"prompt_token_ids": t} for t in ids], params)]
+    elif self._driver is not None:
       req = self._driver.submit(ids, params)
       req.done.wait()
       if req.error is not None:
@@ -331,6 +351,8 @@ class VllmSampler(base_sampler.BaseSampler):
                                       logprobs=logprobs if return_logprobs else None)
 
   def close(self) -> None:
+    if self._step_driver is not None:
+      self._step_driver.shutdown()
     if self._driver is not None:
       self._driver.close()
     if self._tmp is not None:
