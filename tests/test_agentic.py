@@ -256,3 +256,33 @@ def test_function_tool_schema_freeze_and_ordered_parallel_execution():
   out = mgr.execute_calls(calls + [bad], parallel=True)
   assert list(out) == [f"call{i}" for i in range(5)] + ["bad"]
   assert out["call3"] == '{"sum": 4}' and "not registered" in out["bad"]
+
+
+def test_frozen_after_init_mixin():
+  from tunix_b200.utils.immutable import FrozenAfterInit
+
+  class Base(FrozenAfterInit):
+    def __init__(self, a):
+      self.a = a
+      super().__init__()
+
+  class Child(Base):
+    def __init__(self, a, b):
+      self.b = b                 # before and after the parent's constructor: both are still construction
+      super().__init__(a)
+      self.c = a + b
+
+  class Plain(FrozenAfterInit):
+    pass
+
+  x = Child(1, 2)
+  assert (x.a, x.b, x.c) == (1, 2, 3)
+  for mutate in (lambda: setattr(x, "a", 5), lambda: delattr(x, "b"), lambda: setattr(Plain(), "z", 1),
+                 lambda: setattr(Base(1), "a", 2)):
+    with pytest.raises(AttributeError, match="immutable"):
+      mutate()
+  with x.thaw():
+    x.a = 10
+  assert x.a == 10
+  with pytest.raises(AttributeError):
+    x.a = 11

@@ -2,8 +2,7 @@
 
 A tool has a name, a one-line description, an OpenAI function-calling schema and an `apply` (or `apply_async`)
 that returns a `ToolOutput`. Instances are shared between concurrent episodes, so they are frozen once the
-outermost constructor returns: every subclass `__init__` is wrapped by `__init_subclass__`, which counts
-constructor nesting on the instance and locks attribute assignment when the count falls back to zero.
+outermost constructor returns (`utils.immutable.FrozenAfterInit`).
 `FunctionTool` turns a plain Python function into a tool, deriving the parameter schema from its signature.
 """
 from __future__ import annotations
@@ -14,6 +13,8 @@ import functools
 import inspect
 import json
 from typing import Any, Callable, Dict, List, Optional, Union
+
+from ....utils import immutable
 
 
 @dataclasses.dataclass
@@ -45,39 +46,12 @@ def function_schema(name: str, description: str, parameters: Optional[Dict[str, 
                                            "parameters": parameters if parameters is not None else {}}}
 
 
-class BaseTool(abc.ABC):
-  _ctor_depth = 0
-  _frozen = False
-
-  def __init_subclass__(cls, **kwargs):
-    super().__init_subclass__(**kwargs)
-    if "__init__" in cls.__dict__:
-      cls.__init__ = BaseTool._freezing(cls.__dict__["__init__"])
-
-  @staticmethod
-  def _freezing(init: Callable[..., None]) -> Callable[..., None]:
-    @functools.wraps(init)
-    def wrapped(self, *args, **kwargs):
-      object.__setattr__(self, "_ctor_depth", self._ctor_depth + 1)
-      try:
-        init(self, *args, **kwargs)
-      finally:
-        object.__setattr__(self, "_ctor_depth", self._ctor_depth - 1)
-        if self._ctor_depth == 0:
-          object.__setattr__(self, "_frozen", True)
-    return wrapped
+class BaseTool(immutable.FrozenAfterInit, abc.ABC):
 
   def __init__(self, name: str, description: str):
     self.name = name
     self.description = description
-    if type(self).__init__ is BaseTool.__init__:      # no subclass constructor ran: freeze here
-      object.__setattr__(self, "_frozen", True)
-
-  def __setattr__(self, name: str, value: Any):
-    if self._frozen:
-      raise AttributeError(f"Cannot modify immutable {type(self).__name__} instance after initialization "
-                           f"(attempted to set '{name}')")
-    object.__setattr__(self, name, value)
+    super().__init__()
 
   @abc.abstractmethod
   def get_json_schema(self) -> Dict[str, Any]:
