@@ -85,6 +85,7 @@ class VllmConfig:
   init_with_random_weights: bool = True
   seed: int = 0
   server_mode: bool = False
+  request_timeout_s: Optional[float] = 1800.0     # server mode: how long a caller waits for one request
   submission_threshold: int = 0
   submission_timeout_s: float = 0.0
   logprobs_mode: str = "processed_logprobs"
@@ -317,7 +318,8 @@ class VllmSampler(base_sampler.BaseSampler):
     params = self._sampling_params(max_generation_steps, temperature, top_p, top_k, seed, eos_tokens,
                                    return_logprobs)
     if self._step_driver is not None:
-      outs = [f.result() for f in self._step_driver.submit_requests([{"prompt_token_ids": t} for t in ids], params)]
+      futures = self._step_driver.submit_requests([{"prompt_token_ids": t} for t in ids], params)
+      outs = [f.result(timeout=self.config.request_timeout_s) for f in futures]
     elif self._driver is not None:
       req = self._driver.submit(ids, params)
       req.done.wait()
