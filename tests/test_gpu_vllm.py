@@ -70,3 +70,48 @@ def test_real_vllm_engine_generates_with_synced_weights():
   assert served._step_driver.steps >= 12 and served._step_driver.last_error is None
   served.close()
   engine.close()
+
+
+@pytest.mark.skipif(os.environ.get("TUNIX_B200_RUN_VLLM") != "1", reason="set TUNIX_B200_RUN_VLLM=1 (slow engine start)")
+def test_grpo_steps_with_the_vllm_rollout_engine():
+  """`ClusterConfig(rollout_engine="vllm")`: the rollout role is a real vLLM engine that receives the actor's
+  weights after every optimizer step; two GRPO steps run, and the engine's greedy decode follows the actor."""
+  pytest.importorskip("vllm")
+  os.environ.setdefault("VLLM_USE_FLASHINFER_SAMPLER", "0")
+  from tests.test_rl_grpo import ToyTokenizer, prompts_ds, reward_len
+  from tunix_b200 import optim
+  from tunix_b200.common.configs import CacheConfig, ClusterConfig, RLTrainingConfig, Role, RolloutConfig
+  from tunix_b200.generate import sampler as sampler_lib
+  from tunix_b200.models.qwen3.model import ModelConfig
+  from tunix_b200.models.transformer import Transformer
+  from tunix_b200.rl import rl_cluster
+  from tunix_b200.rl.grpo import grpo_learner
+  dev = torch.device("cuda", 0)
+  cfg = ModelConfig(num_layers=2, vocab_size=512, embed_dim=256, hidden_dim=512, num_heads=4, head_dim=64,
+                    num_kv_heads=2, dtype=torch.bfloat16, max_position=128)
+  actor = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.15)
+  reference = Transformer(cfg, device=dev).init_weights(seed=0, scale=0.15)
+  tok = ToyTokenizer(vocab=512)
+  tc = RLTrainingConfig(actor_optimizer=optim.adamw(2e-3), eval_every_n_steps=100, max_steps=2, pbar_description=None)
+  rc = RolloutConfig(max_tokens_to_generate=8, max_prompt_length=8, kv_cache_size=64, temperature=1.0, top_p=1.0,
+                     seed=3, return_logprobs=True, eos_tokens=[511], rollout_vllm_hbm_utilization=0.08,
+                     rollout_vllm_kwargs={"enforce_eager": True, "attention_backend": "TRITON_ATTN",
+                                          "dtype": "bfloat16"})
+  cc = ClusterConfig(role_to_mesh={Role.ACTOR: None, Role.REFERENCE: None, Role.ROLLOUT: None},
+                     rollout_engine="vllm", training_config=tc, rollout_config=rc)
+  cl = rl_cluster.RLCluster(actor=actor, reference=reference, tokenizer=tok, cluster_config=cc)
+  before = {n: p.detach().clone() for n, p in actor.named_parameters()}
+  learner = grpo_learner.GRPOLearner(rl_cluster=cl, algo_config=grpo_learner.GRPOConfig(num_generations=2),
+                                     reward_fns=[reward_len])
+  learner.train(prompts_ds(2))
+  assert cl.actor_trainer.train_steps == 2
+  assert any(not torch.equal(p, before[n]) for n, p in actor.named_parameters())
+  losses = cl._rl_metrics_logger.get_metric_history("", "loss", "train")
+  assert len(losses) == 2 and all(np.isfinite(l) for l in losses)
+  # after the last sync the engine decodes like the trained actor
+  prompts = ["alpha beta gamma", "delta eps zeta"]
+  own = sampler_lib.Sampler(actor, tok, CacheConfig(cache_size=64, num_layers=2, num_kv_heads=2, head_dim=64))
+  a = cl._rollout._sampler(prompts, max_generation_steps=8, temperature=0.0, eos_tokens=[511])
+  b = own(input_strings=prompts, max_generation_steps=8, temperature=0.0, echo=False, pad_output=False, eos_tokens=[511])
+  first = [int(x[0]) == int(y[0]) for x, y in zip(a.tokens, b.tokens)]
+  assert all(first), (a.tokens, b.tokens)
