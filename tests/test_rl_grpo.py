@@ -310,3 +310,31 @@ def test_ppo_end_to_end_with_critic():
   lg = cl._rl_metrics_logger
   assert lg.metric_exists("advantages", "returns/mean", "train")
   assert lg.metric_exists("", "vpred_mean", "train")
+
+
+def test_engine_with_its_own_weight_copy_is_synced_every_step():
+  """An engine that keeps a private copy (vLLM) reports the actor as its model; the learner must still push the
+  parameters after every optimizer step (`holds_own_weights`)."""
+  from tunix_b200.rl.rollout import base_rollout, vanilla_rollout
+
+  class PrivateCopyRollout(vanilla_rollout.VanillaRollout):
+    holds_own_weights = True
+    pushes = 0
+
+    def __init__(self, rollout_actor, tokenizer, mesh, rollout_config):
+      mc = rollout_actor.config
+      super().__init__(rollout_actor, tokenizer, base_rollout.CacheConfig(
+          cache_size=rollout_config.kv_cache_size, num_layers=mc.num_layers, num_kv_heads=mc.num_kv_heads,
+          head_dim=mc.head_dim))
+
+    def update_params(self, params, filter_types=None):
+      type(self).pushes += 1
+
+  import dataclasses
+  cc = dataclasses.replace(make_cluster(max_steps=3).cluster_config, rollout_engine=PrivateCopyRollout)
+  cl2 = rl_cluster.RLCluster(actor=toy_model(), reference=toy_model(), tokenizer=ToyTokenizer(), cluster_config=cc)
+  learner = grpo_learner.GRPOLearner(rl_cluster=cl2, algo_config=grpo_learner.GRPOConfig(num_generations=2),
+                                     reward_fns=reward_len)
+  assert learner.should_sync_weights
+  learner.train(prompts_ds(3))
+  assert PrivateCopyRollout.pushes == 3 and cl2.global_steps == 3

@@ -132,7 +132,8 @@ class AgenticRLLearner(abc.ABC, Generic[TConfig]):
     eng.global_steps = eng.actor_trainer.restored_global_step()
     self._iter_steps = eng.actor_trainer.iter_steps
     self._last_eval_train_step = -1
-    self.should_sync_weights = not rl_utils.is_sharing_weights(eng.actor_trainer.model, eng.rollout.model())
+    self.should_sync_weights = getattr(eng.rollout, "holds_own_weights", False) or \
+        not rl_utils.is_sharing_weights(eng.actor_trainer.model, eng.rollout.model())
     r2m = eng.cluster_config.role_to_mesh
     self.can_enable_async_rollout = r2m[Role.ACTOR] != r2m[Role.ROLLOUT]
     self._compute_logps_micro_batch_size = self._training_config.compute_logps_micro_batch_size or 1

@@ -83,8 +83,9 @@ class RLLearner(abc.ABC):
     self.rl_engine.global_steps = self.rl_engine.actor_trainer.restored_global_step()
     self._iter_steps = 0
     self._eval_iter_steps = 0
-    self.should_sync_weights = not rl_utils.is_sharing_weights(self.rl_engine.actor_trainer.model,
-                                                               self.rl_engine.rollout.model())
+    # an engine with its own copy of the weights (vLLM) needs the transfer even when `model()` is the actor
+    self.should_sync_weights = getattr(self.rl_engine.rollout, "holds_own_weights", False) or \
+        not rl_utils.is_sharing_weights(self.rl_engine.actor_trainer.model, self.rl_engine.rollout.model())
     r2m = self.rl_engine.cluster_config.role_to_mesh
     self.can_enable_async_rollout = r2m.get(Role.ACTOR) != r2m.get(Role.ROLLOUT)
     self.executor = futures.ThreadPoolExecutor(max_workers=1, initializer=_bind_producer_thread,

@@ -20,6 +20,9 @@ class RolloutOutput:
 
 
 class BaseRollout(abc.ABC):
+  # True for engines that keep their own copy of the weights (another process, another layout): the learner then
+  # pushes the actor's parameters after every optimizer step even if `model()` returns the actor itself.
+  holds_own_weights = False
 
   @abc.abstractmethod
   def __init__(self, **kwargs):

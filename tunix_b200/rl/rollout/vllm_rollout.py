@@ -11,6 +11,8 @@ from . import base_rollout
 
 
 class VllmRollout(base_rollout.BaseRollout):
+  holds_own_weights = True       # the engine keeps a copy in its own layout: every optimizer step must be pushed to it
+
   def __init__(self, model: Any, tokenizer: Any, rollout_config: base_rollout.RolloutConfig, mesh=None,
                cache_config_or_size: Any = None):
     from ...generate import vllm_sampler
