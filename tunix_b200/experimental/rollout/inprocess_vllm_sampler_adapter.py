@@ -56,14 +56,7 @@ class InprocessVllmSamplerAdapter(staged_sampler.StagedSampler):
     engine = self._sampler
     sp = engine._sampling_params(params.max_tokens, params.temperature, params.top_p, params.top_k, params.seed,
                                  self._eos, params.return_logprobs)
-    if engine._driver is not None:                    # server mode: one submission thread owns the engine
-      ticket = engine._driver.submit(prompts, sp)
-      ticket.done.wait()
-      if ticket.error is not None:
-        raise ticket.error
-      outs = ticket.result
-    else:
-      outs = engine.llm.generate([{"prompt_token_ids": p} for p in prompts], sp, use_tqdm=False)
+    outs = engine.generate_ids(prompts, sp)
     answers = []
     for req, prompt, out in zip(reqs, prompts, outs):
       completion = out.outputs[0]

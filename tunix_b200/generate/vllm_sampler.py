@@ -305,6 +305,21 @@ class VllmSampler(base_sampler.BaseSampler):
     except ImportError:
       return kw                                # injected engines take the plain dict
 
+  def generate_ids(self, prompt_ids: Sequence[Sequence[int]], params: Any) -> List[Any]:
+    """Engine outputs for token-id prompts, through whichever path this sampler runs: the step-level driver
+    (server mode on an engine that can be stepped), the batching thread around `generate`, or a direct call."""
+    ids = [list(t) for t in prompt_ids]
+    if self._step_driver is not None:
+      futures = self._step_driver.submit_requests([{"prompt_token_ids": t} for t in ids], params)
+      return [f.result(timeout=self.config.request_timeout_s) for f in futures]
+    if self._driver is not None:
+      req = self._driver.submit(ids, params)
+      req.done.wait()
+      if req.error is not None:
+        raise req.error
+      return req.result
+    return self.llm.generate([{"prompt_token_ids": t} for t in ids], params, use_tqdm=False)
+
   def __call__(self, input_strings, max_generation_steps, max_prompt_length=None, temperature=0.0, top_p=None,
                top_k=None, beam_size=None, seed=None, multi_sampling: int = 1, return_logits: bool = False,
                echo: bool = False, pad_output: bool = False, eos_tokens: Optional[Sequence[int]] = None,
@@ -317,17 +332,7 @@ class VllmSampler(base_sampler.BaseSampler):
     ids = [t[-P:] for t in ids]
     params = self._sampling_params(max_generation_steps, temperature, top_p, top_k, seed, eos_tokens,
                                    return_logprobs)
-    if self._step_driver is not None:
-      futures = self._step_driver.submit_requests([{"prompt_token_ids": t} for t in ids], params)
-      outs = [f.result(timeout=self.config.request_timeout_s) for f in futures]
-    elif self._driver is not None:
-      req = self._driver.submit(ids, params)
-      req.done.wait()
-      if req.error is not None:
-        raise req.error
-      outs = req.result
-    else:
-      outs = self.llm.generate([{"prompt_token_ids": t} for t in ids], params, use_tqdm=False)
+    outs = self.generate_ids(ids, params)
     eos = set(eos_tokens) if eos_tokens else {self.tokenizer.eos_id()}
     tokens, logprobs = [], []
     for o in outs:
