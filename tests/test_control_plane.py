@@ -2,6 +2,7 @@
 clock, registry, startup validation, remote execution, weight-sync rounds and their failure
 states. All failures are made on the host: a worker that raises, a reply that is dropped, a
 transfer that does not return in time."""
+import os
 import asyncio
 import threading
 import time
@@ -324,7 +325,10 @@ def test_manifest_validation():
 
 
 # ---- the whole loop in one process ---------------------------------------------------------------
-def test_rl_program_end_to_end_with_workers_and_weight_sync():
+@pytest.mark.parametrize("transport", ["in_process", "host_staged"])
+def test_rl_program_end_to_end_with_workers_and_weight_sync(transport):
+  """`host_staged`: the same program with the weights crossing real TCP sockets between a source endpoint
+  (the trainer worker's) and a destination endpoint (the sampler's), commanded by the coordinator's handler."""
   from tests.test_rl_grpo import ToyTokenizer, toy_model
   from tunix_b200 import optim
   from tunix_b200.common.configs import TrainingConfig
@@ -339,7 +343,14 @@ def test_rl_program_end_to_end_with_workers_and_weight_sync():
 
   tok = ToyTokenizer()
   actor, rollout_model, ref = toy_model(), toy_model(), toy_model()
-  handler = peer_memory_handler.InProcessHandler()
+  endpoints = []
+  if transport == "in_process":
+    handler = source_side = destination_side = peer_memory_handler.InProcessHandler()
+  else:
+    from tunix_b200.experimental.orchestrator import host_staged_handler as hs
+    source_side, destination_side = hs.HostStagedEndpoint(), hs.HostStagedEndpoint()
+    endpoints = [source_side, destination_side]
+    handler = hs.HostStagedHandler(timeout_s=30)
   algo_cfg = GRPOConfig(num_generations=2, beta=0.04)
   loss = function_registry.get_policy_loss_fn("grpo")
 
@@ -349,9 +360,12 @@ def test_rl_program_end_to_end_with_workers_and_weight_sync():
                                                      pad_id=0, eos_id=2), has_aux=True)
     t.with_gen_model_input_fn(lambda x: {"train_example": x})
     return t
-  tw = trainer_worker.TrainerWorker(make_trainer, worker_id="t0", handler=handler)
-  sampler = native_sampler_adapter.NativeSamplerAdapter(rollout_model, tok, handler=handler, worker_id="r0",
+  tw = trainer_worker.TrainerWorker(make_trainer, worker_id="t0", handler=source_side)
+  sampler = native_sampler_adapter.NativeSamplerAdapter(rollout_model, tok, handler=destination_side, worker_id="r0",
                                                         engine_config=EngineConfig(page_size=4, max_batch=8, max_seq_len=32))
+  if endpoints:
+    handler.register_endpoint(tw.work_unit, source_side.address)
+    handler.register_endpoint(sampler.work_unit, destination_side.address)
   rw = rollout_worker.RolloutWorker(lambda: manager_lib.RolloutManager(sampler=sampler, tokenizer=tok, chat_parser=None),
                                     worker_id="r0")
   iw = inference_worker.InferenceWorker({"reference": ref}, worker_id="i0")
@@ -379,6 +393,10 @@ def test_rl_program_end_to_end_with_workers_and_weight_sync():
   for n, p in rollout_model.named_parameters():
     torch.testing.assert_close(p, dict(actor.named_parameters())[n])
   assert all(w.state == S.STOPPED for w in (tw, rw, iw))
+  if endpoints:
+    assert source_side.served["fetch"] == 2 and destination_side.served["pull"] == 2
+  for ep in endpoints:
+    ep.close()
 
 
 def test_remote_execution_over_grpc_loopback():
@@ -416,3 +434,61 @@ def test_remote_execution_over_grpc_loopback():
     asyncio.run(session())
   finally:
     server.shutdown()
+
+
+def test_host_staged_transport_between_processes():
+  """`host_staged_handler`: a source and two destinations in their own OS processes, the handler in this one.
+  Bytes arrive exactly (same dtype) or converted (fp32 staging), stale generations and shape mismatches are
+  refused, an unreachable destination is a known failure."""
+  import subprocess
+  import sys
+  import torch
+  from tests import _host_staged_worker as w
+  from tunix_b200.experimental.orchestrator import host_staged_handler as hs, peer_memory_handler as pmh, weight_sync as ws
+  here = os.path.dirname(os.path.abspath(__file__))
+  procs = []
+
+  def spawn(role, unit, generation=0):
+    p = subprocess.Popen([sys.executable, os.path.join(here, "_host_staged_worker.py"), role, unit, str(generation)],
+                         stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    procs.append(p)
+    return ("127.0.0.1", int(p.stdout.readline()))
+
+  try:
+    src, same, wide = (ws.WorkUnitId("trainer", "t0", 0), ws.WorkUnitId("rollout", "r0", 0),
+                       ws.WorkUnitId("rollout", "r1", 1))
+    addr = {src: spawn("source", hs.unit_key(src), 5), same: spawn("same", hs.unit_key(same)),
+            wide: spawn("wide", hs.unit_key(wide))}
+    handler = hs.HostStagedHandler(addr, timeout_s=30)
+    want = w.tensors(7, torch.bfloat16)
+    handler.register_work_unit(pmh.manifest_of(src, want))
+    assert not handler.transfer([src], [same], "r1", 5).success          # destination never registered
+    handler.register_work_unit(pmh.manifest_of(same, w.tensors(0, torch.bfloat16)))
+    handler.register_work_unit(pmh.manifest_of(wide, w.tensors(0, torch.float32)))
+    stale = handler.transfer([src], [same], "r2", generation=4)
+    assert not stale.success and "generation" in stale.message
+    done = handler.transfer([src], [same, wide], "r3", generation=5)
+    assert done.success and "2 destination" in done.message, done.message
+    # the bf16 destination holds the source's bytes; the fp32 one holds the converted values
+    digest = lambda a, u: hs.call(a, {"op": "checksum", "unit": hs.unit_key(u)})["sha256"]   # noqa: E731
+    assert digest(addr[same], same) == digest(addr[src], src)
+    import hashlib
+    expect = hashlib.sha256()
+    for n in sorted(want):
+      expect.update(n.encode())
+      expect.update(want[n].float().contiguous().view(-1).view(torch.uint8).numpy().tobytes())
+    assert digest(addr[wide], wide) == expect.hexdigest()
+    # a manifest that disagrees on a shape is caught before anything moves
+    bad = dict(w.tensors(0, torch.bfloat16))
+    bad["layers.0.w"] = torch.zeros(16, 47)
+    handler.register_work_unit(pmh.manifest_of(same, bad))
+    assert "shape mismatch" in handler.transfer([src], [same], "r4", 5).message
+    # an endpoint nobody listens on: failure, not an unknown outcome
+    handler.register_work_unit(pmh.manifest_of(same, w.tensors(0, torch.bfloat16)))
+    handler.register_endpoint(same, ("127.0.0.1", 1))
+    gone = handler.transfer([src], [same], "r5", 5)
+    assert not gone.success and "unreachable" in gone.message
+  finally:
+    for p in procs:
+      p.stdin.close()
+      p.wait(timeout=10)
