@@ -27,6 +27,7 @@ late round cannot read half-replaced weights. Every socket operation has a deadl
 from __future__ import annotations
 
 import concurrent.futures
+import contextlib
 import hashlib
 import json
 import socket
@@ -207,11 +208,14 @@ class HostStagedEndpoint:
         staged[i % 2] = (raw, None)
         return
       host = pair.get(i % 2, raw.numel())
-      host.copy_(raw, non_blocking=True)
-      ev = torch.cuda.Event()
-      ev.record()
+      with torch.cuda.device(raw.device):            # this thread's current device is not necessarily the tensor's
+        host.copy_(raw, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
       staged[i % 2] = (host, ev)
 
+    for device in {t.device for t in tensors.values() if t.is_cuda}:
+      torch.cuda.synchronize(device)                 # whatever produced the attached tensors has finished
     moved = 0
     if names:
       stage(0)
@@ -257,14 +261,15 @@ class HostStagedEndpoint:
         host = pair.get(i % 2, int(head["nbytes"]))
         if host.numel():
           _recv_exact(src, memoryview(host.numpy()))
-        if raw is not None and head["dtype"] == str(dst.dtype).replace("torch.", ""):
-          raw.copy_(host, non_blocking=True)               # same dtype: bytes straight into the staging tensor
-        elif host.numel():
-          incoming = host.view(getattr(torch, head["dtype"])).view(dst.shape)
-          dst.copy_(incoming.to(dst.dtype), non_blocking=True)
-        if dst.is_cuda:
-          busy[i % 2] = torch.cuda.Event()
-          busy[i % 2].record()
+        with torch.cuda.device(dst.device) if dst.is_cuda else contextlib.nullcontext():
+          if raw is not None and head["dtype"] == str(dst.dtype).replace("torch.", ""):
+            raw.copy_(host, non_blocking=True)             # same dtype: bytes straight into the staging tensor
+          elif host.numel():
+            incoming = host.view(getattr(torch, head["dtype"])).view(dst.shape)
+            dst.copy_(incoming.to(dst.device, non_blocking=True).to(dst.dtype))
+          if dst.is_cuda:
+            busy[i % 2] = torch.cuda.Event()
+            busy[i % 2].record()
         moved += host.numel()
       tail = _recv_json(src)
       if not tail.get("done"):
