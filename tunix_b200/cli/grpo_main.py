@@ -33,30 +33,34 @@ class GrpoPipeline(base_rl_pipeline.BasePipeline):
     valid = {f.name for f in dataclasses.fields(GRPOConfig)}
     return GRPOConfig(**{k: v for k, v in cfg.items() if k in valid})
 
+  def _pluggable(self, kind: str) -> Dict[str, Any]:
+    """`{kind}_class` (a dotted path) and `{kind}_kwargs` of the config as learner keyword arguments."""
+    path = self.config.get(f"{kind}_class")
+    if not path:
+      return {}
+    return {f"{kind}_class": self._load_class_from_path(path), f"{kind}_kwargs": dict(self.config.get(f"{kind}_kwargs") or {})}
+
+  def _single_turn_learner(self, rl_engine, chat_parser):
+    from ..rl.grpo import grpo_learner
+    algo = grpo_learner.GRPOConfig(**(self.config.get("grpo_config") or {}))
+    return grpo_learner.GRPOLearner(rl_engine=rl_engine, reward_fns=self.obtain_reward_fn(), algo_config=algo)
+
+  def _agentic_learner(self, rl_engine, chat_parser):
+    from ..rl.agentic import agentic_grpo_learner
+    rewards = self.obtain_reward_fn() if self.config.get("reward_functions") else None
+    return agentic_grpo_learner.GRPOLearner(rl_engine=rl_engine, algo_config=self._create_agentic_grpo_config(),
+                                            reward_fns=rewards, chat_parser=chat_parser, **self._pluggable("agent"),
+                                            **self._pluggable("env"))
+
+  _LEARNERS = {"grpo": "_single_turn_learner", "agentic_grpo": "_agentic_learner"}
+
   def _run(self, mode: str = "grpo"):
+    if mode not in self._LEARNERS:
+      raise ValueError(f"Unsupported training_mode {mode!r}")
     tokenizer = self._get_tokenizer()
     chat_parser = self._create_chat_parser(tokenizer)
     dataset, _ = self._get_dataset(tokenizer)
-    rl_engine = self.create_rl_engine(tokenizer)
-    if mode == "grpo":
-      from ..rl.grpo import grpo_learner
-      learner = grpo_learner.GRPOLearner(rl_engine=rl_engine, reward_fns=self.obtain_reward_fn(),
-                                         algo_config=grpo_learner.GRPOConfig(**(self.config.get("grpo_config") or {})))
-      learner.train(dataset)
-      return learner
-    if mode != "agentic_grpo":
-      raise ValueError(f"Unsupported training_mode {mode!r}")
-    from ..rl.agentic.agentic_grpo_learner import GRPOLearner
-    kw: Dict[str, Any] = dict(rl_engine=rl_engine, algo_config=self._create_agentic_grpo_config(),
-                              reward_fns=self.obtain_reward_fn() if self.config.get("reward_functions") else None,
-                              chat_parser=chat_parser)
-    if self.config.get("agent_class"):
-      kw["agent_class"] = self._load_class_from_path(self.config["agent_class"])
-      kw["agent_kwargs"] = dict(self.config.get("agent_kwargs") or {})
-    if self.config.get("env_class"):
-      kw["env_class"] = self._load_class_from_path(self.config["env_class"])
-      kw["env_kwargs"] = dict(self.config.get("env_kwargs") or {})
-    learner = GRPOLearner(**kw)
+    learner = getattr(self, self._LEARNERS[mode])(self.create_rl_engine(tokenizer), chat_parser)
     learner.train(dataset)
     return learner
 
