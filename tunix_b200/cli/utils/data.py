@@ -2,10 +2,12 @@
 from __future__ import annotations
 
 import ast
+import dataclasses
 import functools
 import importlib
 import importlib.util
 import os
+import re
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
 from ...data import ListDataset
@@ -32,45 +34,59 @@ def parse_call_string(arg_string: str) -> Tuple[List[Any], Dict[str, Any]]:
   return [ast.literal_eval(a) for a in call.args], {k.arg: ast.literal_eval(k.value) for k in call.keywords}
 
 
-def _import(specifier: str):
-  if os.path.exists(specifier) and specifier.endswith(".py"):
-    name = os.path.splitext(os.path.basename(specifier))[0]
-    spec = importlib.util.spec_from_file_location(name, specifier)
-    if spec is None or spec.loader is None:
-      raise ImportError(f"Failed to create spec for {specifier}")
-    mod = importlib.util.module_from_spec(spec)
-    try:
-      spec.loader.exec_module(mod)
-    except Exception as e:
-      raise ImportError(f"Failed to execute module {name} from {specifier}: {e}") from e
-    return mod
+def _load_module(where: str):
+  """A dotted module name, or the path of a `.py` file (loaded under its base name)."""
+  from_file = where.endswith(".py") and os.path.exists(where)
   try:
-    return importlib.import_module(specifier)
+    if not from_file:
+      return importlib.import_module(where)
+    name = os.path.splitext(os.path.basename(where))[0]
+    spec = importlib.util.spec_from_file_location(name, where)
+    if spec is None or spec.loader is None:
+      raise ImportError(f"Failed to create spec for {where}")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+  except ImportError:
+    raise
   except Exception as e:
-    raise ImportError(f"Failed to import module {specifier}: {e}") from e
+    raise ImportError(f"Failed to import module {where}: {e}") from e
+
+
+@dataclasses.dataclass(frozen=True)
+class DatasetSpec:
+  """`module[:function[(literal arguments)]]`; `module` may be a file path, also one with a drive letter."""
+  module: str
+  function: str = "create_dataset"
+  args: Tuple[Any, ...] = ()
+  kwargs: Tuple[Tuple[str, Any], ...] = ()
+
+  _FORM = re.compile(r"^(?P<module>(?:[A-Za-z]:(?=[\\/]))?[^:]+)(?::(?P<function>[A-Za-z_]\w*)(?:\((?P<call>.*)\))?)?$", re.S)
+
+  @classmethod
+  def parse(cls, text: str) -> "DatasetSpec":
+    m = cls._FORM.match(text.strip())
+    if m is None:
+      raise ValueError(f"cannot read dataset specifier {text!r}: expected module[:function[(arguments)]]")
+    args, kwargs = parse_call_string(m["call"]) if m["call"] else ([], {})
+    return cls(m["module"], m["function"] or "create_dataset", tuple(args), tuple(kwargs.items()))
+
+  def build(self, **defaults):
+    """Calls the function; arguments written in the specifier win over `defaults`."""
+    return getattr(_load_module(self.module), self.function)(*self.args, **{**defaults, **dict(self.kwargs)})
 
 
 def get_dataset_from_module(specifier: str, tokenizer=None, apply_chat_template_to_dataset: bool = False,
                             **dataset_kwargs):
   """`pkg.mod`, `pkg.mod:func`, `pkg.mod:func('x', split='train')` or `/path/file.py:func`;
   the default function is `create_dataset`."""
-  args_part = ""
-  if "(" in specifier and ":" in specifier:
-    specifier, args_part = specifier.rsplit("(", 1)
-  func_name = ""
-  if ":" in specifier and not (len(specifier) > 1 and specifier[1] == ":" and specifier.count(":") == 1):
-    specifier, func_name = specifier.rsplit(":", 1)
-  mod = _import(specifier)
-  args, kwargs = parse_call_string(args_part.rstrip(")")) if (func_name and args_part) else ([], {})
-  fn = getattr(mod, func_name) if func_name else mod.create_dataset
-  ds = fn(*args, **{**dataset_kwargs, **kwargs})
+  ds = DatasetSpec.parse(specifier).build(**dataset_kwargs)
   if not apply_chat_template_to_dataset:
     return ds
   if tokenizer is None:
     raise ValueError("tokenizer must be provided when apply_chat_template_to_dataset is True.")
-  if not hasattr(ds, "map"):
-    ds = ListDataset(list(ds))
-  return ds.map(functools.partial(apply_chat_template, tokenizer=tokenizer))
+  as_mappable = ds if hasattr(ds, "map") else ListDataset(list(ds))
+  return as_mappable.map(functools.partial(apply_chat_template, tokenizer=tokenizer))
 
 
 def post_init_dataset(dataset, tokenizer, batch_size: int, num_batches: Optional[int], max_prompt_length: Optional[int],
