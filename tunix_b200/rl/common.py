@@ -378,7 +378,9 @@ def reduced_loss_agg(per_token_loss: torch.Tensor, completion_mask: torch.Tensor
                      segment_ids: Optional[torch.Tensor] = None, num_segments: Optional[int] = None,
                      **kwargs: Any) -> torch.Tensor:
   """Eager (divide-now) form of `aggregate_loss`, written independently so the two cross-check;
-  used only for the `reduced_pg_loss` logging metric."""
+  used only for the `reduced_pg_loss` logging metric. Per-sequence means divide by the number of rows that hold
+  at least one unmasked token, exactly like `aggregate_loss` (the reference's eager form averages over all rows,
+  tunix/rl/common.py:1003-1014, and so disagrees with its own deferred form on batches with padding rows)."""
   ptl = per_token_loss.float()
   m = completion_mask.to(ptl.dtype)
   if segment_ids is not None:
@@ -400,11 +402,12 @@ def reduced_loss_agg(per_token_loss: torch.Tensor, completion_mask: torch.Tensor
     raise ValueError(f"Unsupported loss aggregation mode: {loss_agg_mode}. Supported modes: {_MODES}.")
   if loss_agg_mode == "token-mean":
     return (ptl * m).sum() / m.sum().clamp(min=1.0)
+  rows = (m.sum(-1) > 0).sum().clamp(min=1)      # rows without a single unmasked token are padding, not sequences
   if loss_agg_mode == "sequence-mean-token-mean":
-    return ((ptl * m).sum(-1) / m.sum(-1).clamp(min=1.0)).mean()
+    return ((ptl * m).sum(-1) / m.sum(-1).clamp(min=1.0)).sum() / rows
   if loss_agg_mode == "sequence-mean-token-scale":
     norm = _check_get_norm(kwargs, ptl.shape[-1])
-    return ((ptl * m).sum(-1) / max(norm, 1e-6)).mean()
+    return ((ptl * m).sum(-1) / max(norm, 1e-6)).sum() / rows
   if loss_agg_mode == "seq-mean-token-sum":
     act = (m.sum(-1) > 0).float()
     return ((ptl * m).sum(-1) * act).sum() / act.sum().clamp(min=1e-6)
