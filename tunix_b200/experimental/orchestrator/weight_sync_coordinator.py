@@ -17,6 +17,18 @@ Failure handling keeps version consistency and worker health apart:
 After any of the last three the coordinator is poisoned and `sync` raises until
 `reset_after_recovery()`.
 
+Publishing is retried: `post_weight_sync` is idempotent on a worker (its tracker ignores a second delivery),
+so destinations whose publish failed are asked again (`post_retries` times) before the round is judged. If
+after that NO destination has published, the fleet is still uniform and the round is rolled back like any
+other pre-publish failure instead of poisoning the coordinator.
+
+Cancellation (the caller's task is cancelled mid-round) never leaves the fleet quiesced: between the start of
+the downtime and the publish the destinations are rolled back and the sources released before the
+cancellation propagates; a cancellation during the transfer call parks the round as UNKNOWN_TRANSFER_STATE
+(nothing touched, coordinator poisoned); one during the publish lets the publish finish on every destination
+first, so the fleet converges on the new version or, failing that, is reported PARTIALLY_COMMITTED. The
+outcome of a cancelled round is kept in `last_result`.
+
 A failed phase call means "the reply is lost", not "the work did not happen": before deciding,
 the coordinator asks the worker for its round report (`get_weight_sync_status`) and accepts the
 phase if the report proves it. Workers key their round by the (req_id, uuid) carried in
@@ -249,8 +261,10 @@ class WeightSyncCoordinator:
   def __init__(self, handler: weight_sync.WeightSyncHandler, registry: Optional[worker_registry.WorkerRegistry] = None,
                *, sources: Optional[Sequence[Any]] = None, destinations: Optional[Sequence[Any]] = None,
                timeouts: PhaseTimeouts = PhaseTimeouts(), source_role: str = TRAINER_ROLE,
-               destination_role: str = ROLLOUT_ROLE):
+               destination_role: str = ROLLOUT_ROLE, post_retries: int = 1):
     self._handler, self._registry = handler, registry
+    self._post_retries = max(0, int(post_retries))
+    self.last_result: Optional[WeightSyncResult] = None
     self._explicit_sources, self._explicit_destinations = sources, destinations
     self._timeouts = timeouts
     self._source_role, self._destination_role = source_role, destination_role
@@ -364,14 +378,18 @@ class WeightSyncCoordinator:
                        f"{self._last_committed}")
     async with self._lock:
       result = await self._run_round(policy_version)
-    if result.state in _POISONING_STATES:
-      self._poisoned = f"round {result.round_index} ended {result.state.value}"
-    if result.state == RoundState.COMMITTED:
-      self._last_committed = policy_version
-    elif raise_on_failure:
+    self._record(result)
+    if result.state != RoundState.COMMITTED and raise_on_failure:
       raise WeightSyncError(f"weight sync round {result.round_index} ended {result.state.value}: "
                             + "; ".join(result.failures), result)
     return result
+
+  def _record(self, result: WeightSyncResult) -> None:
+    self.last_result = result
+    if result.state in _POISONING_STATES:
+      self._poisoned = f"round {result.round_index} ended {result.state.value}"
+    if result.state == RoundState.COMMITTED:
+      self._last_committed = result.policy_version
 
   async def _run_round(self, policy_version: int) -> WeightSyncResult:
     sources, dests = self._sources(), self._destinations()
@@ -410,52 +428,86 @@ class WeightSyncCoordinator:
       failures = [f"preparation failed: {type(e).__name__}: {e}"] + await self._release(prepared_sources, req)
       return result(RoundState.ABORTED, failures=failures)
 
-    # 2. downtime starts
-    errs = await self._on_all(dests, "pre_weight_sync", req, t.pre)
-    if any(errs.values()):
-      state, reports, fails = await self._rollback(dests, req)
-      fails = [e for e in errs.values() if e] + fails + await self._release(sources, req)
-      return result(state, reports, fails)
-
-    # 3. transport
+    # 2..5: the downtime. `stage` tells the cancellation handler what may have happened so far.
+    stage = "quiesce"
     try:
-      transfer = await asyncio.wait_for(asyncio.get_running_loop().run_in_executor(
-          None, lambda: self._handler.transfer(src_units, dst_units, req_id=req.request_id,
-                                               generation=req.extra_config["uuid"])), timeout=t.transfer)
-    except (asyncio.TimeoutError, weight_sync.TransferOutcomeUnknownError) as e:
-      # the transport may still be writing: abort nothing, release nothing
-      reports = [WorkerRoundReport(worker_id=_worker_id(d), phase=await self._status(d), needs_restart=True)
-                 for d in dests]
-      return result(RoundState.UNKNOWN_TRANSFER_STATE, reports,
-                    [f"transfer outcome unknown: {type(e).__name__}: {e}"])
-    except Exception as e:
-      transfer = weight_sync.TransferResult(req_id=req.request_id, success=False, message=f"{type(e).__name__}: {e}")
-    if not transfer.success:
-      state, reports, fails = await self._rollback(dests, req)
-      fails = [f"transfer failed: {transfer.message}"] + fails + await self._release(sources, req)
-      return result(state, reports, fails)
+      errs = await self._on_all(dests, "pre_weight_sync", req, t.pre)
+      if any(errs.values()):
+        state, reports, fails = await self._rollback(dests, req)
+        fails = [e for e in errs.values() if e] + fails + await self._release(sources, req)
+        return result(state, reports, fails)
 
-    # 4. staging on every destination
-    errs = await self._on_all(dests, "weight_sync", req, t.h2d)
-    if any(errs.values()):
-      state, reports, fails = await self._rollback(dests, req)
-      fails = [e for e in errs.values() if e] + fails + await self._release(sources, req)
-      return result(state, reports, fails)
+      stage = "transfer"
+      try:
+        transfer = await asyncio.wait_for(asyncio.get_running_loop().run_in_executor(
+            None, lambda: self._handler.transfer(src_units, dst_units, req_id=req.request_id,
+                                                 generation=req.extra_config["uuid"])), timeout=t.transfer)
+      except (asyncio.TimeoutError, weight_sync.TransferOutcomeUnknownError) as e:
+        # the transport may still be writing: abort nothing, release nothing
+        return result(RoundState.UNKNOWN_TRANSFER_STATE, await self._parked(dests),
+                      [f"transfer outcome unknown: {type(e).__name__}: {e}"])
+      except asyncio.CancelledError:
+        raise
+      except Exception as e:
+        transfer = weight_sync.TransferResult(req_id=req.request_id, success=False, message=f"{type(e).__name__}: {e}")
+      stage = "stage"
+      if not transfer.success:
+        state, reports, fails = await self._rollback(dests, req)
+        fails = [f"transfer failed: {transfer.message}"] + fails + await self._release(sources, req)
+        return result(state, reports, fails)
 
-    # 5. publish
+      errs = await self._on_all(dests, "weight_sync", req, t.h2d)
+      if any(errs.values()):
+        state, reports, fails = await self._rollback(dests, req)
+        fails = [e for e in errs.values() if e] + fails + await self._release(sources, req)
+        return result(state, reports, fails)
+
+      stage = "publish"
+      return await self._publish(sources, dests, req, result)
+    except asyncio.CancelledError:
+      outcome = await asyncio.shield(self._settle_cancelled(stage, sources, dests, req, result))
+      self._record(outcome)
+      raise
+
+  async def _parked(self, dests: Sequence[Any]) -> List[WorkerRoundReport]:
+    return [WorkerRoundReport(worker_id=_worker_id(d), phase=await self._status(d), needs_restart=True) for d in dests]
+
+  async def _publish(self, sources, dests, req, result) -> WeightSyncResult:
+    """`post_weight_sync` everywhere, retried where it failed; then the verdict."""
+    t = self._timeouts
     errs = await self._on_all(dests, "post_weight_sync", req, t.post)
+    for _ in range(self._post_retries):
+      again = [i for i, e in errs.items() if e]
+      if not again:
+        break
+      retried = await self._on_all([dests[i] for i in again], "post_weight_sync", req, t.post)
+      for slot, i in enumerate(again):
+        errs[i] = retried[slot]
     failed = [i for i, e in errs.items() if e]
-    release_errs = await self._release(sources, req)
     if not failed:
+      release_errs = await self._release(sources, req)
       reports = [WorkerRoundReport(worker_id=_worker_id(d), phase="committed") for d in dests]
       return result(RoundState.COMMITTED, reports, release_errs)
-    reports = []
-    for i, d in enumerate(dests):
-      if errs[i] is None:
-        reports.append(WorkerRoundReport(worker_id=_worker_id(d), phase="committed"))
-      else:
-        reports.append(WorkerRoundReport(worker_id=_worker_id(d), phase=await self._status(d), error=errs[i],
-                                         needs_restart=True))
+    phases = {i: ("committed" if errs[i] is None else await self._status(dests[i])) for i in range(len(dests))}
+    if "committed" not in phases.values() and "unknown" not in phases.values():
+      # nobody published and everybody answers: the fleet is uniform on the old version, so roll back
+      state, reports, fails = await self._rollback(dests, req)
+      fails = [errs[i] for i in failed] + fails + await self._release(sources, req)
+      return result(state, reports, fails)
+    release_errs = await self._release(sources, req)
+    reports = [WorkerRoundReport(worker_id=_worker_id(d), phase=phases[i], error=errs[i] or "",
+                                 needs_restart=errs[i] is not None) for i, d in enumerate(dests)]
     committed = sum(1 for r in reports if r.phase == "committed")
     state = RoundState.PARTIALLY_COMMITTED if committed else RoundState.FAILED_NEEDS_RESTART
     return result(state, reports, [errs[i] for i in failed] + release_errs)
+
+  async def _settle_cancelled(self, stage: str, sources, dests, req, result) -> WeightSyncResult:
+    """Brings a round whose driver was cancelled to a defined end (runs shielded from further cancellation)."""
+    note = f"round cancelled during {stage}"
+    if stage == "transfer":
+      return result(RoundState.UNKNOWN_TRANSFER_STATE, await self._parked(dests), [note])
+    if stage == "publish":
+      outcome = await self._publish(sources, dests, req, result)
+      return dataclasses.replace(outcome, failures=(note,) + tuple(outcome.failures))
+    state, reports, fails = await self._rollback(dests, req)
+    return result(state, reports, [note] + fails + await self._release(sources, req))
