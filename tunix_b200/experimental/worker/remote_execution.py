@@ -17,6 +17,7 @@ import abc
 import asyncio
 import contextlib
 import inspect
+import zlib
 import threading
 import traceback as traceback_lib
 from typing import Any, AsyncIterator, Callable, Dict, List, Optional, Sequence, Tuple, Union
@@ -89,6 +90,7 @@ class RemoteExecutionServer(abc.ABC):
   def __init__(self, instance: Optional[Any] = None):
     self._instance = instance
     self._responses: Optional[asyncio.Queue] = None
+    self._responses_loop: Optional[asyncio.AbstractEventLoop] = None
     self._counter = 0
     self._background: set = set()
 
@@ -103,8 +105,15 @@ class RemoteExecutionServer(abc.ABC):
   def start_serving(self, port: int) -> None: ...
 
   def _queue(self) -> asyncio.Queue:
-    if self._responses is None:
-      self._responses = asyncio.Queue()
+    """The response queue of the running loop. An asyncio queue belongs to the loop that first waited on it; a
+    server that outlives a loop (a second `asyncio.run`, a restarted serving thread) gets a fresh queue, and
+    responses nobody collected move over."""
+    loop = asyncio.get_running_loop()
+    if self._responses is None or self._responses_loop is not loop:
+      fresh: asyncio.Queue = asyncio.Queue()
+      while self._responses is not None and not self._responses.empty():
+        fresh.put_nowait(self._responses.get_nowait())
+      self._responses, self._responses_loop = fresh, loop
     return self._responses
 
   def _resolve(self, request: ExecutionRequest):
@@ -428,8 +437,8 @@ class RoutingActorPool(ActorPool):
       raise TypeError(f"Router object {type(self.router)} must provide a method matching '{method_name}' or be "
                       "callable.")
     key = kwargs.get("route_key")
-    if key is not None:
-      return self._actors[hash(key) % len(self._actors)]
+    if key is not None:      # CRC of the key's text: the same key finds the same actor in every process and run
+      return self._actors[zlib.crc32(repr(key).encode("utf-8")) % len(self._actors)]
     if self.policy == "least_loaded":
       return min(self._actors, key=lambda a: self._inflight[id(a)])
     actor = self._actors[self._idx % len(self._actors)]
