@@ -159,9 +159,12 @@ class CheckpointManager:
       return False
     if force:
       return True
-    if self._pending is not None and not self._pending.done():
-      return False    # a save is still being written; the continuous policy skips this step
-    return bool(self._options.save_decision_policy.should_save(step, self._last_saved_step, self._last_save_time))
+    policy = self._options.save_decision_policy
+    if (isinstance(policy, checkpoint_options.ContinuousCheckpointingPolicy) and self._pending is not None
+        and not self._pending.done()):
+      return False    # "as often as the writer allows": a save is still being written, so this step is skipped
+    # every other policy names the steps it wants; `save` waits for the previous write instead of dropping one
+    return bool(policy.should_save(step, self._last_saved_step, self._last_save_time))
 
   def save(self, step: int, model: torch.nn.Module, optimizer: Any = None, save_only_lora_params: bool = False,
            force: bool = False, custom_metadata: Optional[Mapping[str, Any]] = None) -> bool:
