@@ -16,6 +16,7 @@ import abc
 import asyncio
 import dataclasses
 import logging
+import threading
 from typing import Any, Callable, Iterable, List, Optional, Sequence
 
 import numpy as np
@@ -124,6 +125,8 @@ class StandardRLProgram(RLProgram):
     self.scored_q = tqm.TrajectoryQueueManager.create(group_size=self.group_size)
     self.history: List[RLStepResult] = []
     self._window: Optional[_DispatchWindow] = None        # made inside the running loop
+    self._expected = self._received = 0                   # rollouts asked for / come back
+    self._dispatch_done = False
 
   # ---- stage 1: dispatch
   async def rollout_dispatch_stage(self, engine, train_dataset=None) -> None:
@@ -135,6 +138,17 @@ class StandardRLProgram(RLProgram):
       await window.admit(index)
       await engine.dispatch_rollouts([_as_prompt_item(item, index)], group_size=self.group_size,
                                      policy_version=self.policy_version)
+      self._expected += self.group_size
+    self._dispatch_done = True
+    await self._close_intake_if_complete()
+
+  async def _close_intake_if_complete(self) -> None:
+    """The data has run out once every prompt is dispatched and every rollout asked for has come back: the
+    grouping queue then drains (complete groups still go out, nothing new comes in), which ends the critic, whose
+    exit drains the scored queue, which lets the trainer finish its last - possibly shorter - step and stop. A
+    rollout that never comes back keeps the program waiting; engines bound their rollouts, this program does not."""
+    if self._dispatch_done and self._received >= self._expected:
+      await self.raw_q.prepare_clear()
 
   # ---- stage 2: collect finished rollouts
   async def polling_stage(self, engine) -> None:
@@ -149,6 +163,9 @@ class StandardRLProgram(RLProgram):
         continue
       for item in finished or []:
         await self.raw_q.put(item)
+        self._received += 1
+      if finished:
+        await self._close_intake_if_complete()
 
   # ---- stage 3: score complete groups
   def _score(self, item: Any) -> float:
@@ -163,6 +180,7 @@ class StandardRLProgram(RLProgram):
       except asyncio.CancelledError:
         return
       if not group:
+        await self.scored_q.prepare_clear()      # nothing more will be scored
         return
       rewards = [self._score(item) for item in group]
       payloads = self.algo.create_trainer_payloads(group, rewards=rewards)
@@ -190,22 +208,27 @@ class StandardRLProgram(RLProgram):
     return with_ref
 
   async def _one_step(self, engine) -> _StepLedger:
-    """Accumulates gradients over `mini_batch_size` groups; the optimizer is applied with the very last
-    micro-batch. Returns early (fewer groups) when the scored queue is draining."""
+    """Accumulates gradients over up to `mini_batch_size` groups and applies the optimizer with the very last
+    micro-batch of the step. A group is trained on as soon as it is scored - only its last micro-batch waits
+    until the next group has arrived (or the queue has drained), because that decides whether it closes the
+    step: when the data runs out mid-step the groups that did arrive still get their update."""
     ledger = _StepLedger()
-    for position in range(self.mini_batch_size):
-      items = await self.scored_q.get_batch(num_groups=1)
-      if not items:
-        break
+    items = await self.scored_q.get_batch(num_groups=1)
+    position = 0
+    while items:
       ledger.groups.append(items)
       ledger.rewards.extend(float(getattr(item.traj, "reward", 0.0)) for item in items)
       batches = await self._micro_batches(engine, items)
       ledger.micro_batches += len(batches)
-      closing_group = position == self.mini_batch_size - 1
-      for number, batch in enumerate(batches, start=1):
-        ledger.train_result = await engine.train_step(
-            batch, role=datatypes.Role.ACTOR, accumulate_gradients=True,
-            apply_optimizer=closing_group and number == len(batches))
+      for batch in batches[:-1]:
+        ledger.train_result = await engine.train_step(batch, role=datatypes.Role.ACTOR, accumulate_gradients=True,
+                                                      apply_optimizer=False)
+      last_slot = position == self.mini_batch_size - 1
+      upcoming = [] if last_slot else await self.scored_q.get_batch(num_groups=1)
+      if batches:
+        ledger.train_result = await engine.train_step(batches[-1], role=datatypes.Role.ACTOR,
+                                                      accumulate_gradients=True, apply_optimizer=not upcoming)
+      items, position = upcoming, position + 1
     return ledger
 
   async def train_stage(self, engine, num_steps: Optional[int] = None) -> None:
@@ -232,6 +255,10 @@ class StandardRLProgram(RLProgram):
     """Runs the four stages until the trainer has done `num_steps` (or the data ran out). A failure of the
     dispatcher or the critic cancels training and is re-raised; the poller only logs."""
     self._is_running = True
+    await self.raw_q.clear()                     # a program can be run again: queues and counters start over
+    await self.scored_q.clear()
+    self._expected = self._received = 0
+    self._dispatch_done = False
     self._window = _DispatchWindow(self.mini_batch_size, self.max_staleness)
     self._window.version = self.policy_version
     dispatch = asyncio.create_task(self.rollout_dispatch_stage(engine, train_dataset))
@@ -258,4 +285,22 @@ class StandardRLProgram(RLProgram):
       await asyncio.gather(*helpers, return_exceptions=True)
 
   def run(self, engine, train_dataset=None, num_steps: Optional[int] = None, **kwargs) -> None:
-    asyncio.run(self.run_async(engine, train_dataset, num_steps, **kwargs))
+    """Synchronous entry point. Called where an event loop is already running (a notebook, a coroutine of the
+    caller), the program gets a loop of its own on another thread and the caller blocks until it is done."""
+    try:
+      asyncio.get_running_loop()
+    except RuntimeError:
+      asyncio.run(self.run_async(engine, train_dataset, num_steps, **kwargs))
+      return
+    failure: List[BaseException] = []
+
+    def own_loop():
+      try:
+        asyncio.run(self.run_async(engine, train_dataset, num_steps, **kwargs))
+      except BaseException as e:  # noqa: BLE001 - re-raised in the caller's thread
+        failure.append(e)
+    worker = threading.Thread(target=own_loop, name="rl-program")
+    worker.start()
+    worker.join()
+    if failure:
+      raise failure[0]
