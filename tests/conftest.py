@@ -11,7 +11,16 @@ def pytest_configure(config):
   config.addinivalue_line("markers", "gpu: needs a CUDA device (run with `-m gpu` on a B200)")
 
 
+_DEFAULT_TEST_TIMEOUT_S = 900      # multi-rank tests bound their child processes at 600 s themselves
+
+
 def pytest_collection_modifyitems(config, items):
+  # no test may hang the suite: where the pytest-timeout plugin is installed every test without a limit of its
+  # own gets one (a stuck event loop or a lost collective then fails that test instead of the whole run)
+  if config.pluginmanager.hasplugin("timeout"):
+    for item in items:
+      if item.get_closest_marker("timeout") is None:
+        item.add_marker(pytest.mark.timeout(_DEFAULT_TEST_TIMEOUT_S))
   import torch
   if torch.cuda.is_available():
     return
