@@ -33,6 +33,10 @@ def _response_to_trajectory_item(resp: Any) -> datatypes.TrajectoryItem:
       policy_version=resp.policy_version)
 
 
+def _role_name(role: Any) -> Any:
+  return getattr(role, "value", role)
+
+
 class DistributedRLEngine(rl_engine_interface.AbstractRLEngine):
   def __init__(self, rollout_workers: Sequence[remote_execution.ActorHandle],
                trainer_workers: Mapping[Any, remote_execution.ActorHandle],
@@ -40,8 +44,9 @@ class DistributedRLEngine(rl_engine_interface.AbstractRLEngine):
                weight_sync_coordinator: Any = None):
     self._rollout_workers = list(rollout_workers)
     self._rollout_pool = remote_execution.RoutingActorPool(self._rollout_workers)
-    self._trainer_workers = dict(trainer_workers)
-    self._inference_workers = dict(inference_workers or {})
+    # roles are looked up by their plain name, so `Role.ACTOR` and "actor" name the same worker on either side
+    self._trainer_workers = {_role_name(k): v for k, v in dict(trainer_workers).items()}
+    self._inference_workers = {_role_name(k): v for k, v in dict(inference_workers or {}).items()}
     self._policy_version = 0
     self._weight_sync_coordinator = weight_sync_coordinator
 
@@ -101,7 +106,7 @@ class DistributedRLEngine(rl_engine_interface.AbstractRLEngine):
     return out
 
   def _inference(self, role):
-    w = self._inference_workers.get(role) or self._inference_workers.get(getattr(role, "value", role))
+    w = self._inference_workers.get(_role_name(role))
     if w is None:
       raise ValueError(f"no inference worker registered for role {role}")
     return w
@@ -116,7 +121,7 @@ class DistributedRLEngine(rl_engine_interface.AbstractRLEngine):
 
   async def train_step(self, payload, role=datatypes.Role.ACTOR, accumulate_gradients: bool = False,
                        apply_optimizer: bool = True, skip_jit: bool = False, **kwargs):
-    w = self._trainer_workers.get(role) or self._trainer_workers.get(getattr(role, "value", role))
+    w = self._trainer_workers.get(_role_name(role))
     if w is None:
       raise ValueError(f"no trainer worker registered for role {role}")
     return await w.asubmit("train_step", payload=payload, accumulate_gradients=accumulate_gradients,
