@@ -54,7 +54,10 @@ class AsyncFileWriter:
     self._closed = False
     self.errors = 0
 
-  def _ensure_worker(self) -> None:
+  def _enqueue(self, task: _WriteTask) -> None:
+    """Starts the worker on first use and queues the task, in one critical section with `close`: a task is
+    either refused or lands before the shutdown marker, never behind it (where nothing would ever write it and
+    `flush` would wait forever)."""
     with self._lock:
       if self._closed:
         raise RuntimeError("AsyncFileWriter is closed")
@@ -62,6 +65,7 @@ class AsyncFileWriter:
         self._thread = threading.Thread(
             target=self._worker_loop, name="trajectory-writer", daemon=True)
         self._thread.start()
+      self._queue.put(task)
 
   def write_step(self, *, trajectory_id: str, trajectory_dir: str,
                  metadata_path: str, metadata: pydantic.BaseModel,
@@ -72,8 +76,7 @@ class AsyncFileWriter:
     Serialisation happens here, on the caller's thread, which is the snapshot:
     later changes to `metadata` or `step` do not reach the file.
     """
-    self._ensure_worker()
-    self._queue.put(_WriteTask(
+    self._enqueue(_WriteTask(
         trajectory_id=trajectory_id, trajectory_dir=trajectory_dir,
         metadata_path=metadata_path, metadata_json=_dump_json(metadata),
         step_path=step_path,
@@ -111,9 +114,13 @@ class AsyncFileWriter:
         return
       self._closed = True
       thread = self._thread
+      if thread is not None and thread.is_alive():
+        self._queue.put(None)
     if thread is not None and thread.is_alive():
-      self._queue.put(None)
       thread.join(timeout)
+      if thread.is_alive():
+        log.warning("trajectory writer did not finish within %s s; %d task(s) may be unwritten", timeout,
+                    self._queue.qsize())
 
   def __del__(self) -> None:
     try:
