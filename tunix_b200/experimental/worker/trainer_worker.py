@@ -4,6 +4,7 @@ lifecycle state, and is the SOURCE side of weight-sync rounds."""
 from __future__ import annotations
 
 import functools
+import inspect
 from typing import Any, Callable, Dict, Optional, Sequence
 
 from ..common import datatypes
@@ -160,12 +161,37 @@ class TrainerWorker(abstract_worker.Worker):
     return weight_sync.WorkUnitId(job_name="trainer", job_replica_id=self._worker_id, data_replica_idx=self._rank)
 
   async def prepare_weight_sync(self, sync_request: Any = None, **kwargs) -> Sequence[weight_sync.WorkUnitMetadata]:
-    """Exposes the current weights to the transport and describes them."""
-    self._staged = self._trainer.state_for_weight_sync()
-    attach = getattr(self._handler, "attach", None)
-    if callable(attach):
-      attach(self.work_unit, self._staged)
-    return [peer_memory_handler.manifest_of(self.work_unit, self._staged)]
+    """Exposes the current weights to the transport and describes them. The worker is SYNCING from here until
+    `release_weight_sync`, so no training call changes the weights under the transfer; a failure leaves it in
+    ERROR. A trainer that stages its weights itself (`prepare_weight_sync` of its own) is asked first."""
+    if self.state == WorkerState.PENDING:
+      self.initialize()
+    self.state = WorkerState.SYNCING
+    try:
+      own = getattr(self._trainer, "prepare_weight_sync", None)
+      if callable(own):
+        return await _maybe_await(own(sync_request=sync_request, **kwargs))
+      self._staged = self._trainer.state_for_weight_sync()
+      attach = getattr(self._handler, "attach", None)
+      if callable(attach):
+        attach(self.work_unit, self._staged)
+      return [peer_memory_handler.manifest_of(self.work_unit, self._staged)]
+    except Exception as e:
+      self._last_error = str(e)
+      self._state = WorkerState.ERROR
+      raise
 
-  async def release_weight_sync(self, sync_request: Any = None, **kwargs) -> None:
+  async def release_weight_sync(self, sync_request: Any = None, **kwargs) -> Any:
+    """Ends the round on the source: the staged view is dropped, the trainer's own release hook (when it has one)
+    runs, and the worker serves training calls again - also when the hook raises, since the round is over."""
     self._staged = None
+    try:
+      own = getattr(self._trainer, "release_weight_sync", None)
+      return await _maybe_await(own(sync_request=sync_request, **kwargs)) if callable(own) else None
+    finally:
+      if self.state == WorkerState.SYNCING:
+        self.state = WorkerState.READY
+
+
+async def _maybe_await(value: Any) -> Any:
+  return await value if inspect.isawaitable(value) else value
