@@ -8,8 +8,10 @@ from typing import Optional
 log = logging.getLogger(__name__)
 
 
-@dataclasses.dataclass(kw_only=True)
+@dataclasses.dataclass(kw_only=True, slots=True)
 class AlgorithmConfig:
+  """Fields are keyword-only and the class has slots: a misspelt field is an AttributeError, not a silently ignored
+  setting. Values are checked when the object is built; later assignments are not re-checked."""
   algo_variant: str = "grpo"
   advantage_estimator: str = "grpo"
   policy_loss_fn: str = "grpo"

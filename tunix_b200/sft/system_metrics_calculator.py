@@ -26,11 +26,11 @@ def measure_tflops_per_step(model: Any, tokens_per_step: int, seq_len: Optional[
 
 
 def approximate_tflops_per_second(total_model_params: int, global_batch_size: int, step_time_delta: float) -> float:
-  """`6 * B * params / dt` in TFLOP/s."""
-  if total_model_params <= 0 or global_batch_size <= 0:
-    raise ValueError(f"Input parameters must be positive. Got params: {total_model_params}, batch size: "
-                     f"{global_batch_size}")
-  if step_time_delta <= 0:
-    raise ValueError(f"Step time delta must be positive. Got: {step_time_delta}")
-  total_flops = 6 * global_batch_size * total_model_params
-  return total_flops / step_time_delta / 1e12
+  """`6 * B * params / dt` in TFLOP/s. Inputs that cannot give a rate (no parameters, no batch, no elapsed time: the
+  first step of a run, a clock that did not advance) give 0.0 and a warning rather than ending the training loop
+  over a metric."""
+  if total_model_params <= 0 or global_batch_size <= 0 or step_time_delta <= 0:
+    log.warning("TFLOPS cannot be approximated from params=%s, batch size=%s, step time=%s: all must be positive.",
+                total_model_params, global_batch_size, step_time_delta)
+    return 0.0
+  return 6.0 * global_batch_size * total_model_params / step_time_delta / 1e12
