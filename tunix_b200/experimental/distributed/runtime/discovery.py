@@ -92,6 +92,9 @@ class TcpDiscovery(context.DiscoveryContext):
   def port(self) -> int:
     return self._port
 
+  def is_started(self) -> bool:
+    return self._server is not None and not self._stop.is_set()
+
   def _serve(self) -> None:
     while not self._stop.is_set():
       try:
