@@ -4,10 +4,10 @@
   python -m tunix_b200.experimental.distributed.runtime.main \\
       --process_main=tunix_b200.experimental.distributed.examples.basics.flag.main --message="hi there"
 """
-import argparse
+from . import _flags
 
 
-def main(ctx, argv) -> None:
-  parser = argparse.ArgumentParser()
-  parser.add_argument("--message", type=str, default="")
-  print(parser.parse_args(argv).message)
+def main(ctx, argv) -> str:
+  text = _flags.value(argv, "--message")
+  print(text)
+  return text

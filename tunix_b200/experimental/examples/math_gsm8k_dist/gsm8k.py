@@ -121,37 +121,52 @@ def prompt_items(tasks: List[Tuple[str, str]], generation_kwargs: Dict[str, Any]
   return rows
 
 
-@registry.register_env(GSM8K_ENV_NAME)
-class GSM8KEnv(base_environment.BaseTaskEnv):
-  """One step: the action is the model's answer text; reward 1 when it contains the gold answer."""
+class _OneShot(base_environment.BaseTaskEnv):
+  """A task that ends with the first action; subclasses say how an action scores."""
 
-  def __init__(self, prompt: str = "", gold_answer: str = "", group_id: str = "", pair_index: int = 0,
-               policy_version: int = 0, max_steps: int = 1, **kwargs: Any):
-    super().__init__(task={"prompts": prompt, "gold_answer": gold_answer, "policy_version": policy_version},
-                     max_steps=max_steps, group_id=group_id, pair_index=pair_index, **kwargs)
+  def __init__(self, task: Dict[str, Any], group_id: str = "", pair_index: int = 0, **kwargs: Any):
+    kwargs.setdefault("max_steps", 1)
+    super().__init__(task=task, group_id=group_id, pair_index=pair_index, **kwargs)
 
-  def _initial_observation(self) -> Dict[str, str]:
-    return {"prompts": self.task.get("prompts", "")}
+  def score(self, said: str) -> Tuple[float, Dict[str, Any]]:
+    raise NotImplementedError
 
   def _step_impl(self, action: Any) -> base_environment.EnvStepResult:
     said = str(getattr(action, "action", action))
-    gold = str(self.task.get("gold_answer", ""))
-    correct = bool(gold) and gold in said
-    return base_environment.EnvStepResult(observation={"answer": said, "gold_answer": gold},
-                                          reward=1.0 if correct else 0.0, done=True, info={"correct": correct})
+    reward, info = self.score(said)
+    return base_environment.EnvStepResult(observation={"answer": said, **info.pop("show", {})}, reward=reward,
+                                          done=True, info=info)
+
+
+@registry.register_env(GSM8K_ENV_NAME)
+class GSM8KEnv(_OneShot):
+  """The action is the model's answer text; reward 1 when it contains the gold answer (the lenient check: rollout
+  workers that want the strict one score `extract_answer` through `make_reward_fn("answer")` on the control plane)."""
+
+  def __init__(self, prompt: str = "", gold_answer: str = "", policy_version: int = 0, **kwargs: Any):
+    self.gold = str(gold_answer)
+    super().__init__({"prompts": prompt, "gold_answer": self.gold, "policy_version": policy_version}, **kwargs)
+
+  def _initial_observation(self) -> Dict[str, str]:
+    return {"prompts": self.task["prompts"]}
+
+  def score(self, said: str) -> Tuple[float, Dict[str, Any]]:
+    hit = self.gold != "" and self.gold in said
+    return float(hit), {"correct": hit, "show": {"gold_answer": self.gold}}
 
 
 @registry.register_agent(GSM8K_AGENT_NAME)
 class GSM8KAgent(base_agent.ConversationAgentBase):
-  """Hands the model's text to the environment unchanged."""
+  """Hands the model's text to the environment unchanged and keeps it in the conversation."""
 
   name = GSM8K_AGENT_NAME
+  SYSTEM_PROMPT = "Solve the math problem. Return the final numeric answer clearly."
 
   def __init__(self):
-    super().__init__("Solve the math problem. Return the final numeric answer clearly.")
+    super().__init__(self.SYSTEM_PROMPT)
 
   def update_from_model(self, response: str, **kwargs: Any) -> agent_types.Action:
-    action = agent_types.Action(action=response)
-    self.trajectory.steps.append(agent_types.Step(model_response=response, thought="", action=action))
+    step = agent_types.Step(model_response=response, thought="", action=agent_types.Action(action=response))
+    self.trajectory.steps.append(step)
     self.chat_completions.append({"role": "assistant", "content": response})
-    return action
+    return step.action

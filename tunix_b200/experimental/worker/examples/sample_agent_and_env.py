@@ -11,24 +11,30 @@ Kubernetes or Slurm client): it refuses to be pickled, which is exactly why it h
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Optional
+import dataclasses
+from typing import Any, Dict, Mapping, Optional
 
 from ....rl.agentic.environments import base_environment
 from ...rl.agentic import registry
 
+# What each command can see. A node whose name ends in 3 has a GPU fault that only a GPU query shows.
+_VISIBILITY = {"uptime": lambda node: "OK",
+               "nvidia-smi --query-gpu=ecc.errors": lambda node: _true_state(node)}
+_PLAYBOOK = {"easy": "uptime", "medium": "uptime", "hard": "nvidia-smi --query-gpu=ecc.errors"}
 
+
+@dataclasses.dataclass
 class ClusterClient:
-  """Connection to a (pretend) cluster API. Stateful and process-bound."""
-
-  def __init__(self, endpoint: str = "cluster.local"):
-    self.endpoint, self.connected, self.commands = endpoint, True, 0
+  """Connection to a (pretend) cluster API: stateful, process-bound, unpicklable on purpose."""
+  endpoint: str = "cluster.local"
+  connected: bool = True
+  commands: int = 0
 
   def run(self, node: str, command: str) -> str:
     if not self.connected:
       raise RuntimeError("cluster client is disconnected")
     self.commands += 1
-    status = "DEGRADED" if "gpu" in command and node.endswith("3") else "OK"
-    return f"[{node}] `{command}` -> {status}"
+    return f"[{node}] `{command}` -> {_VISIBILITY.get(command, _sees_nothing)(node)}"
 
   def close(self) -> None:
     self.connected = False
@@ -37,36 +43,49 @@ class ClusterClient:
     raise TypeError("ClusterClient holds a live connection and cannot be pickled")
 
 
-@registry.register_env("cluster")
-class ClusterTaskEnv(base_environment.BaseTaskEnv):
-  """One command against one node. Nodes whose name ends in 3 have a GPU fault that only a GPU query shows: the
-  reward is 1 when the command reports the node's true state, 0 when it calls a faulty node healthy."""
+def _sees_nothing(node: str) -> str:
+  return "OK"
 
-  def __init__(self, task: Optional[Dict[str, Any]] = None, **kwargs):
-    super().__init__(task=task, **kwargs)
-    self.client = ClusterClient()                       # built here, inside the worker process
-    self.node = (task or {}).get("node", "node-0")
+
+def _true_state(node: str) -> str:
+  return "DEGRADED" if node.endswith("3") else "OK"
+
+
+class _ClusterEpisode(base_environment.BaseTaskEnv):
+  """One command against one node: reward 1 when the command reports the node's true state, 0 when it calls a
+  faulty node healthy."""
+
+  client: ClusterClient
+  node: str
 
   def _initial_observation(self) -> Dict[str, Any]:
     return {"observation": f"Connected to {self.node}. Ready for commands."}
 
   def _step_impl(self, action: Any) -> base_environment.EnvStepResult:
-    result = self.client.run(self.node, str(action))
-    found_fault = result.endswith("DEGRADED")
-    missed_fault = self.node.endswith("3") and not found_fault
-    return base_environment.EnvStepResult(observation=result, reward=0.0 if missed_fault else 1.0, done=True,
-                                          info={"node": self.node, "degraded": found_fault})
+    report = self.client.run(self.node, str(action))
+    seen = report.rsplit(" ", 1)[-1]
+    return base_environment.EnvStepResult(observation=report, reward=float(seen == _true_state(self.node)), done=True,
+                                          info={"node": self.node, "degraded": seen == "DEGRADED"})
 
   def close(self) -> None:
     self.client.close()
 
 
-@registry.register_agent("triage")
-class TriageAgent:
-  """Chooses what to run from the task's difficulty (a real agent would ask the policy model)."""
+@registry.register_env("cluster")
+class ClusterTaskEnv(_ClusterEpisode):
+  """Registered under "cluster": the episode plus a client built here, inside the worker process."""
 
-  def __init__(self, system_prompt: str = ""):
-    self.system_prompt = system_prompt
+  def __init__(self, task: Optional[Mapping[str, Any]] = None, **kwargs):
+    task = dict(task or {})
+    super().__init__(task=task, **kwargs)
+    self.node, self.client = task.get("node", "node-0"), ClusterClient()
+
+
+@registry.register_agent("triage")
+@dataclasses.dataclass
+class TriageAgent:
+  """Picks a command from a playbook keyed by the task's difficulty (a real agent would ask the policy model)."""
+  system_prompt: str = ""
 
   def step(self, observation: Any, difficulty: str = "easy") -> str:
-    return "nvidia-smi --query-gpu=ecc.errors" if difficulty == "hard" else "uptime"
+    return _PLAYBOOK.get(difficulty, _PLAYBOOK["easy"])
