@@ -201,3 +201,22 @@ def test_weight_sync_asks_the_coordinator_and_counts_versions():
   assert eng2.policy_version == 0                                                # a failed round publishes nothing
   standalone, _, _ = engine()
   assert asyncio.run(standalone.sync_weights()) == 1                             # colocated weights: versions only
+
+
+def test_the_managed_run_with_simulated_workers_routes_groups_and_trains(capsys):
+  from tunix_b200.experimental.common import datatypes as dt
+  from tunix_b200.experimental.orchestrator import simple_orchestrator_nb as nb
+  out = nb.main(num_steps=2, group_size=2)
+  assert [r.step for r in out["history"]] == [0, 1] and all(r.num_rollouts == 4 for r in out["history"])
+  assert out["optimizer_steps"] == 2 and out["trainer_batches"] == 4
+  # both samples of a prompt were served by the same worker
+  owner = {}
+  for worker, served in out["served"].items():
+    for request_id in served:
+      prompt = request_id.split("_")[1]
+      assert owner.setdefault(prompt, worker) == worker
+  assert sum(len(s) for s in out["served"].values()) == 8
+  assert set(out["states"].values()) == {dt.WorkerState.STOPPED}
+  assert "reward mean" in capsys.readouterr().out
+  again = nb.main(num_steps=2, group_size=2)                  # deterministic
+  assert [r.reward_mean for r in again["history"]] == [r.reward_mean for r in out["history"]]

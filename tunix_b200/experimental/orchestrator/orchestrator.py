@@ -139,3 +139,16 @@ class ClusterOrchestrator:
     if self.engine is None:
       raise RuntimeError("bring_up_workers() must run before a program")
     return program.run(self.engine, train_dataset, num_steps, **kw)
+
+  def run(self, algo: Any, dataset: Any, reward_fns: Optional[Sequence[Any]] = None, assembler: Any = None,
+          num_steps: Optional[int] = None, **program_kwargs: Any) -> rl_program.StandardRLProgram:
+    """The managed run: brings the workers up if nobody has yet, builds a `StandardRLProgram` from the algorithm
+    adapter, the reward functions and the assembler, runs it for `num_steps`, and returns the program (its
+    `history` holds one record per step). Weight sync is part of the program only when this orchestrator was given
+    a coordinator."""
+    if self.engine is None:
+      self.bring_up_workers()
+    program_kwargs.setdefault("sync_weights", self._weight_sync_coordinator is not None)
+    program = rl_program.StandardRLProgram(algo, reward_fns=reward_fns, assembler=assembler, **program_kwargs)
+    self.run_program(program, dataset, num_steps=num_steps)
+    return program
