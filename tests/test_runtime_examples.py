@@ -145,3 +145,43 @@ def test_a_worker_in_another_server_is_driven_through_the_worker_interface():
     remote_worker_server.stop.set()
     t.join(10)
     remote_worker_server.stop.clear()
+
+
+def test_remote_invocation_demo_awaits_and_polls():
+  from tunix_b200.experimental.distributed.examples.vllm_rollout import remote
+  with local_context.LocalProcessContext(ctx_args()) as ctx:
+    out = remote.main(ctx, [])
+  assert out["squares"] == [9, 16, 25] and out["worker_id"].startswith("worker-")
+
+
+@pytest.mark.timeout(300)
+def test_generation_load_is_spread_over_discovered_rollout_workers():
+  from tunix_b200.experimental.distributed.examples.vllm_rollout import orchestrator as load, rollout as load_rollout
+  load_rollout.stop.clear()
+  disc = free_port()
+  out = {}
+  original = load.main
+
+  def recording(ctx, argv):
+    out["summary"] = original(ctx, argv)
+    return out["summary"]
+  load.main = recording
+  worker = lambda wid: ["--process", f"--process_main={EX}.vllm_rollout.rollout.main", f"--discovery_id=rollout-{wid}",   # noqa: E731
+                        f"--discovery_addrs=orchestrator:{disc}", f"--worker_id={wid}", "--port=0", "--max_seq_len=64",
+                        "--max_batch=8"]
+  try:
+    rt_main.main(["prog", "--process", f"--process_main={EX}.vllm_rollout.orchestrator.main",
+                  "--discovery_id=orchestrator", f"--discovery_port={disc}", "--num_requests=12", "--concurrency=4",
+                  "--max_tokens=6", "--wait_s=120", *worker("a"), *worker("b")])
+  finally:
+    load.main = original
+    load_rollout.stop.clear()
+  s = out["summary"]
+  assert not s["failures"], s["failures"]
+  assert sum(s["requests"].values()) == 12 and set(s["requests"]) == {"a", "b"}
+  assert 12 <= sum(s["tokens"].values()) <= 72 and s["requests_per_s"] > 0
+  m = load.RequestStatsMonitor(log_interval_seconds=3600)
+  m.record_request("w", 5); m.record_request("w", 7)
+  assert m.total_requests == 2 and m.summary()["tokens"] == {"w": 12}
+  assert not m.maybe_log_summary() and m.maybe_log_summary(force=True)
+  assert load.RolloutSpec.from_announcement("10.0.0.5", b"a|50081|tiny") == load.RolloutSpec("a", "grpc://10.0.0.5:50081", "tiny")
