@@ -184,7 +184,11 @@ def test_example_scripts_run_on_cpu():
   root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
   env = dict(os.environ, CUDA_VISIBLE_DEVICES="", OMP_NUM_THREADS="2")
   for script, args in (("examples/sft/sft_synthetic.py", ["--steps", "3"]),
-                       ("examples/model_load/from_safetensors.py", [])):
+                       ("examples/model_load/from_safetensors.py", []),
+                       ("examples/distillation/logit_distillation.py", ["--steps", "4", "--teacher-steps", "4"]),
+                       ("examples/qlora/qlora_sft.py", ["--steps", "3"]),
+                       ("examples/dpo/dpo_synthetic.py", ["--steps", "3", "--lora-rank", "4"]),
+                       ("examples/dpo/dpo_synthetic.py", ["--steps", "3", "--algorithm", "orpo"])):
     r = subprocess.run([sys.executable, os.path.join(root, script), *args], env=env, capture_output=True, text=True,
                        timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
