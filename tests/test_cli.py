@@ -187,6 +187,7 @@ def test_example_scripts_run_on_cpu():
                        ("examples/model_load/from_safetensors.py", []),
                        ("examples/distillation/logit_distillation.py", ["--steps", "4", "--teacher-steps", "4"]),
                        ("examples/qlora/qlora_sft.py", ["--steps", "3"]),
+                       ("examples/tools/forward_pass_logit_checker.py", ["--self-test"]),
                        ("examples/dpo/dpo_synthetic.py", ["--steps", "3", "--lora-rank", "4"]),
                        ("examples/dpo/dpo_synthetic.py", ["--steps", "3", "--algorithm", "orpo"])):
     r = subprocess.run([sys.executable, os.path.join(root, script), *args], env=env, capture_output=True, text=True,
